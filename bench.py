@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode throughput of the grouped-expert MoE path on B200.
+
+Workload (N = 1): an OLMoE-shaped MoE stack - 16 distinct layers, each 64 experts, top-8,
+hidden 2048, expert intermediate 1024, SwiGLU, shared fp16 backbones of rank 256, compact3
+experts with block Golomb-Rice bitmaps - at decode batch 128 (batches 1/8/32 are reported
+in `sweep`).  A step pushes one batch through all 16 layers; 16 distinct payloads (~290 MB)
+exceed the 126 MB L2, so every step streams the compressed weights from HBM.  All data is
+seeded synthetic (no checkpoints or datasets are available offline).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+`value`   : tokens/s with inputs resident in HBM, CUDA-graph replay of the step, CUDA events.
+`e2e`     : tokens/s through the public Python API (TrisSparseMoeBlock.forward) with the batch
+            copied from pinned host memory and the result copied back inside the timed region.
+`roofline`: the dominant kernel (grouped compact3 matmul) timed alone with CUDA events over
+            the same 16 payloads: compressed bytes per launch / duration, against the measured
+            HBM copy bandwidth of MEASURED_PEAKS.json.
+`cpu_baseline` / `--impl reference`: the CPU port of the reference's expert-loop path
+            (oracle/cpu_reference_path.py) timed on the host cores on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "oracle")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np
+import torch
+
+LAYERS = 16
+HEADLINE_TOKENS = 128
+SWEEP_TOKENS = (1, 8, 32, 128)
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+LAUNCHES_PER_LAYER = 7  # backbone+router GEMM, top-k, route, gate/up, down backbone, down, combine
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_stack(device, layers=LAYERS, seed=1234, keep_sparse=False):
+    import trismoe_b200 as tm
+    from trismoe_b200 import synth
+
+    blocks, infos = [], []
+    for l in range(layers):
+        layer = synth.synth_layer(synth.OLMOE, seed=seed + l, keep_sparse_gmap=keep_sparse)
+        blk = tm.TrisSparseMoeBlock(2048, 1024, 64, 8, True)
+        blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
+                                  layer["shared_down"], layer["router_weight"], device=device)
+        blocks.append(blk)
+        infos.append(layer)
+    return blocks, infos
+
+
+def layer_algorithmic_bytes(info, active_experts, tokens):
+    """Compressed weight bytes of the active experts + backbones + router + activations in/out;
+    intermediates count zero (the figure an ideally fused layer must move)."""
+    from trismoe_b200 import synth
+
+    shape = synth.OLMOE
+    per_proj = {n: synth.projection_algorithmic_bytes(info[n], active_experts) for n in ("gate", "up", "down")}
+    backbone = 2 * (2 * shape.rank * shape.hidden_size + shape.rank * shape.intermediate_size)
+    router = 2 * shape.num_experts * shape.hidden_size
+    act = 4 * tokens * shape.hidden_size
+    return per_proj, sum(per_proj.values()) + backbone + router + act
+
+
+def time_replays(graph, steps, warmup):
+    for _ in range(warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / steps
+
+
+def capture(fn):
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return graph
+
+
+def run_ours(args):
+    import trismoe_b200 as tm
+    from trismoe_b200 import synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        from trismoe_b200 import expert_parallel
+
+        return expert_parallel.run_bench(args, rank, world, device)
+
+    blocks, infos = build_stack(device)
+    peak, peak_kind = measured_hbm_peak()
+    sampler = ClockSampler(local)
+    results = {}
+    sampler.start()
+    for T in SWEEP_TOKENS:
+        x = synth.synth_activations(T, 2048, seed=T).to(device)
+        outs = [None] * LAYERS
+
+        def step():
+            for l, blk in enumerate(blocks):
+                outs[l] = blk(x.view(1, T, 2048))[0]
+
+        graph = capture(step)
+        steps = args.steps if T == HEADLINE_TOKENS else max(10, args.steps // 2)
+        ms = time_replays(graph, steps, args.warmup)
+        # bytes: which experts each layer activates for this batch
+        total_bytes = 0
+        for blk, info in zip(blocks, infos):
+            logits = torch.nn.functional.linear(x, blk.gate.weight).float()
+            sel = torch.topk(torch.softmax(logits, dim=1), 8, dim=-1)[1]
+            active = sorted(set(sel.reshape(-1).tolist()))
+            total_bytes += layer_algorithmic_bytes(info, active, T)[1]
+        results[T] = {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "us_per_layer": ms * 1e3 / LAYERS,
+                      "algorithmic_mb_per_layer": total_bytes / LAYERS / 1e6,
+                      "layer_gbs": total_bytes / (ms * 1e-3) / 1e9}
+        del graph
+    T = HEADLINE_TOKENS
+    head = results[T]
+
+    # ---- dominant kernel alone: grouped gate/up (SiLU*mul epilogue) and grouped down ----------
+    x = synth.synth_activations(T, 2048, seed=T).to(device)
+    kern = {}
+    routes, hid, byts = [], [], {"pair": 0, "down": 0}
+    for blk, info in zip(blocks, infos):
+        logits = torch.nn.functional.linear(x, blk.gate.weight).float()
+        sel = torch.topk(torch.softmax(logits, dim=1), 8, dim=-1)[1]
+        route = tm.build_grouped_route(sel, 64)
+        routes.append(route)
+        tok = route["grouped_token_indices"]
+        hg = tm.compute_shared_hidden(x, blk.shared_gate).index_select(0, tok)
+        hu = tm.compute_shared_hidden(x, blk.shared_up).index_select(0, tok)
+        hd = torch.randn((tok.numel(), 256), device=device).half()
+        hid.append((hg, hu, hd))
+        active = route["expert_ids"].tolist()
+        per_proj, _ = layer_algorithmic_bytes(info, active, T)
+        byts["pair"] += per_proj["gate"] + per_proj["up"]
+        byts["down"] += per_proj["down"]
+
+    def pair_step():
+        for blk, route, (hg, hu, hd) in zip(blocks, routes, hid):
+            tm.run_grouped_structured_expert_pair_forward(blk._get_grouped_payload("gate"), blk._get_grouped_payload("up"),
+                                                          hg, hu, None, route, fuse_silu_mul=True)
+
+    def down_step():
+        for blk, route, (hg, hu, hd) in zip(blocks, routes, hid):
+            tm.run_grouped_structured_expert_forward(blk._get_grouped_payload("down"), hd, None, route)
+
+    for name, fn in (("pair", pair_step), ("down", down_step)):
+        graph = capture(fn)
+        ms = time_replays(graph, args.steps, args.warmup)
+        kern[name] = {"us_per_launch": ms * 1e3 / LAYERS, "bytes_per_launch": byts[name] / LAYERS,
+                      "gbs": byts[name] / (ms * 1e-3) / 1e9}
+        del graph
+    dom = max(kern, key=lambda n: kern[n]["us_per_launch"])
+    roofline = {
+        "bound": "hbm", "kernel": f"grouped_compact3_kernel ({'gate/up dual + SiLU*mul' if dom == 'pair' else 'down'})",
+        "achieved": round(kern[dom]["gbs"], 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+        "frac": round(kern[dom]["gbs"] / peak, 4), "frac_of_nominal_8TBs": round(kern[dom]["gbs"] / NOMINAL_HBM_GBS, 4),
+        "traffic": None, "us_per_launch": round(kern[dom]["us_per_launch"], 2),
+        "algorithmic_bytes_per_launch": int(kern[dom]["bytes_per_launch"]),
+        "other_kernels": {n: {k: round(v, 2) for k, v in d.items()} for n, d in kern.items() if n != dom},
+        "whole_layer": {"gbs": round(head["layer_gbs"], 1), "frac": round(head["layer_gbs"] / peak, 4),
+                        "frac_of_nominal_8TBs": round(head["layer_gbs"] / NOMINAL_HBM_GBS, 4)},
+    }
+
+    # ---- end to end through the public API with host buffers --------------------------------
+    x_host = synth.synth_activations(T, 2048, seed=T).pin_memory()
+    y_host = torch.empty((T, 2048), dtype=torch.float16).pin_memory()
+    x_dev = torch.empty((T, 2048), dtype=torch.float16, device=device)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y = None
+        for blk in blocks:
+            y = blk(x_dev.view(1, T, 2048))[0]
+        y_host.copy_(y.view(T, 2048), non_blocking=True)
+
+    for _ in range(args.warmup):
+        e2e_step()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    stop.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(start.elapsed_time(stop), (time.perf_counter() - t0) * 1e3) / args.steps
+    clocks = sampler.stop()
+
+    cpu = cpu_baseline(sample_tokens=T)
+    out = {
+        "metric": "decode_tokens_per_s", "value": round(head["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(head["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "OLMoE-shaped 16-layer MoE stack (64 experts top-8, hidden 2048, intermediate 1024, "
+                               "rank-256 fp16 backbones, compact3 + block-GR experts), decode batch 128",
+                   "tokens_per_step": T, "layers": LAYERS, "cold_cache": "16 distinct layer payloads (~290 MB) > 126 MB L2",
+                   "parallelism": "single GPU"},
+        "e2e": {"value": round(T / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": T * 2048 * 2,
+                "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},
+        "gpu_launches": args.steps * LAYERS * LAUNCHES_PER_LAYER,
+        "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+        "sweep": {str(t): {k: round(v, 3) for k, v in r.items()} for t, r in results.items()},
+    }
+    print(json.dumps(out))
+
+
+def cpu_baseline(sample_tokens=HEADLINE_TOKENS, iters=2):
+    """Times the CPU port of the reference path on ONE layer of the stack (the 16 layers are
+    identical in shape) and scales to the 16-layer step."""
+    import cpu_reference_path as cpu
+    from trismoe_b200 import synth
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    layer = synth.synth_layer(synth.OLMOE, seed=1234, keep_sparse_gmap=True, use_block_gr=False)
+    x = synth.synth_activations(sample_tokens, 2048, seed=sample_tokens)
+    cpu.moe_block_forward(x, layer, 8, True)  # warm-up
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        cpu.moe_block_forward(x, layer, 8, True)
+    per_layer = (time.perf_counter() - t0) / iters
+    return {"value": round(sample_tokens / (per_layer * LAYERS), 3), "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"1 of {LAYERS} layers x {sample_tokens} tokens, {iters} timed passes after 1 warm-up, "
+                      f"{per_layer:.3f} s per layer, scaled to the 16-layer step",
+            "s_per_layer": round(per_layer, 4)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    cpu = cpu_baseline(iters=steps)
+    out = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": cpu["value"], "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": round(cpu["s_per_layer"] * LAYERS * 1e3, 1),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "OLMoE-shaped 16-layer MoE stack, decode batch 128 (CPU port of the reference's "
+                               "expert-loop path; the Python reference itself cannot travel to the GPU box)",
+                   "tokens_per_step": HEADLINE_TOKENS, "layers": LAYERS},
+        "cpu_baseline": cpu,
+        "e2e": {"value": cpu["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,263 @@
+/*
+ * trismoe_b200 — C ABI of the B200 (sm_100a) grouped-expert dequant-GEMM runtime for
+ * TriS-MoE compact3 payloads.
+ *
+ * Every entry point takes plain pointers and sizes (device pointers unless the name ends
+ * in `_host`), an explicit cudaStream_t passed as `void*`, and returns an int status
+ * (TRIS_OK == 0).  The library owns no device memory: weights, activations, outputs,
+ * workspaces and derived indexes are caller-owned buffers.  Nothing here falls back to
+ * the CPU; a launch that cannot run returns a non-zero status and `tris_last_error()`
+ * holds the reason for the calling thread.
+ *
+ * Reference interfaces these entry points stand in for are cited per declaration as
+ * path:line inside the TriS-MoE source tree
+ * (QL  = AutoGPTQ/auto_gptq/nn_modules/qlinear/qlinear_cuda.py,
+ *  CPP = AutoGPTQ/autogptq_extension/TriSMoE/TriSMoE_cuda.cpp,
+ *  CU  = AutoGPTQ/autogptq_extension/TriSMoE/TriSMoE_cuda_kernel.cu,
+ *  SC  = AutoGPTQ/auto_gptq/modeling_tris_moe/grouped_payload_sidecar.py,
+ *  MO  = AutoGPTQ/auto_gptq/modeling_tris_moe/modeling_olmoe.py,
+ *  RW  = tools/rewrite_runtime_min_checkpoint.py).
+ */
+#ifndef TRISMOE_B200_H_
+#define TRISMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Mirrors TRIS_COMPACT3_KERNEL_ABI_VERSION (CPP:1138-1139); the payload layout is ABI 2. */
+#define TRIS_COMPACT3_KERNEL_ABI_VERSION 2
+#define TRIS_B200_ABI_VERSION 1
+
+enum {
+  TRIS_OK = 0,
+  TRIS_ERR_INVALID_ARG = 1,   /* null pointer, negative size, inconsistent dims            */
+  TRIS_ERR_UNSUPPORTED = 2,   /* shape/layout this build does not cover                    */
+  TRIS_ERR_CUDA = 3,          /* a CUDA runtime call or launch failed                      */
+  TRIS_ERR_CORRUPT = 4,       /* payload failed validation (offsets, meta, prefixes)      */
+  TRIS_ERR_WORKSPACE = 5,     /* caller workspace too small                               */
+  TRIS_ERR_TIMEOUT = 6        /* a bounded device-side wait ran out (status word set)     */
+};
+
+/* Block Golomb-Rice constants (QL:486-494, CU:63-68). */
+#define TRIS_GR_BLOCK_OUT 64
+#define TRIS_GR_BLOCK_PACKED_ROWS 2
+#define TRIS_GR_BLOCK_WORDS 128
+#define TRIS_GR_META_K_MASK 0xF
+#define TRIS_GR_META_RAW_FLAG 16
+#define TRIS_GR_META_ONE_COUNT_SHIFT 8
+#define TRIS_GR_MAX_K 7
+/* Sub-streams per block recorded by tris_block_gr_build_index (power of two, <= 32). */
+#define TRIS_GR_DEFAULT_SUBSTREAMS 16
+
+/*
+ * One E-stacked compact3 projection, i.e. the dict returned by
+ * build_grouped_precomputed_payload (QL:1512-1636) with every tensor replaced by its
+ * device pointer.  Shapes use O = out_features, r = rank (K), pr = ceil(r/32).
+ */
+typedef struct TrisProjView {
+  int32_t num_experts;          /* E                                                       */
+  int32_t out_features;         /* O                                                       */
+  int32_t rank;                 /* r: columns of the per-expert factor                     */
+  int32_t num_groups;           /* G: row_pack3 is [E, O, G]                               */
+  int32_t sign2_rows;           /* rows of qweight2_sparse  (max over experts)             */
+  int32_t gmap_sparse_rows;     /* rows of q_gmap_sparse (0 when absent)                   */
+  int32_t gr_max_words;         /* words per expert in q_gmap_gr_words (0 when absent)     */
+  int32_t use_block_gr;         /* compact3_use_block_gr                                   */
+  const int32_t* qweight1;               /* [E, pr, O]      sign plane 1                   */
+  const int32_t* qweight2_sparse;        /* [E, sign2_rows, O] sign plane 2, salient cols  */
+  const int32_t* qweight2_sparse_prefix; /* [E, pr+1]                                      */
+  const int32_t* q_gmap_sparse;          /* [E, gmap_sparse_rows, O] (streaming format)    */
+  const int32_t* q_gmap_sparse_prefix;   /* [E, pr+1]                                      */
+  const int32_t* q_gmap_gr_words;        /* [E, gr_max_words]                              */
+  const int32_t* q_gmap_gr_offsets;      /* [E, nblk+1]                                    */
+  const int32_t* q_gmap_gr_meta;         /* [E, nblk]                                      */
+  const int32_t* c_map;                  /* [E, pr]  bit = salient column                  */
+  const int32_t* g_idx;                  /* [E, r]   group of each column                  */
+  const int64_t* col_pack3;              /* [E, r]   4 x fp16                              */
+  const int64_t* row_pack3;              /* [E, O, G] 4 x fp16                             */
+  const void* output_scale;              /* [E, O] fp16 or NULL (has_output_scale False)   */
+  const void* bias;                      /* [E, O] fp16 or NULL                            */
+  /* Derived at load time by tris_block_gr_build_index / tris_build_row_groups.           */
+  const uint32_t* gr_index;              /* [E, nblk, gr_substreams] or NULL               */
+  int32_t gr_substreams;
+  const int32_t* packed_row_group;       /* [E, pr] group id of each 32-column word        */
+  /* When non-NULL, expert e of this view reads q_gmap_sparse row block
+     gmap_slot[e] of a staging buffer instead of row block e (SC:1104-1106). */
+  const int32_t* gmap_slot;
+} TrisProjView;
+
+/*
+ * Grouped route on the device (QL:1328-1338).  Arrays may be padded to E (+1): segment s
+ * is live when s < *num_segments_dev (or s < num_segments when num_segments_dev is NULL).
+ */
+typedef struct TrisRouteView {
+  const int32_t* expert_ids;        /* [>= num_segments] expert of each segment            */
+  const int32_t* segment_offsets;   /* [>= num_segments+1] row range of each segment       */
+  const int32_t* num_segments_dev;  /* optional device scalar (no host sync needed)        */
+  int32_t num_segments;             /* upper bound used to size the grid                   */
+  int32_t num_rows;                 /* R: routed rows                                      */
+  int32_t max_rows_per_segment;     /* upper bound (<= tokens); 0 = num_rows               */
+  const int32_t* row_gather;        /* optional [R]: source row of each grouped row        */
+} TrisRouteView;
+
+/* ---- library / errors -------------------------------------------------------------- */
+
+/* Replaces the import-time ABI check of the pybind11 module (QL:14-37, CPP:1138-1139). */
+int tris_abi_version(void);
+int tris_compact3_kernel_abi_version(void);
+const char* tris_status_string(int status);
+/* Message of the last non-zero status returned on this thread (TORCH_CHECK text in CU). */
+const char* tris_last_error(void);
+
+/* ---- block Golomb-Rice ------------------------------------------------------------- */
+
+/*
+ * Host encoder of one dense packed g_map [pr, O] into the block-GR stream; same format as
+ * QuantLinear._pack_block_gr_gmap_tensor (QL:3793-3859) / pack_block_gr_gmap_tensor
+ * (RW:252-347).  `words_out` needs room for nblk*128 words; `*num_words` receives the
+ * count actually written.
+ */
+int tris_block_gr_encode_host(const int32_t* dense_words, int32_t packed_rows, int32_t out_features,
+                              int32_t force_raw, int32_t* words_out, int64_t words_capacity,
+                              int32_t* offsets_out, int32_t* meta_out, int64_t* num_words);
+
+/* Bytes of the derived sub-stream index for a projection. */
+size_t tris_block_gr_index_bytes(int32_t num_experts, int32_t packed_rows, int32_t out_features,
+                                 int32_t substreams);
+
+/*
+ * Validates offsets/meta of every block (monotone offsets, k <= 7, one_count <= 4096,
+ * stream inside gr_max_words) and records, per block, where each of `substreams` equal
+ * runs of ones starts (bit offset and flat position).  No reference counterpart: the
+ * reference decodes each block on one thread (CU:426-479); this index lets a warp share
+ * a block.  `status_dev` (device int32) receives 0 or TRIS_ERR_CORRUPT.
+ */
+int tris_block_gr_build_index(const TrisProjView* proj, uint32_t* gr_index_out, int32_t substreams,
+                              int32_t* status_dev, void* stream);
+
+/*
+ * Expands the block-GR stream of every expert to the dense packed g_map [E, pr, O]
+ * (what decode_block_gr_block, CU:426-479, leaves in shared memory; also the predecode of
+ * compact3_tris_grouped_block_gr_predecode, CPP / CU:4683-4718, QL:1452-1509).
+ * Runs the same device decoder as the grouped kernels.
+ */
+int tris_block_gr_decode(const TrisProjView* proj, int32_t* dense_out, void* stream);
+
+/* ---- compact3 ---------------------------------------------------------------------- */
+
+/* Per packed row group table + validation of g_idx (prepare_compact3_k64_groups, QL:364-407). */
+int tris_build_row_groups(const int32_t* g_idx, int32_t num_experts, int32_t rank, int32_t num_groups,
+                          int32_t* packed_row_group_out, int32_t* status_dev, void* stream);
+
+/*
+ * Dequantized weights [E, O, r] fp16 (QuantLinear._dequantize_compact3_matrix, QL:4200-4236;
+ * device form load_compact3_weight_from_packs_gmap_word, CU:709-743), produced by the same
+ * tile staging and register unpack code as the grouped kernels.
+ */
+int tris_compact3_dequantize(const TrisProjView* proj, void* weights_out_f16, void* stream);
+
+/* ---- route ------------------------------------------------------------------------- */
+
+/*
+ * build_grouped_route (QL:1301-1378, CPP:741-793) without the host sync: all outputs are
+ * device arrays padded to num_experts(+1).  selected_experts is [T, k] int32.  Rows of one
+ * expert are ordered by ascending flat (token, slot) index.
+ *   perm[R], grouped_token_indices[R], grouped_slots[R], row_of_flat[R] (inverse of perm),
+ *   expert_ids[E] (unused tail = -1), segment_offsets[E+1] (tail = R),
+ *   problem_offsets[E+1] (ceil(len/m_tile) prefix), counts[2] = {num_segments, total_problem_tiles}.
+ */
+int tris_build_grouped_route(const int32_t* selected_experts, int32_t num_tokens, int32_t top_k,
+                             int32_t num_experts, int32_t m_tile, int32_t* perm,
+                             int32_t* grouped_token_indices, int32_t* grouped_slots,
+                             int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets,
+                             int32_t* problem_offsets, int32_t* counts, void* stream);
+
+/*
+ * Router head of OlmoeSparseMoeBlock.forward (MO:1052-1058): softmax over fp32 logits
+ * [T, E], top-k, optional renormalisation.  Outputs selected_experts [T,k] int32 and
+ * routing_weights [T,k] fp32.
+ */
+int tris_router_topk(const float* router_logits, int32_t num_tokens, int32_t num_experts,
+                     int32_t top_k, int32_t norm_topk_prob, int32_t* selected_experts,
+                     float* routing_weights, void* stream);
+
+/* ---- backbone ---------------------------------------------------------------------- */
+
+/*
+ * hidden = x . shared_sv^T (QuantLinear.compute_shared_hidden fp16 branch, QL:4454-4502):
+ * x [N, in] fp16 (rows optionally gathered through row_gather), shared_sv [r, in] fp16,
+ * out [N, r] fp16 (out_is_f32 = 0) or fp32.
+ */
+int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_gather, int32_t num_rows,
+                               int32_t in_features, const void* shared_sv_f16, int32_t rank,
+                               void* out, int32_t out_is_f32, void* stream);
+
+/* ---- grouped expert kernels -------------------------------------------------------- */
+
+/*
+ * compact3_tris_precomputed_grouped_forward[_block_gr] (CPP:795-834, CPP:1018-1063; Python
+ * run_grouped_structured_expert_forward, QL:2131-2335): out[R, O] fp16 = per-segment
+ * dequant(U_e) . hidden rows.  hidden is [*, r] fp16; row i of the grouped order reads
+ * hidden row route->row_gather[i] when row_gather is set, else row i.
+ */
+int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
+                         void* out_f16, void* stream);
+
+/*
+ * compact3_tris_precomputed_grouped_dual_forward[_block_gr] (CPP:1065-1136; Python
+ * run_grouped_structured_expert_pair_forward, QL:2338-2634).  With fuse_silu_mul = 0 writes
+ * out_a and out_b [R, O]; with fuse_silu_mul = 1 writes silu(a) * b to out_a only
+ * (the act_fn(gate) * up of MO:1005) and ignores out_b.
+ */
+int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisProjView* proj_b,
+                              const TrisRouteView* route, const void* hidden_a_f16,
+                              const void* hidden_b_f16, void* out_a_f16, void* out_b_f16,
+                              int32_t fuse_silu_mul, void* stream);
+
+/*
+ * final[T, H] fp16 = sum over slots of routing_weights[t, s] * down_out[row_of_flat[t*k+s]]
+ * (the index_add_ of MO:1038-1043, as a deterministic gather in fp32).
+ */
+int tris_combine_routed(const void* down_out_f16, const int32_t* row_of_flat,
+                        const float* routing_weights, int32_t num_tokens, int32_t top_k,
+                        int32_t hidden_size, void* final_f16, void* stream);
+
+/* ---- whole MoE block --------------------------------------------------------------- */
+
+typedef struct TrisMoeLayerView {
+  int32_t hidden_size;        /* H                                                        */
+  int32_t intermediate_size;  /* I                                                        */
+  int32_t num_experts;        /* E                                                        */
+  int32_t top_k;
+  int32_t norm_topk_prob;
+  const void* router_weight;  /* [E, H] fp16 or NULL when logits are passed in            */
+  const void* shared_gate;    /* [r_gu, H] fp16 backbone of gate_proj                     */
+  const void* shared_up;      /* [r_gu, H] fp16                                           */
+  const void* shared_down;    /* [r_d, I] fp16                                            */
+  TrisProjView gate;          /* O = I, r = r_gu                                          */
+  TrisProjView up;
+  TrisProjView down;          /* O = H, r = r_d                                           */
+} TrisMoeLayerView;
+
+size_t tris_moe_layer_workspace_bytes(const TrisMoeLayerView* layer, int32_t num_tokens);
+
+/*
+ * OlmoeSparseMoeBlock.forward -> _forward_grouped (MO:1046-1105, MO:916-1044) as one
+ * stream-ordered launch sequence with no host synchronisation: router (from router_logits
+ * [T, E] fp32 when given, else x . router_weight^T), route, both input-side backbones,
+ * grouped gate/up with SiLU*mul, down backbone, grouped down, weighted combine.
+ * x, y: [T, H] fp16.  router_logits_out (optional) receives the fp32 logits.
+ */
+int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void* x_f16,
+                           const float* router_logits, int32_t num_tokens, void* y_f16,
+                           float* router_logits_out, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRISMOE_B200_H_ */

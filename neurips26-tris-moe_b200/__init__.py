@@ -1,0 +1,52 @@
+"""trismoe_b200: B200 (sm_100a) grouped-expert dequant-GEMM runtime for TriS-MoE payloads.
+
+The package mirrors the Python surface of the reference's grouped path
+(``auto_gptq/nn_modules/qlinear/qlinear_cuda.py`` and
+``auto_gptq/modeling_tris_moe`` in the TriS-MoE tree) on top of a C-ABI CUDA library
+(``csrc/libtrismoe_b200.so``, declared in ``include/trismoe_b200.h``).  There is no CPU or
+PyTorch fallback: every compute entry point raises if the library or a GPU is missing.
+"""
+from . import _native  # noqa: F401
+from .formats import (  # noqa: F401
+    block_gr_encode,
+    build_compact3_packed_payload,
+    dense_gmap_words,
+    pack_bool_matrix,
+    pack_bool_vector,
+    pack_half4_words,
+    stack_expert_payloads,
+)
+from .qlinear_grouped import (  # noqa: F401
+    TRIS_COMPACT3_KERNEL_ABI_VERSION,
+    ExpertSharedMatrix,
+    build_grouped_precomputed_payload,
+    build_grouped_route,
+    compute_shared_hidden,
+    decode_block_gr_gmap,
+    dequantize_grouped_payload,
+    prepare_grouped_payload,
+    run_grouped_structured_expert_forward,
+    run_grouped_structured_expert_pair_forward,
+)
+from .moe_block import TrisSparseMoeBlock  # noqa: F401
+
+__all__ = [
+    "TRIS_COMPACT3_KERNEL_ABI_VERSION",
+    "ExpertSharedMatrix",
+    "TrisSparseMoeBlock",
+    "block_gr_encode",
+    "build_compact3_packed_payload",
+    "build_grouped_precomputed_payload",
+    "build_grouped_route",
+    "compute_shared_hidden",
+    "decode_block_gr_gmap",
+    "dense_gmap_words",
+    "dequantize_grouped_payload",
+    "pack_bool_matrix",
+    "pack_bool_vector",
+    "pack_half4_words",
+    "prepare_grouped_payload",
+    "run_grouped_structured_expert_forward",
+    "run_grouped_structured_expert_pair_forward",
+    "stack_expert_payloads",
+]

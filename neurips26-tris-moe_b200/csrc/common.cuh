@@ -1,0 +1,70 @@
+// Shared helpers for the trismoe_b200 kernels: status plumbing, PTX wrappers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/trismoe_b200.h"
+
+static_assert(sizeof(TrisProjView) == 176, "TrisProjView layout is part of the ABI");
+static_assert(sizeof(TrisRouteView) == 48, "TrisRouteView layout is part of the ABI");
+
+namespace tris {
+
+// ---- host-side error plumbing ---------------------------------------------------------
+void set_last_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+int check_cuda(cudaError_t err, const char* what);
+
+#define TRIS_REQUIRE(cond, status, ...)            \
+  do {                                             \
+    if (!(cond)) return ::tris::fail((status), __VA_ARGS__); \
+  } while (0)
+
+#define TRIS_CUDA(call)                                              \
+  do {                                                               \
+    int _st = ::tris::check_cuda((call), #call);                     \
+    if (_st != TRIS_OK) return _st;                                  \
+  } while (0)
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// One matrix of the shared skinny GEMM (skinny_gemm.cu): out[n, m] = x[n, :] . a[m, :].
+struct SkinnyProblem {
+  const __half* a;   // [m, k]
+  void* out;         // [n, m] fp16 or fp32
+  int32_t m;
+  int32_t out_is_f32;
+};
+int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather,
+                         int n, int k, cudaStream_t stream);
+
+// ---- device helpers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Programmatic dependent launch: wait for the producer grid's memory to be visible /
+// let the dependent grid start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+}  // namespace tris

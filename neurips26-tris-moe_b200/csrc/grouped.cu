@@ -1,0 +1,448 @@
+// Grouped compact3 dequant-matmul kernels (decode / skinny regime), block-GR index build,
+// and the two dump kernels used by the parity tests.
+//
+// One CTA = one (expert segment, output tile).  Per K chunk it stages the compressed
+// planes (block-GR decode across the CTA's lanes, sign planes, scale tables) into shared
+// memory, then every warp unpacks weights straight into m16n8k16 A fragments and
+// multiplies them with the staged activation rows; no dequantized weight is written
+// anywhere but registers.  fp32 accumulation.
+#include <algorithm>
+
+#include "compact3_tile.cuh"
+
+namespace tris {
+
+// ---- block-GR sub-stream index -----------------------------------------------------------
+__global__ void block_gr_build_index_kernel(TrisProjView v, uint32_t* index_out, int sub, int32_t* status) {
+  const int nblk = proj_num_blocks(v);
+  const long long total = static_cast<long long>(v.num_experts) * nblk;
+  for (long long id = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; id < total;
+       id += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int e = static_cast<int>(id / nblk), bi = static_cast<int>(id % nblk);
+    const int32_t* off = v.q_gmap_gr_offsets + static_cast<size_t>(e) * (nblk + 1);
+    const int begin = off[bi], end = off[bi + 1];
+    const int meta = v.q_gmap_gr_meta[static_cast<size_t>(e) * nblk + bi];
+    uint32_t* out = index_out + static_cast<size_t>(id) * sub;
+    for (int j = 0; j < sub; ++j) out[j] = 0u;
+    const int count = end - begin;
+    const bool raw = (meta & TRIS_GR_META_RAW_FLAG) != 0;
+    const int k = meta & TRIS_GR_META_K_MASK;
+    const int one_count = meta >> TRIS_GR_META_ONE_COUNT_SHIFT;
+    bool ok = begin >= 0 && count >= 0 && end <= v.gr_max_words && count <= TRIS_GR_BLOCK_WORDS;
+    if (bi == 0 && begin != 0) ok = false;
+    if (raw) {
+      ok = ok && count == TRIS_GR_BLOCK_WORDS;
+    } else {
+      ok = ok && k <= TRIS_GR_MAX_K && one_count >= 0 && one_count <= TRIS_GR_BLOCK_WORDS * 32 &&
+           (meta & ~(TRIS_GR_META_K_MASK | (0x1FFF << TRIS_GR_META_ONE_COUNT_SHIFT))) == 0 &&
+           (one_count == 0 || count > 0);
+    }
+    if (!ok) {
+      atomicExch(status, TRIS_ERR_CORRUPT);
+      continue;
+    }
+    if (raw || one_count == 0) continue;
+    const uint32_t* w =
+        reinterpret_cast<const uint32_t*>(v.q_gmap_gr_words) + static_cast<size_t>(e) * v.gr_max_words + begin;
+    const int per = (one_count + sub - 1) / sub;
+    const int total_bits = count << 5;
+    const uint32_t kmask = (1u << k) - 1u;
+    int bitpos = 0, flatpos = 0;
+    bool bad = false;
+    for (int n = 0; n < one_count; ++n) {
+      if (n % per == 0) out[n / per] = static_cast<uint32_t>(bitpos) | (static_cast<uint32_t>(flatpos) << 16);
+      int q = 0;
+      uint32_t bits = gr_peek32(w, count, bitpos);
+      while (bits == 0u) {
+        q += 32;
+        bitpos += 32;
+        if (bitpos >= total_bits) { bad = true; break; }
+        bits = gr_peek32(w, count, bitpos);
+      }
+      if (bad) break;
+      const int t = __ffs(bits) - 1;
+      q += t;
+      bitpos += t + 1;
+      const uint32_t rem = gr_peek32(w, count, bitpos) & kmask;
+      bitpos += k;
+      flatpos += (q << k) | static_cast<int>(rem);
+      if (bitpos > total_bits || flatpos >= TRIS_GR_BLOCK_WORDS * 32) { bad = true; break; }
+      ++flatpos;
+    }
+    if (bad) atomicExch(status, TRIS_ERR_CORRUPT);
+  }
+}
+
+// ---- packed-row group table ---------------------------------------------------------------
+__global__ void build_row_groups_kernel(const int32_t* g_idx, int num_experts, int rank, int num_groups,
+                                        int32_t* out, int32_t* status) {
+  const int pr = (rank + 31) >> 5;
+  const int total = num_experts * pr;
+  for (int id = blockIdx.x * blockDim.x + threadIdx.x; id < total; id += gridDim.x * blockDim.x) {
+    const int e = id / pr, p = id % pr;
+    const int32_t* gi = g_idx + static_cast<size_t>(e) * rank;
+    const int c0 = 32 * p, c1 = min(rank, c0 + 32);
+    const int grp = gi[c0];
+    bool ok = grp >= 0 && grp < num_groups;
+    for (int c = c0 + 1; c < c1; ++c) ok = ok && gi[c] == grp;
+    out[id] = ok ? grp : -1;
+    if (!ok) atomicExch(status, TRIS_ERR_UNSUPPORTED);
+  }
+}
+
+// ---- dump kernels -------------------------------------------------------------------------
+// grid (ceil(O/128), ceil(pr/8), E)
+__global__ void __launch_bounds__(kThreads) block_gr_decode_kernel(TrisProjView v, int32_t* dense_out) {
+  extern __shared__ uint4 smem_raw[];
+  auto& sm = *reinterpret_cast<TileSmem<1, 1>*>(smem_raw);
+  const int o0 = blockIdx.x * 128, p0 = blockIdx.y * KC, e = blockIdx.z;
+  stage_gmap_block_gr<1, 1>(sm, &v, e, o0, p0);
+  const int pr = proj_packed_rows(v);
+  for (int i = threadIdx.x; i < kTileWords; i += kThreads) {
+    const int p = i / 128, o = i % 128;
+    if (p0 + p < pr && o0 + o < v.out_features)
+      dense_out[(static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0 + o] = static_cast<int32_t>(sm.g[i]);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) compact3_dequant_kernel(TrisProjView v, __half* weights_out) {
+  extern __shared__ uint4 smem_raw[];
+  auto& sm = *reinterpret_cast<TileSmem<1, 1>*>(smem_raw);
+  const int o0 = blockIdx.x * 128, p0 = blockIdx.y * KC, e = blockIdx.z;
+  if (v.use_block_gr) stage_gmap_block_gr<1, 1>(sm, &v, e, o0, p0);
+  stage_planes_and_scales<1, 1>(sm, &v, e, o0, p0, nullptr);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int pr = proj_packed_rows(v);
+  for (int p = 0; p < KC && p0 + p < pr; ++p) {
+    uint32_t a[2][4];
+    unpack_fragments<1, 1>(sm, 0, p, warp * 16, lane, a);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int og = o0 + warp * 16 + g + 8 * h;
+      if (og >= v.out_features) continue;
+      __half* row = weights_out + (static_cast<size_t>(e) * v.out_features + og) * v.rank;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int ca = 32 * (p0 + p) + t + 4 * i, cb = ca + 16;
+        if (ca < v.rank) row[ca] = __ushort_as_half(static_cast<unsigned short>(a[h][i] & 0xFFFFu));
+        if (cb < v.rank) row[cb] = __ushort_as_half(static_cast<unsigned short>(a[h][i] >> 16));
+      }
+    }
+  }
+}
+
+// ---- grouped forward ----------------------------------------------------------------------
+struct GroupedArgs {
+  TrisProjView proj[2];
+  const __half* hidden[2];
+  __half* out[2];
+  const int32_t* expert_ids;
+  const int32_t* segment_offsets;
+  const int32_t* num_segments_dev;
+  const int32_t* row_gather;
+  int32_t num_segments;
+  int32_t num_rows;
+};
+
+enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };
+
+// grid (ceil(O/OW), num_segments bound)
+template <int NPROJ, int NT, int EPI>
+__global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid_constant__ GroupedArgs args) {
+  constexpr int OW = Geom<NPROJ>::OW;
+  extern __shared__ uint4 smem_raw[];
+  auto& sm = *reinterpret_cast<TileSmem<NPROJ, NT>*>(smem_raw);
+
+  const int seg = blockIdx.y;
+  const int nseg = args.num_segments_dev ? min(*args.num_segments_dev, args.num_segments) : args.num_segments;
+  if (seg >= nseg) return;
+  const int e = args.expert_ids[seg];
+  const int row_begin = args.segment_offsets[seg];
+  const int row_end = min(args.segment_offsets[seg + 1], args.num_rows);
+  if (e < 0 || e >= args.proj[0].num_experts || row_end <= row_begin) return;
+
+  const int o0 = blockIdx.x * OW;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int proj = (NPROJ == 2) ? (warp >> 2) : 0;
+  const int out_local = (NPROJ == 2) ? (warp & 3) * 16 : warp * 16;
+  const int pr = proj_packed_rows(args.proj[0]);
+  const int num_chunks = (pr + KC - 1) / KC;
+  const bool any_gr = args.proj[0].use_block_gr != 0;
+
+  int staged_chunk = -1;
+  for (int r0 = row_begin; r0 < row_end; r0 += NT * 8) {
+    const int rows = min(NT * 8, row_end - r0);
+    const int nt_count = (rows + 7) >> 3;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
+
+    for (int kc = 0; kc < num_chunks; ++kc) {
+      const int p0 = kc * KC;
+      __syncthreads();  // previous consumers of the tables are done
+      if (staged_chunk != kc) {
+        if (any_gr) stage_gmap_block_gr<NPROJ, NT>(sm, args.proj, e, o0, p0);
+        stage_planes_and_scales<NPROJ, NT>(sm, args.proj, e, o0, p0, nullptr);
+        staged_chunk = kc;
+      }
+      stage_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, nt_count, [&](int n) {
+        if (n >= rows) return -1;
+        return args.row_gather ? args.row_gather[r0 + n] : (r0 + n);
+      });
+      __syncthreads();
+
+      for (int p = 0; p < KC && p0 + p < pr; ++p) {
+        uint32_t a[2][4];
+        unpack_fragments<NPROJ, NT>(sm, proj, p, out_local, lane, a);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          if (nt < nt_count) {
+            const uint4 hv = sm.htab[(((proj * NT + nt) * KC + p) * 8 + g) * 4 + t];
+            mma_m16n8k16(acc[nt], a[0][0], a[1][0], a[0][1], a[1][1], hv.x, hv.y);
+            mma_m16n8k16(acc[nt], a[0][2], a[1][2], a[0][3], a[1][3], hv.z, hv.w);
+          }
+        }
+      }
+    }
+
+    // epilogue: acc[nt] = {(out g, row 2t), (out g, row 2t+1), (out g+8, row 2t), (out g+8, row 2t+1)}
+    const TrisProjView& v = args.proj[proj];
+    float scale[2] = {1.f, 1.f}, bias[2] = {0.f, 0.f};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int og = o0 + out_local + g + 8 * h;
+      if (og < v.out_features) {
+        if (v.output_scale) scale[h] = __half2float(reinterpret_cast<const __half*>(v.output_scale)[static_cast<size_t>(e) * v.out_features + og]);
+        if (v.bias) bias[h] = __half2float(reinterpret_cast<const __half*>(v.bias)[static_cast<size_t>(e) * v.out_features + og]);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[nt][c] = acc[nt][c] * scale[c >> 1] + bias[c >> 1];
+
+    if (EPI == EPI_SILU_MUL) {
+      // up warps (proj 1) hand their tile to the gate warps (proj 0) through shared memory
+      __syncthreads();
+      float* xbuf = reinterpret_cast<float*>(sm.htab);
+      if (proj == 1) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+          *reinterpret_cast<float4*>(xbuf + (((warp & 3) * NT + nt) * 32 + lane) * 4) =
+              make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+      }
+      __syncthreads();
+      if (proj == 0) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const float4 u = *reinterpret_cast<const float4*>(xbuf + (((warp & 3) * NT + nt) * 32 + lane) * 4);
+          const float uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float gv = acc[nt][c];
+            acc[nt][c] = gv / (1.f + __expf(-gv)) * uu[c];
+          }
+        }
+      }
+    }
+    if (EPI == EPI_STORE || proj == 0) {
+      __half* outp = args.out[proj];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int n = nt * 8 + 2 * t + (c & 1);
+          const int og = o0 + out_local + g + 8 * (c >> 1);
+          if (n < rows && og < v.out_features)
+            outp[static_cast<size_t>(r0 + n) * v.out_features + og] = __float2half_rn(acc[nt][c]);
+        }
+      }
+    }
+  }
+}
+
+// ---- host launchers -----------------------------------------------------------------------
+static int validate_proj(const TrisProjView* v, const char* name, bool need_runtime) {
+  TRIS_REQUIRE(v != nullptr, TRIS_ERR_INVALID_ARG, "%s: null projection view", name);
+  TRIS_REQUIRE(v->num_experts > 0 && v->out_features > 0 && v->rank > 0 && v->num_groups > 0,
+               TRIS_ERR_INVALID_ARG, "%s: non-positive dims E=%d O=%d r=%d G=%d", name, v->num_experts,
+               v->out_features, v->rank, v->num_groups);
+  TRIS_REQUIRE(v->qweight1 && v->c_map && v->col_pack3 && v->row_pack3, TRIS_ERR_INVALID_ARG,
+               "%s: qweight1/c_map/col_pack3/row_pack3 must be set", name);
+  TRIS_REQUIRE(v->sign2_rows >= 0 && (v->sign2_rows == 0 || (v->qweight2_sparse && v->qweight2_sparse_prefix)),
+               TRIS_ERR_INVALID_ARG, "%s: qweight2_sparse needs its prefix", name);
+  if (v->use_block_gr) {
+    TRIS_REQUIRE(v->q_gmap_gr_words && v->q_gmap_gr_offsets && v->q_gmap_gr_meta && v->gr_max_words >= 0,
+                 TRIS_ERR_INVALID_ARG, "%s: block-GR tensors missing", name);
+    if (need_runtime) {
+      TRIS_REQUIRE(v->gr_index != nullptr, TRIS_ERR_INVALID_ARG,
+                   "%s: block-GR payload has no sub-stream index (call tris_block_gr_build_index)", name);
+      const int s = v->gr_substreams;
+      TRIS_REQUIRE(s >= 1 && s <= 32 && (s & (s - 1)) == 0, TRIS_ERR_INVALID_ARG,
+                   "%s: gr_substreams=%d must be a power of two <= 32", name, s);
+    }
+  } else {
+    TRIS_REQUIRE(v->gmap_sparse_rows == 0 || (v->q_gmap_sparse && v->q_gmap_sparse_prefix), TRIS_ERR_INVALID_ARG,
+                 "%s: q_gmap_sparse needs its prefix", name);
+  }
+  if (need_runtime)
+    TRIS_REQUIRE(v->packed_row_group != nullptr || v->num_groups == 1, TRIS_ERR_INVALID_ARG,
+                 "%s: packed_row_group missing (call tris_build_row_groups)", name);
+  return TRIS_OK;
+}
+
+template <int NPROJ, int NT, int EPI>
+static int launch_grouped(const GroupedArgs& args, cudaStream_t stream) {
+  const size_t smem = sizeof(TileSmem<NPROJ, NT>);
+  auto kernel = grouped_compact3_kernel<NPROJ, NT, EPI>;
+  static bool configured[64] = {};  // per instantiation, per device
+  int dev = 0;
+  TRIS_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    TRIS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  dim3 grid(ceil_div(args.proj[0].out_features, Geom<NPROJ>::OW), args.num_segments);
+  kernel<<<grid, kThreads, smem, stream>>>(args);
+  return check_cuda(cudaGetLastError(), "grouped_compact3_kernel launch");
+}
+
+template <int NPROJ, int EPI>
+static int dispatch_grouped(const GroupedArgs& args, int max_rows, cudaStream_t stream) {
+  if (max_rows <= 8) return launch_grouped<NPROJ, 1, EPI>(args, stream);
+  if (max_rows <= 16) return launch_grouped<NPROJ, 2, EPI>(args, stream);
+  if (max_rows <= 32) return launch_grouped<NPROJ, 4, EPI>(args, stream);
+  return launch_grouped<NPROJ, 8, EPI>(args, stream);
+}
+
+static int fill_route(GroupedArgs& a, const TrisRouteView* route) {
+  TRIS_REQUIRE(route != nullptr && route->expert_ids && route->segment_offsets, TRIS_ERR_INVALID_ARG,
+               "route: expert_ids/segment_offsets must be set");
+  TRIS_REQUIRE(route->num_segments >= 0 && route->num_rows >= 0, TRIS_ERR_INVALID_ARG, "route: negative sizes");
+  a.expert_ids = route->expert_ids;
+  a.segment_offsets = route->segment_offsets;
+  a.num_segments_dev = route->num_segments_dev;
+  a.row_gather = route->row_gather;
+  a.num_segments = route->num_segments;
+  a.num_rows = route->num_rows;
+  return TRIS_OK;
+}
+
+}  // namespace tris
+
+using namespace tris;
+
+extern "C" size_t tris_block_gr_index_bytes(int32_t num_experts, int32_t packed_rows, int32_t out_features,
+                                            int32_t substreams) {
+  if (num_experts <= 0 || packed_rows <= 0 || out_features <= 0 || substreams <= 0) return 0;
+  const size_t nblk = static_cast<size_t>((packed_rows + 1) / 2) * ((out_features + 63) / 64);
+  return static_cast<size_t>(num_experts) * nblk * substreams * sizeof(uint32_t);
+}
+
+extern "C" int tris_block_gr_build_index(const TrisProjView* proj, uint32_t* gr_index_out, int32_t substreams,
+                                         int32_t* status_dev, void* stream) {
+  int st = validate_proj(proj, "tris_block_gr_build_index", false);
+  if (st != TRIS_OK) return st;
+  TRIS_REQUIRE(proj->use_block_gr, TRIS_ERR_INVALID_ARG, "tris_block_gr_build_index: payload is not block-GR");
+  TRIS_REQUIRE(gr_index_out && status_dev, TRIS_ERR_INVALID_ARG, "tris_block_gr_build_index: null output");
+  TRIS_REQUIRE(substreams >= 1 && substreams <= 32 && (substreams & (substreams - 1)) == 0, TRIS_ERR_INVALID_ARG,
+               "tris_block_gr_build_index: substreams=%d must be a power of two <= 32", substreams);
+  const int pr = (proj->rank + 31) / 32;
+  const long long total = static_cast<long long>(proj->num_experts) * ((pr + 1) / 2) * ((proj->out_features + 63) / 64);
+  const int threads = 128;
+  const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 65535));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TRIS_CUDA(cudaMemsetAsync(status_dev, 0, sizeof(int32_t), s));
+  block_gr_build_index_kernel<<<blocks, threads, 0, s>>>(*proj, gr_index_out, substreams, status_dev);
+  return check_cuda(cudaGetLastError(), "block_gr_build_index_kernel launch");
+}
+
+extern "C" int tris_build_row_groups(const int32_t* g_idx, int32_t num_experts, int32_t rank, int32_t num_groups,
+                                     int32_t* packed_row_group_out, int32_t* status_dev, void* stream) {
+  TRIS_REQUIRE(g_idx && packed_row_group_out && status_dev, TRIS_ERR_INVALID_ARG, "tris_build_row_groups: null pointer");
+  TRIS_REQUIRE(num_experts > 0 && rank > 0 && num_groups > 0, TRIS_ERR_INVALID_ARG, "tris_build_row_groups: bad dims");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int total = num_experts * ((rank + 31) / 32);
+  TRIS_CUDA(cudaMemsetAsync(status_dev, 0, sizeof(int32_t), s));
+  build_row_groups_kernel<<<ceil_div(total, 128), 128, 0, s>>>(g_idx, num_experts, rank, num_groups,
+                                                               packed_row_group_out, status_dev);
+  return check_cuda(cudaGetLastError(), "build_row_groups_kernel launch");
+}
+
+extern "C" int tris_block_gr_decode(const TrisProjView* proj, int32_t* dense_out, void* stream) {
+  int st = validate_proj(proj, "tris_block_gr_decode", true);
+  if (st != TRIS_OK) return st;
+  TRIS_REQUIRE(proj->use_block_gr && dense_out, TRIS_ERR_INVALID_ARG, "tris_block_gr_decode: needs a block-GR payload and an output");
+  const int pr = (proj->rank + 31) / 32;
+  dim3 grid(ceil_div(proj->out_features, 128), ceil_div(pr, KC), proj->num_experts);
+  const size_t smem = sizeof(TileSmem<1, 1>);
+  TRIS_CUDA(cudaFuncSetAttribute(block_gr_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  block_gr_decode_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(*proj, dense_out);
+  return check_cuda(cudaGetLastError(), "block_gr_decode_kernel launch");
+}
+
+extern "C" int tris_compact3_dequantize(const TrisProjView* proj, void* weights_out_f16, void* stream) {
+  int st = validate_proj(proj, "tris_compact3_dequantize", true);
+  if (st != TRIS_OK) return st;
+  TRIS_REQUIRE(weights_out_f16, TRIS_ERR_INVALID_ARG, "tris_compact3_dequantize: null output");
+  const int pr = (proj->rank + 31) / 32;
+  dim3 grid(ceil_div(proj->out_features, 128), ceil_div(pr, KC), proj->num_experts);
+  const size_t smem = sizeof(TileSmem<1, 1>);
+  TRIS_CUDA(cudaFuncSetAttribute(compact3_dequant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  compact3_dequant_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      *proj, static_cast<__half*>(weights_out_f16));
+  return check_cuda(cudaGetLastError(), "compact3_dequant_kernel launch");
+}
+
+extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
+                                    void* out_f16, void* stream) {
+  int st = validate_proj(proj, "tris_grouped_forward", true);
+  if (st != TRIS_OK) return st;
+  TRIS_REQUIRE(hidden_f16 && out_f16, TRIS_ERR_INVALID_ARG, "tris_grouped_forward: null hidden/out");
+  GroupedArgs a{};
+  st = fill_route(a, route);
+  if (st != TRIS_OK) return st;
+  if (a.num_segments == 0 || a.num_rows == 0) return TRIS_OK;
+  a.proj[0] = *proj;
+  a.proj[1] = *proj;
+  a.hidden[0] = a.hidden[1] = static_cast<const __half*>(hidden_f16);
+  a.out[0] = a.out[1] = static_cast<__half*>(out_f16);
+  const int max_rows = route->max_rows_per_segment > 0 ? route->max_rows_per_segment : route->num_rows;
+  return dispatch_grouped<1, EPI_STORE>(a, max_rows, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisProjView* proj_b,
+                                         const TrisRouteView* route, const void* hidden_a_f16,
+                                         const void* hidden_b_f16, void* out_a_f16, void* out_b_f16,
+                                         int32_t fuse_silu_mul, void* stream) {
+  int st = validate_proj(proj_a, "tris_grouped_pair_forward(a)", true);
+  if (st != TRIS_OK) return st;
+  st = validate_proj(proj_b, "tris_grouped_pair_forward(b)", true);
+  if (st != TRIS_OK) return st;
+  TRIS_REQUIRE(proj_a->num_experts == proj_b->num_experts && proj_a->out_features == proj_b->out_features &&
+                   proj_a->rank == proj_b->rank,
+               TRIS_ERR_UNSUPPORTED, "tris_grouped_pair_forward: the two projections must share E, O and r");
+  TRIS_REQUIRE((proj_a->use_block_gr != 0) == (proj_b->use_block_gr != 0) &&
+                   (!proj_a->use_block_gr || proj_a->gr_substreams == proj_b->gr_substreams),
+               TRIS_ERR_UNSUPPORTED, "tris_grouped_pair_forward: the two projections must share the g_map format");
+  TRIS_REQUIRE(hidden_a_f16 && hidden_b_f16 && out_a_f16 && (fuse_silu_mul || out_b_f16), TRIS_ERR_INVALID_ARG,
+               "tris_grouped_pair_forward: null hidden/out");
+  GroupedArgs a{};
+  st = fill_route(a, route);
+  if (st != TRIS_OK) return st;
+  if (a.num_segments == 0 || a.num_rows == 0) return TRIS_OK;
+  a.proj[0] = *proj_a;
+  a.proj[1] = *proj_b;
+  a.hidden[0] = static_cast<const __half*>(hidden_a_f16);
+  a.hidden[1] = static_cast<const __half*>(hidden_b_f16);
+  a.out[0] = static_cast<__half*>(out_a_f16);
+  a.out[1] = static_cast<__half*>(out_b_f16);
+  const int max_rows = route->max_rows_per_segment > 0 ? route->max_rows_per_segment : route->num_rows;
+  if (fuse_silu_mul) return dispatch_grouped<2, EPI_SILU_MUL>(a, max_rows, static_cast<cudaStream_t>(stream));
+  return dispatch_grouped<2, EPI_STORE>(a, max_rows, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,155 @@
+// Whole MoE block as one stream-ordered launch sequence (no host synchronisation):
+//   router logits + both input-side backbones  (one skinny-GEMM launch sharing x)
+//   softmax/top-k, grouped route
+//   grouped gate/up with SiLU*mul epilogue
+//   down backbone on the routed rows
+//   grouped down
+//   weighted combine back to token order
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace tris {
+struct LayerWorkspace {
+  float* logits;
+  int32_t* selected;
+  float* weights;
+  int32_t* perm;
+  int32_t* tok;
+  int32_t* slot;
+  int32_t* row_of_flat;
+  int32_t* expert_ids;
+  int32_t* segment_offsets;
+  int32_t* problem_offsets;
+  int32_t* counts;
+  __half* hidden_gate;
+  __half* hidden_up;
+  __half* mlp;
+  __half* hidden_down;
+  __half* down_out;
+  size_t bytes;
+};
+
+static LayerWorkspace carve(const TrisMoeLayerView* L, int T, char* base) {
+  LayerWorkspace w{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    char* p = base ? base + off : nullptr;
+    off += (bytes + 255) & ~static_cast<size_t>(255);
+    return p;
+  };
+  const size_t R = static_cast<size_t>(T) * L->top_k;
+  const size_t E = L->num_experts;
+  w.logits = reinterpret_cast<float*>(take(sizeof(float) * T * E));
+  w.selected = reinterpret_cast<int32_t*>(take(4 * R));
+  w.weights = reinterpret_cast<float*>(take(4 * R));
+  w.perm = reinterpret_cast<int32_t*>(take(4 * R));
+  w.tok = reinterpret_cast<int32_t*>(take(4 * R));
+  w.slot = reinterpret_cast<int32_t*>(take(4 * R));
+  w.row_of_flat = reinterpret_cast<int32_t*>(take(4 * R));
+  w.expert_ids = reinterpret_cast<int32_t*>(take(4 * E));
+  w.segment_offsets = reinterpret_cast<int32_t*>(take(4 * (E + 1)));
+  w.problem_offsets = reinterpret_cast<int32_t*>(take(4 * (E + 1)));
+  w.counts = reinterpret_cast<int32_t*>(take(8));
+  w.hidden_gate = reinterpret_cast<__half*>(take(2 * static_cast<size_t>(T) * L->gate.rank));
+  w.hidden_up = reinterpret_cast<__half*>(take(2 * static_cast<size_t>(T) * L->up.rank));
+  w.mlp = reinterpret_cast<__half*>(take(2 * R * L->intermediate_size));
+  w.hidden_down = reinterpret_cast<__half*>(take(2 * R * L->down.rank));
+  w.down_out = reinterpret_cast<__half*>(take(2 * R * L->hidden_size));
+  w.bytes = off;
+  return w;
+}
+
+static int validate_layer(const TrisMoeLayerView* L) {
+  TRIS_REQUIRE(L != nullptr, TRIS_ERR_INVALID_ARG, "moe layer: null view");
+  TRIS_REQUIRE(L->hidden_size > 0 && L->intermediate_size > 0 && L->num_experts > 0 && L->top_k > 0 &&
+                   L->top_k <= L->num_experts,
+               TRIS_ERR_INVALID_ARG, "moe layer: bad dims H=%d I=%d E=%d k=%d", L->hidden_size, L->intermediate_size,
+               L->num_experts, L->top_k);
+  TRIS_REQUIRE(L->shared_gate && L->shared_up && L->shared_down, TRIS_ERR_INVALID_ARG, "moe layer: backbone matrices missing");
+  TRIS_REQUIRE(L->gate.out_features == L->intermediate_size && L->up.out_features == L->intermediate_size &&
+                   L->down.out_features == L->hidden_size,
+               TRIS_ERR_INVALID_ARG, "moe layer: projection out_features do not match H/I");
+  TRIS_REQUIRE(L->gate.num_experts == L->num_experts && L->up.num_experts == L->num_experts &&
+                   L->down.num_experts == L->num_experts,
+               TRIS_ERR_INVALID_ARG, "moe layer: projection expert counts differ");
+  return TRIS_OK;
+}
+}  // namespace tris
+
+using namespace tris;
+
+extern "C" size_t tris_moe_layer_workspace_bytes(const TrisMoeLayerView* layer, int32_t num_tokens) {
+  if (layer == nullptr || num_tokens < 0 || validate_layer(layer) != TRIS_OK) return 0;
+  return carve(layer, num_tokens, nullptr).bytes;
+}
+
+extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void* x_f16, const float* router_logits,
+                                      int32_t num_tokens, void* y_f16, float* router_logits_out, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  int st = validate_layer(layer);
+  if (st != TRIS_OK) return st;
+  TRIS_REQUIRE(x_f16 && y_f16, TRIS_ERR_INVALID_ARG, "tris_moe_layer_forward: null x/y");
+  TRIS_REQUIRE(num_tokens >= 0, TRIS_ERR_INVALID_ARG, "tris_moe_layer_forward: negative token count");
+  TRIS_REQUIRE(router_logits || layer->router_weight, TRIS_ERR_INVALID_ARG,
+               "tris_moe_layer_forward: need router_logits or a router weight");
+  if (num_tokens == 0) return TRIS_OK;
+  const int T = num_tokens;
+  TRIS_REQUIRE(workspace != nullptr, TRIS_ERR_WORKSPACE, "tris_moe_layer_forward: null workspace");
+  LayerWorkspace w = carve(layer, T, static_cast<char*>(workspace));
+  TRIS_REQUIRE(workspace_bytes >= w.bytes, TRIS_ERR_WORKSPACE, "tris_moe_layer_forward: workspace %zu < %zu bytes",
+               workspace_bytes, w.bytes);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int R = T * layer->top_k;
+  const __half* x = static_cast<const __half*>(x_f16);
+
+  // 1. backbones (+ router logits) share one pass over x
+  SkinnyProblem probs[3];
+  int np = 0;
+  probs[np++] = {static_cast<const __half*>(layer->shared_gate), w.hidden_gate, layer->gate.rank, 0};
+  probs[np++] = {static_cast<const __half*>(layer->shared_up), w.hidden_up, layer->up.rank, 0};
+  const float* logits = router_logits;
+  if (logits == nullptr) {
+    float* dst = router_logits_out ? router_logits_out : w.logits;
+    probs[np++] = {static_cast<const __half*>(layer->router_weight), dst, layer->num_experts, 1};
+    logits = dst;
+  } else if (router_logits_out && router_logits_out != router_logits) {
+    TRIS_CUDA(cudaMemcpyAsync(router_logits_out, router_logits, sizeof(float) * T * layer->num_experts,
+                              cudaMemcpyDeviceToDevice, s));
+  }
+  st = launch_shared_hidden(probs, np, x, nullptr, T, layer->hidden_size, s);
+  if (st != TRIS_OK) return st;
+
+  // 2. router + route
+  st = tris_router_topk(logits, T, layer->num_experts, layer->top_k, layer->norm_topk_prob, w.selected, w.weights, s);
+  if (st != TRIS_OK) return st;
+  st = tris_build_grouped_route(w.selected, T, layer->top_k, layer->num_experts, 4, w.perm, w.tok, w.slot,
+                                w.row_of_flat, w.expert_ids, w.segment_offsets, w.problem_offsets, w.counts, s);
+  if (st != TRIS_OK) return st;
+
+  TrisRouteView route{};
+  route.expert_ids = w.expert_ids;
+  route.segment_offsets = w.segment_offsets;
+  route.num_segments_dev = w.counts;
+  route.num_segments = std::min(layer->num_experts, R);
+  route.num_rows = R;
+  route.max_rows_per_segment = T;  // top-k experts of a token are distinct
+
+  // 3. gate/up + SiLU*mul; rows read the per-token backbone outputs through tok[]
+  route.row_gather = w.tok;
+  st = tris_grouped_pair_forward(&layer->gate, &layer->up, &route, w.hidden_gate, w.hidden_up, w.mlp, nullptr, 1, s);
+  if (st != TRIS_OK) return st;
+
+  // 4. down backbone on routed rows
+  SkinnyProblem down{static_cast<const __half*>(layer->shared_down), w.hidden_down, layer->down.rank, 0};
+  st = launch_shared_hidden(&down, 1, w.mlp, nullptr, R, layer->intermediate_size, s);
+  if (st != TRIS_OK) return st;
+
+  // 5. grouped down
+  route.row_gather = nullptr;
+  st = tris_grouped_forward(&layer->down, &route, w.hidden_down, w.down_out, s);
+  if (st != TRIS_OK) return st;
+
+  // 6. combine
+  return tris_combine_routed(w.down_out, w.row_of_flat, w.weights, T, layer->top_k, layer->hidden_size, y_f16, s);
+}

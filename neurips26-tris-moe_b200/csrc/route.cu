@@ -1,0 +1,209 @@
+// Router head (softmax + top-k), grouped route construction and the weighted combine.
+//
+// The route is built entirely on the device and written into arrays padded to the number
+// of experts, so the launch sequence of a layer never waits on the host.
+#include "common.cuh"
+
+namespace tris {
+
+constexpr int kRouteThreads = 1024;
+constexpr int kMaxExpertsPerLane = 8;  // experts <= 256
+
+// One warp per token.  Ties go to the lower expert index.
+__global__ void router_topk_kernel(const float* __restrict__ logits, int num_tokens, int num_experts, int top_k,
+                                   int norm, int32_t* __restrict__ selected, float* __restrict__ weights) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= num_tokens) return;
+  pdl_wait();
+  const float* row = logits + static_cast<size_t>(warp) * num_experts;
+  float v[kMaxExpertsPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = (e < num_experts) ? row[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = (e < num_experts) ? expf(v[i] - mx) : -1.f;  // probabilities are >= 0; -1 marks "taken/absent"
+    if (e < num_experts) sum += v[i];
+  }
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  const float inv = 1.f / sum;
+  float picked_sum = 0.f;
+  float my_w = 0.f;  // lane s keeps the weight of slot s (top_k <= 32)
+  int my_e = 0;
+  for (int s = 0; s < top_k; ++s) {
+    float best = -1.f;
+    int best_e = 0x7FFFFFFF;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (v[i] > best) { best = v[i]; best_e = e; }  // ascending e inside a lane: first max wins
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      if (lane + 32 * i == best_e) v[i] = -1.f;
+    const float p = best * inv;
+    picked_sum += p;
+    if (lane == s) { my_w = p; my_e = best_e; }
+  }
+  if (lane < top_k) {
+    selected[static_cast<size_t>(warp) * top_k + lane] = my_e;
+    weights[static_cast<size_t>(warp) * top_k + lane] = norm ? my_w / picked_sum : my_w;
+  }
+}
+
+// Single CTA.  Counting sort of the flat (token, slot) list by expert, stable in flat order.
+__global__ void __launch_bounds__(kRouteThreads) build_route_kernel(
+    const int32_t* __restrict__ selected, int num_tokens, int top_k, int num_experts, int m_tile,
+    int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
+    int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
+    int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
+  extern __shared__ int32_t sh[];
+  int32_t* count = sh;                 // [E]
+  int32_t* start = sh + num_experts;   // [E] first grouped row of each expert
+  const int R = num_tokens * top_k;
+  const int tid = threadIdx.x;
+  pdl_wait();
+  for (int e = tid; e < num_experts; e += kRouteThreads) count[e] = 0;
+  __syncthreads();
+  for (int f = tid; f < R; f += kRouteThreads) {
+    const int e = selected[f];
+    if (e >= 0 && e < num_experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int rows = 0, tiles = 0, nseg = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      start[e] = rows;
+      const int c = count[e];
+      if (c > 0) {
+        expert_ids[nseg] = e;
+        segment_offsets[nseg] = rows;
+        problem_offsets[nseg] = tiles;
+        rows += c;
+        tiles += (c + m_tile - 1) / m_tile;
+        ++nseg;
+      }
+    }
+    for (int s = nseg; s <= num_experts; ++s) {
+      segment_offsets[s] = rows;
+      problem_offsets[s] = tiles;
+      if (s < num_experts) expert_ids[s] = -1;
+    }
+    counts_out[0] = nseg;
+    counts_out[1] = tiles;
+  }
+  __syncthreads();
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int e = warp; e < num_experts; e += kRouteThreads / 32) {
+    if (count[e] == 0) continue;
+    int running = start[e];
+    for (int base = 0; base < R; base += 32) {
+      const int f = base + lane;
+      const bool hit = f < R && selected[f] == e;
+      const unsigned bal = __ballot_sync(0xFFFFFFFFu, hit);
+      if (hit) {
+        const int pos = running + __popc(bal & ((1u << lane) - 1u));
+        perm[pos] = f;
+        tok[pos] = f / top_k;
+        slot[pos] = f - (f / top_k) * top_k;
+        row_of_flat[f] = pos;
+      }
+      running += __popc(bal);
+    }
+  }
+}
+
+// final[t, :] = sum_s w[t, s] * rows[row_of_flat[t*k+s], :]; one thread per 8 output halves.
+__global__ void combine_routed_kernel(const __half* __restrict__ rows, const int32_t* __restrict__ row_of_flat,
+                                      const float* __restrict__ weights, int num_tokens, int top_k, int hidden,
+                                      __half* __restrict__ out) {
+  const int vec_per_row = hidden >> 3;
+  const long long id = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (id >= static_cast<long long>(num_tokens) * vec_per_row) return;
+  const int t = static_cast<int>(id / vec_per_row), c = static_cast<int>(id % vec_per_row) * 8;
+  pdl_wait();
+  float acc[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+  for (int s = 0; s < top_k; ++s) {
+    const int r = row_of_flat[t * top_k + s];
+    const float w = weights[t * top_k + s];
+    const uint4 v = *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(r) * hidden + c);
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float2 f = __half22float2(h2[u]);
+      acc[2 * u] += w * f.x;
+      acc[2 * u + 1] += w * f.y;
+    }
+  }
+  uint4 o;
+  __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) oh[u] = __floats2half2_rn(acc[2 * u], acc[2 * u + 1]);
+  *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden + c) = o;
+}
+
+}  // namespace tris
+
+using namespace tris;
+
+extern "C" int tris_router_topk(const float* router_logits, int32_t num_tokens, int32_t num_experts, int32_t top_k,
+                                int32_t norm_topk_prob, int32_t* selected_experts, float* routing_weights,
+                                void* stream) {
+  TRIS_REQUIRE(router_logits && selected_experts && routing_weights, TRIS_ERR_INVALID_ARG, "tris_router_topk: null pointer");
+  TRIS_REQUIRE(num_tokens >= 0 && num_experts > 0 && top_k > 0 && top_k <= num_experts, TRIS_ERR_INVALID_ARG,
+               "tris_router_topk: bad sizes T=%d E=%d k=%d", num_tokens, num_experts, top_k);
+  TRIS_REQUIRE(num_experts <= 32 * kMaxExpertsPerLane && top_k <= 32, TRIS_ERR_UNSUPPORTED,
+               "tris_router_topk: supports up to %d experts and top-32", 32 * kMaxExpertsPerLane);
+  if (num_tokens == 0) return TRIS_OK;
+  const int threads = 128;
+  router_topk_kernel<<<ceil_div(num_tokens * 32, threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      router_logits, num_tokens, num_experts, top_k, norm_topk_prob, selected_experts, routing_weights);
+  return check_cuda(cudaGetLastError(), "router_topk_kernel launch");
+}
+
+extern "C" int tris_build_grouped_route(const int32_t* selected_experts, int32_t num_tokens, int32_t top_k,
+                                        int32_t num_experts, int32_t m_tile, int32_t* perm,
+                                        int32_t* grouped_token_indices, int32_t* grouped_slots, int32_t* row_of_flat,
+                                        int32_t* expert_ids, int32_t* segment_offsets, int32_t* problem_offsets,
+                                        int32_t* counts, void* stream) {
+  TRIS_REQUIRE(selected_experts && perm && grouped_token_indices && grouped_slots && row_of_flat && expert_ids &&
+                   segment_offsets && problem_offsets && counts,
+               TRIS_ERR_INVALID_ARG, "tris_build_grouped_route: null pointer");
+  TRIS_REQUIRE(num_tokens >= 0 && top_k > 0 && num_experts > 0 && m_tile > 0, TRIS_ERR_INVALID_ARG,
+               "tris_build_grouped_route: bad sizes T=%d k=%d E=%d m_tile=%d", num_tokens, top_k, num_experts, m_tile);
+  TRIS_REQUIRE(num_experts <= 4096, TRIS_ERR_UNSUPPORTED, "tris_build_grouped_route: more than 4096 experts");
+  build_route_kernel<<<1, kRouteThreads, 2 * num_experts * sizeof(int32_t), static_cast<cudaStream_t>(stream)>>>(
+      selected_experts, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices, grouped_slots,
+      row_of_flat, expert_ids, segment_offsets, problem_offsets, counts);
+  return check_cuda(cudaGetLastError(), "build_route_kernel launch");
+}
+
+extern "C" int tris_combine_routed(const void* down_out_f16, const int32_t* row_of_flat, const float* routing_weights,
+                                   int32_t num_tokens, int32_t top_k, int32_t hidden_size, void* final_f16,
+                                   void* stream) {
+  TRIS_REQUIRE(down_out_f16 && row_of_flat && routing_weights && final_f16, TRIS_ERR_INVALID_ARG, "tris_combine_routed: null pointer");
+  TRIS_REQUIRE(num_tokens >= 0 && top_k > 0 && hidden_size > 0, TRIS_ERR_INVALID_ARG, "tris_combine_routed: bad sizes");
+  TRIS_REQUIRE((hidden_size & 7) == 0, TRIS_ERR_UNSUPPORTED, "tris_combine_routed: hidden_size must be a multiple of 8");
+  if (num_tokens == 0) return TRIS_OK;
+  const long long total = static_cast<long long>(num_tokens) * (hidden_size / 8);
+  const int threads = 256;
+  combine_routed_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(down_out_f16), row_of_flat, routing_weights, num_tokens, top_k, hidden_size,
+      static_cast<__half*>(final_f16));
+  return check_cuda(cudaGetLastError(), "combine_routed_kernel launch");
+}

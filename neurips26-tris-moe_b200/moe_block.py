@@ -1,0 +1,166 @@
+"""MoE block on the trismoe_b200 runtime, mirroring ``OlmoeSparseMoeBlock``
+(``auto_gptq/modeling_tris_moe/modeling_olmoe.py:621-1105`` in the TriS-MoE tree; the
+Mixtral and Qwen2-MoE blocks call the same operators with other shapes).
+
+``forward`` runs the whole block through one C-ABI call (``tris_moe_layer_forward``):
+router, route, both input-side backbones, grouped gate/up with SiLU*mul, down backbone,
+grouped down and the weighted combine, stream-ordered with no host synchronisation.
+``forward_grouped_ops`` composes the same result from the individual reference-named
+operators, the way ``_forward_grouped`` (modeling_olmoe.py:916-1044) does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+from torch import nn
+
+from . import _native
+from ._native import TrisMoeLayerView
+from .qlinear_grouped import (
+    build_grouped_route,
+    compute_shared_hidden,
+    prepare_grouped_payload,
+    proj_view,
+    run_grouped_structured_expert_forward,
+    run_grouped_structured_expert_pair_forward,
+)
+
+
+class TrisSparseMoeBlock(nn.Module):
+    """Quantized grouped-expert MoE layer.
+
+    Args mirror the HF config fields the reference block reads: ``hidden_size``,
+    ``intermediate_size``, ``num_experts``, ``num_experts_per_tok``, ``norm_topk_prob``.
+    Weights are attached with :meth:`load_grouped_payloads`.
+    """
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, num_experts_per_tok: int,
+                 norm_topk_prob: bool = False):
+        super().__init__()
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.num_experts = int(num_experts)
+        self.top_k = int(num_experts_per_tok)
+        self.norm_topk_prob = bool(norm_topk_prob)
+        self.gate = nn.Linear(self.hidden_size, self.num_experts, bias=False, dtype=torch.float16)
+        self.register_buffer("shared_gate", torch.zeros((0, 0), dtype=torch.float16))
+        self.register_buffer("shared_up", torch.zeros((0, 0), dtype=torch.float16))
+        self.register_buffer("shared_down", torch.zeros((0, 0), dtype=torch.float16))
+        self._grouped_payload_cache: dict = {}
+        self._layer_view: Optional[TrisMoeLayerView] = None
+        self._workspace: Optional[torch.Tensor] = None
+
+    # -- loading ---------------------------------------------------------------------------
+    def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate: torch.Tensor,
+                              shared_up: torch.Tensor, shared_down: torch.Tensor,
+                              router_weight: Optional[torch.Tensor] = None, device=None) -> "TrisSparseMoeBlock":
+        """Attaches the E-stacked payloads (``enable_grouped_deployment_only``,
+        modeling_olmoe.py:732-804) and the three fp16 backbones, moving everything to
+        ``device`` and deriving the decode index once."""
+        dev = torch.device(device) if device is not None else gate["qweight1"].device
+        self._grouped_payload_cache = {
+            "gate": prepare_grouped_payload(gate, dev),
+            "up": prepare_grouped_payload(up, dev),
+            "down": prepare_grouped_payload(down, dev),
+        }
+        self.shared_gate = shared_gate.to(dev, torch.float16).contiguous()
+        self.shared_up = shared_up.to(dev, torch.float16).contiguous()
+        self.shared_down = shared_down.to(dev, torch.float16).contiguous()
+        if router_weight is not None:
+            self.gate.weight = nn.Parameter(router_weight.to(dev, torch.float16).contiguous(), requires_grad=False)
+        else:
+            self.gate.to(dev)
+        self._layer_view = None
+        return self
+
+    def _get_grouped_payload(self, cache_key: str) -> dict:
+        if cache_key not in self._grouped_payload_cache:
+            raise RuntimeError(f"trismoe_b200: grouped payload '{cache_key}' was not loaded")
+        return self._grouped_payload_cache[cache_key]
+
+    def layer_view(self) -> TrisMoeLayerView:
+        views = [proj_view(self._get_grouped_payload(k)) for k in ("gate", "up", "down")]
+        if self._layer_view is None or any(self._get_grouped_payload(k).get("_tris_layer_dirty") for k in ("gate", "up", "down")):
+            v = TrisMoeLayerView()
+            v.hidden_size, v.intermediate_size = self.hidden_size, self.intermediate_size
+            v.num_experts, v.top_k, v.norm_topk_prob = self.num_experts, self.top_k, int(self.norm_topk_prob)
+            v.router_weight = self.gate.weight.data_ptr()
+            v.shared_gate = self.shared_gate.data_ptr()
+            v.shared_up = self.shared_up.data_ptr()
+            v.shared_down = self.shared_down.data_ptr()
+            v.gate, v.up, v.down = views
+            for k in ("gate", "up", "down"):
+                self._get_grouped_payload(k)["_tris_layer_dirty"] = False
+            self._layer_view = v
+        return self._layer_view
+
+    def workspace(self, num_tokens: int, device) -> torch.Tensor:
+        lib = _native.load()
+        need = int(lib.tris_moe_layer_workspace_bytes(C.byref(self.layer_view()), int(num_tokens)))
+        if need == 0 and num_tokens > 0:
+            raise RuntimeError("trismoe_b200: invalid layer view (workspace size query failed)")
+        if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
+            self._workspace = torch.empty((need,), dtype=torch.uint8, device=device)
+        return self._workspace
+
+    # -- forward ---------------------------------------------------------------------------
+    def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
+        """Returns ``(final_hidden_states [B, S, H], router_logits [T, E])`` like
+        ``OlmoeSparseMoeBlock.forward`` (modeling_olmoe.py:1046-1105).  ``router_logits``
+        (fp32 ``[T, E]``) may be passed in to skip the router linear."""
+        _native.require_cuda(hidden_states, "TrisSparseMoeBlock.forward")
+        if hidden_states.dtype != torch.float16:
+            raise RuntimeError(f"trismoe_b200: grouped expert kernels require float16 hidden states, got {hidden_states.dtype}")
+        lib = _native.load()
+        shape = hidden_states.shape
+        x = hidden_states.reshape(-1, shape[-1]).contiguous()
+        T = int(x.shape[0])
+        dev = x.device
+        y = torch.empty_like(x)
+        if router_logits is not None:
+            logits = router_logits.reshape(T, self.num_experts).to(torch.float32).contiguous()
+            logits_in, logits_out = logits.data_ptr(), None
+        else:
+            logits = torch.empty((T, self.num_experts), dtype=torch.float32, device=dev)
+            logits_in, logits_out = None, logits.data_ptr()
+        if T:
+            ws = self.workspace(T, dev)
+            with torch.cuda.device(dev):
+                _native.check(
+                    lib.tris_moe_layer_forward(C.byref(self.layer_view()), x.data_ptr(), logits_in, T, y.data_ptr(),
+                                               logits_out, ws.data_ptr(), ws.numel(),
+                                               torch.cuda.current_stream(dev).cuda_stream),
+                    "moe_layer_forward",
+                )
+        return y.reshape(shape), logits
+
+    def forward_grouped_ops(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
+        """Same result as :meth:`forward`, composed from the reference-named operators in
+        the order of ``_forward_grouped`` (modeling_olmoe.py:916-1044); torch is used only
+        for the glue the reference also does in torch (softmax/top-k, gathers, act*mul,
+        index_add_)."""
+        shape = hidden_states.shape
+        x = hidden_states.reshape(-1, shape[-1])
+        if router_logits is None:
+            router_logits = torch.nn.functional.linear(x, self.gate.weight)
+        routing = torch.softmax(router_logits, dim=1, dtype=torch.float)
+        routing, selected = torch.topk(routing, self.top_k, dim=-1)
+        if self.norm_topk_prob:
+            routing = routing / routing.sum(dim=-1, keepdim=True)
+        routing = routing.to(x.dtype)
+        route = build_grouped_route(selected, self.num_experts)
+        tok, slots = route["grouped_token_indices"], route["grouped_slots"]
+        x_grouped = x.index_select(0, tok)
+        grouped_routing = routing[tok, slots].unsqueeze(-1)
+        gate_hidden = compute_shared_hidden(x, self.shared_gate).index_select(0, tok)
+        up_hidden = compute_shared_hidden(x, self.shared_up).index_select(0, tok)
+        gate_out, up_out = run_grouped_structured_expert_pair_forward(
+            self._get_grouped_payload("gate"), self._get_grouped_payload("up"), gate_hidden, up_hidden, x_grouped, route)
+        mlp = torch.nn.functional.silu(gate_out) * up_out
+        down_hidden = compute_shared_hidden(mlp, self.shared_down)
+        down_out = run_grouped_structured_expert_forward(self._get_grouped_payload("down"), down_hidden, mlp, route)
+        final = x.new_zeros(x.shape)
+        final.index_add_(0, tok, (down_out * grouped_routing).to(x.dtype))
+        return final.reshape(shape), router_logits

@@ -1,0 +1,468 @@
+"""Grouped compact3 operators with the names and argument order of the reference module
+``auto_gptq/nn_modules/qlinear/qlinear_cuda.py`` (TriS-MoE tree), running on the
+trismoe_b200 CUDA library.
+
+Covered surface: ``build_grouped_precomputed_payload`` (qlinear_cuda.py:1512),
+``build_grouped_route`` (:1301), ``run_grouped_structured_expert_forward`` (:2131),
+``run_grouped_structured_expert_pair_forward`` (:2338), ``compute_shared_hidden`` (:4454,
+fp16 backbone branch) and ``ExpertSharedMatrix`` (:2787, fp16 ``shared_sv`` only).
+
+Error behaviour follows the reference wrappers: shape/dtype mismatches return ``None``
+(the reference's "kernel unavailable" signal); anything the library itself rejects, a
+missing library, or tensors that are not on a CUDA device raise ``RuntimeError`` - there
+is no CPU or PyTorch fallback to fall back to.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native
+from ._native import TrisProjView, TrisRouteView
+from .formats import stack_expert_payloads
+
+TRIS_COMPACT3_KERNEL_ABI_VERSION = 2
+GROUPED_SEGMENT_M_TILE = 4
+DEFAULT_GR_SUBSTREAMS = 16
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None or t.numel() == 0:
+        return None
+    return t.data_ptr()
+
+
+def _ensure(t: torch.Tensor, dtype, device) -> torch.Tensor:
+    if t.dtype != dtype or t.device != device or not t.is_contiguous():
+        t = t.to(device=device, dtype=dtype).contiguous()
+    return t
+
+
+# ---------------------------------------------------------------------------------------
+# payloads
+# ---------------------------------------------------------------------------------------
+def prepare_grouped_payload(payload: dict, device=None, gr_substreams: int = DEFAULT_GR_SUBSTREAMS) -> dict:
+    """Moves an E-stacked payload to ``device`` and derives what the kernels need beyond the
+    reference tensors: the per-packed-row group table (validating ``g_idx`` as
+    ``prepare_compact3_k64_groups`` does, qlinear_cuda.py:364-407) and, for block-GR
+    payloads, the sub-stream index (validating offsets/meta).  Runs once at load time and
+    synchronises to read the validation status.  Idempotent."""
+    if payload.get("_tris_prepared") and (device is None or payload["qweight1"].device == torch.device(device)):
+        return payload
+    lib = _native.load()
+    dev = torch.device(device) if device is not None else payload["qweight1"].device
+    if dev.type != "cuda":
+        raise RuntimeError("trismoe_b200 prepare_grouped_payload: payloads must live on a CUDA device")
+    i32 = torch.int32
+    for key in ("qweight1", "qweight2_sparse", "qweight2_sparse_prefix", "q_gmap_sparse", "q_gmap_sparse_prefix",
+                "q_gmap_gr_words", "q_gmap_gr_offsets", "q_gmap_gr_meta", "c_map", "g_idx"):
+        if isinstance(payload.get(key), torch.Tensor):
+            payload[key] = _ensure(payload[key], i32, dev)
+    for key in ("col_pack3", "row_pack3"):
+        payload[key] = _ensure(payload[key], torch.int64, dev)
+    for key in ("output_scale", "bias"):
+        if isinstance(payload.get(key), torch.Tensor):
+            payload[key] = _ensure(payload[key], torch.float16, dev)
+    qw1 = payload["qweight1"]
+    if qw1.dim() != 3:
+        raise RuntimeError("trismoe_b200: qweight1 must be [experts, packed_rows, out_features]")
+    E, pr, O = (int(s) for s in qw1.shape)
+    rank = int(payload["g_idx"].shape[-1])
+    row_pack = payload["row_pack3"]
+    G = int(row_pack.shape[2]) if row_pack.dim() == 3 else 1
+    if pr != math.ceil(rank / 32) or tuple(payload["col_pack3"].shape) != (E, rank) or tuple(row_pack.shape[:2]) != (E, O):
+        raise RuntimeError("trismoe_b200: inconsistent compact3 payload shapes")
+    status = torch.zeros((2,), dtype=i32, device=dev)
+    stream = _stream_ptr(dev)
+    with torch.cuda.device(dev):
+        groups = torch.empty((E, pr), dtype=i32, device=dev)
+        _native.check(
+            lib.tris_build_row_groups(payload["g_idx"].data_ptr(), E, rank, G, groups.data_ptr(), status[0:].data_ptr(), stream),
+            "build_row_groups",
+        )
+        payload["_tris_packed_row_group"] = groups
+        payload["_tris_dims"] = (E, O, rank, G)
+        use_gr = bool(payload.get("compact3_use_block_gr", False)) and payload["q_gmap_gr_offsets"].numel() > 0
+        payload["_tris_gr_index"] = None
+        payload["_tris_gr_substreams"] = 0
+        if use_gr:
+            nblk = math.ceil(pr / 2) * math.ceil(O / 64)
+            if tuple(payload["q_gmap_gr_offsets"].shape) != (E, nblk + 1) or tuple(payload["q_gmap_gr_meta"].shape) != (E, nblk):
+                raise RuntimeError("trismoe_b200: block-GR offsets/meta have the wrong shape")
+            index = torch.empty((E, nblk, gr_substreams), dtype=i32, device=dev)
+            payload["_tris_gr_substreams"] = int(gr_substreams)
+            view = _build_view(payload, need_index=False)
+            _native.check(
+                lib.tris_block_gr_build_index(C.byref(view), index.data_ptr(), gr_substreams, status[1:].data_ptr(), stream),
+                "block_gr_build_index",
+            )
+            payload["_tris_gr_index"] = index
+    st = status.cpu().tolist()
+    if st[0] != 0:
+        raise RuntimeError("trismoe_b200: g_idx is not constant inside every 32-column word (unsupported layout)")
+    if st[1] != 0:
+        raise RuntimeError("trismoe_b200: corrupt block-GR stream (offsets/meta/bit stream failed validation)")
+    payload["_tris_prepared"] = True
+    payload["_tris_view"] = _build_view(payload, need_index=True)
+    return payload
+
+
+def _build_view(payload: dict, need_index: bool) -> TrisProjView:
+    E, O, rank, G = payload["_tris_dims"]
+    use_gr = bool(payload.get("compact3_use_block_gr", False)) and payload["q_gmap_gr_offsets"].numel() > 0
+    v = TrisProjView()
+    v.num_experts, v.out_features, v.rank, v.num_groups = E, O, rank, G
+    v.sign2_rows = int(payload["qweight2_sparse"].shape[1]) if payload["qweight2_sparse"].dim() == 3 else 0
+    gsp = payload.get("q_gmap_sparse")
+    v.gmap_sparse_rows = int(gsp.shape[1]) if isinstance(gsp, torch.Tensor) and gsp.dim() == 3 else 0
+    v.gr_max_words = int(payload["q_gmap_gr_words"].shape[1]) if use_gr else 0
+    v.use_block_gr = int(use_gr)
+    v.qweight1 = _ptr(payload["qweight1"])
+    v.qweight2_sparse = _ptr(payload["qweight2_sparse"])
+    v.qweight2_sparse_prefix = _ptr(payload["qweight2_sparse_prefix"])
+    v.q_gmap_sparse = _ptr(gsp) if isinstance(gsp, torch.Tensor) else None
+    v.q_gmap_sparse_prefix = _ptr(payload["q_gmap_sparse_prefix"])
+    v.q_gmap_gr_words = _ptr(payload["q_gmap_gr_words"]) if use_gr else None
+    v.q_gmap_gr_offsets = _ptr(payload["q_gmap_gr_offsets"]) if use_gr else None
+    v.q_gmap_gr_meta = _ptr(payload["q_gmap_gr_meta"]) if use_gr else None
+    v.c_map = _ptr(payload["c_map"])
+    v.g_idx = _ptr(payload["g_idx"])
+    v.col_pack3 = _ptr(payload["col_pack3"])
+    v.row_pack3 = _ptr(payload["row_pack3"])
+    has_scale = bool(payload.get("has_output_scale", False))
+    v.output_scale = _ptr(payload.get("output_scale")) if has_scale else None
+    v.bias = _ptr(payload.get("bias")) if payload.get("has_bias", False) else None
+    v.gr_index = _ptr(payload.get("_tris_gr_index")) if need_index else None
+    v.gr_substreams = int(payload.get("_tris_gr_substreams", 0))
+    v.packed_row_group = _ptr(payload["_tris_packed_row_group"])
+    slot = payload.get("_tris_gmap_slot")
+    v.gmap_slot = _ptr(slot) if isinstance(slot, torch.Tensor) else None
+    return v
+
+
+def proj_view(payload: dict) -> TrisProjView:
+    """ctypes view of a prepared payload (rebuilt when staging swaps the bitmap buffer)."""
+    if not payload.get("_tris_prepared"):
+        prepare_grouped_payload(payload)
+    if payload.get("_tris_view_dirty"):
+        payload["_tris_view"] = _build_view(payload, need_index=True)
+        payload["_tris_view_dirty"] = False
+    return payload["_tris_view"]
+
+
+def build_grouped_precomputed_payload(modules, device, dtype=torch.float16):
+    """``build_grouped_precomputed_payload`` (qlinear_cuda.py:1512-1636).  ``modules`` is a
+    sequence of per-expert payload dicts (the output of ``build_compact3_packed_payload``)
+    or of objects carrying one as ``.compact3_payload``.  Returns ``None`` for an empty
+    list, like the reference."""
+    if len(modules) == 0:
+        return None
+    if dtype != torch.float16:
+        return None
+    dicts = [m if isinstance(m, dict) else getattr(m, "compact3_payload") for m in modules]
+    stacked = stack_expert_payloads(dicts, device="cpu", use_block_gr=True)
+    return prepare_grouped_payload(stacked, device)
+
+
+def decode_block_gr_gmap(payload: dict) -> torch.Tensor:
+    """Dense packed g_map ``[E, pr, O]`` int32 decoded on the GPU from the block-GR stream
+    (the shared-memory image of ``decode_block_gr_block``, TriSMoE_cuda_kernel.cu:426-479)."""
+    lib = _native.load()
+    view = proj_view(payload)
+    dev = payload["qweight1"].device
+    E, O, rank, _ = payload["_tris_dims"]
+    out = torch.empty((E, math.ceil(rank / 32), O), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _native.check(lib.tris_block_gr_decode(C.byref(view), out.data_ptr(), _stream_ptr(dev)), "block_gr_decode")
+    return out
+
+
+def dequantize_grouped_payload(payload: dict) -> torch.Tensor:
+    """fp16 weights ``[E, O, r]`` from the kernels' own unpack path
+    (``_dequantize_compact3_matrix``, qlinear_cuda.py:4200-4236)."""
+    lib = _native.load()
+    view = proj_view(payload)
+    dev = payload["qweight1"].device
+    E, O, rank, _ = payload["_tris_dims"]
+    out = torch.empty((E, O, rank), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        _native.check(lib.tris_compact3_dequantize(C.byref(view), out.data_ptr(), _stream_ptr(dev)), "compact3_dequantize")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# route
+# ---------------------------------------------------------------------------------------
+def _empty_grouped_route(device):
+    z_long = torch.empty((0,), device=device, dtype=torch.long)
+    z_i32 = torch.empty((0,), device=device, dtype=torch.int32)
+    zero = torch.zeros((1,), device=device, dtype=torch.int32)
+    return {
+        "perm": z_long, "grouped_token_indices": z_long, "grouped_slots": z_long,
+        "grouped_expert_ids": z_i32, "expert_ids": z_i32, "segment_offsets": zero, "problem_offsets": zero.clone(),
+        "total_problem_tiles": torch.zeros((1,), dtype=torch.int64), "total_problem_tiles_host": 0,
+    }
+
+
+def build_grouped_route(selected_experts: torch.Tensor, num_experts: int, m_tile: int = GROUPED_SEGMENT_M_TILE):
+    """``build_grouped_route`` (qlinear_cuda.py:1301-1378): same keys, dtypes and sizes.
+    Rows inside a segment are in ascending (token, slot) order.  Reads the number of active
+    experts back to size the tensors (the reference does the same, TriSMoE_cuda.cpp:781)."""
+    if selected_experts.dim() != 2:
+        return None
+    device = selected_experts.device
+    if m_tile <= 0:
+        return _empty_grouped_route(device)
+    _native.require_cuda(selected_experts, "build_grouped_route")
+    T, k = (int(s) for s in selected_experts.shape)
+    R = T * k
+    if R == 0:
+        return _empty_grouped_route(device)
+    lib = _native.load()
+    sel = selected_experts.to(torch.int32).contiguous()
+    E = int(num_experts)
+    buf = torch.empty((4 * R + 3 * E + 2 + 2,), dtype=torch.int32, device=device)
+    perm, tok, slot, rof = (buf[i * R:(i + 1) * R] for i in range(4))
+    base = 4 * R
+    expert_ids = buf[base: base + E]
+    seg = buf[base + E: base + 2 * E + 1]
+    prob = buf[base + 2 * E + 1: base + 3 * E + 2]
+    counts = buf[base + 3 * E + 2: base + 3 * E + 4]
+    with torch.cuda.device(device):
+        _native.check(
+            lib.tris_build_grouped_route(sel.data_ptr(), T, k, E, int(m_tile), perm.data_ptr(), tok.data_ptr(),
+                                         slot.data_ptr(), rof.data_ptr(), expert_ids.data_ptr(), seg.data_ptr(),
+                                         prob.data_ptr(), counts.data_ptr(), _stream_ptr(device)),
+            "build_grouped_route",
+        )
+    nseg, tiles = (int(v) for v in counts.cpu().tolist())
+    expert_ids = expert_ids[:nseg].contiguous()
+    seg = seg[: nseg + 1].contiguous()
+    lengths = (seg[1:] - seg[:-1])
+    return {
+        "perm": perm.to(torch.long),
+        "grouped_token_indices": tok.to(torch.long),
+        "grouped_slots": slot.to(torch.long),
+        "grouped_expert_ids": torch.repeat_interleave(expert_ids, lengths, output_size=R).contiguous(),
+        "expert_ids": expert_ids,
+        "segment_offsets": seg,
+        "problem_offsets": prob[: nseg + 1].contiguous(),
+        "total_problem_tiles": torch.tensor([tiles], dtype=torch.int64),
+        "total_problem_tiles_host": tiles,
+        "_row_of_flat": rof,
+        "_max_rows_per_segment": T,
+    }
+
+
+def _coerce_grouped_route(route_or_lengths, device, expert_ids=None):
+    if isinstance(route_or_lengths, dict):
+        return route_or_lengths
+    lengths = torch.as_tensor(route_or_lengths, dtype=torch.long).reshape(-1)
+    if lengths.numel() == 0 or bool((lengths < 0).any()):
+        return None
+    ids = torch.arange(lengths.numel(), dtype=torch.int32) if expert_ids is None else torch.as_tensor(expert_ids, dtype=torch.int32).reshape(-1)
+    if ids.numel() != lengths.numel():
+        return None
+    keep = lengths > 0
+    lengths, ids = lengths[keep], ids[keep]
+    seg = torch.cat([torch.zeros(1, dtype=torch.long), torch.cumsum(lengths, 0)]).to(torch.int32)
+    return {
+        "expert_ids": ids.to(device), "segment_offsets": seg.to(device),
+        "_max_rows_per_segment": int(lengths.max().item()) if lengths.numel() else 0,
+    }
+
+
+def _route_view(route: dict, num_rows: int, keep: list) -> TrisRouteView:
+    rv = TrisRouteView()
+    ids = route["expert_ids"]
+    seg = route["segment_offsets"]
+    if ids.dtype != torch.int32 or not ids.is_contiguous():
+        ids = ids.to(torch.int32).contiguous()
+    if seg.dtype != torch.int32 or not seg.is_contiguous():
+        seg = seg.to(torch.int32).contiguous()
+    keep += [ids, seg]
+    rv.expert_ids = ids.data_ptr() if ids.numel() else None
+    rv.segment_offsets = seg.data_ptr()
+    rv.num_segments_dev = None
+    rv.num_segments = int(ids.numel())
+    rv.num_rows = int(num_rows)
+    rv.max_rows_per_segment = int(route.get("_max_rows_per_segment", 0) or 0)
+    rv.row_gather = None
+    return rv
+
+
+def _ns_payload_is_noop(ns_payload) -> bool:
+    if ns_payload is None:
+        return True
+    if isinstance(ns_payload, dict):
+        rank = ns_payload.get("rank", ns_payload.get("ns_rank", 0))
+        try:
+            return int(rank) == 0
+        except (TypeError, ValueError):
+            return False
+    return False
+
+
+# ---------------------------------------------------------------------------------------
+# grouped operators
+# ---------------------------------------------------------------------------------------
+def run_grouped_structured_expert_forward(
+    payload_or_modules,
+    hidden_grouped: torch.Tensor,
+    x_grouped: torch.Tensor,
+    grouped_route_or_segment_lengths,
+    expert_modules=None,
+    expert_ids=None,
+    ns_payload=None,
+    prefer_ns_fused_decode: bool = False,
+):
+    """``run_grouped_structured_expert_forward`` (qlinear_cuda.py:2131-2335): ``[R, O]`` fp16 =
+    per-segment ``dequant(U_e) @ hidden_grouped`` rows.  ``x_grouped`` is only read by
+    null-space compensation, which must be rank 0 here."""
+    _native.require_cuda(hidden_grouped, "run_grouped_structured_expert_forward")
+    if hidden_grouped.dtype != torch.float16:
+        return None
+    if x_grouped is not None and (x_grouped.device != hidden_grouped.device or x_grouped.dtype != hidden_grouped.dtype):
+        return None
+    if hidden_grouped.dim() != 2 or (x_grouped is not None and (x_grouped.dim() != 2 or x_grouped.size(0) != hidden_grouped.size(0))):
+        return None
+    route = _coerce_grouped_route(grouped_route_or_segment_lengths, hidden_grouped.device, expert_ids=expert_ids)
+    if route is None:
+        return None
+    tok = route.get("grouped_token_indices")
+    if tok is not None and tok.numel() not in (0, hidden_grouped.size(0)):
+        return None
+    payload = payload_or_modules if isinstance(payload_or_modules, dict) else build_grouped_precomputed_payload(
+        payload_or_modules, hidden_grouped.device, hidden_grouped.dtype)
+    if payload is None:
+        return None
+    if not _ns_payload_is_noop(ns_payload):
+        raise RuntimeError("trismoe_b200: null-space compensation of rank > 0 is not supported by this build")
+    lib = _native.load()
+    view = proj_view(payload)
+    E, O, rank, _ = payload["_tris_dims"]
+    if hidden_grouped.size(1) != rank:
+        return None
+    hidden = hidden_grouped.contiguous()
+    R = int(hidden.size(0))
+    out = torch.empty((R, O), dtype=torch.float16, device=hidden.device)
+    if R == 0:
+        return out
+    keep: list = []
+    rv = _route_view(route, R, keep)
+    with torch.cuda.device(hidden.device):
+        _native.check(
+            lib.tris_grouped_forward(C.byref(view), C.byref(rv), hidden.data_ptr(), out.data_ptr(), _stream_ptr(hidden.device)),
+            "grouped_forward",
+        )
+    return out
+
+
+def run_grouped_structured_expert_pair_forward(
+    payload_or_modules_a,
+    payload_or_modules_b,
+    hidden_grouped_a: torch.Tensor,
+    hidden_grouped_b: torch.Tensor,
+    x_grouped: torch.Tensor,
+    grouped_route_or_segment_lengths,
+    expert_modules_a=None,
+    expert_modules_b=None,
+    expert_ids=None,
+    ns_payload_a=None,
+    ns_payload_b=None,
+    fuse_silu_mul: bool = False,
+):
+    """``run_grouped_structured_expert_pair_forward`` (qlinear_cuda.py:2338-2634): gate and up
+    in one launch, returning ``(out_a, out_b)``.  With ``fuse_silu_mul=True`` (an addition)
+    returns ``(silu(out_a) * out_b, None)`` computed in fp32 inside the kernel."""
+    _native.require_cuda(hidden_grouped_a, "run_grouped_structured_expert_pair_forward")
+    if hidden_grouped_a.dtype != torch.float16 or hidden_grouped_b.dtype != torch.float16:
+        return None, None
+    if hidden_grouped_a.dim() != 2 or hidden_grouped_b.shape != hidden_grouped_a.shape:
+        return None, None
+    if hidden_grouped_b.device != hidden_grouped_a.device:
+        return None, None
+    route = _coerce_grouped_route(grouped_route_or_segment_lengths, hidden_grouped_a.device, expert_ids=expert_ids)
+    if route is None:
+        return None, None
+    dev, dt = hidden_grouped_a.device, hidden_grouped_a.dtype
+    pa = payload_or_modules_a if isinstance(payload_or_modules_a, dict) else build_grouped_precomputed_payload(payload_or_modules_a, dev, dt)
+    pb = payload_or_modules_b if isinstance(payload_or_modules_b, dict) else build_grouped_precomputed_payload(payload_or_modules_b, dev, dt)
+    if pa is None or pb is None:
+        return None, None
+    if not (_ns_payload_is_noop(ns_payload_a) and _ns_payload_is_noop(ns_payload_b)):
+        raise RuntimeError("trismoe_b200: null-space compensation of rank > 0 is not supported by this build")
+    lib = _native.load()
+    va, vb = proj_view(pa), proj_view(pb)
+    _, O, rank, _ = pa["_tris_dims"]
+    if hidden_grouped_a.size(1) != rank:
+        return None, None
+    ha, hb = hidden_grouped_a.contiguous(), hidden_grouped_b.contiguous()
+    R = int(ha.size(0))
+    out_a = torch.empty((R, O), dtype=torch.float16, device=dev)
+    out_b = None if fuse_silu_mul else torch.empty((R, O), dtype=torch.float16, device=dev)
+    if R == 0:
+        return out_a, out_b
+    keep: list = []
+    rv = _route_view(route, R, keep)
+    with torch.cuda.device(dev):
+        _native.check(
+            lib.tris_grouped_pair_forward(C.byref(va), C.byref(vb), C.byref(rv), ha.data_ptr(), hb.data_ptr(),
+                                          out_a.data_ptr(), None if out_b is None else out_b.data_ptr(),
+                                          int(bool(fuse_silu_mul)), _stream_ptr(dev)),
+            "grouped_pair_forward",
+        )
+    return out_a, out_b
+
+
+# ---------------------------------------------------------------------------------------
+# backbone
+# ---------------------------------------------------------------------------------------
+def compute_shared_hidden(x: torch.Tensor, shared_sv: torch.Tensor) -> torch.Tensor:
+    """``hidden = x @ shared_sv.T`` in fp16 with fp32 accumulation
+    (``QuantLinear.compute_shared_hidden`` fp16 branch, qlinear_cuda.py:4454-4502)."""
+    _native.require_cuda(x, "compute_shared_hidden")
+    if x.dtype != torch.float16 or shared_sv.dtype != torch.float16:
+        raise RuntimeError("trismoe_b200 compute_shared_hidden: fp16 activations and backbone required")
+    lib = _native.load()
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    sv = shared_sv.contiguous()
+    rank, in_features = (int(s) for s in sv.shape)
+    if x2.shape[1] != in_features:
+        raise RuntimeError("trismoe_b200 compute_shared_hidden: x and shared_sv disagree on in_features")
+    out = torch.empty((x2.shape[0], rank), dtype=torch.float16, device=x.device)
+    if x2.shape[0]:
+        with torch.cuda.device(x.device):
+            _native.check(
+                lib.tris_shared_hidden_forward(x2.data_ptr(), None, int(x2.shape[0]), in_features, sv.data_ptr(), rank,
+                                               out.data_ptr(), 0, _stream_ptr(x.device)),
+                "shared_hidden_forward",
+            )
+    return out.reshape(x.shape[:-1] + (rank,))
+
+
+class ExpertSharedMatrix(torch.nn.Module):
+    """Holder of one shared input-side backbone ``shared_sv [r, in]`` fp16
+    (``ExpertSharedMatrix``, qlinear_cuda.py:2787-2968; the 4-bit packed form is not covered)."""
+
+    def __init__(self, weight_dtype=torch.float16):
+        super().__init__()
+        self.register_buffer("shared_sv", torch.zeros((0, 0), dtype=weight_dtype))
+
+    def set_shared_sv(self, payload):
+        tensor = payload if isinstance(payload, torch.Tensor) else payload["shared_sv"]
+        self.shared_sv = tensor.to(dtype=torch.float16).contiguous()
+        return self
+
+    def get_shared_sv(self, device, dtype=torch.float16):
+        return self.shared_sv.to(device=device, dtype=dtype)
+
+    def compute_shared_hidden(self, x: torch.Tensor) -> torch.Tensor:
+        return compute_shared_hidden(x, self.shared_sv)

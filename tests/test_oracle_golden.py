@@ -1,0 +1,152 @@
+"""CPU tests: the oracle and the host-side format code against fixtures produced by the
+TriS-MoE reference's own Python code (tests/golden/make_golden.py)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import trismoe_oracle as orc
+from helpers import PAYLOAD_KEYS, golden_expert_payload, golden_raw_expert, load_golden, to_numpy_payload
+
+
+@pytest.mark.parametrize("name", ["proj_ragged.npz", "proj_r256.npz"])
+def test_packers_match_reference_payload(lib, name):
+    import trismoe_b200 as tm
+
+    z = load_golden(name)
+    E, O, r, group = (int(v) for v in z["dims"])
+    for e in range(E):
+        raw = golden_raw_expert(z, e, O, r)
+        mine = tm.build_compact3_packed_payload(
+            b1=raw["b1"], b2=raw["b2"], g_map_non_salient=raw["g_map"], c_map=raw["c_map"], g_idx=raw["g_idx"],
+            scales_s_r1=raw["s_r1"], scales_s_r2=raw["s_r2"], scales_ns_d_r1=raw["ns_d_r1"],
+            scales_ns_nd_r1=raw["ns_nd_r1"], scales_s_c1=raw["s_c1"], scales_s_c2=raw["s_c2"],
+            scales_ns_d_c1=raw["ns_d_c1"], scales_ns_nd_c1=raw["ns_nd_c1"])
+        for k in PAYLOAD_KEYS:
+            ref = z[f"ref{e}_{k}"]
+            got = mine[k].numpy()
+            assert got.dtype == ref.dtype, k
+            assert got.shape == ref.shape, (k, got.shape, ref.shape)
+            assert np.array_equal(got, ref), k
+        dense = tm.dense_gmap_words(raw["g_map"], raw["c_map"]).numpy()
+        assert np.array_equal(dense, z[f"ref{e}_dense_gmap"])
+
+
+@pytest.mark.parametrize("name", ["proj_ragged.npz", "proj_r256.npz"])
+def test_block_gr_encoder_and_oracle_decoder_match_reference(lib, name):
+    import trismoe_b200 as tm
+
+    z = load_golden(name)
+    E, O, r, _ = (int(v) for v in z["dims"])
+    pr = math.ceil(r / 32)
+    for e in range(E):
+        dense = z[f"ref{e}_dense_gmap"]
+        words, offsets, meta = tm.block_gr_encode(torch.from_numpy(dense.copy()))
+        assert np.array_equal(words.numpy(), z[f"ref{e}_gr_words"])
+        assert np.array_equal(offsets.numpy(), z[f"ref{e}_gr_offsets"])
+        assert np.array_equal(meta.numpy(), z[f"ref{e}_gr_meta"])
+        decoded = orc.gr_decode_tensor(z[f"ref{e}_gr_words"], z[f"ref{e}_gr_offsets"], z[f"ref{e}_gr_meta"], pr, O)
+        assert np.array_equal(decoded.view(np.int32), dense)
+
+
+def test_block_gr_sweep_all_k_raw_and_empty(lib):
+    import trismoe_b200 as tm
+
+    z = load_golden("block_gr_sweep.npz")
+    seen_k, raw_blocks, empty_blocks = set(), 0, 0
+    for tag in ("a", "b", "braw"):
+        dense = z["b_dense" if tag == "braw" else f"{tag}_dense"]
+        words, offsets, meta = tm.block_gr_encode(torch.from_numpy(dense.copy()), force_raw=(tag == "braw"))
+        assert np.array_equal(words.numpy(), z[f"{tag}_words"])
+        assert np.array_equal(offsets.numpy(), z[f"{tag}_offsets"])
+        assert np.array_equal(meta.numpy(), z[f"{tag}_meta"])
+        decoded = orc.gr_decode_tensor(z[f"{tag}_words"], z[f"{tag}_offsets"], z[f"{tag}_meta"], *dense.shape)
+        assert np.array_equal(decoded.view(np.int32), dense)
+        for m in z[f"{tag}_meta"]:
+            if int(m) & 16:
+                raw_blocks += 1
+            else:
+                seen_k.add(int(m) & 15)
+                empty_blocks += int(m) >> 8 == 0
+    assert {0, 1, 2, 4, 5, 6, 7} <= seen_k
+    assert raw_blocks >= 2 and empty_blocks >= 1
+
+
+@pytest.mark.parametrize("name", ["proj_ragged.npz", "proj_r256.npz"])
+def test_oracle_dequant_bit_exact_vs_reference(name):
+    z = load_golden(name)
+    E, O, r, _ = (int(v) for v in z["dims"])
+    for e in range(E):
+        sal = orc.unpack_vector(z[f"ref{e}_c_map_packed"], r)
+        gbits = orc.restore_sparse(z[f"ref{e}_q_gmap_sparse"], ~sal, O)
+        # the GR route to the same bits
+        dense = orc.gr_decode_tensor(z[f"ref{e}_gr_words"], z[f"ref{e}_gr_offsets"], z[f"ref{e}_gr_meta"],
+                                     math.ceil(r / 32), O)
+        assert np.array_equal(orc.unpack_rows(dense, r), gbits)
+        w = orc.dequantize_compact3(z[f"ref{e}_qweight1"], z[f"ref{e}_qweight2_sparse"], gbits,
+                                    z[f"ref{e}_c_map_packed"], z[f"ref{e}_g_idx"], z[f"ref{e}_col_pack3"],
+                                    z[f"ref{e}_row_pack3"], r)
+        ref = z[f"ref{e}_weight_f16"]
+        assert np.array_equal(orc.canonical_half_bits(w), orc.canonical_half_bits(ref))
+
+
+def _layer_from_golden(z):
+    import trismoe_b200 as tm
+
+    E, k, H, I, r, group, T = (int(v) for v in z["dims"])
+    payloads, weights, shared = {}, {}, {}
+    for name in ("gate", "up", "down"):
+        experts = [golden_expert_payload(z, f"{name}{e}") for e in range(E)]
+        payloads[name] = tm.stack_expert_payloads(experts, use_block_gr=True)
+        np_payload = to_numpy_payload(payloads[name])
+        weights[name] = [orc.dequantize_expert(np_payload, e) for e in range(E)]
+        shared[name] = z[f"shared_{name}"]
+    return (E, k, H, I, r, group, T), payloads, weights, shared
+
+
+def test_oracle_layer_matches_reference_block(lib):
+    """fp32 oracle vs the reference's fp16 CPU block output: same routing, outputs within
+    fp16 round-off of each other."""
+    z = load_golden("moe_layer_small.npz")
+    (E, k, H, I, r, group, T), payloads, weights, shared = _layer_from_golden(z)
+    x = z["x"]
+    logits = z["ref_router_logits_f16"].astype(np.float32)
+    sel, _ = orc.router_topk(logits, k, True)
+    assert np.array_equal(np.sort(sel, axis=1), np.sort(z["ref_selected"], axis=1))
+    y = orc.moe_layer_fp32(x, logits, weights, shared, k, True)
+    max_abs, mean_rel = orc.error_metrics(z["ref_y_f16"], y)
+    assert np.abs(y).mean() > 1e-3  # the comparison is not vacuous
+    assert max_abs <= 2e-2 and mean_rel <= 5e-3, (max_abs, mean_rel)
+    route = orc.build_route(sel, E)
+    for key in ("grouped_expert_ids", "expert_ids", "segment_offsets", "problem_offsets"):
+        assert np.array_equal(route[key], z["ref_route_" + key]), key
+    assert route["total_problem_tiles_host"] == int(z["ref_route_total_problem_tiles"][0])
+    # rows of a segment: same token multiset as the reference's (its sort is not stable)
+    seg = route["segment_offsets"]
+    for s in range(len(seg) - 1):
+        mine = np.sort(route["grouped_token_indices"][seg[s]: seg[s + 1]])
+        ref = np.sort(z["ref_route_grouped_token_indices"][seg[s]: seg[s + 1]])
+        assert np.array_equal(mine, ref)
+
+
+def test_synth_payload_round_trip(lib):
+    """Synthetic generator: GR streams decode back to the dense map, stacked tensors have
+    the documented shapes, oracle weights are finite and non-trivial."""
+    from trismoe_b200 import synth
+
+    shape = synth.LayerShape(96, 160, 5, 2, rank=80, group_size=16)
+    layer = synth.synth_layer(shape, seed=3, keep_sparse_gmap=True)
+    for name, O in (("gate", 160), ("up", 160), ("down", 96)):
+        p = layer[name]
+        pr = 3
+        assert tuple(p["qweight1"].shape) == (5, pr, O)
+        assert tuple(p["q_gmap_gr_offsets"].shape) == (5, 2 * math.ceil(O / 64) + 1)
+        npp = to_numpy_payload(p)
+        for e in range(5):
+            dense = orc.gr_decode_tensor(npp["q_gmap_gr_words"][e], npp["q_gmap_gr_offsets"][e], npp["q_gmap_gr_meta"][e], pr, O)
+            assert np.array_equal(dense.view(np.int32), npp["_dense_gmap_words"][e])
+            sal = orc.unpack_vector(npp["c_map"][e], 80)
+            assert np.array_equal(orc.unpack_rows(dense, 80), orc.restore_sparse(npp["q_gmap_sparse"][e], ~sal, O))
+        w = orc.dequantize_expert(npp, 0)
+        assert np.isfinite(w.astype(np.float32)).all() and np.abs(w.astype(np.float32)).mean() > 1e-3
