@@ -203,7 +203,7 @@ def case_layer(QL, MO, PU):
 def main():
     torch.manual_seed(0)
     QL, MO, PU = load_reference()
-    case_projection(QL, PU, "proj_ragged.npz", 1, E=3, O=96, r=80, group=16, in_features=160, p_sal=0.15, p_g=0.1,
+    case_projection(QL, PU, "proj_ragged.npz", 1, E=3, O=96, r=80, group=32, in_features=160, p_sal=0.15, p_g=0.1,
                     unit_cols=False)
     case_projection(QL, PU, "proj_r256.npz", 2, E=2, O=128, r=256, group=128, in_features=512, p_sal=0.1, p_g=0.1,
                     unit_cols=True)

@@ -112,7 +112,7 @@ def test_corrupt_stream_is_rejected_at_prepare(tm):
 def small_layer(tm):
     from trismoe_b200 import synth
 
-    shape = synth.LayerShape(192, 160, 6, 2, rank=80, group_size=16, norm_topk_prob=True)
+    shape = synth.LayerShape(192, 160, 6, 2, rank=80, group_size=32, norm_topk_prob=True)
     layer = synth.synth_layer(shape, seed=5, keep_sparse_gmap=True)
     for name in ("gate", "up", "down"):  # larger backbones keep this tiny layer's outputs well inside fp16 range
         layer["shared_" + name] = (layer["shared_" + name].float() * 6.0).half()
