@@ -339,14 +339,57 @@ def run_reference(args):
     print(json.dumps(out))
 
 
+def run_ncu_case(args):
+    """Small fixed launch sequence for profiler captures (no timing, no graphs):
+    `layer`   - one warm-up pass and one pass of the whole block over `--layers` layers;
+    `grouped` - two passes of the grouped gate/up and grouped down kernels alone."""
+    import trismoe_b200 as tm
+    from trismoe_b200 import synth
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    T = args.tokens
+    blocks, _ = build_stack(device, layers=args.layers)
+    x = synth.synth_activations(T, 2048, seed=T).to(device)
+    if args.ncu_case == "layer":
+        for _ in range(2):
+            for blk in blocks:
+                blk(x.view(1, T, 2048))
+            torch.cuda.synchronize()
+        return
+    prepared = []
+    for blk in blocks:
+        logits = torch.nn.functional.linear(x, blk.gate.weight).float()
+        sel = torch.topk(torch.softmax(logits, dim=1), 8, dim=-1)[1]
+        route = tm.build_grouped_route(sel, 64)
+        tok = route["grouped_token_indices"]
+        hg = tm.compute_shared_hidden(x, blk.shared_gate).index_select(0, tok)
+        hu = tm.compute_shared_hidden(x, blk.shared_up).index_select(0, tok)
+        hd = torch.randn((tok.numel(), 256), device=device).half()
+        prepared.append((blk, route, hg, hu, hd))
+    torch.cuda.synchronize()
+    for _ in range(2):
+        for blk, route, hg, hu, hd in prepared:
+            tm.run_grouped_structured_expert_pair_forward(blk._get_grouped_payload("gate"), blk._get_grouped_payload("up"),
+                                                          hg, hu, None, route, fuse_silu_mul=True)
+            tm.run_grouped_structured_expert_forward(blk._get_grouped_payload("down"), hd, None, route)
+        torch.cuda.synchronize()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ncu-case", default=None, choices=["layer", "grouped"],
+                    help="run a short untimed launch sequence for a profiler capture and exit")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers for --ncu-case")
+    ap.add_argument("--tokens", type=int, default=HEADLINE_TOKENS, help="decode batch for --ncu-case")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.ncu_case:
+        return run_ncu_case(args)
     if args.impl == "reference":
         run_reference(args)
     else:
