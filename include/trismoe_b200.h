@@ -102,7 +102,19 @@ typedef struct TrisRouteView {
   int32_t num_rows;                 /* R: routed rows                                      */
   int32_t max_rows_per_segment;     /* upper bound (<= tokens); 0 = num_rows               */
   const int32_t* row_gather;        /* optional [R]: source row of each grouped row        */
+  int32_t* status_dev;              /* optional device int32: set to TRIS_ERR_TIMEOUT when a
+                                       bounded wait inside a kernel ran out                */
+  int32_t flags;                    /* TRIS_ROUTE_* bits                                   */
 } TrisRouteView;
+
+/* Activation rows handed to the grouped kernels are "pair-interleaved": inside every group
+   of 32 columns, column j sits at position 2*(j%16) + j/16 (what tris_shared_hidden_forward
+   writes with out_mode = TRIS_OUT_F16_PAIR_INTERLEAVED).  Needs rank % 32 == 0. */
+#define TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED 1
+
+#define TRIS_OUT_F16 0
+#define TRIS_OUT_F32 1
+#define TRIS_OUT_F16_PAIR_INTERLEAVED 2
 
 /* ---- library / errors -------------------------------------------------------------- */
 
@@ -190,11 +202,11 @@ int tris_router_topk(const float* router_logits, int32_t num_tokens, int32_t num
 /*
  * hidden = x . shared_sv^T (QuantLinear.compute_shared_hidden fp16 branch, QL:4454-4502):
  * x [N, in] fp16 (rows optionally gathered through row_gather), shared_sv [r, in] fp16,
- * out [N, r] fp16 (out_is_f32 = 0) or fp32.
+ * out [N, r] in the layout named by out_mode (TRIS_OUT_*).
  */
 int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_gather, int32_t num_rows,
                                int32_t in_features, const void* shared_sv_f16, int32_t rank,
-                               void* out, int32_t out_is_f32, void* stream);
+                               void* out, int32_t out_mode, void* stream);
 
 /* ---- grouped expert kernels -------------------------------------------------------- */
 

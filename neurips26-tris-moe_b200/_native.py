@@ -37,7 +37,7 @@ class TrisRouteView(C.Structure):
     _fields_ = [
         ("expert_ids", _vp), ("segment_offsets", _vp), ("num_segments_dev", _vp),
         ("num_segments", _i32), ("num_rows", _i32), ("max_rows_per_segment", _i32),
-        ("row_gather", _vp),
+        ("row_gather", _vp), ("status_dev", _vp), ("flags", _i32),
     ]
 
 

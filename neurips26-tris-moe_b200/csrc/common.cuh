@@ -8,7 +8,7 @@
 #include "../../include/trismoe_b200.h"
 
 static_assert(sizeof(TrisProjView) == 176, "TrisProjView layout is part of the ABI");
-static_assert(sizeof(TrisRouteView) == 48, "TrisRouteView layout is part of the ABI");
+static_assert(sizeof(TrisRouteView) == 64, "TrisRouteView layout is part of the ABI");
 
 namespace tris {
 
@@ -33,9 +33,9 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // One matrix of the shared skinny GEMM (skinny_gemm.cu): out[n, m] = x[n, :] . a[m, :].
 struct SkinnyProblem {
   const __half* a;   // [m, k]
-  void* out;         // [n, m] fp16 or fp32
+  void* out;         // [n, m], layout TRIS_OUT_*
   int32_t m;
-  int32_t out_is_f32;
+  int32_t out_mode;
 };
 int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather,
                          int n, int k, cudaStream_t stream);

@@ -9,13 +9,26 @@
 // 32-bit words per bit plane and 8 block-GR blocks (block = 2 packed rows x 64 outputs,
 // QL:486-494 / CU:63-68 of the TriS-MoE tree).
 //
+// Staging.  Everything bulky comes in through untiled TMA copies (cp.async.bulk) that
+// complete on mbarriers: warp 0 issues the copies whose addresses need no table lookup
+// (sign plane rows, column and row scale packs, the block-GR sub-stream index), warp 1
+// reads offsets/prefixes and issues the dependent ones (block-GR word spans or sparse
+// g_map rows, salient sign rows), warp 2 issues one copy per activation row.  A copy whose
+// source or size is not 16-byte aligned (odd shapes) is done with plain loads by the lane
+// that would have issued it.  Waits on the mbarriers are bounded; a time-out is reported
+// through a status word and the CTA leaves without storing results.
+//
 // Column order inside a packed row.  Dot products do not care about the order of K, so a
 // lane never moves bits sideways: lane (g = lane/4, t = lane%4) of a warp owns outputs
-// g and g+8 of its 16-output sub-tile and, in every 32-column word, the eight columns
-// {t+4i, t+4i+16 : i = 0..3}.  Columns j and j+16 sit 16 bits apart in the word, i.e. in
+// g and g+8 of its 16-output sub-tile and, in every 32-column word, the four column pairs
+// (4t+i, 4t+i+16), i = 0..3.  Columns j and j+16 sit 16 bits apart in the word, i.e. in
 // the same position of the two halves of a half2, so one shift lines a bit pair up with
-// the sign bits (15, 31) or with the byte MSBs that PRMT can replicate into a 16-bit
-// select mask.  The activation rows are staged in shared memory in the same order.
+// the sign bits (15, 31), which are also the byte MSBs that PRMT can replicate into a
+// 16-bit select mask.  Activation rows are consumed "pair-interleaved": inside every group
+// of 32 columns, column j sits at position 2*(j%16) + j/16, so a lane's B fragment for a
+// packed row is one 16-byte shared-memory load.  The backbone GEMM writes that order
+// directly; row-major activations handed in through the operator API are re-ordered while
+// they are staged.
 #pragma once
 #include "common.cuh"
 
@@ -23,33 +36,64 @@ namespace tris {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
-constexpr int KC = 8;            // packed rows per K chunk
-constexpr int kTileWords = 1024; // words per bit plane per chunk (all projections)
+constexpr int KC = 8;             // packed rows per K chunk
+constexpr int kTileWords = 1024;  // words per bit plane per chunk (all projections)
 constexpr int kBlocksPerChunk = 8;
+constexpr int kSparseRows = 9;    // sparse plane rows a 256-column chunk can touch
+constexpr int kRawWords = 1152;   // kSparseRows * 128
+constexpr int kHiddenRowBytes = 576;  // 512 B of activations + 64 B so that 8 rows hit 8 bank groups
+constexpr int kRowTabEntries = 1024;
 
 template <int NPROJ>
 struct Geom {
   static constexpr int OW = 128 / NPROJ;  // outputs per projection per CTA
   static constexpr int NOB = OW / 64;     // block-GR out blocks per projection per CTA
+  static constexpr int SPAN = NOB * 128 + 8;  // words reserved per block-GR span
+};
+
+struct PackedRowInfo {
+  uint32_t cw;      // c_map word (bit = salient column)
+  int32_t rank2;    // salient columns below this packed row, relative to the staged sign2 rows
+  int32_t rankg;    // non-salient columns below it, relative to the staged sparse g_map rows
+  int32_t gslot;    // row scale slot of this packed row
 };
 
 // Shared-memory image of one chunk.  NT = number of 8-row activation tiles staged.
 template <int NPROJ, int NT>
-struct alignas(16) TileSmem {
-  uint4 coltab[NPROJ * KC * 16];            // [proj][p][i][t] -> {cd2, cnd2, c1_2, c2_2}
-  uint4 htab[NPROJ * NT * KC * 32];         // [proj][nt][p][n][t] -> 8 halves (B fragments)
-  uint2 rowtab[kTileWords];                 // [proj][p][o] -> row_pack3 word of the row's group
-  uint32_t s1[kTileWords];                  // sign plane 1
-  uint32_t g[kTileWords];                   // decoded g_map, then the select plane
-  uint32_t grw[kBlocksPerChunk * 128 + 8];  // staged block-GR words
-  uint32_t gridx[kBlocksPerChunk * 32];     // staged sub-stream index
-  int32_t binfo[kBlocksPerChunk * 4];       // {begin, count, meta, block index}
-  uint32_t cw[NPROJ * KC];                  // c_map word of each packed row
+struct alignas(128) TileSmem {
+  uint8_t hrows[NPROJ * NT * 8 * kHiddenRowBytes];  // [proj][row] pair-interleaved activations
+  uint32_t s1[kTileWords];                           // sign plane 1, [proj][p][o]
+  uint2 colraw[NPROJ * 256];                         // col_pack3 of the chunk's columns
+  uint2 rowtab[kRowTabEntries];                      // [proj][o][slot] row_pack3 words
+  uint32_t s2raw[kRawWords];                         // [proj][row][o] salient sign rows
+  uint32_t gmraw[kRawWords + 8];                     // block-GR spans or sparse g_map rows
+  uint32_t gridx[kBlocksPerChunk * 32];              // block-GR sub-stream index
+  uint4 coltab[NPROJ * KC * 16];                     // [proj][p][i][t] -> {cd2, cnd2, c1_2, c2_2}
+  uint32_t g[kTileWords];                            // decoded g_map, then the select plane
+  PackedRowInfo ptab[NPROJ * (KC + 1)];
+  int32_t binfo[kBlocksPerChunk * 4];                // {word offset in gmraw, count, meta, -}
+  uint64_t mbar[3];                                  // A: table-free copies, B: dependent copies, H: activations
+  int32_t row_stride;
 };
 
 __device__ __forceinline__ int proj_packed_rows(const TrisProjView& v) { return (v.rank + 31) >> 5; }
 __device__ __forceinline__ int proj_num_blocks(const TrisProjView& v) {
   return ((proj_packed_rows(v) + 1) >> 1) * ((v.out_features + 63) >> 6);
+}
+
+// ---- copies ---------------------------------------------------------------------------
+// One lane moves nwords 32-bit words global -> shared: a TMA bulk copy when both ends are
+// 16-byte aligned and the size is a multiple of 16 bytes, plain loads otherwise.  Returns
+// the bytes the mbarrier must expect.
+__device__ __forceinline__ uint32_t lane_copy(uint32_t* dst, const uint32_t* src, int nwords, uint64_t* bar) {
+  if (nwords <= 0) return 0;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(src) | smem_u32(dst)) & 15u) == 0 && (nwords & 3) == 0;
+  if (aligned) {
+    bulk_g2s(dst, src, static_cast<uint32_t>(nwords) * 4u, bar);
+    return static_cast<uint32_t>(nwords) * 4u;
+  }
+  for (int w = 0; w < nwords; ++w) dst[w] = src[w];
+  return 0;
 }
 
 // ---- block Golomb-Rice ----------------------------------------------------------------
@@ -64,36 +108,63 @@ __device__ __forceinline__ uint32_t gr_peek32(const uint32_t* w, int nwords, int
   return __funnelshift_r(lo, hi, bitpos & 31);
 }
 
-// Decodes `n_ones` codewords starting at (bitpos, flatpos) and calls set(flat) for each.
-template <typename SetBit>
-__device__ __forceinline__ void gr_decode_run(const uint32_t* w, int nwords, int k, int n_ones,
-                                              int bitpos, int flatpos, SetBit set) {
+// Decodes `n_ones` codewords starting at (bitpos, flatpos).  Bits that fall into the same
+// 32-bit output word are gathered in a register and handed to flush(word_index, mask).
+template <typename Flush>
+__device__ __forceinline__ void gr_decode_run(const uint32_t* w, int nwords, int k, int n_ones, int bitpos,
+                                              int flatpos, Flush flush) {
   const int total_bits = nwords << 5;
   const uint32_t kmask = (1u << k) - 1u;
+  uint32_t v = gr_peek32(w, nwords, bitpos);
+  int avail = 32;
+  int cur_word = -1;
+  uint32_t cur_mask = 0u;
   for (int n = 0; n < n_ones; ++n) {
     int q = 0;
-    uint32_t v = gr_peek32(w, nwords, bitpos);
-    while (v == 0u) {
-      q += 32;
-      bitpos += 32;
-      if (bitpos >= total_bits) return;  // stream ran out: malformed, stop
+    int t = __ffs(v) - 1;
+    if (v == 0u || t + 1 + k > avail) {
+      // refill at the current position; long zero runs advance 32 bits at a time
       v = gr_peek32(w, nwords, bitpos);
+      avail = 32;
+      while (v == 0u) {
+        q += 32;
+        bitpos += 32;
+        if (bitpos >= total_bits) { n = n_ones; break; }  // stream ran out: malformed, stop
+        v = gr_peek32(w, nwords, bitpos);
+      }
+      if (v == 0u) break;
+      t = __ffs(v) - 1;
+      if (t + 1 + k > 32) {  // remainder straddles the window: re-anchor it after the one
+        bitpos += t + 1;
+        q += t;
+        v = gr_peek32(w, nwords, bitpos);
+        const uint32_t rem = v & kmask;
+        v = (k == 32) ? 0u : (v >> k);
+        avail = 32 - k;
+        bitpos += k;
+        flatpos += (q << k) | static_cast<int>(rem);
+        goto emit;
+      }
     }
-    const int t = __ffs(v) - 1;
-    q += t;
-    bitpos += t + 1;
-    uint32_t rem;
-    if (t + 1 + k <= 32) {
-      rem = (t == 31) ? 0u : ((v >> (t + 1)) & kmask);
-    } else {
-      rem = gr_peek32(w, nwords, bitpos) & kmask;
+    {
+      const int used = t + 1 + k;
+      const uint32_t rem = (t == 31) ? 0u : ((v >> (t + 1)) & kmask);
+      v = (used >= 32) ? 0u : (v >> used);
+      avail -= used;
+      bitpos += used;
+      flatpos += ((q + t) << k) | static_cast<int>(rem);
     }
-    bitpos += k;
-    flatpos += (q << k) | static_cast<int>(rem);
-    if (flatpos >= TRIS_GR_BLOCK_WORDS * 32) return;
-    set(flatpos);
+  emit:
+    if (flatpos >= TRIS_GR_BLOCK_WORDS * 32) break;
+    if ((flatpos >> 5) != cur_word) {
+      if (cur_mask) flush(cur_word, cur_mask);
+      cur_word = flatpos >> 5;
+      cur_mask = 0u;
+    }
+    cur_mask |= 1u << (flatpos & 31);
     ++flatpos;
   }
+  if (cur_mask) flush(cur_word, cur_mask);
 }
 
 // Word index inside the chunk planes of flat word `wl` (0..127) of chunk-local block b.
@@ -107,107 +178,15 @@ __device__ __forceinline__ int block_word_to_tile(int b, int wl) {
   return (proj * KC + 2 * kbl + (wl >> 6)) * OW + obl * 64 + (wl & 63);
 }
 
-// Fills sm.g with the dense g_map words of the chunk (zeros where a projection has no
-// block-GR stream).  All 256 threads must call; ends with a barrier.
-template <int NPROJ, int NT>
-__device__ __forceinline__ void stage_gmap_block_gr(TileSmem<NPROJ, NT>& sm, const TrisProjView* views,
-                                                    int e, int o0, int p0) {
-  constexpr int NOB = Geom<NPROJ>::NOB;
-  const int tid = threadIdx.x;
-  if (tid < kBlocksPerChunk) {
-    const int b = tid;
-    const int obl = b % NOB;
-    const int kbl = (b / NOB) & 3;
-    const TrisProjView& v = views[b / (NOB * 4)];
-    const int pr = proj_packed_rows(v);
-    const int nkb = (pr + 1) >> 1;
-    const int nob = (v.out_features + 63) >> 6;
-    const int kb = (p0 >> 1) + kbl;
-    const int ob = (o0 >> 6) + obl;
-    int begin = 0, count = 0, meta = 0, bi = 0;
-    if (v.use_block_gr && v.q_gmap_gr_words != nullptr && kb < nkb && ob < nob) {
-      const int nblk = nkb * nob;
-      bi = kb * nob + ob;
-      const int32_t* off = v.q_gmap_gr_offsets + static_cast<size_t>(e) * (nblk + 1);
-      begin = off[bi];
-      const int end = off[bi + 1];
-      meta = v.q_gmap_gr_meta[static_cast<size_t>(e) * nblk + bi];
-      count = end - begin;
-      if (count > TRIS_GR_BLOCK_WORDS) count = TRIS_GR_BLOCK_WORDS;
-      if (begin < 0 || count < 0 || begin + count > v.gr_max_words) count = 0;
-    }
-    sm.binfo[b * 4 + 0] = begin;
-    sm.binfo[b * 4 + 1] = count;
-    sm.binfo[b * 4 + 2] = meta;
-    sm.binfo[b * 4 + 3] = bi;
-  }
-  __syncthreads();
-  for (int i = tid; i < kBlocksPerChunk * 128; i += kThreads) {
-    const int b = i >> 7, wl = i & 127;
-    const int count = sm.binfo[b * 4 + 1];
-    uint32_t word = 0u;
-    if (wl < count) {
-      const TrisProjView& v = views[b / (NOB * 4)];
-      word = static_cast<uint32_t>(
-          v.q_gmap_gr_words[static_cast<size_t>(e) * v.gr_max_words + sm.binfo[b * 4 + 0] + wl]);
-    }
-    sm.grw[i] = word;
-    const bool raw = (sm.binfo[b * 4 + 2] & TRIS_GR_META_RAW_FLAG) != 0;
-    sm.g[block_word_to_tile<NPROJ>(b, wl)] = raw ? word : 0u;
-  }
-  const int sub = views[0].gr_substreams;
-  for (int i = tid; i < kBlocksPerChunk * sub; i += kThreads) {
-    const int b = i / sub, j = i - b * sub;
-    const TrisProjView& v = views[b / (NOB * 4)];
-    uint32_t packed = 0u;
-    if (sm.binfo[b * 4 + 1] > 0 && v.gr_index != nullptr) {
-      const size_t nblk = static_cast<size_t>(proj_num_blocks(v));
-      packed = v.gr_index[(static_cast<size_t>(e) * nblk + sm.binfo[b * 4 + 3]) * sub + j];
-    }
-    sm.gridx[b * 32 + j] = packed;
-  }
-  __syncthreads();
-  for (int i = tid; i < kBlocksPerChunk * sub; i += kThreads) {
-    const int b = i / sub, j = i - b * sub;
-    const int count = sm.binfo[b * 4 + 1];
-    const int meta = sm.binfo[b * 4 + 2];
-    if (count <= 0 || (meta & TRIS_GR_META_RAW_FLAG)) continue;
-    const int k = meta & TRIS_GR_META_K_MASK;
-    const int one_count = meta >> TRIS_GR_META_ONE_COUNT_SHIFT;
-    const int per = (one_count + sub - 1) / sub;
-    const int first = j * per;
-    if (per == 0 || first >= one_count) continue;
-    const int n_ones = min(per, one_count - first);
-    const uint32_t packed = sm.gridx[b * 32 + j];
-    uint32_t* gbase = sm.g;
-    gr_decode_run(sm.grw + b * 128, count, k, n_ones, static_cast<int>(packed & 0xFFFFu),
-                  static_cast<int>(packed >> 16), [&](int flat) {
-                    atomicOr(gbase + block_word_to_tile<NPROJ>(b, flat >> 5), 1u << (flat & 31));
-                  });
-  }
-  __syncthreads();
-}
-
 // ---- bit-plane helpers ----------------------------------------------------------------
-// 32 bits of the column-bit stream of one output, starting at `rank` (sparse planes pack
-// only the active columns, 32 per row; utils/pack_utils.py:19-52).
-__device__ __forceinline__ uint32_t sparse_bits_at(const int32_t* plane, int rows, int o_stride, int rank,
-                                                   int need) {
-  const int q = rank >> 5, sh = rank & 31;
-  const uint32_t lo = (q < rows) ? static_cast<uint32_t>(plane[static_cast<size_t>(q) * o_stride]) : 0u;
-  uint32_t hi = 0u;
-  if (sh + need > 32 && q + 1 < rows) hi = static_cast<uint32_t>(plane[static_cast<size_t>(q + 1) * o_stride]);
-  return __funnelshift_r(lo, hi, sh);
-}
-
 // Places the low popc(mask) bits of `bits` at the set positions of `mask`, ascending.
 __device__ __forceinline__ uint32_t deposit_bits(uint32_t bits, uint32_t mask) {
   uint32_t out = 0u;
   while (mask) {
-    const int pos = __ffs(mask) - 1;
-    out |= (bits & 1u) << pos;
+    const uint32_t low = mask & (0u - mask);
+    out |= (0u - (bits & 1u)) & low;
     bits >>= 1;
-    mask &= mask - 1;
+    mask ^= low;
   }
   return out;
 }
@@ -215,151 +194,415 @@ __device__ __forceinline__ uint32_t deposit_bits(uint32_t bits, uint32_t mask) {
 // Opens a zero gap at every set position of `holes` (ascending), shifting higher bits up.
 __device__ __forceinline__ uint32_t spread_around(uint32_t bits, uint32_t holes) {
   while (holes) {
-    const int pos = __ffs(holes) - 1;
-    const uint32_t low = (1u << pos) - 1u;
+    const uint32_t low = (holes & (0u - holes)) - 1u;
     bits = (bits & low) | ((bits & ~low) << 1);
     holes &= holes - 1;
   }
   return bits;
 }
 
-// ---- chunk staging --------------------------------------------------------------------
-// Builds sign plane, select plane and the scale tables of the chunk from global memory.
-// Preconditions: sm.g holds the dense g_map words for projections stored as block-GR.
-// Select plane: for a non-salient column the g_map bit (1 -> "d" scale pair, CU:736-737);
-// for a salient column XNOR(sign1, sign2), because
-//   fp16(+-a +- b) = sign1 * fp16(a + (sign1*sign2) b)
-// so a salient weight is again "pick one of two magnitudes, then apply sign1" with
-// magnitudes fp16(a+b) and fp16(a-b).
+// 32 bits starting at bit `rank` of the column-bit stream of output o stored as rows of
+// 32 bits in shared memory ([row][o], row stride OW words).
+__device__ __forceinline__ uint32_t staged_bits_at(const uint32_t* rows, int ow, int o, int rank) {
+  const int q = rank >> 5, sh = rank & 31;
+  const uint32_t lo = (q < kSparseRows) ? rows[q * ow + o] : 0u;
+  const uint32_t hi = (sh != 0 && q + 1 < kSparseRows) ? rows[(q + 1) * ow + o] : 0u;
+  return __funnelshift_r(lo, hi, sh);
+}
+
+// ---- stage 1: issue -------------------------------------------------------------------
+// Called by all threads after a barrier that ended every earlier use of the staging
+// buffers.  Warps 0 and 1 issue the weight copies of chunk (e, o0, p0); warp 3 fills ptab.
 template <int NPROJ, int NT>
-__device__ __forceinline__ void stage_planes_and_scales(TileSmem<NPROJ, NT>& sm, const TrisProjView* views,
-                                                        int e, int o0, int p0, uint32_t* gmap_dump) {
+__device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
+                                                    int o0, int p0) {
   constexpr int OW = Geom<NPROJ>::OW;
-  const int tid = threadIdx.x;
-  for (int i = tid; i < kTileWords; i += kThreads) {
-    const int proj = i / (KC * OW);
-    const int p = (i / OW) % KC;
-    const int o = i % OW;
-    const TrisProjView& v = views[proj];
-    const int pr = proj_packed_rows(v);
-    const int pg = p0 + p, og = o0 + o;
-    uint32_t s1 = 0u, sel = 0u;
-    uint2 rp = make_uint2(0u, 0u);
-    if (pg < pr && og < v.out_features) {
-      const int O = v.out_features;
-      s1 = static_cast<uint32_t>(v.qweight1[(static_cast<size_t>(e) * pr + pg) * O + og]);
-      const uint32_t cwv = static_cast<uint32_t>(v.c_map[static_cast<size_t>(e) * pr + pg]);
-      uint32_t s2 = 0u;
-      const int cnt = __popc(cwv);
-      if (cnt > 0 && v.qweight2_sparse != nullptr) {
-        const int rank0 = v.qweight2_sparse_prefix[static_cast<size_t>(e) * (pr + 1) + pg];
-        const uint32_t bits = sparse_bits_at(
-            v.qweight2_sparse + static_cast<size_t>(e) * v.sign2_rows * O + og, v.sign2_rows, O, rank0, cnt);
-        s2 = deposit_bits(bits, cwv);
+  constexpr int NOB = Geom<NPROJ>::NOB;
+  constexpr int SPAN = Geom<NPROJ>::SPAN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (warp == 0) {
+    // ---- copies whose addresses need nothing but (e, o0, p0) ---------------------------
+    fence_proxy_async();
+    uint32_t bytes = 0;
+    uint64_t* bar = &sm.mbar[0];
+    if (lane < NPROJ * KC) {  // sign plane rows
+      const int proj = lane / KC, p = lane % KC;
+      const TrisProjView& v = views[proj];
+      const int pr = proj_packed_rows(v);
+      const int wv = min(OW, v.out_features - o0);
+      if (p0 + p < pr && wv > 0)
+        bytes += lane_copy(sm.s1 + (proj * KC + p) * OW,
+                           reinterpret_cast<const uint32_t*>(v.qweight1) +
+                               (static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0,
+                           wv, bar);
+    } else if (lane < 16 + NPROJ) {  // column scale packs
+      const int proj = lane - 16;
+      if (proj >= 0) {
+        const TrisProjView& v = views[proj];
+        const int c0 = 32 * p0, c1 = min(v.rank, 32 * (p0 + KC));
+        if (c1 > c0)
+          bytes += lane_copy(reinterpret_cast<uint32_t*>(sm.colraw + proj * 256),
+                             reinterpret_cast<const uint32_t*>(v.col_pack3 + static_cast<size_t>(e) * v.rank + c0),
+                             2 * (c1 - c0), bar);
       }
-      uint32_t gm;
-      if (v.use_block_gr) {
-        gm = sm.g[i];
-      } else {
-        const int ncols = min(32, v.rank - 32 * pg);
-        const uint32_t colmask = (ncols >= 32) ? 0xFFFFFFFFu : ((1u << ncols) - 1u);
-        const uint32_t nsmask = ~cwv & colmask;
-        gm = 0u;
-        if (nsmask != 0u && v.q_gmap_sparse != nullptr) {
-          const int rank0 = v.q_gmap_sparse_prefix[static_cast<size_t>(e) * (pr + 1) + pg];
-          const int slot = v.gmap_slot ? v.gmap_slot[e] : e;
-          const uint32_t bits = sparse_bits_at(
-              v.q_gmap_sparse + static_cast<size_t>(slot) * v.gmap_sparse_rows * O + og,
-              v.gmap_sparse_rows, O, rank0, __popc(nsmask));
-          gm = spread_around(bits, cwv & colmask) & nsmask;
+    } else if (lane >= 18 && lane < 18 + NPROJ) {  // row scale packs, all groups, when they fit
+      const int proj = lane - 18;
+      const TrisProjView& v = views[proj];
+      const int G = v.num_groups;
+      const int wv = min(OW, v.out_features - o0);
+      if (G * NPROJ * OW <= kRowTabEntries && wv > 0)
+        bytes += lane_copy(reinterpret_cast<uint32_t*>(sm.rowtab + proj * OW * G),
+                           reinterpret_cast<const uint32_t*>(v.row_pack3 + (static_cast<size_t>(e) * v.out_features + o0) * G),
+                           2 * wv * G, bar);
+    } else if (lane >= 20 && lane < 20 + kBlocksPerChunk) {  // block-GR sub-stream index
+      const int b = lane - 20;
+      const TrisProjView& v = views[b / (NOB * 4)];
+      if (v.use_block_gr && v.gr_index != nullptr) {
+        const int pr = proj_packed_rows(v);
+        const int nkb = (pr + 1) >> 1, nob = (v.out_features + 63) >> 6;
+        const int kb = (p0 >> 1) + ((b / NOB) & 3), ob = (o0 >> 6) + (b % NOB);
+        if (kb < nkb && ob < nob) {
+          const size_t bi = static_cast<size_t>(e) * nkb * nob + static_cast<size_t>(kb) * nob + ob;
+          bytes += lane_copy(sm.gridx + b * 32, v.gr_index + bi * v.gr_substreams, v.gr_substreams, bar);
         }
       }
-      if (gmap_dump) gmap_dump[i] = gm;
-      sel = (gm & ~cwv) | (cwv & ~(s1 ^ s2));
-      const int grp = v.packed_row_group ? v.packed_row_group[static_cast<size_t>(e) * pr + pg] : 0;
-      if (grp >= 0 && grp < v.num_groups) {
-        const unsigned long long w = static_cast<unsigned long long>(
-            v.row_pack3[(static_cast<size_t>(e) * O + og) * v.num_groups + grp]);
-        rp = make_uint2(static_cast<uint32_t>(w), static_cast<uint32_t>(w >> 32));
-      }
-    } else if (gmap_dump) {
-      gmap_dump[i] = 0u;
     }
-    sm.s1[i] = s1;
-    sm.g[i] = sel;
-    sm.rowtab[i] = rp;
+    if (bytes) mbar_arrive_expect_tx(bar, bytes);
+    else mbar_arrive(bar);
+  } else if (warp == 1) {
+    // ---- copies that need offsets / prefixes -------------------------------------------
+    fence_proxy_async();
+    uint32_t bytes = 0;
+    uint64_t* bar = &sm.mbar[1];
+    if (lane < NPROJ * 4) {  // one block-GR span = the NOB blocks of (proj, k block)
+      const int proj = lane >> 2, kbl = lane & 3;
+      const TrisProjView& v = views[proj];
+      const int pr = proj_packed_rows(v);
+      const int nkb = (pr + 1) >> 1, nob = (v.out_features + 63) >> 6;
+      const int kb = (p0 >> 1) + kbl, ob0 = o0 >> 6;
+      int begins[NOB + 1];
+      int metas[NOB];
+      bool ok = v.use_block_gr && v.q_gmap_gr_words != nullptr && kb < nkb;
+#pragma unroll
+      for (int j = 0; j < NOB; ++j) metas[j] = 0;
+#pragma unroll
+      for (int j = 0; j <= NOB; ++j) begins[j] = 0;
+      int nvalid = 0;
+      if (ok) {
+        nvalid = min(NOB, nob - ob0);
+        const int nblk = nkb * nob;
+        const int32_t* off = v.q_gmap_gr_offsets + static_cast<size_t>(e) * (nblk + 1) + kb * nob + ob0;
+        const int32_t* met = v.q_gmap_gr_meta + static_cast<size_t>(e) * nblk + kb * nob + ob0;
+#pragma unroll
+        for (int j = 0; j <= NOB; ++j)
+          if (j <= nvalid) begins[j] = off[j];
+#pragma unroll
+        for (int j = 0; j < NOB; ++j)
+          if (j < nvalid) metas[j] = met[j];
+      }
+      const int first = begins[0];
+      int last = first;
+#pragma unroll
+      for (int j = 0; j < NOB; ++j) {
+        const int b = lane * NOB + j;
+        int count = (j < nvalid) ? begins[j + 1] - begins[j] : 0;
+        if (count < 0 || count > TRIS_GR_BLOCK_WORDS || begins[j] < 0 || begins[j] + count > v.gr_max_words ||
+            begins[j] < last)
+          count = 0;  // corrupt offsets were already rejected at load time; stay in bounds regardless
+        if (count > 0) last = begins[j] + count;
+        sm.binfo[b * 4 + 1] = count;
+        sm.binfo[b * 4 + 2] = metas[j];
+        sm.binfo[b * 4 + 0] = begins[j];  // made relative below
+      }
+      int nwords = last - first;
+      if (nwords < 0 || nwords > NOB * TRIS_GR_BLOCK_WORDS) {
+        nwords = 0;
+#pragma unroll
+        for (int j = 0; j < NOB; ++j) sm.binfo[(lane * NOB + j) * 4 + 1] = 0;
+      }
+      uint32_t* region = sm.gmraw + lane * SPAN;
+      int shift = 0;
+      if (nwords > 0) {
+        const size_t abs0 = static_cast<size_t>(e) * v.gr_max_words + first;
+        const size_t total = static_cast<size_t>(v.num_experts) * v.gr_max_words;
+        const uint32_t* base = reinterpret_cast<const uint32_t*>(v.q_gmap_gr_words);
+        const bool base_aligned = (reinterpret_cast<uintptr_t>(base) & 15u) == 0;
+        shift = base_aligned ? static_cast<int>(abs0 & 3) : 0;  // words above a 16-byte boundary
+        const size_t a0 = abs0 - shift;
+        size_t a1 = base_aligned ? ((abs0 + nwords + 3) & ~static_cast<size_t>(3)) : (abs0 + nwords);
+        if (a1 > total) a1 = abs0 + nwords;
+        const int n_al = static_cast<int>(a1 - a0);
+        if ((n_al & 3) == 0 && a0 + n_al <= total) {
+          bytes += lane_copy(region, base + a0, n_al, bar);
+        } else {
+          const int bulk = (n_al >> 2) << 2;
+          bytes += lane_copy(region, base + a0, bulk, bar);
+          for (int w = bulk; w < n_al; ++w) region[w] = base[a0 + w];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < NOB; ++j) {
+        const int b = lane * NOB + j;
+        sm.binfo[b * 4 + 0] = lane * SPAN + shift + (sm.binfo[b * 4 + 0] - first);
+      }
+    } else if (lane >= 8 && lane < 8 + NPROJ) {  // salient sign rows
+      const int proj = lane - 8;
+      const TrisProjView& v = views[proj];
+      const int pr = proj_packed_rows(v);
+      const int wv = min(OW, v.out_features - o0);
+      if (v.sign2_rows > 0 && v.qweight2_sparse != nullptr && p0 < pr && wv > 0) {
+        const int32_t* pre = v.qweight2_sparse_prefix + static_cast<size_t>(e) * (pr + 1);
+        const int r0 = pre[p0], r1 = pre[min(pr, p0 + KC)];
+        const int q0 = max(0, r0 >> 5);
+        const int q1 = min(min(v.sign2_rows, (r1 + 31) >> 5), q0 + kSparseRows);
+        for (int q = q0; q < q1; ++q)
+          bytes += lane_copy(sm.s2raw + (proj * kSparseRows + (q - q0)) * OW,
+                             reinterpret_cast<const uint32_t*>(v.qweight2_sparse) +
+                                 (static_cast<size_t>(e) * v.sign2_rows + q) * v.out_features + o0,
+                             wv, bar);
+      }
+    } else if (lane >= 12 && lane < 12 + NPROJ) {  // sparse g_map rows (streaming format)
+      const int proj = lane - 12;
+      const TrisProjView& v = views[proj];
+      const int pr = proj_packed_rows(v);
+      const int wv = min(OW, v.out_features - o0);
+      if (!v.use_block_gr && v.gmap_sparse_rows > 0 && v.q_gmap_sparse != nullptr && p0 < pr && wv > 0) {
+        const int32_t* pre = v.q_gmap_sparse_prefix + static_cast<size_t>(e) * (pr + 1);
+        const int r0 = pre[p0], r1 = pre[min(pr, p0 + KC)];
+        const int slot = v.gmap_slot ? v.gmap_slot[e] : e;
+        const int q0 = max(0, r0 >> 5);
+        const int q1 = min(min(v.gmap_sparse_rows, (r1 + 31) >> 5), q0 + kSparseRows);
+        for (int q = q0; q < q1; ++q)
+          bytes += lane_copy(sm.gmraw + (proj * kSparseRows + (q - q0)) * OW,
+                             reinterpret_cast<const uint32_t*>(v.q_gmap_sparse) +
+                                 (static_cast<size_t>(slot) * v.gmap_sparse_rows + q) * v.out_features + o0,
+                             wv, bar);
+      }
+    }
+    if (bytes) mbar_arrive_expect_tx(bar, bytes);
+    else mbar_arrive(bar);
+  } else if (warp == 3) {
+    // ---- per packed row table -----------------------------------------------------------
+    if (lane < NPROJ * 16) {
+      const int proj = lane >> 4, p = lane & 15;
+      if (p <= KC) {
+        const TrisProjView& v = views[proj];
+        const int pr = proj_packed_rows(v);
+        const int pg = p0 + p;
+        PackedRowInfo info{0u, 0, 0, 0};
+        if (p0 < pr) {
+          const int pc = min(pg, pr);
+          int base2 = 0, baseg = 0;
+          if (v.qweight2_sparse_prefix) {
+            const int32_t* pre = v.qweight2_sparse_prefix + static_cast<size_t>(e) * (pr + 1);
+            base2 = max(0, pre[p0] >> 5) << 5;
+            info.rank2 = pre[pc] - base2;
+          }
+          if (!v.use_block_gr && v.q_gmap_sparse_prefix) {
+            const int32_t* pre = v.q_gmap_sparse_prefix + static_cast<size_t>(e) * (pr + 1);
+            baseg = max(0, pre[p0] >> 5) << 5;
+            info.rankg = pre[pc] - baseg;
+          }
+          if (pg < pr) {
+            info.cw = static_cast<uint32_t>(v.c_map[static_cast<size_t>(e) * pr + pg]);
+            const int grp = v.packed_row_group ? v.packed_row_group[static_cast<size_t>(e) * pr + pg] : 0;
+            const bool all_groups = v.num_groups * NPROJ * OW <= kRowTabEntries;
+            info.gslot = all_groups ? min(max(grp, 0), v.num_groups - 1) : (p < KC ? p : 0);
+          }
+        }
+        sm.ptab[proj * (KC + 1) + p] = info;
+      }
+    }
+    if (lane == 0) {
+      const int G = views[0].num_groups;
+      sm.row_stride = (G * NPROJ * OW <= kRowTabEntries) ? G : KC;
+    }
   }
+}
+
+// Activation rows.  row_src(n) returns the source row of local row n or -1 for padding.
+// `interleaved` activations are copied as they are (one TMA copy per row, issued by warp
+// 2); row-major ones are re-ordered by all threads.  All threads must call.
+template <int NPROJ, int NT, typename RowSrc>
+__device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, const __half* const* hidden,
+                                                   const TrisProjView* views, int p0, int nrows, bool interleaved,
+                                                   RowSrc row_src) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = views[0].rank;
+  const int c0 = 32 * p0;
+  const int ncols = min(256, rank - c0);
+  const bool tma_rows = interleaved;  // callers pass interleaved only when rank % 32 == 0
+  if (tma_rows) {
+    if (warp == 2) {
+      fence_proxy_async();
+      uint32_t bytes = 0;
+      for (int i = lane; i < NPROJ * nrows; i += 32) {
+        const int proj = i / nrows, n = i - proj * nrows;
+        const int src = row_src(n);
+        if (src >= 0)
+          bytes += lane_copy(reinterpret_cast<uint32_t*>(sm.hrows + (proj * NT * 8 + n) * kHiddenRowBytes),
+                             reinterpret_cast<const uint32_t*>(hidden[proj] + static_cast<size_t>(src) * rank + c0),
+                             ncols >> 1, &sm.mbar[2]);
+      }
+      if (bytes) mbar_arrive_expect_tx(&sm.mbar[2], bytes);
+      else mbar_arrive(&sm.mbar[2]);
+    }
+    return;
+  }
+  if (warp == 2) mbar_arrive(&sm.mbar[2]);
+  // row-major activations: 8 columns per item, scattered to their pair-interleaved positions
+  const int items = NPROJ * nrows * 32;
+  for (int i = threadIdx.x; i < items; i += kThreads) {
+    const int j8 = i & 31;  // 8-column group inside the chunk
+    const int n = (i >> 5) % nrows;
+    const int proj = i / (32 * nrows);
+    const int col = c0 + 8 * j8;
+    const int src = row_src(n);
+    __half vals[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) vals[u] = __ushort_as_half(0);
+    if (src >= 0 && col < rank) {
+      const __half* rowp = hidden[proj] + static_cast<size_t>(src) * rank + col;
+      if ((rank & 7) == 0 && col + 8 <= rank && (reinterpret_cast<uintptr_t>(rowp) & 15u) == 0) {
+        *reinterpret_cast<uint4*>(vals) = *reinterpret_cast<const uint4*>(rowp);
+      } else {
+        for (int u = 0; u < 8 && col + u < rank; ++u) vals[u] = rowp[u];
+      }
+    }
+    __half* dst = reinterpret_cast<__half*>(sm.hrows + (proj * NT * 8 + n) * kHiddenRowBytes);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int j = (8 * j8 + u) & 31;
+      dst[((8 * j8) & ~31) + 2 * (j & 15) + (j >> 4)] = vals[u];
+    }
+  }
+}
+
+// ---- stage 2: decode + tables ---------------------------------------------------------
+// All threads.  Waits for the weight copies, expands the block-GR blocks into sm.g (and
+// optionally hands the dense g_map words to `dump`), builds select plane and column table.
+// Returns false when a wait timed out.
+template <int NPROJ, int NT>
+__device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
+                                                     int o0, int p0, uint32_t parity, uint32_t* gmap_dump) {
+  constexpr int OW = Geom<NPROJ>::OW;
+  constexpr int NOB = Geom<NPROJ>::NOB;
+  const int tid = threadIdx.x;
+  bool ok = mbar_wait_bounded(&sm.mbar[0], parity);
+
+  // column table: pairs (4t+i, 4t+i+16); scales a column does not use are zeroed so that
+  // one fused multiply-add serves salient and non-salient halves alike
   for (int i = tid; i < NPROJ * KC * 16; i += kThreads) {
     const int proj = i / (KC * 16);
     const int p = (i >> 4) % KC;
     const int ii = (i >> 2) & 3;
     const int t = i & 3;
     const TrisProjView& v = views[proj];
-    const int pr = proj_packed_rows(v);
-    const int pg = p0 + p;
-    uint4 entry = make_uint4(0u, 0u, 0u, 0u);
-    uint32_t cwv = 0u;
-    if (pg < pr) {
-      cwv = static_cast<uint32_t>(v.c_map[static_cast<size_t>(e) * pr + pg]);
-      const int ja = t + 4 * ii, jb = ja + 16;
-      unsigned long long pa = 0ull, pb = 0ull;
-      if (32 * pg + ja < v.rank) pa = static_cast<unsigned long long>(v.col_pack3[static_cast<size_t>(e) * v.rank + 32 * pg + ja]);
-      if (32 * pg + jb < v.rank) pb = static_cast<unsigned long long>(v.col_pack3[static_cast<size_t>(e) * v.rank + 32 * pg + jb]);
-      const bool sa = (cwv >> ja) & 1u, sb = (cwv >> jb) & 1u;
-      // col_pack3 halves: (s_c1, s_c2, ns_d_c1, ns_nd_c1) at bits 0/16/32/48 (utils/pack_utils.py:55-64)
-      const uint32_t c1a = pa & 0xFFFFu, c2a = (pa >> 16) & 0xFFFFu, cda = (pa >> 32) & 0xFFFFu, cna = (pa >> 48) & 0xFFFFu;
-      const uint32_t c1b = pb & 0xFFFFu, c2b = (pb >> 16) & 0xFFFFu, cdb = (pb >> 32) & 0xFFFFu, cnb = (pb >> 48) & 0xFFFFu;
-      entry.x = (sa ? 0u : cda) | ((sb ? 0u : cdb) << 16);
-      entry.y = (sa ? 0u : cna) | ((sb ? 0u : cnb) << 16);
-      entry.z = (sa ? c1a : 0u) | ((sb ? c1b : 0u) << 16);
-      entry.w = (sa ? c2a : 0u) | ((sb ? c2b : 0u) << 16);
-    }
-    sm.coltab[i] = entry;
-    if ((i & 15) == 0) sm.cw[proj * KC + p] = cwv;
+    const uint32_t cwv = sm.ptab[proj * (KC + 1) + p].cw;
+    const int ja = 4 * t + ii, jb = ja + 16;
+    const int ca = 32 * (p0 + p) + ja, cb = ca + 16;
+    uint2 pa = make_uint2(0u, 0u), pb = make_uint2(0u, 0u);
+    if (ca < v.rank) pa = sm.colraw[proj * 256 + 32 * p + ja];
+    if (cb < v.rank) pb = sm.colraw[proj * 256 + 32 * p + jb];
+    const bool sa = (cwv >> ja) & 1u, sb = (cwv >> jb) & 1u;
+    // col_pack3 halves: (s_c1, s_c2, ns_d_c1, ns_nd_c1) at bits 0/16/32/48 (utils/pack_utils.py:55-64)
+    uint4 entry;
+    entry.x = (sa ? 0u : (pa.y & 0xFFFFu)) | ((sb ? 0u : (pb.y & 0xFFFFu)) << 16);
+    entry.y = (sa ? 0u : (pa.y >> 16)) | ((sb ? 0u : (pb.y >> 16)) << 16);
+    entry.z = (sa ? (pa.x & 0xFFFFu) : 0u) | ((sb ? (pb.x & 0xFFFFu) : 0u) << 16);
+    entry.w = (sa ? (pa.x >> 16) : 0u) | ((sb ? (pb.x >> 16) : 0u) << 16);
+    sm.coltab[((proj * KC + p) * 4 + ii) * 4 + t] = entry;
   }
-}
-
-// Stages NT*8 activation rows of the chunk's 256 columns in fragment order.
-// row_src(n) returns the hidden row of local row n, or -1 for padding.
-template <int NPROJ, int NT, typename RowSrc>
-__device__ __forceinline__ void stage_hidden(TileSmem<NPROJ, NT>& sm, const __half* const* hidden,
-                                             const TrisProjView* views, int p0, int nt_count, RowSrc row_src) {
-  const int tid = threadIdx.x;
-  __half* dst = reinterpret_cast<__half*>(sm.htab);
-  const int items = NPROJ * nt_count * 8 * KC * 4;
-  for (int i = tid; i < items; i += kThreads) {
-    const int j0 = (i & 3) * 8;
-    const int p = (i >> 2) % KC;
-    const int n_local = (i / (4 * KC)) % (nt_count * 8);
-    const int proj = i / (4 * KC * nt_count * 8);
-    const int rank = views[proj].rank;
-    const int col = 32 * (p0 + p) + j0;
-    const int src = row_src(n_local);
-    __half vals[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) vals[u] = __ushort_as_half(0);
-    if (src >= 0 && col < rank) {
-      const __half* rowp = hidden[proj] + static_cast<size_t>(src) * rank + col;
-      if ((rank & 7) == 0 && col + 8 <= rank) {
-        *reinterpret_cast<uint4*>(vals) = *reinterpret_cast<const uint4*>(rowp);
-      } else {
-        for (int u = 0; u < 8 && col + u < rank; ++u) vals[u] = rowp[u];
+  // row scale packs when the projection has too many groups to stage them all
+  if (sm.row_stride == KC && views[0].num_groups * NPROJ * OW > kRowTabEntries) {
+    for (int i = tid; i < kRowTabEntries; i += kThreads) {
+      const int p = i % KC;
+      const int o = (i / KC) % OW;
+      const int proj = i / (KC * OW);
+      const TrisProjView& v = views[proj];
+      const int pr = proj_packed_rows(v);
+      uint2 rp = make_uint2(0u, 0u);
+      if (p0 + p < pr && o0 + o < v.out_features) {
+        const int grp = v.packed_row_group ? v.packed_row_group[static_cast<size_t>(e) * pr + p0 + p] : 0;
+        if (grp >= 0 && grp < v.num_groups) {
+          const unsigned long long w = static_cast<unsigned long long>(
+              v.row_pack3[(static_cast<size_t>(e) * v.out_features + o0 + o) * v.num_groups + grp]);
+          rp = make_uint2(static_cast<uint32_t>(w), static_cast<uint32_t>(w >> 32));
+        }
       }
-    }
-    const int nt = n_local >> 3, n = n_local & 7;
-    const size_t base = ((static_cast<size_t>(proj) * NT + nt) * KC + p) * 8 + n;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int j = j0 + u;
-      const int t = j & 3, ii = (j >> 2) & 3, hi = j >> 4;
-      dst[(base * 4 + t) * 8 + 2 * ii + hi] = vals[u];
+      sm.rowtab[i] = rp;
     }
   }
+
+  ok = mbar_wait_bounded(&sm.mbar[1], parity) && ok;
+  const bool gr = views[0].use_block_gr != 0;
+  if (gr) {
+    // zero the blocks (raw blocks are copied verbatim)
+    for (int i = tid; i < kBlocksPerChunk * 128; i += kThreads) {
+      const int b = i >> 7, wl = i & 127;
+      const bool raw = (sm.binfo[b * 4 + 2] & TRIS_GR_META_RAW_FLAG) != 0;
+      uint32_t word = 0u;
+      if (raw && wl < sm.binfo[b * 4 + 1]) word = sm.gmraw[sm.binfo[b * 4 + 0] + wl];
+      sm.g[block_word_to_tile<NPROJ>(b, wl)] = word;
+    }
+    __syncthreads();
+    const int sub = views[0].gr_substreams;
+    for (int i = tid; i < kBlocksPerChunk * sub; i += kThreads) {
+      const int b = i / sub, j = i - b * sub;
+      const int count = sm.binfo[b * 4 + 1];
+      const int meta = sm.binfo[b * 4 + 2];
+      if (count <= 0 || (meta & TRIS_GR_META_RAW_FLAG)) continue;
+      const int k = meta & TRIS_GR_META_K_MASK;
+      const int one_count = meta >> TRIS_GR_META_ONE_COUNT_SHIFT;
+      const int per = (one_count + sub - 1) / sub;
+      const int first = j * per;
+      if (per == 0 || first >= one_count) continue;
+      const int n_ones = min(per, one_count - first);
+      const uint32_t packed = sm.gridx[b * 32 + j];
+      uint32_t* gbase = sm.g;
+      gr_decode_run(sm.gmraw + sm.binfo[b * 4 + 0], count, k, n_ones, static_cast<int>(packed & 0xFFFFu),
+                    static_cast<int>(packed >> 16), [&](int word, uint32_t mask) {
+                      atomicOr(gbase + block_word_to_tile<NPROJ>(b, word), mask);
+                    });
+    }
+    __syncthreads();
+  }
+
+  // select plane: for a non-salient column the g_map bit (1 -> "d" scale pair, CU:736-737);
+  // for a salient column XNOR(sign1, sign2), because
+  //   fp16(+-a +- b) = sign1 * fp16(a + (sign1*sign2) b)
+  // so a salient weight is again "pick one of two magnitudes, then apply sign1" with
+  // magnitudes fp16(a+b) and fp16(a-b).
+  for (int i = tid; i < kTileWords; i += kThreads) {
+    const int proj = i / (KC * OW);
+    const int p = (i / OW) % KC;
+    const int o = i % OW;
+    const TrisProjView& v = views[proj];
+    const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
+    const uint32_t cwv = info.cw;
+    const uint32_t s1 = sm.s1[i];
+    uint32_t s2 = 0u;
+    if (cwv) s2 = deposit_bits(staged_bits_at(sm.s2raw + proj * kSparseRows * OW, OW, o, info.rank2), cwv);
+    uint32_t gm;
+    if (gr) {
+      gm = sm.g[i];
+    } else {
+      const int ncols = min(32, v.rank - 32 * (p0 + p));
+      const uint32_t colmask = (ncols >= 32) ? 0xFFFFFFFFu : (ncols <= 0 ? 0u : ((1u << ncols) - 1u));
+      const uint32_t nsmask = ~cwv & colmask;
+      gm = 0u;
+      if (nsmask) gm = spread_around(staged_bits_at(sm.gmraw + proj * kSparseRows * OW, OW, o, info.rankg), cwv & colmask) & nsmask;
+    }
+    if (gmap_dump) gmap_dump[i] = gm;
+    sm.g[i] = (gm & ~cwv) | (cwv & ~(s1 ^ s2));
+  }
+  return ok;
 }
 
 // ---- register unpack ------------------------------------------------------------------
 // Weights of packed row p for the lane's two outputs (h = 0: out g, h = 1: out g+8) and
-// four column pairs (t+4i, t+4i+16) as half2 bit patterns a[h][i].
+// four column pairs (4t+i, 4t+i+16) as half2 bit patterns a[h][i].
 // Exact arithmetic of _dequantize_compact3_matrix (QL:4200-4236): each product rounded to
 // fp16 once, salient weight = fp16(+-p1 +- p2).
 template <int NPROJ, int NT>
@@ -367,28 +610,30 @@ __device__ __forceinline__ void unpack_fragments(const TileSmem<NPROJ, NT>& sm, 
                                                  int lane, uint32_t (&a)[2][4]) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int g = lane >> 2, t = lane & 3;
-  const uint32_t cwv = sm.cw[proj * KC + p];
+  const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
+  const uint32_t cwv = info.cw;
+  const int rs = sm.row_stride;
   uint4 ct[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) ct[i] = sm.coltab[((proj * KC + p) * 4 + i) * 4 + t];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int idx = (proj * KC + p) * OW + out_local + g + 8 * h;
+    const int o = out_local + g + 8 * h;
+    const int idx = (proj * KC + p) * OW + o;
     const uint32_t s1 = sm.s1[idx];
     const uint32_t se = sm.g[idx];
-    const uint2 rp = sm.rowtab[idx];
+    const uint2 rp = sm.rowtab[(proj * OW + o) * rs + info.gslot];
     // row_pack3 halves: (s_r1, s_r2, ns_d_r1, ns_nd_r1)
     const __half2 r1 = u32_as_h2(prmt(rp.x, 0u, 0x1010u));
     const __half2 r2 = u32_as_h2(prmt(rp.x, 0u, 0x3232u));
     const __half2 rd = u32_as_h2(prmt(rp.y, 0u, 0x1010u));
     const __half2 rn = u32_as_h2(prmt(rp.y, 0u, 0x3232u));
-    const uint32_t st = s1 << (3 - t);   // column t+4i at bit 3+4i, column t+4i+16 at bit 19+4i
-    const uint32_t gt = se << (3 - t);
-    const uint32_t gt4 = gt << 4;
+    const uint32_t st = s1 << (12 - 4 * t);  // column 4t+i at bit 12+i, column 4t+i+16 at bit 28+i
+    const uint32_t gt = se << (12 - 4 * t);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       __half2 ca, cb;
-      const uint32_t pairmask = 0x000F000Fu << (4 * i);  // columns of pair i over all four t
+      const uint32_t pairmask = 0x11111111u << i;  // columns of pair i over all four t
       if (cwv & pairmask) {
         const __half2 p1 = __hmul2_rn(u32_as_h2(ct[i].z), r1);
         const __half2 p2 = __hmul2_rn(u32_as_h2(ct[i].w), r2);
@@ -401,15 +646,19 @@ __device__ __forceinline__ void unpack_fragments(const TileSmem<NPROJ, NT>& sm, 
         ca = __hmul2_rn(u32_as_h2(ct[i].x), rd);
         cb = __hmul2_rn(u32_as_h2(ct[i].y), rn);
       }
-      // select mask: replicate the select bit of each half over its 16 bits
-      const uint32_t src = (i & 1) ? gt : gt4;               // i=1,3 use gt; i=0,2 use gt<<4
-      const uint32_t m = prmt(src, 0u, (i >= 2) ? 0xBB99u : 0xAA88u);
+      // select mask: replicate bits 15 and 31 over their halves
+      const uint32_t m = prmt(gt << (3 - i), 0u, 0xBB99u);
       const uint32_t mag = (h2_as_u32(ca) & m) | (h2_as_u32(cb) & ~m);
       // sign: plane bit 1 -> +, 0 -> -   (QL:4213)
-      const uint32_t sbits = st << (12 - 4 * i);             // pair i at bits 15 and 31
-      a[h][i] = mag ^ (~sbits & 0x80008000u);
+      a[h][i] = mag ^ (~(st << (3 - i)) & 0x80008000u);
     }
   }
+}
+
+// B fragments of packed row p, local activation row `n`: 8 halves in pair order.
+template <int NPROJ, int NT>
+__device__ __forceinline__ uint4 load_b_fragments(const TileSmem<NPROJ, NT>& sm, int proj, int n, int p, int t) {
+  return *reinterpret_cast<const uint4*>(sm.hrows + (proj * NT * 8 + n) * kHiddenRowBytes + p * 64 + t * 16);
 }
 
 }  // namespace tris

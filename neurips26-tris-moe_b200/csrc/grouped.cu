@@ -6,6 +6,8 @@
 // memory, then every warp unpacks weights straight into m16n8k16 A fragments and
 // multiplies them with the staged activation rows; no dequantized weight is written
 // anywhere but registers.  fp32 accumulation.
+#include <math.h>
+
 #include <algorithm>
 
 #include "compact3_tile.cuh"
@@ -91,43 +93,66 @@ __global__ void build_row_groups_kernel(const int32_t* g_idx, int num_experts, i
 }
 
 // ---- dump kernels -------------------------------------------------------------------------
-// grid (ceil(O/128), ceil(pr/8), E)
-__global__ void __launch_bounds__(kThreads) block_gr_decode_kernel(TrisProjView v, int32_t* dense_out) {
-  extern __shared__ uint4 smem_raw[];
-  auto& sm = *reinterpret_cast<TileSmem<1, 1>*>(smem_raw);
-  const int o0 = blockIdx.x * 128, p0 = blockIdx.y * KC, e = blockIdx.z;
-  stage_gmap_block_gr<1, 1>(sm, &v, e, o0, p0);
-  const int pr = proj_packed_rows(v);
-  for (int i = threadIdx.x; i < kTileWords; i += kThreads) {
-    const int p = i / 128, o = i % 128;
-    if (p0 + p < pr && o0 + o < v.out_features)
-      dense_out[(static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0 + o] = static_cast<int32_t>(sm.g[i]);
+__device__ __forceinline__ void init_barriers(uint64_t* mbar) {
+  if (threadIdx.x == 0) {
+    mbar_init(&mbar[0], 32);
+    mbar_init(&mbar[1], 32);
+    mbar_init(&mbar[2], 32);
+    fence_mbar_init();
   }
+  __syncthreads();
 }
 
-__global__ void __launch_bounds__(kThreads) compact3_dequant_kernel(TrisProjView v, __half* weights_out) {
+// Second, equally bounded, wait for copies that may still be in flight before a CTA that
+// saw a time-out leaves; then the status word is set.
+template <typename Smem>
+__device__ __forceinline__ void leave_after_timeout(Smem& sm, uint32_t par_w, uint32_t par_h, int32_t* status) {
+  mbar_wait_bounded(&sm.mbar[0], par_w);
+  mbar_wait_bounded(&sm.mbar[1], par_w);
+  mbar_wait_bounded(&sm.mbar[2], par_h);
+  if (threadIdx.x == 0 && status) atomicExch(status, TRIS_ERR_TIMEOUT);
+}
+
+// grid (ceil(O/128), ceil(pr/8), E); dense_out and weights_out may each be null
+__global__ void __launch_bounds__(kThreads) compact3_dump_kernel(TrisProjView v, int32_t* dense_out,
+                                                                  __half* weights_out, int32_t* status) {
   extern __shared__ uint4 smem_raw[];
   auto& sm = *reinterpret_cast<TileSmem<1, 1>*>(smem_raw);
   const int o0 = blockIdx.x * 128, p0 = blockIdx.y * KC, e = blockIdx.z;
-  if (v.use_block_gr) stage_gmap_block_gr<1, 1>(sm, &v, e, o0, p0);
-  stage_planes_and_scales<1, 1>(sm, &v, e, o0, p0, nullptr);
+  init_barriers(sm.mbar);
+  stage_issue_weights<1, 1>(sm, &v, e, o0, p0);
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
+  uint32_t* dump = reinterpret_cast<uint32_t*>(sm.hrows);  // 4608 B >= 1024 words
+  const bool ok = stage_finish_weights<1, 1>(sm, &v, e, o0, p0, 0u, dense_out ? dump : nullptr);
+  if (__syncthreads_or(!ok)) {
+    if (threadIdx.x == 0 && status) atomicExch(status, TRIS_ERR_TIMEOUT);
+    return;
+  }
   const int pr = proj_packed_rows(v);
-  for (int p = 0; p < KC && p0 + p < pr; ++p) {
-    uint32_t a[2][4];
-    unpack_fragments<1, 1>(sm, 0, p, warp * 16, lane, a);
+  if (dense_out) {
+    for (int i = threadIdx.x; i < kTileWords; i += kThreads) {
+      const int p = i / 128, o = i % 128;
+      if (p0 + p < pr && o0 + o < v.out_features)
+        dense_out[(static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0 + o] = static_cast<int32_t>(dump[i]);
+    }
+  }
+  if (weights_out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    for (int p = 0; p < KC && p0 + p < pr; ++p) {
+      uint32_t a[2][4];
+      unpack_fragments<1, 1>(sm, 0, p, warp * 16, lane, a);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int og = o0 + warp * 16 + g + 8 * h;
-      if (og >= v.out_features) continue;
-      __half* row = weights_out + (static_cast<size_t>(e) * v.out_features + og) * v.rank;
+      for (int h = 0; h < 2; ++h) {
+        const int og = o0 + warp * 16 + g + 8 * h;
+        if (og >= v.out_features) continue;
+        __half* row = weights_out + (static_cast<size_t>(e) * v.out_features + og) * v.rank;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int ca = 32 * (p0 + p) + t + 4 * i, cb = ca + 16;
-        if (ca < v.rank) row[ca] = __ushort_as_half(static_cast<unsigned short>(a[h][i] & 0xFFFFu));
-        if (cb < v.rank) row[cb] = __ushort_as_half(static_cast<unsigned short>(a[h][i] >> 16));
+        for (int i = 0; i < 4; ++i) {
+          const int ca = 32 * (p0 + p) + 4 * t + i, cb = ca + 16;
+          if (ca < v.rank) row[ca] = __ushort_as_half(static_cast<unsigned short>(a[h][i] & 0xFFFFu));
+          if (cb < v.rank) row[cb] = __ushort_as_half(static_cast<unsigned short>(a[h][i] >> 16));
+        }
       }
     }
   }
@@ -142,8 +167,10 @@ struct GroupedArgs {
   const int32_t* segment_offsets;
   const int32_t* num_segments_dev;
   const int32_t* row_gather;
+  int32_t* status;
   int32_t num_segments;
   int32_t num_rows;
+  int32_t hidden_interleaved;
 };
 
 enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };
@@ -155,6 +182,8 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
   extern __shared__ uint4 smem_raw[];
   auto& sm = *reinterpret_cast<TileSmem<NPROJ, NT>*>(smem_raw);
 
+  init_barriers(sm.mbar);
+  pdl_wait();  // route arrays and activations come from earlier kernels of the stream
   const int seg = blockIdx.y;
   const int nseg = args.num_segments_dev ? min(*args.num_segments_dev, args.num_segments) : args.num_segments;
   if (seg >= nseg) return;
@@ -170,9 +199,10 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
   const int out_local = (NPROJ == 2) ? (warp & 3) * 16 : warp * 16;
   const int pr = proj_packed_rows(args.proj[0]);
   const int num_chunks = (pr + KC - 1) / KC;
-  const bool any_gr = args.proj[0].use_block_gr != 0;
+  const bool interleaved = args.hidden_interleaved != 0;
 
   int staged_chunk = -1;
+  uint32_t par_w = 0u, par_h = 0u;
   for (int r0 = row_begin; r0 < row_end; r0 += NT * 8) {
     const int rows = min(NT * 8, row_end - r0);
     const int nt_count = (rows + 7) >> 3;
@@ -184,17 +214,25 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
 
     for (int kc = 0; kc < num_chunks; ++kc) {
       const int p0 = kc * KC;
-      __syncthreads();  // previous consumers of the tables are done
-      if (staged_chunk != kc) {
-        if (any_gr) stage_gmap_block_gr<NPROJ, NT>(sm, args.proj, e, o0, p0);
-        stage_planes_and_scales<NPROJ, NT>(sm, args.proj, e, o0, p0, nullptr);
-        staged_chunk = kc;
-      }
-      stage_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, nt_count, [&](int n) {
-        if (n >= rows) return -1;
+      __syncthreads();  // previous consumers of the staging buffers are done
+      const bool need_w = staged_chunk != kc;
+      if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, o0, p0);
+      stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, [&](int n) {
         return args.row_gather ? args.row_gather[r0 + n] : (r0 + n);
       });
       __syncthreads();
+      bool ok = true;
+      if (need_w) {
+        ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, e, o0, p0, par_w, nullptr);
+        par_w ^= 1u;
+        staged_chunk = kc;
+      }
+      ok = mbar_wait_bounded(&sm.mbar[2], par_h) && ok;
+      par_h ^= 1u;
+      if (__syncthreads_or(!ok)) {
+        leave_after_timeout(sm, par_w ^ 1u, par_h ^ 1u, args.status);
+        return;
+      }
 
       for (int p = 0; p < KC && p0 + p < pr; ++p) {
         uint32_t a[2][4];
@@ -202,7 +240,7 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           if (nt < nt_count) {
-            const uint4 hv = sm.htab[(((proj * NT + nt) * KC + p) * 8 + g) * 4 + t];
+            const uint4 hv = load_b_fragments<NPROJ, NT>(sm, proj, nt * 8 + g, p, t);
             mma_m16n8k16(acc[nt], a[0][0], a[1][0], a[0][1], a[1][1], hv.x, hv.y);
             mma_m16n8k16(acc[nt], a[0][2], a[1][2], a[0][3], a[1][3], hv.z, hv.w);
           }
@@ -229,7 +267,7 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
     if (EPI == EPI_SILU_MUL) {
       // up warps (proj 1) hand their tile to the gate warps (proj 0) through shared memory
       __syncthreads();
-      float* xbuf = reinterpret_cast<float*>(sm.htab);
+      float* xbuf = reinterpret_cast<float*>(sm.hrows);
       if (proj == 1) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -264,6 +302,7 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
       }
     }
   }
+  pdl_launch_dependents();
 }
 
 // ---- host launchers -----------------------------------------------------------------------
@@ -330,7 +369,19 @@ static int fill_route(GroupedArgs& a, const TrisRouteView* route) {
   a.row_gather = route->row_gather;
   a.num_segments = route->num_segments;
   a.num_rows = route->num_rows;
+  a.status = route->status_dev;
+  a.hidden_interleaved = (route->flags & TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED) != 0;
   return TRIS_OK;
+}
+
+// Rows per activation tile: sized for the typical segment (mean + 4 sigma of a balanced
+// router), never above the caller's bound; longer segments take several passes.
+static int rows_hint(const TrisRouteView* route) {
+  const int bound = route->max_rows_per_segment > 0 ? route->max_rows_per_segment : route->num_rows;
+  if (route->num_segments <= 0) return bound;
+  const double mean = static_cast<double>(route->num_rows) / route->num_segments;
+  const int typical = static_cast<int>(mean + 4.0 * sqrt(mean) + 1.0);
+  return std::max(1, std::min(bound, typical));
 }
 
 }  // namespace tris
@@ -381,9 +432,9 @@ extern "C" int tris_block_gr_decode(const TrisProjView* proj, int32_t* dense_out
   const int pr = (proj->rank + 31) / 32;
   dim3 grid(ceil_div(proj->out_features, 128), ceil_div(pr, KC), proj->num_experts);
   const size_t smem = sizeof(TileSmem<1, 1>);
-  TRIS_CUDA(cudaFuncSetAttribute(block_gr_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  block_gr_decode_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(*proj, dense_out);
-  return check_cuda(cudaGetLastError(), "block_gr_decode_kernel launch");
+  TRIS_CUDA(cudaFuncSetAttribute(compact3_dump_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  compact3_dump_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(*proj, dense_out, nullptr, nullptr);
+  return check_cuda(cudaGetLastError(), "compact3_dump_kernel launch");
 }
 
 extern "C" int tris_compact3_dequantize(const TrisProjView* proj, void* weights_out_f16, void* stream) {
@@ -393,10 +444,10 @@ extern "C" int tris_compact3_dequantize(const TrisProjView* proj, void* weights_
   const int pr = (proj->rank + 31) / 32;
   dim3 grid(ceil_div(proj->out_features, 128), ceil_div(pr, KC), proj->num_experts);
   const size_t smem = sizeof(TileSmem<1, 1>);
-  TRIS_CUDA(cudaFuncSetAttribute(compact3_dequant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  compact3_dequant_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      *proj, static_cast<__half*>(weights_out_f16));
-  return check_cuda(cudaGetLastError(), "compact3_dequant_kernel launch");
+  TRIS_CUDA(cudaFuncSetAttribute(compact3_dump_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  compact3_dump_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      *proj, nullptr, static_cast<__half*>(weights_out_f16), nullptr);
+  return check_cuda(cudaGetLastError(), "compact3_dump_kernel launch");
 }
 
 extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
@@ -408,11 +459,13 @@ extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteVie
   st = fill_route(a, route);
   if (st != TRIS_OK) return st;
   if (a.num_segments == 0 || a.num_rows == 0) return TRIS_OK;
+  TRIS_REQUIRE(!a.hidden_interleaved || proj->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
+               "tris_grouped_forward: pair-interleaved activations need rank % 32 == 0");
   a.proj[0] = *proj;
   a.proj[1] = *proj;
   a.hidden[0] = a.hidden[1] = static_cast<const __half*>(hidden_f16);
   a.out[0] = a.out[1] = static_cast<__half*>(out_f16);
-  const int max_rows = route->max_rows_per_segment > 0 ? route->max_rows_per_segment : route->num_rows;
+  const int max_rows = rows_hint(route);
   return dispatch_grouped<1, EPI_STORE>(a, max_rows, static_cast<cudaStream_t>(stream));
 }
 
@@ -425,8 +478,8 @@ extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisP
   st = validate_proj(proj_b, "tris_grouped_pair_forward(b)", true);
   if (st != TRIS_OK) return st;
   TRIS_REQUIRE(proj_a->num_experts == proj_b->num_experts && proj_a->out_features == proj_b->out_features &&
-                   proj_a->rank == proj_b->rank,
-               TRIS_ERR_UNSUPPORTED, "tris_grouped_pair_forward: the two projections must share E, O and r");
+                   proj_a->rank == proj_b->rank && proj_a->num_groups == proj_b->num_groups,
+               TRIS_ERR_UNSUPPORTED, "tris_grouped_pair_forward: the two projections must share E, O, r and G");
   TRIS_REQUIRE((proj_a->use_block_gr != 0) == (proj_b->use_block_gr != 0) &&
                    (!proj_a->use_block_gr || proj_a->gr_substreams == proj_b->gr_substreams),
                TRIS_ERR_UNSUPPORTED, "tris_grouped_pair_forward: the two projections must share the g_map format");
@@ -436,13 +489,15 @@ extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisP
   st = fill_route(a, route);
   if (st != TRIS_OK) return st;
   if (a.num_segments == 0 || a.num_rows == 0) return TRIS_OK;
+  TRIS_REQUIRE(!a.hidden_interleaved || proj_a->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
+               "tris_grouped_pair_forward: pair-interleaved activations need rank % 32 == 0");
   a.proj[0] = *proj_a;
   a.proj[1] = *proj_b;
   a.hidden[0] = static_cast<const __half*>(hidden_a_f16);
   a.hidden[1] = static_cast<const __half*>(hidden_b_f16);
   a.out[0] = static_cast<__half*>(out_a_f16);
   a.out[1] = static_cast<__half*>(out_b_f16);
-  const int max_rows = route->max_rows_per_segment > 0 ? route->max_rows_per_segment : route->num_rows;
+  const int max_rows = rows_hint(route);
   if (fuse_silu_mul) return dispatch_grouped<2, EPI_SILU_MUL>(a, max_rows, static_cast<cudaStream_t>(stream));
   return dispatch_grouped<2, EPI_STORE>(a, max_rows, static_cast<cudaStream_t>(stream));
 }

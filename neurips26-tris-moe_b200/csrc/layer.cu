@@ -50,7 +50,7 @@ static LayerWorkspace carve(const TrisMoeLayerView* L, int T, char* base) {
   w.expert_ids = reinterpret_cast<int32_t*>(take(4 * E));
   w.segment_offsets = reinterpret_cast<int32_t*>(take(4 * (E + 1)));
   w.problem_offsets = reinterpret_cast<int32_t*>(take(4 * (E + 1)));
-  w.counts = reinterpret_cast<int32_t*>(take(8));
+  w.counts = reinterpret_cast<int32_t*>(take(16));  // {segments, problem tiles, status, -}
   w.hidden_gate = reinterpret_cast<__half*>(take(2 * static_cast<size_t>(T) * L->gate.rank));
   w.hidden_up = reinterpret_cast<__half*>(take(2 * static_cast<size_t>(T) * L->up.rank));
   w.mlp = reinterpret_cast<__half*>(take(2 * R * L->intermediate_size));
@@ -106,12 +106,14 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
   // 1. backbones (+ router logits) share one pass over x
   SkinnyProblem probs[3];
   int np = 0;
-  probs[np++] = {static_cast<const __half*>(layer->shared_gate), w.hidden_gate, layer->gate.rank, 0};
-  probs[np++] = {static_cast<const __half*>(layer->shared_up), w.hidden_up, layer->up.rank, 0};
+  const int gu_mode = (layer->gate.rank % 32 == 0) ? TRIS_OUT_F16_PAIR_INTERLEAVED : TRIS_OUT_F16;
+  const int down_mode = (layer->down.rank % 32 == 0) ? TRIS_OUT_F16_PAIR_INTERLEAVED : TRIS_OUT_F16;
+  probs[np++] = {static_cast<const __half*>(layer->shared_gate), w.hidden_gate, layer->gate.rank, gu_mode};
+  probs[np++] = {static_cast<const __half*>(layer->shared_up), w.hidden_up, layer->up.rank, gu_mode};
   const float* logits = router_logits;
   if (logits == nullptr) {
     float* dst = router_logits_out ? router_logits_out : w.logits;
-    probs[np++] = {static_cast<const __half*>(layer->router_weight), dst, layer->num_experts, 1};
+    probs[np++] = {static_cast<const __half*>(layer->router_weight), dst, layer->num_experts, TRIS_OUT_F32};
     logits = dst;
   } else if (router_logits_out && router_logits_out != router_logits) {
     TRIS_CUDA(cudaMemcpyAsync(router_logits_out, router_logits, sizeof(float) * T * layer->num_experts,
@@ -137,16 +139,19 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
 
   // 3. gate/up + SiLU*mul; rows read the per-token backbone outputs through tok[]
   route.row_gather = w.tok;
+  route.status_dev = w.counts + 2;
+  route.flags = (gu_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED : 0;
   st = tris_grouped_pair_forward(&layer->gate, &layer->up, &route, w.hidden_gate, w.hidden_up, w.mlp, nullptr, 1, s);
   if (st != TRIS_OK) return st;
 
   // 4. down backbone on routed rows
-  SkinnyProblem down{static_cast<const __half*>(layer->shared_down), w.hidden_down, layer->down.rank, 0};
+  SkinnyProblem down{static_cast<const __half*>(layer->shared_down), w.hidden_down, layer->down.rank, down_mode};
   st = launch_shared_hidden(&down, 1, w.mlp, nullptr, R, layer->intermediate_size, s);
   if (st != TRIS_OK) return st;
 
   // 5. grouped down
   route.row_gather = nullptr;
+  route.flags = (down_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED : 0;
   st = tris_grouped_forward(&layer->down, &route, w.hidden_down, w.down_out, s);
   if (st != TRIS_OK) return st;
 

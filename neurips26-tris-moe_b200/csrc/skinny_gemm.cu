@@ -107,8 +107,14 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const __gri
       const int n = n0 + nt * 8 + 2 * (ln & 3) + (c & 1);
       const int m = m0 + (ln >> 2) + 8 * (c >> 1);
       if (n < args.n && m < pb.m) {
-        if (pb.out_is_f32) static_cast<float*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = v;
-        else static_cast<__half*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = __float2half_rn(v);
+        if (pb.out_mode == TRIS_OUT_F32) {
+          static_cast<float*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = v;
+        } else {
+          // pair-interleaved: column j of a 32-column group goes to 2*(j%16) + j/16
+          const int mm = (pb.out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED)
+                             ? ((m & ~31) | ((m & 15) << 1) | ((m >> 4) & 1)) : m;
+          static_cast<__half*>(pb.out)[static_cast<size_t>(n) * pb.m + mm] = __float2half_rn(v);
+        }
       }
     }
   }
@@ -172,10 +178,14 @@ using namespace tris;
 
 extern "C" int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_gather, int32_t num_rows,
                                           int32_t in_features, const void* shared_sv_f16, int32_t rank,
-                                          void* out, int32_t out_is_f32, void* stream) {
+                                          void* out, int32_t out_mode, void* stream) {
   TRIS_REQUIRE(x_f16 && shared_sv_f16 && out, TRIS_ERR_INVALID_ARG, "tris_shared_hidden_forward: null pointer");
   TRIS_REQUIRE(rank > 0, TRIS_ERR_INVALID_ARG, "tris_shared_hidden_forward: rank=%d", rank);
-  SkinnyProblem pb{static_cast<const __half*>(shared_sv_f16), out, rank, out_is_f32};
+  TRIS_REQUIRE(out_mode >= TRIS_OUT_F16 && out_mode <= TRIS_OUT_F16_PAIR_INTERLEAVED, TRIS_ERR_INVALID_ARG,
+               "tris_shared_hidden_forward: unknown out_mode %d", out_mode);
+  TRIS_REQUIRE(out_mode != TRIS_OUT_F16_PAIR_INTERLEAVED || rank % 32 == 0, TRIS_ERR_INVALID_ARG,
+               "tris_shared_hidden_forward: the pair-interleaved layout needs rank % 32 == 0");
+  SkinnyProblem pb{static_cast<const __half*>(shared_sv_f16), out, rank, out_mode};
   return launch_shared_hidden(&pb, 1, static_cast<const __half*>(x_f16), row_gather, num_rows, in_features,
                               static_cast<cudaStream_t>(stream));
 }

@@ -295,6 +295,8 @@ def _route_view(route: dict, num_rows: int, keep: list) -> TrisRouteView:
     rv.num_rows = int(num_rows)
     rv.max_rows_per_segment = int(route.get("_max_rows_per_segment", 0) or 0)
     rv.row_gather = None
+    rv.status_dev = None
+    rv.flags = 0
     return rv
 
 

@@ -137,6 +137,35 @@ def test_dequant_synth_block_gr_and_sparse_formats(tm, small_layer):
         _assert_half_bits_equal(tm.dequantize_grouped_payload(p2).cpu().numpy(), ref)
 
 
+def _grouped_reference(weights, hidden, route):
+    return _grouped_reference_impl(weights, hidden, route)
+
+
+def test_odd_shapes_take_the_unaligned_copy_path(tm):
+    """Outputs not a multiple of 4 and rank not a multiple of 8: every staged row is
+    misaligned for TMA, so the plain-load fallback of each copy is what runs."""
+    from trismoe_b200 import synth
+
+    shape = synth.LayerShape(70, 90, 3, 2, rank=44, group_size=32)
+    layer = synth.synth_layer(shape, seed=9, keep_sparse_gmap=True)
+    rng = np.random.default_rng(4)
+    for name, O in (("gate", 90), ("down", 70)):
+        npp = to_numpy_payload(layer[name])
+        ref = np.stack([orc.dequantize_expert(npp, e) for e in range(3)])
+        for fmt in ("block_gr", "sparse"):
+            src = dict(layer[name])
+            src["compact3_use_block_gr"] = fmt == "block_gr"
+            p = _cuda_payload(tm, src)
+            if fmt == "block_gr":
+                assert np.array_equal(tm.decode_block_gr_gmap(p).cpu().numpy(), layer[name]["_dense_gmap_words"].numpy())
+            _assert_half_bits_equal(tm.dequantize_grouped_payload(p).cpu().numpy(), ref)
+            h = rng.standard_normal((7, 44)).astype(np.float16)
+            out = tm.run_grouped_structured_expert_forward(p, torch.from_numpy(h).cuda(), None, [3, 0, 4])
+            want = _grouped_reference(list(ref), h, {"expert_ids": np.array([0, 2]), "segment_offsets": np.array([0, 3, 7])})
+            max_abs, mean_rel = orc.error_metrics(out.float().cpu().numpy(), want)
+            assert max_abs <= MAX_ABS and mean_rel <= MEAN_REL, (max_abs, mean_rel)
+
+
 # ---------------------------------------------------------------------------------------
 # (3) backbone, (4) route, (5) router
 # ---------------------------------------------------------------------------------------
@@ -196,7 +225,7 @@ def test_router_topk_matches_oracle(tm, T, E, k, norm):
 # ---------------------------------------------------------------------------------------
 # (6) grouped operators against the fp32 oracle
 # ---------------------------------------------------------------------------------------
-def _grouped_reference(weights, hidden, route):
+def _grouped_reference_impl(weights, hidden, route):
     out = np.zeros((hidden.shape[0], weights[0].shape[0]), dtype=np.float32)
     seg = route["segment_offsets"]
     for s, e in enumerate(route["expert_ids"]):
