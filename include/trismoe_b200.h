@@ -51,7 +51,7 @@ enum {
 #define TRIS_GR_META_ONE_COUNT_SHIFT 8
 #define TRIS_GR_MAX_K 7
 /* Sub-streams per block recorded by tris_block_gr_build_index (power of two, <= 32). */
-#define TRIS_GR_DEFAULT_SUBSTREAMS 16
+#define TRIS_GR_DEFAULT_SUBSTREAMS 32
 
 /*
  * One E-stacked compact3 projection, i.e. the dict returned by

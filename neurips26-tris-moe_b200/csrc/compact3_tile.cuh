@@ -32,6 +32,10 @@
 #pragma once
 #include "common.cuh"
 
+#ifndef TRIS_SUBMARK
+#define TRIS_SUBMARK(k) do { } while (0)
+#endif
+
 namespace tris {
 
 constexpr int kThreads = 256;
@@ -108,63 +112,41 @@ __device__ __forceinline__ uint32_t gr_peek32(const uint32_t* w, int nwords, int
   return __funnelshift_r(lo, hi, bitpos & 31);
 }
 
-// Decodes `n_ones` codewords starting at (bitpos, flatpos).  Bits that fall into the same
-// 32-bit output word are gathered in a register and handed to flush(word_index, mask).
-template <typename Flush>
+// Window of 32 stream bits at `bitpos`, no bounds checks: callers keep bitpos below the
+// end of the block's words and the staging buffer has slack behind every span.
+__device__ __forceinline__ uint32_t gr_peek32_unchecked(const uint32_t* w, int bitpos) {
+  const int wi = bitpos >> 5;
+  return __funnelshift_r(w[wi], w[wi + 1], bitpos & 31);
+}
+
+// Decodes `n_ones` codewords starting at (bitpos, flatpos) and calls set(flat) for each
+// one.  The common case (terminating one and remainder inside one 32-bit window) is
+// straight-line code; zero runs of 32 or more and remainders that straddle the window take
+// the rare branches.
+template <typename SetBit>
 __device__ __forceinline__ void gr_decode_run(const uint32_t* w, int nwords, int k, int n_ones, int bitpos,
-                                              int flatpos, Flush flush) {
+                                              int flatpos, SetBit set) {
   const int total_bits = nwords << 5;
   const uint32_t kmask = (1u << k) - 1u;
-  uint32_t v = gr_peek32(w, nwords, bitpos);
-  int avail = 32;
-  int cur_word = -1;
-  uint32_t cur_mask = 0u;
   for (int n = 0; n < n_ones; ++n) {
+    if (bitpos >= total_bits) return;  // stream ran out: malformed, stop
+    uint32_t v = gr_peek32_unchecked(w, bitpos);
     int q = 0;
-    int t = __ffs(v) - 1;
-    if (v == 0u || t + 1 + k > avail) {
-      // refill at the current position; long zero runs advance 32 bits at a time
-      v = gr_peek32(w, nwords, bitpos);
-      avail = 32;
-      while (v == 0u) {
-        q += 32;
-        bitpos += 32;
-        if (bitpos >= total_bits) { n = n_ones; break; }  // stream ran out: malformed, stop
-        v = gr_peek32(w, nwords, bitpos);
-      }
-      if (v == 0u) break;
-      t = __ffs(v) - 1;
-      if (t + 1 + k > 32) {  // remainder straddles the window: re-anchor it after the one
-        bitpos += t + 1;
-        q += t;
-        v = gr_peek32(w, nwords, bitpos);
-        const uint32_t rem = v & kmask;
-        v = (k == 32) ? 0u : (v >> k);
-        avail = 32 - k;
-        bitpos += k;
-        flatpos += (q << k) | static_cast<int>(rem);
-        goto emit;
-      }
+    while (v == 0u) {
+      q += 32;
+      bitpos += 32;
+      if (bitpos >= total_bits) return;
+      v = gr_peek32_unchecked(w, bitpos);
     }
-    {
-      const int used = t + 1 + k;
-      const uint32_t rem = (t == 31) ? 0u : ((v >> (t + 1)) & kmask);
-      v = (used >= 32) ? 0u : (v >> used);
-      avail -= used;
-      bitpos += used;
-      flatpos += ((q + t) << k) | static_cast<int>(rem);
-    }
-  emit:
-    if (flatpos >= TRIS_GR_BLOCK_WORDS * 32) break;
-    if ((flatpos >> 5) != cur_word) {
-      if (cur_mask) flush(cur_word, cur_mask);
-      cur_word = flatpos >> 5;
-      cur_mask = 0u;
-    }
-    cur_mask |= 1u << (flatpos & 31);
+    const int t = __ffs(v) - 1;
+    uint32_t rem = ((v >> t) >> 1) & kmask;
+    if (t + 1 + k > 32) rem = gr_peek32_unchecked(w, bitpos + t + 1) & kmask;
+    bitpos += t + 1 + k;
+    flatpos += ((q + t) << k) + static_cast<int>(rem);
+    if (flatpos >= TRIS_GR_BLOCK_WORDS * 32) return;
+    set(flatpos);
     ++flatpos;
   }
-  if (cur_mask) flush(cur_word, cur_mask);
 }
 
 // Word index inside the chunk planes of flat word `wl` (0..127) of chunk-local block b.
@@ -487,9 +469,9 @@ template <int NPROJ, int NT>
 __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
                                                      int o0, int p0, uint32_t parity, uint32_t* gmap_dump) {
   constexpr int OW = Geom<NPROJ>::OW;
-  constexpr int NOB = Geom<NPROJ>::NOB;
   const int tid = threadIdx.x;
   bool ok = mbar_wait_bounded(&sm.mbar[0], parity);
+  TRIS_SUBMARK(6);
 
   // column table: pairs (4t+i, 4t+i+16); scales a column does not use are zeroed so that
   // one fused multiply-add serves salient and non-salient halves alike
@@ -536,6 +518,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
   }
 
   ok = mbar_wait_bounded(&sm.mbar[1], parity) && ok;
+  TRIS_SUBMARK(7);
   const bool gr = views[0].use_block_gr != 0;
   if (gr) {
     // zero the blocks (raw blocks are copied verbatim)
@@ -560,10 +543,10 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
       if (per == 0 || first >= one_count) continue;
       const int n_ones = min(per, one_count - first);
       const uint32_t packed = sm.gridx[b * 32 + j];
-      uint32_t* gbase = sm.g;
+      uint32_t* gblock = sm.g + block_word_to_tile<NPROJ>(b, 0);  // word wl of the block sits at (wl>>6)*OW + (wl&63)
       gr_decode_run(sm.gmraw + sm.binfo[b * 4 + 0], count, k, n_ones, static_cast<int>(packed & 0xFFFFu),
-                    static_cast<int>(packed >> 16), [&](int word, uint32_t mask) {
-                      atomicOr(gbase + block_word_to_tile<NPROJ>(b, word), mask);
+                    static_cast<int>(packed >> 16), [&](int flat) {
+                      atomicOr(gblock + ((flat >> 11) * OW) + ((flat >> 5) & 63), 1u << (flat & 31));
                     });
     }
     __syncthreads();

@@ -10,6 +10,19 @@
 
 #include <algorithm>
 
+// Development builds (-DTRIS_PHASE_TIMERS) stamp clock64() at phase boundaries of every CTA.
+#ifdef TRIS_PHASE_TIMERS
+namespace tris { __device__ long long* g_phase_stamps = nullptr; }
+#define TRIS_MARK(k)                                                                                          \
+  do {                                                                                                        \
+    if (threadIdx.x == 0 && ::tris::g_phase_stamps)                                                           \
+      ::tris::g_phase_stamps[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (k)] = clock64(); \
+  } while (0)
+#define TRIS_SUBMARK(k) TRIS_MARK(k)
+#else
+#define TRIS_MARK(k) do { } while (0)
+#endif
+
 #include "compact3_tile.cuh"
 
 namespace tris {
@@ -177,11 +190,12 @@ enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };
 
 // grid (ceil(O/OW), num_segments bound)
 template <int NPROJ, int NT, int EPI>
-__global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid_constant__ GroupedArgs args) {
+__global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_kernel(const __grid_constant__ GroupedArgs args) {
   constexpr int OW = Geom<NPROJ>::OW;
   extern __shared__ uint4 smem_raw[];
   auto& sm = *reinterpret_cast<TileSmem<NPROJ, NT>*>(smem_raw);
 
+  TRIS_MARK(0);
   init_barriers(sm.mbar);
   pdl_wait();  // route arrays and activations come from earlier kernels of the stream
   const int seg = blockIdx.y;
@@ -221,18 +235,21 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
         return args.row_gather ? args.row_gather[r0 + n] : (r0 + n);
       });
       __syncthreads();
+      TRIS_MARK(1);
       bool ok = true;
       if (need_w) {
         ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, e, o0, p0, par_w, nullptr);
         par_w ^= 1u;
         staged_chunk = kc;
       }
+      TRIS_MARK(2);
       ok = mbar_wait_bounded(&sm.mbar[2], par_h) && ok;
       par_h ^= 1u;
       if (__syncthreads_or(!ok)) {
         leave_after_timeout(sm, par_w ^ 1u, par_h ^ 1u, args.status);
         return;
       }
+      TRIS_MARK(3);
 
       for (int p = 0; p < KC && p0 + p < pr; ++p) {
         uint32_t a[2][4];
@@ -248,6 +265,7 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
       }
     }
 
+    TRIS_MARK(4);
     // epilogue: acc[nt] = {(out g, row 2t), (out g, row 2t+1), (out g+8, row 2t), (out g+8, row 2t+1)}
     const TrisProjView& v = args.proj[proj];
     float scale[2] = {1.f, 1.f}, bias[2] = {0.f, 0.f};
@@ -271,13 +289,15 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
       if (proj == 1) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
-          *reinterpret_cast<float4*>(xbuf + (((warp & 3) * NT + nt) * 32 + lane) * 4) =
-              make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+          if (nt < nt_count)
+            *reinterpret_cast<float4*>(xbuf + (((warp & 3) * NT + nt) * 32 + lane) * 4) =
+                make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
       }
       __syncthreads();
       if (proj == 0) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
+          if (nt >= nt_count) break;
           const float4 u = *reinterpret_cast<const float4*>(xbuf + (((warp & 3) * NT + nt) * 32 + lane) * 4);
           const float uu[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -292,6 +312,7 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
       __half* outp = args.out[proj];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
+        if (nt >= nt_count) break;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int n = nt * 8 + 2 * t + (c & 1);
@@ -302,6 +323,7 @@ __global__ void __launch_bounds__(kThreads) grouped_compact3_kernel(const __grid
       }
     }
   }
+  TRIS_MARK(5);
   pdl_launch_dependents();
 }
 
@@ -380,7 +402,7 @@ static int rows_hint(const TrisRouteView* route) {
   const int bound = route->max_rows_per_segment > 0 ? route->max_rows_per_segment : route->num_rows;
   if (route->num_segments <= 0) return bound;
   const double mean = static_cast<double>(route->num_rows) / route->num_segments;
-  const int typical = static_cast<int>(mean + 4.0 * sqrt(mean) + 1.0);
+  const int typical = static_cast<int>(mean + 4.0 * sqrt(mean));
   return std::max(1, std::min(bound, typical));
 }
 
@@ -501,3 +523,9 @@ extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisP
   if (fuse_silu_mul) return dispatch_grouped<2, EPI_SILU_MUL>(a, max_rows, static_cast<cudaStream_t>(stream));
   return dispatch_grouped<2, EPI_STORE>(a, max_rows, static_cast<cudaStream_t>(stream));
 }
+
+#ifdef TRIS_PHASE_TIMERS
+extern "C" int tris_debug_set_phase_stamps(long long* stamps) {
+  return check_cuda(cudaMemcpyToSymbol(tris::g_phase_stamps, &stamps, sizeof(stamps)), "set phase stamps");
+}
+#endif

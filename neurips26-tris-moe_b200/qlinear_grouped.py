@@ -26,7 +26,7 @@ from .formats import stack_expert_payloads
 
 TRIS_COMPACT3_KERNEL_ABI_VERSION = 2
 GROUPED_SEGMENT_M_TILE = 4
-DEFAULT_GR_SUBSTREAMS = 16
+DEFAULT_GR_SUBSTREAMS = 32
 
 
 def _stream_ptr(device) -> int:
