@@ -38,7 +38,54 @@ struct SkinnyProblem {
   int32_t out_mode;
 };
 int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather,
-                         int n, int k, cudaStream_t stream);
+                         int n, int k, cudaStream_t stream, bool pdl = false);
+
+// Launch with optional programmatic dependent launch (the kernel may start while its
+// predecessor in the stream drains; it must execute griddepcontrol.wait before touching
+// anything the predecessor writes) and an optional cluster size along z.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool pdl, int cluster_z, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = cluster_z;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Options of the launches the fused layer path makes.
+struct LaunchOpts {
+  bool pdl = false;                  // programmatic dependent launch
+  bool weights_before_wait = false;  // the route was complete before the predecessor kernel started
+};
+int grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16, void* out_f16,
+                         cudaStream_t stream, LaunchOpts opts);
+int grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjView* proj_b, const TrisRouteView* route,
+                              const void* hidden_a_f16, const void* hidden_b_f16, void* out_a_f16, void* out_b_f16,
+                              int fuse_silu_mul, cudaStream_t stream, LaunchOpts opts);
+int combine_routed_impl(const void* down_out_f16, const int32_t* row_of_flat, const float* routing_weights,
+                        int num_tokens, int top_k, int hidden_size, void* final_f16, cudaStream_t stream, bool pdl);
+int launch_router_route(const float* logits, int num_tokens, int num_experts, int top_k, int norm, int m_tile,
+                        int32_t* selected, float* weights, int32_t* perm, int32_t* tok, int32_t* slot,
+                        int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets, int32_t* problem_offsets,
+                        int32_t* counts, cudaStream_t stream);
 
 // ---- device helpers -------------------------------------------------------------------
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {

@@ -471,7 +471,6 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
   constexpr int OW = Geom<NPROJ>::OW;
   const int tid = threadIdx.x;
   bool ok = mbar_wait_bounded(&sm.mbar[0], parity);
-  TRIS_SUBMARK(6);
 
   // column table: pairs (4t+i, 4t+i+16); scales a column does not use are zeroed so that
   // one fused multiply-add serves salient and non-salient halves alike
@@ -550,6 +549,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
                     });
     }
     __syncthreads();
+    TRIS_SUBMARK(6);
   }
 
   // select plane: for a non-salient column the g_map bit (1 -> "d" scale pair, CU:736-737);
@@ -584,58 +584,78 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
 }
 
 // ---- register unpack ------------------------------------------------------------------
-// Weights of packed row p for the lane's two outputs (h = 0: out g, h = 1: out g+8) and
-// four column pairs (4t+i, 4t+i+16) as half2 bit patterns a[h][i].
-// Exact arithmetic of _dequantize_compact3_matrix (QL:4200-4236): each product rounded to
-// fp16 once, salient weight = fp16(+-p1 +- p2).
+// Row scale pairs of one output for the current group, broadcast to both halves.
+struct RowScales {
+  __half2 r1, r2, rd, rn;  // row_pack3 halves: (s_r1, s_r2, ns_d_r1, ns_nd_r1)
+};
+__device__ __forceinline__ RowScales broadcast_row_scales(uint2 rp) {
+  RowScales r;
+  r.r1 = u32_as_h2(prmt(rp.x, 0u, 0x1010u));
+  r.r2 = u32_as_h2(prmt(rp.x, 0u, 0x3232u));
+  r.rd = u32_as_h2(prmt(rp.y, 0u, 0x1010u));
+  r.rn = u32_as_h2(prmt(rp.y, 0u, 0x3232u));
+  return r;
+}
+
+// Weights of one packed row for one output and the lane's four column pairs (4t+i, 4t+i+16)
+// as half2 bit patterns.  Exact arithmetic of _dequantize_compact3_matrix (QL:4200-4236):
+// each product rounded to fp16 once, salient weight = fp16(+-p1 +- p2).  `any_salient` is
+// warp-uniform (a property of the packed row), so the branch does not diverge.
+__device__ __forceinline__ void unpack_row(uint32_t s1, uint32_t se, const RowScales& rs, const uint4 (&ct)[4],
+                                           bool any_salient, int t, uint32_t (&a)[4]) {
+  const uint32_t st = s1 << (12 - 4 * t);  // column 4t+i at bit 12+i, column 4t+i+16 at bit 28+i
+  const uint32_t gt = se << (12 - 4 * t);
+  __half2 ca[4], cb[4];
+  if (any_salient) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 p1 = __hmul2_rn(u32_as_h2(ct[i].z), rs.r1);
+      const __half2 p2 = __hmul2_rn(u32_as_h2(ct[i].w), rs.r2);
+      // the non-salient half has p1 = p2 = 0, the salient half has cd = cnd = 0
+      ca[i] = __hfma2(u32_as_h2(ct[i].x), rs.rd, __hadd2_rn(p1, p2));
+      cb[i] = __hfma2(u32_as_h2(ct[i].y), rs.rn, __hsub2_rn(p1, p2));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      ca[i] = __hmul2_rn(u32_as_h2(ct[i].x), rs.rd);
+      cb[i] = __hmul2_rn(u32_as_h2(ct[i].y), rs.rn);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // select mask: replicate bits 15 and 31 over their halves
+    const uint32_t m = prmt(gt << (3 - i), 0u, 0xBB99u);
+    const uint32_t mag = (h2_as_u32(ca[i]) & m) | (h2_as_u32(cb[i]) & ~m);
+    // sign: plane bit 1 -> +, 0 -> -   (QL:4213)
+    a[i] = mag ^ (~(st << (3 - i)) & 0x80008000u);
+  }
+}
+
+// Fragments of packed row p for the lane's two outputs (h = 0: out g, h = 1: out g+8).
+// `rs` caches the row scales of the group slot `rs_slot` across packed rows.
 template <int NPROJ, int NT>
 __device__ __forceinline__ void unpack_fragments(const TileSmem<NPROJ, NT>& sm, int proj, int p, int out_local,
-                                                 int lane, uint32_t (&a)[2][4]) {
+                                                 int lane, RowScales (&rs)[2], int& rs_slot, uint32_t (&a)[2][4]) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int g = lane >> 2, t = lane & 3;
   const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
-  const uint32_t cwv = info.cw;
-  const int rs = sm.row_stride;
+  if (info.gslot != rs_slot) {  // warp-uniform; groups span several packed rows
+    rs_slot = info.gslot;
+    const int stride = sm.row_stride;
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      rs[h] = broadcast_row_scales(sm.rowtab[(proj * OW + out_local + g + 8 * h) * stride + rs_slot]);
+  }
   uint4 ct[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) ct[i] = sm.coltab[((proj * KC + p) * 4 + i) * 4 + t];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int o = out_local + g + 8 * h;
-    const int idx = (proj * KC + p) * OW + o;
-    const uint32_t s1 = sm.s1[idx];
-    const uint32_t se = sm.g[idx];
-    const uint2 rp = sm.rowtab[(proj * OW + o) * rs + info.gslot];
-    // row_pack3 halves: (s_r1, s_r2, ns_d_r1, ns_nd_r1)
-    const __half2 r1 = u32_as_h2(prmt(rp.x, 0u, 0x1010u));
-    const __half2 r2 = u32_as_h2(prmt(rp.x, 0u, 0x3232u));
-    const __half2 rd = u32_as_h2(prmt(rp.y, 0u, 0x1010u));
-    const __half2 rn = u32_as_h2(prmt(rp.y, 0u, 0x3232u));
-    const uint32_t st = s1 << (12 - 4 * t);  // column 4t+i at bit 12+i, column 4t+i+16 at bit 28+i
-    const uint32_t gt = se << (12 - 4 * t);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __half2 ca, cb;
-      const uint32_t pairmask = 0x11111111u << i;  // columns of pair i over all four t
-      if (cwv & pairmask) {
-        const __half2 p1 = __hmul2_rn(u32_as_h2(ct[i].z), r1);
-        const __half2 p2 = __hmul2_rn(u32_as_h2(ct[i].w), r2);
-        const __half2 ssum = __hadd2_rn(p1, p2);
-        const __half2 sdif = __hsub2_rn(p1, p2);
-        // the non-salient half has p1 = p2 = 0, the salient half has cd = cnd = 0
-        ca = __hfma2(u32_as_h2(ct[i].x), rd, ssum);
-        cb = __hfma2(u32_as_h2(ct[i].y), rn, sdif);
-      } else {
-        ca = __hmul2_rn(u32_as_h2(ct[i].x), rd);
-        cb = __hmul2_rn(u32_as_h2(ct[i].y), rn);
-      }
-      // select mask: replicate bits 15 and 31 over their halves
-      const uint32_t m = prmt(gt << (3 - i), 0u, 0xBB99u);
-      const uint32_t mag = (h2_as_u32(ca) & m) | (h2_as_u32(cb) & ~m);
-      // sign: plane bit 1 -> +, 0 -> -   (QL:4213)
-      a[h][i] = mag ^ (~(st << (3 - i)) & 0x80008000u);
-    }
-  }
+  const int idx = (proj * KC + p) * OW + out_local + g;
+  const uint32_t s1a = sm.s1[idx], s1b = sm.s1[idx + 8];
+  const uint32_t sea = sm.g[idx], seb = sm.g[idx + 8];
+  const bool any_salient = info.cw != 0u;
+  unpack_row(s1a, sea, rs[0], ct, any_salient, t, a[0]);
+  unpack_row(s1b, seb, rs[1], ct, any_salient, t, a[1]);
 }
 
 // B fragments of packed row p, local activation row `n`: 8 halves in pair order.

@@ -152,9 +152,11 @@ __global__ void __launch_bounds__(kThreads) compact3_dump_kernel(TrisProjView v,
   if (weights_out) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    RowScales rs[2];
+    int rs_slot = -1;
     for (int p = 0; p < KC && p0 + p < pr; ++p) {
       uint32_t a[2][4];
-      unpack_fragments<1, 1>(sm, 0, p, warp * 16, lane, a);
+      unpack_fragments<1, 1>(sm, 0, p, warp * 16, lane, rs, rs_slot, a);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int og = o0 + warp * 16 + g + 8 * h;
@@ -184,6 +186,7 @@ struct GroupedArgs {
   int32_t num_segments;
   int32_t num_rows;
   int32_t hidden_interleaved;
+  int32_t weights_before_wait;  // route arrays were final before the predecessor kernel started
 };
 
 enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };
@@ -197,7 +200,14 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
 
   TRIS_MARK(0);
   init_barriers(sm.mbar);
-  pdl_wait();  // route arrays and activations come from earlier kernels of the stream
+  // Activations come from the predecessor kernel; the route arrays too, unless the caller
+  // says they are older, in which case the weight staging below overlaps the predecessor.
+  bool waited = false;
+  if (!args.weights_before_wait) {
+    pdl_wait();
+    pdl_launch_dependents();
+    waited = true;
+  }
   const int seg = blockIdx.y;
   const int nseg = args.num_segments_dev ? min(*args.num_segments_dev, args.num_segments) : args.num_segments;
   if (seg >= nseg) return;
@@ -230,10 +240,9 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       const int p0 = kc * KC;
       __syncthreads();  // previous consumers of the staging buffers are done
       const bool need_w = staged_chunk != kc;
+      auto row_src = [&](int n) { return args.row_gather ? args.row_gather[r0 + n] : (r0 + n); };
       if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, o0, p0);
-      stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, [&](int n) {
-        return args.row_gather ? args.row_gather[r0 + n] : (r0 + n);
-      });
+      if (waited) stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, row_src);
       __syncthreads();
       TRIS_MARK(1);
       bool ok = true;
@@ -241,6 +250,13 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
         ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, e, o0, p0, par_w, nullptr);
         par_w ^= 1u;
         staged_chunk = kc;
+      }
+      if (!waited) {  // first pass of a CTA that staged its weights ahead of the predecessor's end
+        pdl_wait();
+        pdl_launch_dependents();
+        waited = true;
+        stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, row_src);
+        __syncthreads();
       }
       TRIS_MARK(2);
       ok = mbar_wait_bounded(&sm.mbar[2], par_h) && ok;
@@ -251,9 +267,13 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       }
       TRIS_MARK(3);
 
-      for (int p = 0; p < KC && p0 + p < pr; ++p) {
+      RowScales rs[2];
+      int rs_slot = -1;
+      const int p_end = min(KC, pr - p0);
+#pragma unroll 2
+      for (int p = 0; p < p_end; ++p) {
         uint32_t a[2][4];
-        unpack_fragments<NPROJ, NT>(sm, proj, p, out_local, lane, a);
+        unpack_fragments<NPROJ, NT>(sm, proj, p, out_local, lane, rs, rs_slot, a);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           if (nt < nt_count) {
@@ -324,7 +344,6 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
     }
   }
   TRIS_MARK(5);
-  pdl_launch_dependents();
 }
 
 // ---- host launchers -----------------------------------------------------------------------
@@ -358,7 +377,7 @@ static int validate_proj(const TrisProjView* v, const char* name, bool need_runt
 }
 
 template <int NPROJ, int NT, int EPI>
-static int launch_grouped(const GroupedArgs& args, cudaStream_t stream) {
+static int launch_grouped(const GroupedArgs& args, cudaStream_t stream, bool pdl) {
   const size_t smem = sizeof(TileSmem<NPROJ, NT>);
   auto kernel = grouped_compact3_kernel<NPROJ, NT, EPI>;
   static bool configured[64] = {};  // per instantiation, per device
@@ -369,16 +388,16 @@ static int launch_grouped(const GroupedArgs& args, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid(ceil_div(args.proj[0].out_features, Geom<NPROJ>::OW), args.num_segments);
-  kernel<<<grid, kThreads, smem, stream>>>(args);
-  return check_cuda(cudaGetLastError(), "grouped_compact3_kernel launch");
+  return check_cuda(launch_kernel(kernel, grid, dim3(kThreads), smem, stream, pdl, 1, args),
+                    "grouped_compact3_kernel launch");
 }
 
 template <int NPROJ, int EPI>
-static int dispatch_grouped(const GroupedArgs& args, int max_rows, cudaStream_t stream) {
-  if (max_rows <= 8) return launch_grouped<NPROJ, 1, EPI>(args, stream);
-  if (max_rows <= 16) return launch_grouped<NPROJ, 2, EPI>(args, stream);
-  if (max_rows <= 32) return launch_grouped<NPROJ, 4, EPI>(args, stream);
-  return launch_grouped<NPROJ, 8, EPI>(args, stream);
+static int dispatch_grouped(const GroupedArgs& args, int max_rows, cudaStream_t stream, bool pdl) {
+  if (max_rows <= 8) return launch_grouped<NPROJ, 1, EPI>(args, stream, pdl);
+  if (max_rows <= 16) return launch_grouped<NPROJ, 2, EPI>(args, stream, pdl);
+  if (max_rows <= 32) return launch_grouped<NPROJ, 4, EPI>(args, stream, pdl);
+  return launch_grouped<NPROJ, 8, EPI>(args, stream, pdl);
 }
 
 static int fill_route(GroupedArgs& a, const TrisRouteView* route) {
@@ -472,8 +491,8 @@ extern "C" int tris_compact3_dequantize(const TrisProjView* proj, void* weights_
   return check_cuda(cudaGetLastError(), "compact3_dump_kernel launch");
 }
 
-extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
-                                    void* out_f16, void* stream) {
+int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
+                               void* out_f16, cudaStream_t stream, LaunchOpts opts) {
   int st = validate_proj(proj, "tris_grouped_forward", true);
   if (st != TRIS_OK) return st;
   TRIS_REQUIRE(hidden_f16 && out_f16, TRIS_ERR_INVALID_ARG, "tris_grouped_forward: null hidden/out");
@@ -487,14 +506,19 @@ extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteVie
   a.proj[1] = *proj;
   a.hidden[0] = a.hidden[1] = static_cast<const __half*>(hidden_f16);
   a.out[0] = a.out[1] = static_cast<__half*>(out_f16);
-  const int max_rows = rows_hint(route);
-  return dispatch_grouped<1, EPI_STORE>(a, max_rows, static_cast<cudaStream_t>(stream));
+  a.weights_before_wait = opts.pdl && opts.weights_before_wait;
+  return dispatch_grouped<1, EPI_STORE>(a, rows_hint(route), stream, opts.pdl);
 }
 
-extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisProjView* proj_b,
-                                         const TrisRouteView* route, const void* hidden_a_f16,
-                                         const void* hidden_b_f16, void* out_a_f16, void* out_b_f16,
-                                         int32_t fuse_silu_mul, void* stream) {
+extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
+                                    void* out_f16, void* stream) {
+  return grouped_forward_impl(proj, route, hidden_f16, out_f16, static_cast<cudaStream_t>(stream), LaunchOpts{});
+}
+
+int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjView* proj_b,
+                                    const TrisRouteView* route, const void* hidden_a_f16, const void* hidden_b_f16,
+                                    void* out_a_f16, void* out_b_f16, int fuse_silu_mul, cudaStream_t stream,
+                                    LaunchOpts opts) {
   int st = validate_proj(proj_a, "tris_grouped_pair_forward(a)", true);
   if (st != TRIS_OK) return st;
   st = validate_proj(proj_b, "tris_grouped_pair_forward(b)", true);
@@ -519,9 +543,18 @@ extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisP
   a.hidden[1] = static_cast<const __half*>(hidden_b_f16);
   a.out[0] = static_cast<__half*>(out_a_f16);
   a.out[1] = static_cast<__half*>(out_b_f16);
+  a.weights_before_wait = opts.pdl && opts.weights_before_wait;
   const int max_rows = rows_hint(route);
-  if (fuse_silu_mul) return dispatch_grouped<2, EPI_SILU_MUL>(a, max_rows, static_cast<cudaStream_t>(stream));
-  return dispatch_grouped<2, EPI_STORE>(a, max_rows, static_cast<cudaStream_t>(stream));
+  if (fuse_silu_mul) return dispatch_grouped<2, EPI_SILU_MUL>(a, max_rows, stream, opts.pdl);
+  return dispatch_grouped<2, EPI_STORE>(a, max_rows, stream, opts.pdl);
+}
+
+extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisProjView* proj_b,
+                                         const TrisRouteView* route, const void* hidden_a_f16,
+                                         const void* hidden_b_f16, void* out_a_f16, void* out_b_f16,
+                                         int32_t fuse_silu_mul, void* stream) {
+  return grouped_pair_forward_impl(proj_a, proj_b, route, hidden_a_f16, hidden_b_f16, out_a_f16, out_b_f16,
+                                   fuse_silu_mul, static_cast<cudaStream_t>(stream), LaunchOpts{});
 }
 
 #ifdef TRIS_PHASE_TIMERS

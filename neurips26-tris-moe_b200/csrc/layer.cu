@@ -103,31 +103,41 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
   const int R = T * layer->top_k;
   const __half* x = static_cast<const __half*>(x_f16);
 
-  // 1. backbones (+ router logits) share one pass over x
-  SkinnyProblem probs[3];
-  int np = 0;
+  // Launch order.  With logits given, router + route run first, so that the grouped
+  // gate/up kernel can stage its weights while the backbone GEMM is still running
+  // (programmatic dependent launch); otherwise the logits come out of the backbone GEMM.
   const int gu_mode = (layer->gate.rank % 32 == 0) ? TRIS_OUT_F16_PAIR_INTERLEAVED : TRIS_OUT_F16;
   const int down_mode = (layer->down.rank % 32 == 0) ? TRIS_OUT_F16_PAIR_INTERLEAVED : TRIS_OUT_F16;
+  SkinnyProblem probs[3];
+  int np = 0;
   probs[np++] = {static_cast<const __half*>(layer->shared_gate), w.hidden_gate, layer->gate.rank, gu_mode};
   probs[np++] = {static_cast<const __half*>(layer->shared_up), w.hidden_up, layer->up.rank, gu_mode};
+  const bool logits_given = router_logits != nullptr;
   const float* logits = router_logits;
-  if (logits == nullptr) {
+  if (logits_given) {
+    if (router_logits_out && router_logits_out != router_logits)
+      TRIS_CUDA(cudaMemcpyAsync(router_logits_out, router_logits, sizeof(float) * T * layer->num_experts,
+                                cudaMemcpyDeviceToDevice, s));
+  } else {
     float* dst = router_logits_out ? router_logits_out : w.logits;
     probs[np++] = {static_cast<const __half*>(layer->router_weight), dst, layer->num_experts, TRIS_OUT_F32};
     logits = dst;
-  } else if (router_logits_out && router_logits_out != router_logits) {
-    TRIS_CUDA(cudaMemcpyAsync(router_logits_out, router_logits, sizeof(float) * T * layer->num_experts,
-                              cudaMemcpyDeviceToDevice, s));
   }
-  st = launch_shared_hidden(probs, np, x, nullptr, T, layer->hidden_size, s);
+  auto route_launch = [&]() {
+    return launch_router_route(logits, T, layer->num_experts, layer->top_k, layer->norm_topk_prob, 4, w.selected,
+                               w.weights, w.perm, w.tok, w.slot, w.row_of_flat, w.expert_ids, w.segment_offsets,
+                               w.problem_offsets, w.counts, s);
+  };
+  if (logits_given) {
+    st = route_launch();
+    if (st != TRIS_OK) return st;
+  }
+  st = launch_shared_hidden(probs, np, x, nullptr, T, layer->hidden_size, s, /*pdl=*/logits_given);
   if (st != TRIS_OK) return st;
-
-  // 2. router + route
-  st = tris_router_topk(logits, T, layer->num_experts, layer->top_k, layer->norm_topk_prob, w.selected, w.weights, s);
-  if (st != TRIS_OK) return st;
-  st = tris_build_grouped_route(w.selected, T, layer->top_k, layer->num_experts, 4, w.perm, w.tok, w.slot,
-                                w.row_of_flat, w.expert_ids, w.segment_offsets, w.problem_offsets, w.counts, s);
-  if (st != TRIS_OK) return st;
+  if (!logits_given) {
+    st = route_launch();
+    if (st != TRIS_OK) return st;
+  }
 
   TrisRouteView route{};
   route.expert_ids = w.expert_ids;
@@ -136,25 +146,29 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
   route.num_segments = std::min(layer->num_experts, R);
   route.num_rows = R;
   route.max_rows_per_segment = T;  // top-k experts of a token are distinct
-
-  // 3. gate/up + SiLU*mul; rows read the per-token backbone outputs through tok[]
-  route.row_gather = w.tok;
   route.status_dev = w.counts + 2;
+
+  // gate/up + SiLU*mul; rows read the per-token backbone outputs through tok[]
+  route.row_gather = w.tok;
   route.flags = (gu_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED : 0;
-  st = tris_grouped_pair_forward(&layer->gate, &layer->up, &route, w.hidden_gate, w.hidden_up, w.mlp, nullptr, 1, s);
+  LaunchOpts opts;
+  opts.pdl = true;
+  opts.weights_before_wait = logits_given;
+  st = grouped_pair_forward_impl(&layer->gate, &layer->up, &route, w.hidden_gate, w.hidden_up, w.mlp, nullptr, 1, s, opts);
   if (st != TRIS_OK) return st;
 
-  // 4. down backbone on routed rows
+  // down backbone on routed rows
   SkinnyProblem down{static_cast<const __half*>(layer->shared_down), w.hidden_down, layer->down.rank, down_mode};
-  st = launch_shared_hidden(&down, 1, w.mlp, nullptr, R, layer->intermediate_size, s);
+  st = launch_shared_hidden(&down, 1, w.mlp, nullptr, R, layer->intermediate_size, s, /*pdl=*/true);
   if (st != TRIS_OK) return st;
 
-  // 5. grouped down
+  // grouped down: the route is older than the GEMM before it, so weights stage early
   route.row_gather = nullptr;
   route.flags = (down_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED : 0;
-  st = tris_grouped_forward(&layer->down, &route, w.hidden_down, w.down_out, s);
+  opts.weights_before_wait = true;
+  st = grouped_forward_impl(&layer->down, &route, w.hidden_down, w.down_out, s, opts);
   if (st != TRIS_OK) return st;
 
-  // 6. combine
-  return tris_combine_routed(w.down_out, w.row_of_flat, w.weights, T, layer->top_k, layer->hidden_size, y_f16, s);
+  // combine
+  return combine_routed_impl(w.down_out, w.row_of_flat, w.weights, T, layer->top_k, layer->hidden_size, y_f16, s, true);
 }

@@ -9,14 +9,9 @@ namespace tris {
 constexpr int kRouteThreads = 1024;
 constexpr int kMaxExpertsPerLane = 8;  // experts <= 256
 
-// One warp per token.  Ties go to the lower expert index.
-__global__ void router_topk_kernel(const float* __restrict__ logits, int num_tokens, int num_experts, int top_k,
-                                   int norm, int32_t* __restrict__ selected, float* __restrict__ weights) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= num_tokens) return;
-  pdl_wait();
-  const float* row = logits + static_cast<size_t>(warp) * num_experts;
+// Softmax + top-k of one token by one warp.  Ties go to the lower expert index.
+__device__ __forceinline__ void topk_one_token(const float* __restrict__ row, int num_experts, int top_k, int norm,
+                                               int32_t* __restrict__ selected, float* __restrict__ weights, int lane) {
   float v[kMaxExpertsPerLane];
   float mx = -INFINITY;
 #pragma unroll
@@ -59,23 +54,32 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int num_tok
     if (lane == s) { my_w = p; my_e = best_e; }
   }
   if (lane < top_k) {
-    selected[static_cast<size_t>(warp) * top_k + lane] = my_e;
-    weights[static_cast<size_t>(warp) * top_k + lane] = norm ? my_w / picked_sum : my_w;
+    selected[lane] = my_e;
+    weights[lane] = norm ? my_w / picked_sum : my_w;
   }
 }
 
+// One warp per token.
+__global__ void router_topk_kernel(const float* __restrict__ logits, int num_tokens, int num_experts, int top_k,
+                                   int norm, int32_t* __restrict__ selected, float* __restrict__ weights) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= num_tokens) return;
+  pdl_wait();
+  topk_one_token(logits + static_cast<size_t>(warp) * num_experts, num_experts, top_k, norm,
+                 selected + static_cast<size_t>(warp) * top_k, weights + static_cast<size_t>(warp) * top_k, lane);
+}
+
 // Single CTA.  Counting sort of the flat (token, slot) list by expert, stable in flat order.
-__global__ void __launch_bounds__(kRouteThreads) build_route_kernel(
-    const int32_t* __restrict__ selected, int num_tokens, int top_k, int num_experts, int m_tile,
+__device__ __forceinline__ void build_route_body(
+    int32_t* sh, const int32_t* selected, int num_tokens, int top_k, int num_experts, int m_tile,
     int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
     int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
     int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
-  extern __shared__ int32_t sh[];
   int32_t* count = sh;                 // [E]
   int32_t* start = sh + num_experts;   // [E] first grouped row of each expert
   const int R = num_tokens * top_k;
   const int tid = threadIdx.x;
-  pdl_wait();
   for (int e = tid; e < num_experts; e += kRouteThreads) count[e] = 0;
   __syncthreads();
   for (int f = tid; f < R; f += kRouteThreads) {
@@ -126,6 +130,35 @@ __global__ void __launch_bounds__(kRouteThreads) build_route_kernel(
   }
 }
 
+__global__ void __launch_bounds__(kRouteThreads) build_route_kernel(
+    const int32_t* __restrict__ selected, int num_tokens, int top_k, int num_experts, int m_tile,
+    int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
+    int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
+    int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
+  extern __shared__ int32_t sh[];
+  pdl_wait();
+  build_route_body(sh, selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat, expert_ids,
+                   segment_offsets, problem_offsets, counts_out);
+}
+
+// Router head and route in one single-CTA launch (decode-sized batches).
+__global__ void __launch_bounds__(kRouteThreads) router_route_kernel(
+    const float* __restrict__ logits, int num_tokens, int top_k, int num_experts, int norm, int m_tile,
+    int32_t* selected, float* __restrict__ weights, int32_t* __restrict__ perm, int32_t* __restrict__ tok,
+    int32_t* __restrict__ slot, int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids,
+    int32_t* __restrict__ segment_offsets, int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
+  extern __shared__ int32_t sh[];
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int tk = warp; tk < num_tokens; tk += kRouteThreads / 32)
+    topk_one_token(logits + static_cast<size_t>(tk) * num_experts, num_experts, top_k, norm,
+                   selected + static_cast<size_t>(tk) * top_k, weights + static_cast<size_t>(tk) * top_k, lane);
+  __syncthreads();  // selected[] written above is read back by every thread below
+  pdl_launch_dependents();
+  build_route_body(sh, selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat, expert_ids,
+                   segment_offsets, problem_offsets, counts_out);
+}
+
 // final[t, :] = sum_s w[t, s] * rows[row_of_flat[t*k+s], :]; one thread per 8 output halves.
 __global__ void combine_routed_kernel(const __half* __restrict__ rows, const int32_t* __restrict__ row_of_flat,
                                       const float* __restrict__ weights, int num_tokens, int top_k, int hidden,
@@ -155,6 +188,19 @@ __global__ void combine_routed_kernel(const __half* __restrict__ rows, const int
 #pragma unroll
   for (int u = 0; u < 4; ++u) oh[u] = __floats2half2_rn(acc[2 * u], acc[2 * u + 1]);
   *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden + c) = o;
+}
+
+// Router + route in one launch; used by the fused layer path.
+int launch_router_route(const float* logits, int num_tokens, int num_experts, int top_k, int norm, int m_tile,
+                        int32_t* selected, float* weights, int32_t* perm, int32_t* tok, int32_t* slot,
+                        int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets, int32_t* problem_offsets,
+                        int32_t* counts, cudaStream_t stream) {
+  TRIS_REQUIRE(num_experts <= 32 * kMaxExpertsPerLane && top_k <= 32 && top_k <= num_experts, TRIS_ERR_UNSUPPORTED,
+               "router: supports up to %d experts and top-32", 32 * kMaxExpertsPerLane);
+  router_route_kernel<<<1, kRouteThreads, 2 * num_experts * sizeof(int32_t), stream>>>(
+      logits, num_tokens, top_k, num_experts, norm, m_tile, selected, weights, perm, tok, slot, row_of_flat, expert_ids,
+      segment_offsets, problem_offsets, counts);
+  return check_cuda(cudaGetLastError(), "router_route_kernel launch");
 }
 
 }  // namespace tris
@@ -193,17 +239,25 @@ extern "C" int tris_build_grouped_route(const int32_t* selected_experts, int32_t
   return check_cuda(cudaGetLastError(), "build_route_kernel launch");
 }
 
-extern "C" int tris_combine_routed(const void* down_out_f16, const int32_t* row_of_flat, const float* routing_weights,
-                                   int32_t num_tokens, int32_t top_k, int32_t hidden_size, void* final_f16,
-                                   void* stream) {
+int tris::combine_routed_impl(const void* down_out_f16, const int32_t* row_of_flat, const float* routing_weights,
+                              int num_tokens, int top_k, int hidden_size, void* final_f16, cudaStream_t stream,
+                              bool pdl) {
   TRIS_REQUIRE(down_out_f16 && row_of_flat && routing_weights && final_f16, TRIS_ERR_INVALID_ARG, "tris_combine_routed: null pointer");
   TRIS_REQUIRE(num_tokens >= 0 && top_k > 0 && hidden_size > 0, TRIS_ERR_INVALID_ARG, "tris_combine_routed: bad sizes");
   TRIS_REQUIRE((hidden_size & 7) == 0, TRIS_ERR_UNSUPPORTED, "tris_combine_routed: hidden_size must be a multiple of 8");
   if (num_tokens == 0) return TRIS_OK;
   const long long total = static_cast<long long>(num_tokens) * (hidden_size / 8);
   const int threads = 256;
-  combine_routed_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(down_out_f16), row_of_flat, routing_weights, num_tokens, top_k, hidden_size,
-      static_cast<__half*>(final_f16));
-  return check_cuda(cudaGetLastError(), "combine_routed_kernel launch");
+  return check_cuda(launch_kernel(combine_routed_kernel, dim3(static_cast<unsigned>((total + threads - 1) / threads)),
+                                  dim3(threads), 0, stream, pdl, 1, static_cast<const __half*>(down_out_f16),
+                                  row_of_flat, routing_weights, num_tokens, top_k, hidden_size,
+                                  static_cast<__half*>(final_f16)),
+                    "combine_routed_kernel launch");
+}
+
+extern "C" int tris_combine_routed(const void* down_out_f16, const int32_t* row_of_flat, const float* routing_weights,
+                                   int32_t num_tokens, int32_t top_k, int32_t hidden_size, void* final_f16,
+                                   void* stream) {
+  return combine_routed_impl(down_out_f16, row_of_flat, routing_weights, num_tokens, top_k, hidden_size, final_f16,
+                             static_cast<cudaStream_t>(stream), false);
 }

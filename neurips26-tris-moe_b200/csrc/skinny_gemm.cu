@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const __gri
   const __half* arow_a = pb.a + static_cast<size_t>(min(ma, pb.m - 1)) * K;
   const __half* arow_b = pb.a + static_cast<size_t>(min(mb, pb.m - 1)) * K;
   pdl_wait();  // x and row_gather may come from the preceding kernel
+  pdl_launch_dependents();  // the next kernel may stage its weights while this one runs
   const __half* xrow[NT];
   bool xvalid[NT];
 #pragma unroll
@@ -86,7 +87,6 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const __gri
       mma_m16n8k16(acc[nt], va.z, vb.z, va.w, vb.w, xv[nt].z, xv[nt].w);
     }
   }
-  pdl_launch_dependents();
 
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -122,25 +122,15 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const __gri
 }
 
 template <int NT>
-static int launch_skinny(const SkinnyArgs& args, int mtiles, int ksplit, cudaStream_t stream) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(mtiles, ceil_div(args.n, NT * 8), ksplit);
-  cfg.blockDim = dim3(kSkinnyThreads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = ksplit;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT>, args), "skinny_gemm_kernel launch");
+static int launch_skinny(const SkinnyArgs& args, int mtiles, int ksplit, cudaStream_t stream, bool pdl) {
+  return check_cuda(launch_kernel(skinny_gemm_kernel<NT>, dim3(mtiles, ceil_div(args.n, NT * 8), ksplit),
+                                  dim3(kSkinnyThreads), 0, stream, pdl, ksplit, args),
+                    "skinny_gemm_kernel launch");
 }
 
 // Launches up to kMaxProblems matrices that share x.
 int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather,
-                         int n, int k, cudaStream_t stream) {
+                         int n, int k, cudaStream_t stream, bool pdl) {
   TRIS_REQUIRE(num_problems >= 1 && num_problems <= kMaxProblems, TRIS_ERR_INVALID_ARG, "shared hidden: bad problem count");
   TRIS_REQUIRE(n >= 0 && k > 0, TRIS_ERR_INVALID_ARG, "shared hidden: bad sizes n=%d k=%d", n, k);
   TRIS_REQUIRE((k & 7) == 0, TRIS_ERR_UNSUPPORTED, "shared hidden: in_features=%d must be a multiple of 8", k);
@@ -165,10 +155,10 @@ int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __h
   while (ksplit < 8 && mtiles * row_chunks * ksplit < 296 && k / (ksplit * 2) >= 128) ksplit *= 2;
   args.k_per_cta = ceil_div(ceil_div(k, ksplit), 32) * 32;
   switch (nt) {
-    case 1: return launch_skinny<1>(args, mtiles, ksplit, stream);
-    case 2: return launch_skinny<2>(args, mtiles, ksplit, stream);
-    case 4: return launch_skinny<4>(args, mtiles, ksplit, stream);
-    default: return launch_skinny<8>(args, mtiles, ksplit, stream);
+    case 1: return launch_skinny<1>(args, mtiles, ksplit, stream, pdl);
+    case 2: return launch_skinny<2>(args, mtiles, ksplit, stream, pdl);
+    case 4: return launch_skinny<4>(args, mtiles, ksplit, stream, pdl);
+    default: return launch_skinny<8>(args, mtiles, ksplit, stream, pdl);
   }
 }
 
