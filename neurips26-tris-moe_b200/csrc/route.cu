@@ -70,63 +70,109 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int num_tok
                  selected + static_cast<size_t>(warp) * top_k, weights + static_cast<size_t>(warp) * top_k, lane);
 }
 
-// Single CTA.  Counting sort of the flat (token, slot) list by expert, stable in flat order.
+// Single CTA.  Stable counting sort of the flat (token, slot) list by expert: every warp owns
+// a contiguous chunk of the list, counts its experts, a scan over (expert, warp) turns the
+// counts into write offsets, and a second pass places the elements in order.
+// `sh` holds (34 * E) ints: count[E], start[E], per-warp counts/offsets [32][E].
 __device__ __forceinline__ void build_route_body(
     int32_t* sh, const int32_t* selected, int num_tokens, int top_k, int num_experts, int m_tile,
     int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
     int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
     int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
-  int32_t* count = sh;                 // [E]
-  int32_t* start = sh + num_experts;   // [E] first grouped row of each expert
+  constexpr int NW = kRouteThreads / 32;
+  int32_t* count = sh;                      // [E]
+  int32_t* start = sh + num_experts;        // [E] first grouped row of each expert
+  int32_t* woff = sh + 2 * num_experts;     // [NW][E]
   const int R = num_tokens * top_k;
   const int tid = threadIdx.x;
-  for (int e = tid; e < num_experts; e += kRouteThreads) count[e] = 0;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int chunk = ((R + NW - 1) / NW + 31) & ~31;  // elements per warp, whole 32-element batches
+  const int f0 = warp * chunk, f1 = min(R, f0 + chunk);
+  for (int i = tid; i < NW * num_experts; i += kRouteThreads) woff[i] = 0;
   __syncthreads();
-  for (int f = tid; f < R; f += kRouteThreads) {
-    const int e = selected[f];
-    if (e >= 0 && e < num_experts) atomicAdd(&count[e], 1);
+  for (int base = f0; base < f1; base += 32) {
+    const int f = base + lane;
+    int e = (f < f1) ? selected[f] : -1;
+    if (e >= num_experts) e = -1;
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+    if (e >= 0 && lane == __ffs(peers) - 1) woff[warp * num_experts + e] += __popc(peers);
+    __syncwarp();
   }
   __syncthreads();
-  if (tid == 0) {
-    int rows = 0, tiles = 0, nseg = 0;
-    for (int e = 0; e < num_experts; ++e) {
-      start[e] = rows;
+  for (int e = tid; e < num_experts; e += kRouteThreads) {
+    int total = 0;
+    for (int w = 0; w < NW; ++w) total += woff[w * num_experts + e];
+    count[e] = total;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // each lane owns a contiguous run of experts; warp scan of (segments, rows, tiles)
+    const int epl = (num_experts + 31) / 32;
+    const int e0 = lane * epl, e1 = min(num_experts, e0 + epl);
+    int segs = 0, rows = 0, tiles = 0;
+    for (int e = e0; e < e1; ++e) {
+      const int c = count[e];
+      if (c > 0) { ++segs; rows += c; tiles += (c + m_tile - 1) / m_tile; }
+    }
+    int psegs = segs, prows = rows, ptiles = tiles;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xFFFFFFFFu, psegs, o);
+      const int b = __shfl_up_sync(0xFFFFFFFFu, prows, o);
+      const int c = __shfl_up_sync(0xFFFFFFFFu, ptiles, o);
+      if (lane >= o) { psegs += a; prows += b; ptiles += c; }
+    }
+    const int nseg = __shfl_sync(0xFFFFFFFFu, psegs, 31);
+    const int nrows = __shfl_sync(0xFFFFFFFFu, prows, 31);
+    const int ntiles = __shfl_sync(0xFFFFFFFFu, ptiles, 31);
+    int s = psegs - segs, r = prows - rows, t = ptiles - tiles;  // exclusive prefixes
+    for (int e = e0; e < e1; ++e) {
+      start[e] = r;
       const int c = count[e];
       if (c > 0) {
-        expert_ids[nseg] = e;
-        segment_offsets[nseg] = rows;
-        problem_offsets[nseg] = tiles;
-        rows += c;
-        tiles += (c + m_tile - 1) / m_tile;
-        ++nseg;
+        expert_ids[s] = e;
+        segment_offsets[s] = r;
+        problem_offsets[s] = t;
+        r += c;
+        t += (c + m_tile - 1) / m_tile;
+        ++s;
       }
     }
-    for (int s = nseg; s <= num_experts; ++s) {
-      segment_offsets[s] = rows;
-      problem_offsets[s] = tiles;
-      if (s < num_experts) expert_ids[s] = -1;
+    for (int q = nseg + lane; q <= num_experts; q += 32) {
+      segment_offsets[q] = nrows;
+      problem_offsets[q] = ntiles;
+      if (q < num_experts) expert_ids[q] = -1;
     }
-    counts_out[0] = nseg;
-    counts_out[1] = tiles;
+    if (lane == 0) {
+      counts_out[0] = nseg;
+      counts_out[1] = ntiles;
+    }
   }
   __syncthreads();
-  const int warp = tid >> 5, lane = tid & 31;
-  for (int e = warp; e < num_experts; e += kRouteThreads / 32) {
-    if (count[e] == 0) continue;
-    int running = start[e];
-    for (int base = 0; base < R; base += 32) {
-      const int f = base + lane;
-      const bool hit = f < R && selected[f] == e;
-      const unsigned bal = __ballot_sync(0xFFFFFFFFu, hit);
-      if (hit) {
-        const int pos = running + __popc(bal & ((1u << lane) - 1u));
-        perm[pos] = f;
-        tok[pos] = f / top_k;
-        slot[pos] = f - (f / top_k) * top_k;
-        row_of_flat[f] = pos;
-      }
-      running += __popc(bal);
+  for (int e = tid; e < num_experts; e += kRouteThreads) {  // counts -> write offsets per warp
+    int run = start[e];
+    for (int w = 0; w < NW; ++w) {
+      const int c = woff[w * num_experts + e];
+      woff[w * num_experts + e] = run;
+      run += c;
     }
+  }
+  __syncthreads();
+  for (int base = f0; base < f1; base += 32) {
+    const int f = base + lane;
+    int e = (f < f1) ? selected[f] : -1;
+    if (e >= num_experts) e = -1;
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+    if (e >= 0) {
+      const int pos = woff[warp * num_experts + e] + __popc(peers & ((1u << lane) - 1u));
+      perm[pos] = f;
+      const int tk = f / top_k;
+      tok[pos] = tk;
+      slot[pos] = f - tk * top_k;
+      row_of_flat[f] = pos;
+    }
+    __syncwarp();
+    if (e >= 0 && lane == __ffs(peers) - 1) woff[warp * num_experts + e] += __popc(peers);
+    __syncwarp();
   }
 }
 
@@ -134,9 +180,10 @@ __global__ void __launch_bounds__(kRouteThreads) build_route_kernel(
     const int32_t* __restrict__ selected, int num_tokens, int top_k, int num_experts, int m_tile,
     int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
     int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
-    int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
+    int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out, int sel_cap) {
   extern __shared__ int32_t sh[];
   pdl_wait();
+  pdl_launch_dependents();
   build_route_body(sh, selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat, expert_ids,
                    segment_offsets, problem_offsets, counts_out);
 }
@@ -146,7 +193,8 @@ __global__ void __launch_bounds__(kRouteThreads) router_route_kernel(
     const float* __restrict__ logits, int num_tokens, int top_k, int num_experts, int norm, int m_tile,
     int32_t* selected, float* __restrict__ weights, int32_t* __restrict__ perm, int32_t* __restrict__ tok,
     int32_t* __restrict__ slot, int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids,
-    int32_t* __restrict__ segment_offsets, int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
+    int32_t* __restrict__ segment_offsets, int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out,
+    int sel_cap) {
   extern __shared__ int32_t sh[];
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -155,8 +203,8 @@ __global__ void __launch_bounds__(kRouteThreads) router_route_kernel(
                    selected + static_cast<size_t>(tk) * top_k, weights + static_cast<size_t>(tk) * top_k, lane);
   __syncthreads();  // selected[] written above is read back by every thread below
   pdl_launch_dependents();
-  build_route_body(sh, selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat, expert_ids,
-                   segment_offsets, problem_offsets, counts_out);
+  build_route_body(sh, selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat,
+                   expert_ids, segment_offsets, problem_offsets, counts_out);
 }
 
 // final[t, :] = sum_s w[t, s] * rows[row_of_flat[t*k+s], :]; one thread per 8 output halves.
@@ -171,16 +219,29 @@ __global__ void combine_routed_kernel(const __half* __restrict__ rows, const int
   float acc[8];
 #pragma unroll
   for (int u = 0; u < 8; ++u) acc[u] = 0.f;
-  for (int s = 0; s < top_k; ++s) {
-    const int r = row_of_flat[t * top_k + s];
-    const float w = weights[t * top_k + s];
-    const uint4 v = *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(r) * hidden + c);
-    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+  for (int s0 = 0; s0 < top_k; s0 += 8) {  // indices, then rows, 8 at a time: loads of a batch are independent
+    int r[8];
+    float w[8];
+    uint4 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float2 f = __half22float2(h2[u]);
-      acc[2 * u] += w * f.x;
-      acc[2 * u + 1] += w * f.y;
+    for (int j = 0; j < 8; ++j) {
+      const bool in = s0 + j < top_k;
+      r[j] = in ? row_of_flat[t * top_k + s0 + j] : 0;
+      w[j] = in ? weights[t * top_k + s0 + j] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      v[j] = (s0 + j < top_k) ? *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(r[j]) * hidden + c)
+                              : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 f = __half22float2(h2[u]);
+        acc[2 * u] += w[j] * f.x;
+        acc[2 * u + 1] += w[j] * f.y;
+      }
     }
   }
   uint4 o;
@@ -190,17 +251,38 @@ __global__ void combine_routed_kernel(const __half* __restrict__ rows, const int
   *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden + c) = o;
 }
 
-// Router + route in one launch; used by the fused layer path.
+static int route_smem_bytes(int num_experts, int rows, int* sel_cap) {
+  (void)rows;
+  *sel_cap = 0;
+  return static_cast<int>((2 + kRouteThreads / 32) * num_experts * sizeof(int32_t));
+}
+
+// Router head + route for the fused layer path: one single-CTA launch for batches of up to
+// 32 tokens (one warp per token), otherwise a token-parallel top-k launch followed by the
+// single-CTA route kernel.
 int launch_router_route(const float* logits, int num_tokens, int num_experts, int top_k, int norm, int m_tile,
                         int32_t* selected, float* weights, int32_t* perm, int32_t* tok, int32_t* slot,
                         int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets, int32_t* problem_offsets,
                         int32_t* counts, cudaStream_t stream) {
   TRIS_REQUIRE(num_experts <= 32 * kMaxExpertsPerLane && top_k <= 32 && top_k <= num_experts, TRIS_ERR_UNSUPPORTED,
                "router: supports up to %d experts and top-32", 32 * kMaxExpertsPerLane);
-  router_route_kernel<<<1, kRouteThreads, 2 * num_experts * sizeof(int32_t), stream>>>(
-      logits, num_tokens, top_k, num_experts, norm, m_tile, selected, weights, perm, tok, slot, row_of_flat, expert_ids,
-      segment_offsets, problem_offsets, counts);
-  return check_cuda(cudaGetLastError(), "router_route_kernel launch");
+  int sel_cap = 0;
+  const int smem = route_smem_bytes(num_experts, num_tokens * top_k, &sel_cap);
+  if (num_tokens <= kRouteThreads / 32) {
+    router_route_kernel<<<1, kRouteThreads, smem, stream>>>(logits, num_tokens, top_k, num_experts, norm, m_tile,
+                                                            selected, weights, perm, tok, slot, row_of_flat,
+                                                            expert_ids, segment_offsets, problem_offsets, counts, sel_cap);
+    return check_cuda(cudaGetLastError(), "router_route_kernel launch");
+  }
+  const int threads = 128;
+  router_topk_kernel<<<ceil_div(num_tokens * 32, threads), threads, 0, stream>>>(logits, num_tokens, num_experts, top_k,
+                                                                                 norm, selected, weights);
+  int st = check_cuda(cudaGetLastError(), "router_topk_kernel launch");
+  if (st != TRIS_OK) return st;
+  return check_cuda(launch_kernel(build_route_kernel, dim3(1), dim3(kRouteThreads), smem, stream, /*pdl=*/true, 1,
+                                  static_cast<const int32_t*>(selected), num_tokens, top_k, num_experts, m_tile, perm,
+                                  tok, slot, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, sel_cap),
+                    "build_route_kernel launch");
 }
 
 }  // namespace tris
@@ -232,10 +314,12 @@ extern "C" int tris_build_grouped_route(const int32_t* selected_experts, int32_t
                TRIS_ERR_INVALID_ARG, "tris_build_grouped_route: null pointer");
   TRIS_REQUIRE(num_tokens >= 0 && top_k > 0 && num_experts > 0 && m_tile > 0, TRIS_ERR_INVALID_ARG,
                "tris_build_grouped_route: bad sizes T=%d k=%d E=%d m_tile=%d", num_tokens, top_k, num_experts, m_tile);
-  TRIS_REQUIRE(num_experts <= 4096, TRIS_ERR_UNSUPPORTED, "tris_build_grouped_route: more than 4096 experts");
-  build_route_kernel<<<1, kRouteThreads, 2 * num_experts * sizeof(int32_t), static_cast<cudaStream_t>(stream)>>>(
+  TRIS_REQUIRE(num_experts <= 320, TRIS_ERR_UNSUPPORTED, "tris_build_grouped_route: more than 320 experts");
+  int sel_cap = 0;
+  const int smem = route_smem_bytes(num_experts, num_tokens * top_k, &sel_cap);
+  build_route_kernel<<<1, kRouteThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       selected_experts, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices, grouped_slots,
-      row_of_flat, expert_ids, segment_offsets, problem_offsets, counts);
+      row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, sel_cap);
   return check_cuda(cudaGetLastError(), "build_route_kernel launch");
 }
 
