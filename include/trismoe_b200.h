@@ -269,6 +269,31 @@ int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void* x_f16,
                            float* router_logits_out, void* workspace, size_t workspace_bytes,
                            void* stream);
 
+/*
+ * Same computation as tris_moe_layer_forward for callers that cannot provide a workspace
+ * because they are not allowed to allocate device memory: for example a serving process
+ * whose memory pool claimed the whole GPU at start-up (a later cudaMalloc fails or
+ * fragments the pool), a plugin running under a host framework that forbids driver
+ * allocations on its worker threads, or a latency-critical loop where an allocation's
+ * implicit device synchronisation is not acceptable.  This entry point has no counterpart
+ * in the reference.
+ *
+ * The scratch lives in a file-scope device array of TRIS_STATIC_SCRATCH_BYTES inside the
+ * library; every GPU that calls this function holds that much memory until the process
+ * exits.  Batches whose scratch need (tris_moe_layer_workspace_bytes) exceeds it are rejected
+ * with TRIS_ERR_WORKSPACE and a message naming both sizes.  The function calls no cudaMalloc,
+ * cudaFree or other allocating routine.  The first call on each device looks up the array's
+ * device address (cudaGetSymbolAddress, with that device current); make that first call
+ * outside any stream capture.  All calls on a device share the one array, which keeps the
+ * previous call's contents (the words that must start at zero are cleared on the stream
+ * first): calls that can overlap on the GPU, e.g. on two streams, race and must be ordered by
+ * the caller.  x, y, router_logits, router_logits_out as in tris_moe_layer_forward.
+ */
+#define TRIS_STATIC_SCRATCH_BYTES (8u << 20)
+int tris_moe_layer_forward_static(const TrisMoeLayerView* layer, const void* x_f16,
+                                  const float* router_logits, int32_t num_tokens, void* y_f16,
+                                  float* router_logits_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -71,7 +71,9 @@ SIGNATURES = {
     "tris_combine_routed": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "tris_moe_layer_workspace_bytes": (C.c_size_t, [_P(TrisMoeLayerView), _i32]),
     "tris_moe_layer_forward": (C.c_int, [_P(TrisMoeLayerView), _vp, _vp, _i32, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "tris_moe_layer_forward_static": (C.c_int, [_P(TrisMoeLayerView), _vp, _vp, _i32, _vp, _vp, _vp]),
 }
+STATIC_SCRATCH_BYTES = 8 << 20
 
 _lib = None
 

@@ -6,6 +6,7 @@
 //   grouped down
 //   weighted combine back to token order
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -171,4 +172,50 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
 
   // combine
   return combine_routed_impl(w.down_out, w.row_of_flat, w.weights, T, layer->top_k, layer->hidden_size, y_f16, s, true);
+}
+
+// ---- variant that allocates nothing ----------------------------------------------------------
+// Scratch for tris_moe_layer_forward_static.  Lives in every process image that loads the
+// library, once per GPU that touches it, until the process exits.
+static __device__ __align__(256) unsigned char g_layer_static_scratch[TRIS_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_ptr[64] = {};  // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int tris_moe_layer_forward_static(const TrisMoeLayerView* layer, const void* x_f16,
+                                             const float* router_logits, int32_t num_tokens, void* y_f16,
+                                             float* router_logits_out, void* stream) {
+  int st = validate_layer(layer);
+  if (st != TRIS_OK) return st;
+  TRIS_REQUIRE(num_tokens >= 0, TRIS_ERR_INVALID_ARG, "tris_moe_layer_forward_static: negative token count");
+  if (num_tokens == 0) return TRIS_OK;
+  LayerWorkspace probe = carve(layer, num_tokens, nullptr);
+  TRIS_REQUIRE(probe.bytes <= TRIS_STATIC_SCRATCH_BYTES, TRIS_ERR_WORKSPACE,
+               "tris_moe_layer_forward_static: %d tokens need %zu bytes of scratch, the built-in array holds %u; "
+               "use tris_moe_layer_forward with a caller workspace",
+               num_tokens, probe.bytes, static_cast<unsigned>(TRIS_STATIC_SCRATCH_BYTES));
+  int dev = -1;
+  TRIS_CUDA(cudaGetDevice(&dev));
+  TRIS_REQUIRE(dev >= 0 && dev < 64, TRIS_ERR_UNSUPPORTED, "tris_moe_layer_forward_static: device ordinal %d", dev);
+  void* scratch = nullptr;
+  {
+    // In host code the array's name is only a handle; the kernels need its device address,
+    // which is looked up once per device with that device current.
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+      void* ptr = nullptr;
+      TRIS_CUDA(cudaGetSymbolAddress(&ptr, g_layer_static_scratch));
+      TRIS_REQUIRE(ptr != nullptr, TRIS_ERR_CUDA, "tris_moe_layer_forward_static: no device address for the scratch array");
+      g_static_scratch_ptr[dev] = ptr;
+    }
+    scratch = g_static_scratch_ptr[dev];
+  }
+  // The array keeps whatever the previous call left.  Everything the launch sequence reads it
+  // writes first, except the status/count words, which are cleared here.
+  LayerWorkspace w = carve(layer, num_tokens, static_cast<char*>(scratch));
+  TRIS_CUDA(cudaMemsetAsync(w.counts, 0, 16, static_cast<cudaStream_t>(stream)));
+  return tris_moe_layer_forward(layer, x_f16, router_logits, num_tokens, y_f16, router_logits_out, scratch,
+                                TRIS_STATIC_SCRATCH_BYTES, stream);
 }
