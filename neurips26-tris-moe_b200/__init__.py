@@ -29,6 +29,7 @@ from .qlinear_grouped import (  # noqa: F401
     run_grouped_structured_expert_pair_forward,
 )
 from .moe_block import TrisSparseMoeBlock  # noqa: F401
+from . import clocks, expert_parallel, synth  # noqa: F401
 
 __all__ = [
     "TRIS_COMPACT3_KERNEL_ABI_VERSION",

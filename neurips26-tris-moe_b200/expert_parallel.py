@@ -1,0 +1,331 @@
+"""Expert-parallel MoE block: experts sharded over the GPUs of one node, tokens local to each
+rank, routed rows exchanged with NCCL all-to-all over NVLink.
+
+The reference is single-GPU (``grouped_payload_sidecar.py:867-868`` enforces one device), so
+this module has no counterpart there; it composes the same operators as
+``OlmoeSparseMoeBlock._forward_grouped`` (``modeling_olmoe.py:916-1044``) around two exchanges:
+
+    rank-local:  router -> route (rows sorted by expert, hence by owner rank)
+                 input-side backbones on the local tokens (replicated fp16 matrices)
+    dispatch:    all-to-all of [rows, 2*r] backbone outputs + one int32 expert id per row
+                 (2*r = 512 halves per row instead of the 2048-wide activation)
+    owner rank:  route over the received rows, grouped gate/up + SiLU*mul, down backbone,
+                 grouped down
+    combine:     all-to-all of [rows, H] results back to the token's rank, weighted gather
+
+Rank ``g`` of ``N`` owns experts ``[g*E/N, (g+1)*E/N)``.  Exact split sizes are exchanged first
+(one small all-to-all and a host read), so no row is dropped and no padding crosses NVLink.
+The communication plan is plain torch and runs on CPU tensors with the gloo backend, which is
+how it is tested without GPUs; the expert computation is a callable.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import time
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+from ._native import TrisRouteView
+from .qlinear_grouped import prepare_grouped_payload, proj_view
+
+_SHARD_KEYS = ("qweight1", "qweight2_sparse", "qweight2_sparse_prefix", "q_gmap_sparse", "q_gmap_sparse_prefix",
+               "q_gmap_gr_words", "q_gmap_gr_offsets", "q_gmap_gr_meta", "c_map", "g_idx", "col_pack3", "row_pack3",
+               "output_scale", "bias")
+
+
+def expert_range(num_experts: int, rank: int, world: int):
+    """Experts owned by ``rank``: contiguous, sizes differ by at most one."""
+    base, extra = divmod(num_experts, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def owner_of(experts: torch.Tensor, num_experts: int, world: int) -> torch.Tensor:
+    """Owner rank of each expert id (same partition as :func:`expert_range`)."""
+    base, extra = divmod(num_experts, world)
+    big = extra * (base + 1)
+    e = experts.to(torch.long)
+    return torch.where(e < big, e // max(base + 1, 1), extra + (e - big) // max(base, 1))
+
+
+def shard_payload(payload: dict, rank: int, world: int) -> dict:
+    """Slice of an E-stacked payload holding only the experts ``rank`` owns."""
+    E = int(payload["qweight1"].shape[0])
+    lo, hi = expert_range(E, rank, world)
+    out = {}
+    for key, val in payload.items():
+        if key.startswith("_"):
+            continue
+        if key in _SHARD_KEYS and isinstance(val, torch.Tensor) and val.dim() >= 1 and val.shape[0] == E:
+            out[key] = val[lo:hi].contiguous().clone()
+        else:
+            out[key] = val
+    if "_gr_words_used" in payload:
+        out["_gr_words_used"] = payload["_gr_words_used"][lo:hi]
+    return out
+
+
+class DispatchPlan:
+    """Who sends which routed rows where.  Built from the grouped expert id of every row
+    (ascending, so rows are already ordered by owner rank)."""
+
+    def __init__(self, grouped_expert_ids: torch.Tensor, num_experts: int, group=None):
+        world = dist.get_world_size(group)
+        owners = owner_of(grouped_expert_ids, num_experts, world)
+        send_counts = torch.bincount(owners, minlength=world).to(torch.long)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+        self.send_splits = send_counts.cpu().tolist()  # host read: sizes of the variable all-to-all
+        self.recv_splits = recv_counts.cpu().tolist()
+        self.num_send = int(sum(self.send_splits))
+        self.num_recv = int(sum(self.recv_splits))
+        self.group = group
+
+    def dispatch(self, rows: torch.Tensor) -> torch.Tensor:
+        out = rows.new_empty((self.num_recv,) + tuple(rows.shape[1:]))
+        dist.all_to_all_single(out, rows.contiguous(), self.recv_splits, self.send_splits, group=self.group)
+        return out
+
+    def combine(self, rows: torch.Tensor) -> torch.Tensor:
+        out = rows.new_empty((self.num_send,) + tuple(rows.shape[1:]))
+        dist.all_to_all_single(out, rows.contiguous(), self.send_splits, self.recv_splits, group=self.group)
+        return out
+
+
+def expert_parallel_exchange(hidden_grouped: torch.Tensor, grouped_expert_ids: torch.Tensor, num_experts: int,
+                             compute: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], group=None) -> torch.Tensor:
+    """Dispatch rows (already grouped by ascending expert id) to their owner ranks, run
+    ``compute(received_rows, received_local_expert_ids)`` there and bring the results back in
+    the sender's row order.  Device-agnostic: used with gloo/CPU tensors in the tests."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    plan = DispatchPlan(grouped_expert_ids, num_experts, group)
+    recv_rows = plan.dispatch(hidden_grouped)
+    recv_ids = plan.dispatch(grouped_expert_ids.to(torch.int32))
+    lo, _ = expert_range(num_experts, rank, world)
+    result = compute(recv_rows, recv_ids - lo)
+    return plan.combine(result)
+
+
+class ExpertParallelMoeBlock(torch.nn.Module):
+    """MoE block whose experts are sharded over the ranks of ``group`` (one process per GPU)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int, norm_topk_prob: bool,
+                 group=None):
+        super().__init__()
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.num_experts, self.top_k, self.norm_topk_prob = int(num_experts), int(top_k), bool(norm_topk_prob)
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.lo, self.hi = expert_range(self.num_experts, self.rank, self.world)
+        self.payloads: dict = {}
+        self.shared: dict = {}
+        self.router_weight: Optional[torch.Tensor] = None
+
+    def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate, shared_up, shared_down,
+                              router_weight=None, device=None, already_sharded: bool = False):
+        dev = torch.device(device)
+        for name, p in (("gate", gate), ("up", up), ("down", down)):
+            local = p if already_sharded else shard_payload(p, self.rank, self.world)
+            self.payloads[name] = prepare_grouped_payload(local, dev)
+        self.shared = {"gate": shared_gate.to(dev, torch.float16).contiguous(),
+                       "up": shared_up.to(dev, torch.float16).contiguous(),
+                       "down": shared_down.to(dev, torch.float16).contiguous()}
+        if router_weight is not None:
+            self.router_weight = router_weight.to(dev, torch.float16).contiguous()
+        return self
+
+    # -- C-ABI helpers ---------------------------------------------------------------------
+    def _route(self, selected_i32: torch.Tensor, num_experts: int):
+        lib = _native.load()
+        T, k = (int(s) for s in selected_i32.shape)
+        R, E, dev = T * k, num_experts, selected_i32.device
+        buf = torch.empty((4 * R + 3 * E + 6,), dtype=torch.int32, device=dev)
+        perm, tok, slot, rof = (buf[i * R:(i + 1) * R] for i in range(4))
+        ids = buf[4 * R: 4 * R + E]
+        seg = buf[4 * R + E: 4 * R + 2 * E + 1]
+        prob = buf[4 * R + 2 * E + 1: 4 * R + 3 * E + 2]
+        counts = buf[4 * R + 3 * E + 2: 4 * R + 3 * E + 6]
+        _native.check(lib.tris_build_grouped_route(selected_i32.data_ptr(), T, k, E, 4, perm.data_ptr(), tok.data_ptr(),
+                                                   slot.data_ptr(), rof.data_ptr(), ids.data_ptr(), seg.data_ptr(),
+                                                   prob.data_ptr(), counts.data_ptr(),
+                                                   torch.cuda.current_stream(dev).cuda_stream), "build_grouped_route")
+        return {"perm": perm, "tok": tok, "slot": slot, "row_of_flat": rof, "expert_ids": ids, "segment_offsets": seg,
+                "counts": counts, "_buf": buf, "rows": R, "experts": E, "max_rows": T}
+
+    def _route_view(self, route: dict, row_gather, interleaved: bool) -> TrisRouteView:
+        rv = TrisRouteView()
+        rv.expert_ids = route["expert_ids"].data_ptr()
+        rv.segment_offsets = route["segment_offsets"].data_ptr()
+        rv.num_segments_dev = route["counts"].data_ptr()
+        rv.num_segments = min(route["experts"], route["rows"])
+        rv.num_rows = route["rows"]
+        rv.max_rows_per_segment = route["max_rows"]
+        rv.row_gather = None if row_gather is None else row_gather.data_ptr()
+        rv.status_dev = None
+        rv.flags = 1 if interleaved else 0
+        return rv
+
+    def _backbone(self, x: torch.Tensor, sv: torch.Tensor, interleaved: bool) -> torch.Tensor:
+        lib = _native.load()
+        out = torch.empty((x.shape[0], sv.shape[0]), dtype=torch.float16, device=x.device)
+        if x.shape[0]:
+            _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, int(x.shape[0]), int(x.shape[1]), sv.data_ptr(),
+                                                         int(sv.shape[0]), out.data_ptr(), 2 if interleaved else 0,
+                                                         torch.cuda.current_stream(x.device).cuda_stream), "shared_hidden")
+        return out
+
+    def _local_experts(self, recv_hidden: torch.Tensor, recv_local_ids: torch.Tensor) -> torch.Tensor:
+        """gate/up -> SiLU*mul -> down for the rows this rank received; returns [rows, H] in the
+        received order."""
+        lib = _native.load()
+        dev = recv_hidden.device
+        Rr = int(recv_hidden.shape[0])
+        out = torch.empty((Rr, self.hidden_size), dtype=torch.float16, device=dev)
+        if Rr == 0:
+            return out
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        r_gu = int(self.shared["gate"].shape[0])
+        r_d = int(self.shared["down"].shape[0])
+        inter_gu, inter_d = r_gu % 32 == 0, r_d % 32 == 0
+        hg = recv_hidden[:, :r_gu].contiguous()
+        hu = recv_hidden[:, r_gu:].contiguous()
+        route = self._route(recv_local_ids.reshape(Rr, 1).contiguous(), self.hi - self.lo)
+        route["max_rows"] = Rr
+        va, vb, vd = (proj_view(self.payloads[n]) for n in ("gate", "up", "down"))
+        mlp = torch.empty((Rr, self.intermediate_size), dtype=torch.float16, device=dev)
+        rv = self._route_view(route, route["tok"], inter_gu)
+        _native.check(lib.tris_grouped_pair_forward(C.byref(va), C.byref(vb), C.byref(rv), hg.data_ptr(), hu.data_ptr(),
+                                                    mlp.data_ptr(), None, 1, stream), "grouped_pair_forward")
+        hd = self._backbone(mlp, self.shared["down"], inter_d)
+        down = torch.empty((Rr, self.hidden_size), dtype=torch.float16, device=dev)
+        rv = self._route_view(route, None, inter_d)
+        _native.check(lib.tris_grouped_forward(C.byref(vd), C.byref(rv), hd.data_ptr(), down.data_ptr(), stream),
+                      "grouped_forward")
+        ones = torch.ones((Rr,), dtype=torch.float32, device=dev)
+        _native.check(lib.tris_combine_routed(down.data_ptr(), route["row_of_flat"].data_ptr(), ones.data_ptr(), Rr, 1,
+                                              self.hidden_size, out.data_ptr(), stream), "ungroup")
+        return out
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
+        """``hidden_states`` are this rank's tokens ``[..., H]`` fp16; returns
+        ``(final_hidden_states, router_logits)`` for them."""
+        _native.require_cuda(hidden_states, "ExpertParallelMoeBlock.forward")
+        lib = _native.load()
+        shape = hidden_states.shape
+        x = hidden_states.reshape(-1, shape[-1]).contiguous()
+        T, dev = int(x.shape[0]), x.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        with torch.cuda.device(dev):
+            if router_logits is None:
+                router_logits = self._backbone_f32(x)
+            logits = router_logits.reshape(T, self.num_experts).to(torch.float32).contiguous()
+            sel = torch.empty((T, self.top_k), dtype=torch.int32, device=dev)
+            wts = torch.empty((T, self.top_k), dtype=torch.float32, device=dev)
+            if T:
+                _native.check(lib.tris_router_topk(logits.data_ptr(), T, self.num_experts, self.top_k,
+                                                   int(self.norm_topk_prob), sel.data_ptr(), wts.data_ptr(), stream), "router_topk")
+            route = self._route(sel, self.num_experts)
+            r_gu = int(self.shared["gate"].shape[0])
+            inter = r_gu % 32 == 0
+            hidden = torch.cat([self._backbone(x, self.shared["gate"], inter),
+                                self._backbone(x, self.shared["up"], inter)], dim=1)
+            tok = route["tok"].to(torch.long)
+            grouped_hidden = hidden.index_select(0, tok)
+            grouped_ids = sel.reshape(-1).index_select(0, route["perm"].to(torch.long))
+            returned = expert_parallel_exchange(grouped_hidden, grouped_ids, self.num_experts, self._local_experts,
+                                                self.group)
+            y = torch.empty_like(x)
+            if T:
+                _native.check(lib.tris_combine_routed(returned.data_ptr(), route["row_of_flat"].data_ptr(), wts.data_ptr(),
+                                                      T, self.top_k, self.hidden_size, y.data_ptr(), stream), "combine")
+        return y.reshape(shape), logits
+
+    def _backbone_f32(self, x: torch.Tensor) -> torch.Tensor:
+        if self.router_weight is None:
+            raise RuntimeError("trismoe_b200: no router weight loaded and no router_logits given")
+        lib = _native.load()
+        out = torch.empty((x.shape[0], self.num_experts), dtype=torch.float32, device=x.device)
+        if x.shape[0]:
+            _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, int(x.shape[0]), int(x.shape[1]),
+                                                         self.router_weight.data_ptr(), self.num_experts, out.data_ptr(), 1,
+                                                         torch.cuda.current_stream(x.device).cuda_stream), "router")
+        return out
+
+
+# ---------------------------------------------------------------------------------------
+# benchmark leg for N > 1 (called by bench.py under torchrun)
+# ---------------------------------------------------------------------------------------
+def run_bench(args, rank: int, world: int, device) -> None:
+    """Weak scaling: every rank decodes its own batch of 128 tokens through 16 layers whose
+    experts are sharded over the ranks.  Timed on the device (CUDA events), max over ranks."""
+    from . import synth
+    from .clocks import ClockSampler
+
+    layers, T = 16, 128
+    shape = synth.OLMOE
+    blocks = []
+    for l in range(layers):
+        layer = synth.synth_layer(shape, seed=1234 + l)  # same seed on every rank: identical full payloads
+        blk = ExpertParallelMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
+        blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
+                                  layer["shared_down"], layer["router_weight"], device=device)
+        blocks.append(blk)
+    x = synth.synth_activations(T, shape.hidden_size, seed=1000 + rank).to(device)
+    x_host = x.cpu().pin_memory()
+    y_host = torch.empty_like(x_host).pin_memory()
+
+    def step(inp):
+        y = None
+        for blk in blocks:
+            y = blk(inp.view(1, T, -1))[0]
+        return y
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = torch.tensor([start.elapsed_time(stop) / steps], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    sampler = ClockSampler(device.index or 0)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda: step(x), args.steps, args.warmup)
+
+    def e2e():
+        xd = x_host.to(device, non_blocking=True)
+        y_host.copy_(step(xd).view(T, -1), non_blocking=True)
+
+    e2e_ms = timed(e2e, args.steps, args.warmup)
+    if rank == 0:
+        clocks = sampler.stop()
+        total = T * world
+        print(json.dumps({
+            "metric": "decode_tokens_per_s", "value": round(total / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "OLMoE-shaped 16-layer MoE stack, decode batch 128 per GPU, experts sharded over the "
+                                   "GPUs (expert parallel), NCCL all-to-all dispatch and combine",
+                       "tokens_per_step": total, "layers": layers, "parallelism": f"ep{world}",
+                       "cold_cache": "16 distinct layer payloads per rank"},
+            "e2e": {"value": round(total / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": T * 2048 * 2,
+                    "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},
+            "gpu_launches": args.steps * layers * 12,
+            "roofline": None, "cpu_baseline": None, "clocks": clocks,
+        }))
+    dist.barrier()

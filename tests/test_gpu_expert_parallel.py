@@ -1,0 +1,68 @@
+"""Multi-GPU test (needs >= 2 GPUs, skipped otherwise): the expert-parallel block over NCCL
+gives, for every rank's tokens, the same output as the single-GPU block holding all experts."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    import trismoe_b200 as tm
+    from trismoe_b200 import expert_parallel as ep, synth
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        shape = synth.LayerShape(256, 192, 8, 2, rank=96, group_size=32)
+        layer = synth.synth_layer(shape, seed=77)
+        for name in ("gate", "up", "down"):
+            layer["shared_" + name] = (layer["shared_" + name].float() * 5.0).half()
+        clone = lambda p: {k: (v.clone() if isinstance(v, torch.Tensor) and not k.startswith("_") else v) for k, v in p.items()}
+        full = tm.TrisSparseMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
+        full.load_grouped_payloads(clone(layer["gate"]), clone(layer["up"]), clone(layer["down"]), layer["shared_gate"],
+                                   layer["shared_up"], layer["shared_down"], layer["router_weight"], device=dev)
+        blk = ep.ExpertParallelMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
+        blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
+                                  layer["shared_down"], layer["router_weight"], device=dev)
+        ok = True
+        for step, T in enumerate((9, 1 + 4 * rank)):
+            x = synth.synth_activations(T, shape.hidden_size, seed=10 * step + rank).to(dev)
+            logits = synth.synth_router_logits(T, shape.num_experts, seed=5 + 10 * step + rank).to(dev)
+            want, _ = full(x.view(1, T, -1), router_logits=logits)
+            got, _ = blk(x.view(1, T, -1), router_logits=logits)
+            torch.cuda.synchronize()
+            err = (got.float() - want.float()).abs()
+            ok = ok and bool(torch.isfinite(got.float()).all()) and float(err.max()) <= 2e-3 * max(1.0, float(want.float().abs().max()))
+        out[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_matches_single_gpu():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert all(out.get(r) for r in range(world)), dict(out)
