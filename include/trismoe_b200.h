@@ -178,7 +178,8 @@ int tris_compact3_dequantize(const TrisProjView* proj, void* weights_out_f16, vo
  * build_grouped_route (QL:1301-1378, CPP:741-793) without the host sync: all outputs are
  * device arrays padded to num_experts(+1).  selected_experts is [T, k] int32.  Rows of one
  * expert are ordered by ascending flat (token, slot) index.
- *   perm[R], grouped_token_indices[R], grouped_slots[R], row_of_flat[R] (inverse of perm),
+ *   perm[R], grouped_token_indices[R], grouped_slots[R], row_of_flat[R] (inverse of perm; -1 for
+ *   entries whose expert id is outside [0, E), which are left out of every segment),
  *   expert_ids[E] (unused tail = -1), segment_offsets[E+1] (tail = R),
  *   problem_offsets[E+1] (ceil(len/m_tile) prefix), counts[2] = {num_segments, total_problem_tiles}.
  */
@@ -202,11 +203,13 @@ int tris_router_topk(const float* router_logits, int32_t num_tokens, int32_t num
 /*
  * hidden = x . shared_sv^T (QuantLinear.compute_shared_hidden fp16 branch, QL:4454-4502):
  * x [N, in] fp16 (rows optionally gathered through row_gather), shared_sv [r, in] fp16,
- * out [N, r] in the layout named by out_mode (TRIS_OUT_*).
+ * out [N, r] in the layout named by out_mode (TRIS_OUT_*).  num_rows_dev (optional device
+ * scalar, final before the launch is enqueued) limits the work to the first *num_rows_dev rows.
  */
 int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_gather, int32_t num_rows,
-                               int32_t in_features, const void* shared_sv_f16, int32_t rank,
-                               void* out, int32_t out_mode, void* stream);
+                               const int32_t* num_rows_dev, int32_t in_features,
+                               const void* shared_sv_f16, int32_t rank, void* out, int32_t out_mode,
+                               void* stream);
 
 /* ---- grouped expert kernels -------------------------------------------------------- */
 
@@ -232,7 +235,8 @@ int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisProjView* pr
 
 /*
  * final[T, H] fp16 = sum over slots of routing_weights[t, s] * down_out[row_of_flat[t*k+s]]
- * (the index_add_ of MO:1038-1043, as a deterministic gather in fp32).
+ * (the index_add_ of MO:1038-1043, as a deterministic gather in fp32).  A negative row index
+ * contributes nothing.
  */
 int tris_combine_routed(const void* down_out_f16, const int32_t* row_of_flat,
                         const float* routing_weights, int32_t num_tokens, int32_t top_k,

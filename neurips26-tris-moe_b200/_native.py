@@ -65,7 +65,7 @@ SIGNATURES = {
     "tris_compact3_dequantize": (C.c_int, [_P(TrisProjView), _vp, _vp]),
     "tris_build_grouped_route": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tris_router_topk": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
-    "tris_shared_hidden_forward": (C.c_int, [_vp, _vp, _i32, _i32, _vp, _i32, _vp, _i32, _vp]),
+    "tris_shared_hidden_forward": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _vp]),
     "tris_grouped_forward": (C.c_int, [_P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp]),
     "tris_grouped_pair_forward": (C.c_int, [_P(TrisProjView), _P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp, _vp, _i32, _vp]),
     "tris_combine_routed": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),

@@ -38,7 +38,7 @@ struct SkinnyProblem {
   int32_t out_mode;
 };
 int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather,
-                         int n, int k, cudaStream_t stream, bool pdl = false);
+                         int n, int k, cudaStream_t stream, bool pdl = false, const int32_t* n_dev = nullptr);
 
 // Launch with optional programmatic dependent launch (the kernel may start while its
 // predecessor in the stream drains; it must execute griddepcontrol.wait before touching

@@ -169,6 +169,8 @@ __device__ __forceinline__ void build_route_body(
       tok[pos] = tk;
       slot[pos] = f - tk * top_k;
       row_of_flat[f] = pos;
+    } else if (f < f1) {
+      row_of_flat[f] = -1;  // expert id out of range (padding rows of a fixed-capacity exchange)
     }
     __syncwarp();
     if (e >= 0 && lane == __ffs(peers) - 1) woff[warp * num_experts + e] += __popc(peers);
@@ -231,8 +233,9 @@ __global__ void combine_routed_kernel(const __half* __restrict__ rows, const int
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j)
-      v[j] = (s0 + j < top_k) ? *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(r[j]) * hidden + c)
-                              : make_uint4(0u, 0u, 0u, 0u);
+      v[j] = (s0 + j < top_k && r[j] >= 0)
+                 ? *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(r[j]) * hidden + c)
+                 : make_uint4(0u, 0u, 0u, 0u);  // negative index = no row (contributes zero)
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);

@@ -23,6 +23,7 @@ struct SkinnyArgs {
   int32_t num_problems;
   const __half* x;            // [*, k]
   const int32_t* row_gather;  // optional [n]
+  const int32_t* n_dev;       // optional device scalar: only the first *n_dev rows are live
   int32_t n;
   int32_t k;
   int32_t k_per_cta;          // multiple of 32
@@ -53,12 +54,13 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const __gri
   const __half* arow_b = pb.a + static_cast<size_t>(min(mb, pb.m - 1)) * K;
   pdl_wait();  // x and row_gather may come from the preceding kernel
   pdl_launch_dependents();  // the next kernel may stage its weights while this one runs
+  const int n_live = args.n_dev ? min(args.n, *args.n_dev) : args.n;
   const __half* xrow[NT];
   bool xvalid[NT];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int n = n0 + nt * 8 + g;
-    xvalid[nt] = n < args.n;
+    xvalid[nt] = n < n_live;
     const int src = xvalid[nt] ? (args.row_gather ? args.row_gather[n] : n) : 0;
     xrow[nt] = args.x + static_cast<size_t>(src) * K;
   }
@@ -106,7 +108,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const __gri
       const int c = i & 3, ln = (i >> 2) & 31, nt = i >> 7;
       const int n = n0 + nt * 8 + 2 * (ln & 3) + (c & 1);
       const int m = m0 + (ln >> 2) + 8 * (c >> 1);
-      if (n < args.n && m < pb.m) {
+      if (n < n_live && m < pb.m) {
         if (pb.out_mode == TRIS_OUT_F32) {
           static_cast<float*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = v;
         } else {
@@ -130,7 +132,7 @@ static int launch_skinny(const SkinnyArgs& args, int mtiles, int ksplit, cudaStr
 
 // Launches up to kMaxProblems matrices that share x.
 int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather,
-                         int n, int k, cudaStream_t stream, bool pdl) {
+                         int n, int k, cudaStream_t stream, bool pdl, const int32_t* n_dev) {
   TRIS_REQUIRE(num_problems >= 1 && num_problems <= kMaxProblems, TRIS_ERR_INVALID_ARG, "shared hidden: bad problem count");
   TRIS_REQUIRE(n >= 0 && k > 0, TRIS_ERR_INVALID_ARG, "shared hidden: bad sizes n=%d k=%d", n, k);
   TRIS_REQUIRE((k & 7) == 0, TRIS_ERR_UNSUPPORTED, "shared hidden: in_features=%d must be a multiple of 8", k);
@@ -145,6 +147,7 @@ int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __h
   args.num_problems = num_problems;
   args.x = x;
   args.row_gather = row_gather;
+  args.n_dev = n_dev;
   args.n = n;
   args.k = k;
   const int nt = n <= 8 ? 1 : (n <= 16 ? 2 : (n <= 32 ? 4 : 8));
@@ -167,8 +170,9 @@ int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __h
 using namespace tris;
 
 extern "C" int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_gather, int32_t num_rows,
-                                          int32_t in_features, const void* shared_sv_f16, int32_t rank,
-                                          void* out, int32_t out_mode, void* stream) {
+                                          const int32_t* num_rows_dev, int32_t in_features,
+                                          const void* shared_sv_f16, int32_t rank, void* out, int32_t out_mode,
+                                          void* stream) {
   TRIS_REQUIRE(x_f16 && shared_sv_f16 && out, TRIS_ERR_INVALID_ARG, "tris_shared_hidden_forward: null pointer");
   TRIS_REQUIRE(rank > 0, TRIS_ERR_INVALID_ARG, "tris_shared_hidden_forward: rank=%d", rank);
   TRIS_REQUIRE(out_mode >= TRIS_OUT_F16 && out_mode <= TRIS_OUT_F16_PAIR_INTERLEAVED, TRIS_ERR_INVALID_ARG,
@@ -177,5 +181,5 @@ extern "C" int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_
                "tris_shared_hidden_forward: the pair-interleaved layout needs rank % 32 == 0");
   SkinnyProblem pb{static_cast<const __half*>(shared_sv_f16), out, rank, out_mode};
   return launch_shared_hidden(&pb, 1, static_cast<const __half*>(x_f16), row_gather, num_rows, in_features,
-                              static_cast<cudaStream_t>(stream));
+                              static_cast<cudaStream_t>(stream), false, num_rows_dev);
 }

@@ -170,16 +170,18 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         rv.flags = 1 if interleaved else 0
         return rv
 
-    def _backbone(self, x: torch.Tensor, sv: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    def _backbone(self, x: torch.Tensor, sv: torch.Tensor, interleaved: bool, live_rows=None) -> torch.Tensor:
         lib = _native.load()
         out = torch.empty((x.shape[0], sv.shape[0]), dtype=torch.float16, device=x.device)
         if x.shape[0]:
-            _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, int(x.shape[0]), int(x.shape[1]), sv.data_ptr(),
+            _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, int(x.shape[0]),
+                                                         None if live_rows is None else live_rows.data_ptr(),
+                                                         int(x.shape[1]), sv.data_ptr(),
                                                          int(sv.shape[0]), out.data_ptr(), 2 if interleaved else 0,
                                                          torch.cuda.current_stream(x.device).cuda_stream), "shared_hidden")
         return out
 
-    def _local_experts(self, recv_hidden: torch.Tensor, recv_local_ids: torch.Tensor) -> torch.Tensor:
+    def _local_experts(self, recv_hidden: torch.Tensor, recv_local_ids: torch.Tensor, rows_hint: int = 0) -> torch.Tensor:
         """gate/up -> SiLU*mul -> down for the rows this rank received; returns [rows, H] in the
         received order."""
         lib = _native.load()
@@ -195,13 +197,14 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         hg = recv_hidden[:, :r_gu].contiguous()
         hu = recv_hidden[:, r_gu:].contiguous()
         route = self._route(recv_local_ids.reshape(Rr, 1).contiguous(), self.hi - self.lo)
-        route["max_rows"] = Rr
+        route["max_rows"] = rows_hint if rows_hint > 0 else Rr
         va, vb, vd = (proj_view(self.payloads[n]) for n in ("gate", "up", "down"))
         mlp = torch.empty((Rr, self.intermediate_size), dtype=torch.float16, device=dev)
         rv = self._route_view(route, route["tok"], inter_gu)
         _native.check(lib.tris_grouped_pair_forward(C.byref(va), C.byref(vb), C.byref(rv), hg.data_ptr(), hu.data_ptr(),
                                                     mlp.data_ptr(), None, 1, stream), "grouped_pair_forward")
-        hd = self._backbone(mlp, self.shared["down"], inter_d)
+        live = route["segment_offsets"][route["experts"]:]  # total routed rows, on the device
+        hd = self._backbone(mlp, self.shared["down"], inter_d, live_rows=live)
         down = torch.empty((Rr, self.hidden_size), dtype=torch.float16, device=dev)
         rv = self._route_view(route, None, inter_d)
         _native.check(lib.tris_grouped_forward(C.byref(vd), C.byref(rv), hd.data_ptr(), down.data_ptr(), stream),
@@ -211,9 +214,15 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                                               self.hidden_size, out.data_ptr(), stream), "ungroup")
         return out
 
-    def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
+    def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None, exact_splits: bool = False):
         """``hidden_states`` are this rank's tokens ``[..., H]`` fp16; returns
-        ``(final_hidden_states, router_logits)`` for them."""
+        ``(final_hidden_states, router_logits)`` for them.
+
+        Default exchange: fixed capacity (``T*k`` rows per peer, the worst case, so nothing is
+        ever dropped), equal-split all-to-all, padding rows marked with expert id -1.  Nothing
+        is read back to the host, so the step can be captured in a CUDA graph.
+        ``exact_splits=True`` exchanges the row counts first and sends exactly the routed rows
+        (one host read per call)."""
         _native.require_cuda(hidden_states, "ExpertParallelMoeBlock.forward")
         lib = _native.load()
         shape = hidden_states.shape
@@ -234,16 +243,45 @@ class ExpertParallelMoeBlock(torch.nn.Module):
             inter = r_gu % 32 == 0
             hidden = torch.cat([self._backbone(x, self.shared["gate"], inter),
                                 self._backbone(x, self.shared["up"], inter)], dim=1)
-            tok = route["tok"].to(torch.long)
-            grouped_hidden = hidden.index_select(0, tok)
+            grouped_hidden = hidden.index_select(0, route["tok"].to(torch.long))
             grouped_ids = sel.reshape(-1).index_select(0, route["perm"].to(torch.long))
-            returned = expert_parallel_exchange(grouped_hidden, grouped_ids, self.num_experts, self._local_experts,
-                                                self.group)
             y = torch.empty_like(x)
+            if exact_splits:
+                returned = expert_parallel_exchange(grouped_hidden, grouped_ids, self.num_experts, self._local_experts,
+                                                    self.group)
+                index = route["row_of_flat"]
+            else:
+                returned, dest = self._padded_exchange(grouped_hidden, grouped_ids, T * self.top_k)
+                index = dest.index_select(0, route["row_of_flat"].to(torch.long)).to(torch.int32)
             if T:
-                _native.check(lib.tris_combine_routed(returned.data_ptr(), route["row_of_flat"].data_ptr(), wts.data_ptr(),
+                _native.check(lib.tris_combine_routed(returned.data_ptr(), index.data_ptr(), wts.data_ptr(),
                                                       T, self.top_k, self.hidden_size, y.data_ptr(), stream), "combine")
         return y.reshape(shape), logits
+
+    def _padded_exchange(self, grouped_hidden: torch.Tensor, grouped_ids: torch.Tensor, capacity: int):
+        """Fixed-capacity exchange; every rank must call it with the same ``capacity``.  Returns
+        the result rows laid out [peer, capacity, H] (flattened) and, for every grouped row,
+        its index in that layout."""
+        dev, N = grouped_hidden.device, self.world
+        R, W = int(grouped_hidden.shape[0]), int(grouped_hidden.shape[1])
+        owners = owner_of(grouped_ids, self.num_experts, N)
+        counts = (owners.unsqueeze(1) == torch.arange(N, device=dev).unsqueeze(0)).sum(dim=0)
+        rank_start = torch.cumsum(counts, 0) - counts
+        dest = owners * capacity + (torch.arange(R, device=dev) - rank_start.index_select(0, owners))
+        send_rows = torch.zeros((N * capacity, W), dtype=grouped_hidden.dtype, device=dev)
+        send_ids = torch.full((N * capacity,), -1, dtype=torch.int32, device=dev)
+        send_rows.index_copy_(0, dest, grouped_hidden)
+        send_ids.index_copy_(0, dest, grouped_ids.to(torch.int32))
+        recv_rows = torch.empty_like(send_rows)
+        recv_ids = torch.empty_like(send_ids)
+        dist.all_to_all_single(recv_rows, send_rows, group=self.group)
+        dist.all_to_all_single(recv_ids, send_ids, group=self.group)
+        local_ids = torch.where(recv_ids >= 0, recv_ids - self.lo, recv_ids)
+        expected = max(1, (N * R) // max(1, self.hi - self.lo))  # rows per local expert if routing is balanced
+        result = self._local_experts(recv_rows, local_ids, rows_hint=int(expected + 4 * expected ** 0.5))
+        back = torch.empty_like(result)
+        dist.all_to_all_single(back, result, group=self.group)
+        return back, dest
 
     def _backbone_f32(self, x: torch.Tensor) -> torch.Tensor:
         if self.router_weight is None:
@@ -251,7 +289,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         lib = _native.load()
         out = torch.empty((x.shape[0], self.num_experts), dtype=torch.float32, device=x.device)
         if x.shape[0]:
-            _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, int(x.shape[0]), int(x.shape[1]),
+            _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, int(x.shape[0]), None, int(x.shape[1]),
                                                          self.router_weight.data_ptr(), self.num_experts, out.data_ptr(), 1,
                                                          torch.cuda.current_stream(x.device).cuda_stream), "router")
         return out
@@ -305,7 +343,26 @@ def run_bench(args, rank: int, world: int, device) -> None:
     sampler = ClockSampler(device.index or 0)
     if rank == 0:
         sampler.start()
-    ms = timed(lambda: step(x), args.steps, args.warmup)
+    # one CUDA graph per step (kernels and NCCL all-to-alls); eager launches if capture is refused
+    graph, mode = None, "eager"
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step(x)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(x)
+        mode = "cuda graph"
+    except Exception as exc:  # noqa: BLE001
+        graph = None
+        mode = f"eager ({type(exc).__name__})"
+        torch.cuda.synchronize()
+    ms = timed((graph.replay if graph is not None else (lambda: step(x))), args.steps, args.warmup)
 
     def e2e():
         xd = x_host.to(device, non_blocking=True)
@@ -321,7 +378,7 @@ def run_bench(args, rank: int, world: int, device) -> None:
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "OLMoE-shaped 16-layer MoE stack, decode batch 128 per GPU, experts sharded over the "
                                    "GPUs (expert parallel), NCCL all-to-all dispatch and combine",
-                       "tokens_per_step": total, "layers": layers, "parallelism": f"ep{world}",
+                       "tokens_per_step": total, "layers": layers, "parallelism": f"ep{world}", "launch_mode": mode,
                        "cold_cache": "16 distinct layer payloads per rank"},
             "e2e": {"value": round(total / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": T * 2048 * 2,
                     "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},

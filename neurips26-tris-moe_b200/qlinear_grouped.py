@@ -443,7 +443,7 @@ def compute_shared_hidden(x: torch.Tensor, shared_sv: torch.Tensor) -> torch.Ten
     if x2.shape[0]:
         with torch.cuda.device(x.device):
             _native.check(
-                lib.tris_shared_hidden_forward(x2.data_ptr(), None, int(x2.shape[0]), in_features, sv.data_ptr(), rank,
+                lib.tris_shared_hidden_forward(x2.data_ptr(), None, int(x2.shape[0]), None, in_features, sv.data_ptr(), rank,
                                                out.data_ptr(), 0, _stream_ptr(x.device)),
                 "shared_hidden_forward",
             )
