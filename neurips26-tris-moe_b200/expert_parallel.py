@@ -125,6 +125,14 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         self.payloads: dict = {}
         self.shared: dict = {}
         self.router_weight: Optional[torch.Tensor] = None
+        self.capacity_tokens = 0  # tokens per rank the fixed-capacity exchange is sized for
+
+    def set_capacity(self, max_tokens_per_rank: int) -> "ExpertParallelMoeBlock":
+        """Sizes the fixed-capacity exchange: every rank must use the same value, at least the
+        largest per-rank batch (each peer slot holds ``max_tokens_per_rank * top_k`` rows, the
+        worst case, so no routed row can be dropped)."""
+        self.capacity_tokens = int(max_tokens_per_rank)
+        return self
 
     def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate, shared_up, shared_down,
                               router_weight=None, device=None, already_sharded: bool = False):
@@ -251,7 +259,13 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                                                     self.group)
                 index = route["row_of_flat"]
             else:
-                returned, dest = self._padded_exchange(grouped_hidden, grouped_ids, T * self.top_k)
+                if self.capacity_tokens <= 0:
+                    raise RuntimeError("trismoe_b200: call set_capacity(max tokens per rank) on every rank before a "
+                                       "fixed-capacity forward, or pass exact_splits=True")
+                if T > self.capacity_tokens:
+                    raise RuntimeError(f"trismoe_b200: batch of {T} tokens exceeds the exchange capacity "
+                                       f"{self.capacity_tokens} set with set_capacity()")
+                returned, dest = self._padded_exchange(grouped_hidden, grouped_ids, self.capacity_tokens * self.top_k)
                 index = dest.index_select(0, route["row_of_flat"].to(torch.long)).to(torch.int32)
             if T:
                 _native.check(lib.tris_combine_routed(returned.data_ptr(), index.data_ptr(), wts.data_ptr(),
@@ -312,7 +326,7 @@ def run_bench(args, rank: int, world: int, device) -> None:
         blk = ExpertParallelMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
         blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
                                   layer["shared_down"], layer["router_weight"], device=device)
-        blocks.append(blk)
+        blocks.append(blk.set_capacity(T))
     x = synth.synth_activations(T, shape.hidden_size, seed=1000 + rank).to(device)
     x_host = x.cpu().pin_memory()
     y_host = torch.empty_like(x_host).pin_memory()
@@ -356,7 +370,7 @@ def run_bench(args, rank: int, world: int, device) -> None:
         dist.barrier()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            step(x)
+            y_static = step(x)
         mode = "cuda graph"
     except Exception as exc:  # noqa: BLE001
         graph = None
@@ -365,8 +379,13 @@ def run_bench(args, rank: int, world: int, device) -> None:
     ms = timed((graph.replay if graph is not None else (lambda: step(x))), args.steps, args.warmup)
 
     def e2e():
-        xd = x_host.to(device, non_blocking=True)
-        y_host.copy_(step(xd).view(T, -1), non_blocking=True)
+        if graph is not None:  # the captured step reads x and leaves its result in y_static
+            x.copy_(x_host, non_blocking=True)
+            graph.replay()
+            y_host.copy_(y_static.view(T, -1), non_blocking=True)
+        else:
+            xd = x_host.to(device, non_blocking=True)
+            y_host.copy_(step(xd).view(T, -1), non_blocking=True)
 
     e2e_ms = timed(e2e, args.steps, args.warmup)
     if rank == 0:
