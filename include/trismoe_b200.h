@@ -88,6 +88,10 @@ typedef struct TrisProjView {
   /* When non-NULL, expert e of this view reads q_gmap_sparse row block
      gmap_slot[e] of a staging buffer instead of row block e (SC:1104-1106). */
   const int32_t* gmap_slot;
+  /* When non-NULL, every E-stacked tensor of this view (q_gmap_sparse included, unless
+     gmap_slot overrides it) is a staging buffer in which expert e occupies row block
+     expert_slot[e]: the layout tris_page_experts fills from pinned host memory. */
+  const int32_t* expert_slot;
 } TrisProjView;
 
 /*
@@ -241,6 +245,29 @@ int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisProjView* pr
 int tris_combine_routed(const void* down_out_f16, const int32_t* row_of_flat,
                         const float* routing_weights, int32_t num_tokens, int32_t top_k,
                         int32_t hidden_size, void* final_f16, void* stream);
+
+/* ---- streaming ----------------------------------------------------------------------- */
+
+/* One tensor to page: expert e's block of `bytes_per_expert` bytes (a multiple of 16) is
+   copied from host_src + e * bytes_per_expert to dst + slot * bytes_per_expert. */
+typedef struct TrisPageJob {
+  const void* host_src;      /* pinned, device-accessible host memory, [E, bytes_per_expert]  */
+  void* dst;                 /* device staging buffer, [slots, bytes_per_expert]              */
+  int64_t bytes_per_expert;
+} TrisPageJob;
+#define TRIS_MAX_PAGE_JOBS 16
+
+/*
+ * Streaming loader step (GroupedQGmapCPUStagingManager.run_grouped / stage, SC:943-1136):
+ * for every live segment s of the route, copies the blocks of expert expert_ids[s] of each
+ * job from pinned host memory into slot s of the job's staging buffer and records
+ * slot_table[expert] = s.  The copy is a kernel that reads host memory directly, driven by
+ * the device-side route, so the host never learns which experts are active and nothing
+ * synchronises; run it on a side stream and order it with events.  slot_table is [E] int32.
+ */
+int tris_page_experts(const TrisPageJob* jobs, int32_t num_jobs, const int32_t* expert_ids,
+                      const int32_t* num_segments_dev, int32_t num_segments, int32_t num_experts,
+                      int32_t* slot_table, void* stream);
 
 /* ---- whole MoE block --------------------------------------------------------------- */
 

@@ -29,8 +29,12 @@ class TrisProjView(C.Structure):
         ("q_gmap_gr_words", _vp), ("q_gmap_gr_offsets", _vp), ("q_gmap_gr_meta", _vp),
         ("c_map", _vp), ("g_idx", _vp), ("col_pack3", _vp), ("row_pack3", _vp),
         ("output_scale", _vp), ("bias", _vp),
-        ("gr_index", _vp), ("gr_substreams", _i32), ("packed_row_group", _vp), ("gmap_slot", _vp),
+        ("gr_index", _vp), ("gr_substreams", _i32), ("packed_row_group", _vp), ("gmap_slot", _vp), ("expert_slot", _vp),
     ]
+
+
+class TrisPageJob(C.Structure):
+    _fields_ = [("host_src", _vp), ("dst", _vp), ("bytes_per_expert", C.c_int64)]
 
 
 class TrisRouteView(C.Structure):
@@ -69,6 +73,7 @@ SIGNATURES = {
     "tris_grouped_forward": (C.c_int, [_P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp]),
     "tris_grouped_pair_forward": (C.c_int, [_P(TrisProjView), _P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp, _vp, _i32, _vp]),
     "tris_combine_routed": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "tris_page_experts": (C.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _vp]),
     "tris_moe_layer_workspace_bytes": (C.c_size_t, [_P(TrisMoeLayerView), _i32]),
     "tris_moe_layer_forward": (C.c_int, [_P(TrisMoeLayerView), _vp, _vp, _i32, _vp, _vp, _vp, C.c_size_t, _vp]),
     "tris_moe_layer_forward_static": (C.c_int, [_P(TrisMoeLayerView), _vp, _vp, _i32, _vp, _vp, _vp]),

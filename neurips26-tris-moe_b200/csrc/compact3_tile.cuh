@@ -195,9 +195,12 @@ __device__ __forceinline__ uint32_t staged_bits_at(const uint32_t* rows, int ow,
 // ---- stage 1: issue -------------------------------------------------------------------
 // Called by all threads after a barrier that ended every earlier use of the staging
 // buffers.  Warps 0 and 1 issue the weight copies of chunk (e, o0, p0); warp 3 fills ptab.
+// `e` indexes the bulky E-stacked tensors (sign planes, bitmap data, scale packs: a staging
+// slot when the payload is paged in), `ex` is the expert id and indexes the small tables
+// (c_map, prefixes, packed-row groups, block-GR offsets and meta), which stay resident.
 template <int NPROJ, int NT>
 __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
-                                                    int o0, int p0) {
+                                                    int ex, int o0, int p0) {
   constexpr int OW = Geom<NPROJ>::OW;
   constexpr int NOB = Geom<NPROJ>::NOB;
   constexpr int SPAN = Geom<NPROJ>::SPAN;
@@ -274,8 +277,8 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
       if (ok) {
         nvalid = min(NOB, nob - ob0);
         const int nblk = nkb * nob;
-        const int32_t* off = v.q_gmap_gr_offsets + static_cast<size_t>(e) * (nblk + 1) + kb * nob + ob0;
-        const int32_t* met = v.q_gmap_gr_meta + static_cast<size_t>(e) * nblk + kb * nob + ob0;
+        const int32_t* off = v.q_gmap_gr_offsets + static_cast<size_t>(ex) * (nblk + 1) + kb * nob + ob0;
+        const int32_t* met = v.q_gmap_gr_meta + static_cast<size_t>(ex) * nblk + kb * nob + ob0;
 #pragma unroll
         for (int j = 0; j <= NOB; ++j)
           if (j <= nvalid) begins[j] = off[j];
@@ -334,7 +337,7 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
       const int pr = proj_packed_rows(v);
       const int wv = min(OW, v.out_features - o0);
       if (v.sign2_rows > 0 && v.qweight2_sparse != nullptr && p0 < pr && wv > 0) {
-        const int32_t* pre = v.qweight2_sparse_prefix + static_cast<size_t>(e) * (pr + 1);
+        const int32_t* pre = v.qweight2_sparse_prefix + static_cast<size_t>(ex) * (pr + 1);
         const int r0 = pre[p0], r1 = pre[min(pr, p0 + KC)];
         const int q0 = max(0, r0 >> 5);
         const int q1 = min(min(v.sign2_rows, (r1 + 31) >> 5), q0 + kSparseRows);
@@ -350,9 +353,9 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
       const int pr = proj_packed_rows(v);
       const int wv = min(OW, v.out_features - o0);
       if (!v.use_block_gr && v.gmap_sparse_rows > 0 && v.q_gmap_sparse != nullptr && p0 < pr && wv > 0) {
-        const int32_t* pre = v.q_gmap_sparse_prefix + static_cast<size_t>(e) * (pr + 1);
+        const int32_t* pre = v.q_gmap_sparse_prefix + static_cast<size_t>(ex) * (pr + 1);
         const int r0 = pre[p0], r1 = pre[min(pr, p0 + KC)];
-        const int slot = v.gmap_slot ? v.gmap_slot[e] : e;
+        const int slot = v.gmap_slot ? v.gmap_slot[ex] : e;
         const int q0 = max(0, r0 >> 5);
         const int q1 = min(min(v.gmap_sparse_rows, (r1 + 31) >> 5), q0 + kSparseRows);
         for (int q = q0; q < q1; ++q)
@@ -377,18 +380,18 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
           const int pc = min(pg, pr);
           int base2 = 0, baseg = 0;
           if (v.qweight2_sparse_prefix) {
-            const int32_t* pre = v.qweight2_sparse_prefix + static_cast<size_t>(e) * (pr + 1);
+            const int32_t* pre = v.qweight2_sparse_prefix + static_cast<size_t>(ex) * (pr + 1);
             base2 = max(0, pre[p0] >> 5) << 5;
             info.rank2 = pre[pc] - base2;
           }
           if (!v.use_block_gr && v.q_gmap_sparse_prefix) {
-            const int32_t* pre = v.q_gmap_sparse_prefix + static_cast<size_t>(e) * (pr + 1);
+            const int32_t* pre = v.q_gmap_sparse_prefix + static_cast<size_t>(ex) * (pr + 1);
             baseg = max(0, pre[p0] >> 5) << 5;
             info.rankg = pre[pc] - baseg;
           }
           if (pg < pr) {
-            info.cw = static_cast<uint32_t>(v.c_map[static_cast<size_t>(e) * pr + pg]);
-            const int grp = v.packed_row_group ? v.packed_row_group[static_cast<size_t>(e) * pr + pg] : 0;
+            info.cw = static_cast<uint32_t>(v.c_map[static_cast<size_t>(ex) * pr + pg]);
+            const int grp = v.packed_row_group ? v.packed_row_group[static_cast<size_t>(ex) * pr + pg] : 0;
             const bool all_groups = v.num_groups * NPROJ * OW <= kRowTabEntries;
             info.gslot = all_groups ? min(max(grp, 0), v.num_groups - 1) : (p < KC ? p : 0);
           }
@@ -467,7 +470,7 @@ __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, cons
 // Returns false when a wait timed out.
 template <int NPROJ, int NT>
 __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
-                                                     int o0, int p0, uint32_t parity, uint32_t* gmap_dump) {
+                                                     int ex, int o0, int p0, uint32_t parity, uint32_t* gmap_dump) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int tid = threadIdx.x;
   bool ok = mbar_wait_bounded(&sm.mbar[0], parity);
@@ -505,7 +508,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
       const int pr = proj_packed_rows(v);
       uint2 rp = make_uint2(0u, 0u);
       if (p0 + p < pr && o0 + o < v.out_features) {
-        const int grp = v.packed_row_group ? v.packed_row_group[static_cast<size_t>(e) * pr + p0 + p] : 0;
+        const int grp = v.packed_row_group ? v.packed_row_group[static_cast<size_t>(ex) * pr + p0 + p] : 0;
         if (grp >= 0 && grp < v.num_groups) {
           const unsigned long long w = static_cast<unsigned long long>(
               v.row_pack3[(static_cast<size_t>(e) * v.out_features + o0 + o) * v.num_groups + grp]);

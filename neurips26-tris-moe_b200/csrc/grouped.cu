@@ -131,12 +131,13 @@ __global__ void __launch_bounds__(kThreads) compact3_dump_kernel(TrisProjView v,
                                                                   __half* weights_out, int32_t* status) {
   extern __shared__ uint4 smem_raw[];
   auto& sm = *reinterpret_cast<TileSmem<1, 1>*>(smem_raw);
-  const int o0 = blockIdx.x * 128, p0 = blockIdx.y * KC, e = blockIdx.z;
+  const int o0 = blockIdx.x * 128, p0 = blockIdx.y * KC;
+  const int e = v.expert_slot ? v.expert_slot[blockIdx.z] : blockIdx.z;  // payload row block of the expert
   init_barriers(sm.mbar);
-  stage_issue_weights<1, 1>(sm, &v, e, o0, p0);
+  stage_issue_weights<1, 1>(sm, &v, e, static_cast<int>(blockIdx.z), o0, p0);
   __syncthreads();
   uint32_t* dump = reinterpret_cast<uint32_t*>(sm.hrows);  // 4608 B >= 1024 words
-  const bool ok = stage_finish_weights<1, 1>(sm, &v, e, o0, p0, 0u, dense_out ? dump : nullptr);
+  const bool ok = stage_finish_weights<1, 1>(sm, &v, e, static_cast<int>(blockIdx.z), o0, p0, 0u, dense_out ? dump : nullptr);
   if (__syncthreads_or(!ok)) {
     if (threadIdx.x == 0 && status) atomicExch(status, TRIS_ERR_TIMEOUT);
     return;
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(kThreads) compact3_dump_kernel(TrisProjView v,
     for (int i = threadIdx.x; i < kTileWords; i += kThreads) {
       const int p = i / 128, o = i % 128;
       if (p0 + p < pr && o0 + o < v.out_features)
-        dense_out[(static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0 + o] = static_cast<int32_t>(dump[i]);
+        dense_out[(static_cast<size_t>(blockIdx.z) * pr + p0 + p) * v.out_features + o0 + o] = static_cast<int32_t>(dump[i]);
     }
   }
   if (weights_out) {
@@ -161,7 +162,7 @@ __global__ void __launch_bounds__(kThreads) compact3_dump_kernel(TrisProjView v,
       for (int h = 0; h < 2; ++h) {
         const int og = o0 + warp * 16 + g + 8 * h;
         if (og >= v.out_features) continue;
-        __half* row = weights_out + (static_cast<size_t>(e) * v.out_features + og) * v.rank;
+        __half* row = weights_out + (static_cast<size_t>(blockIdx.z) * v.out_features + og) * v.rank;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int ca = 32 * (p0 + p) + 4 * t + i, cb = ca + 16;
@@ -211,10 +212,12 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
   const int seg = blockIdx.y;
   const int nseg = args.num_segments_dev ? min(*args.num_segments_dev, args.num_segments) : args.num_segments;
   if (seg >= nseg) return;
-  const int e = args.expert_ids[seg];
+  const int expert = args.expert_ids[seg];
   const int row_begin = args.segment_offsets[seg];
   const int row_end = min(args.segment_offsets[seg + 1], args.num_rows);
-  if (e < 0 || e >= args.proj[0].num_experts || row_end <= row_begin) return;
+  if (expert < 0 || expert >= args.proj[0].num_experts || row_end <= row_begin) return;
+  // row block of the expert inside the payload tensors (a staging slot when they are paged in)
+  const int e = args.proj[0].expert_slot ? args.proj[0].expert_slot[expert] : expert;
 
   const int o0 = blockIdx.x * OW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -241,13 +244,13 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       __syncthreads();  // previous consumers of the staging buffers are done
       const bool need_w = staged_chunk != kc;
       auto row_src = [&](int n) { return args.row_gather ? args.row_gather[r0 + n] : (r0 + n); };
-      if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, o0, p0);
+      if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0);
       if (waited) stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, row_src);
       __syncthreads();
       TRIS_MARK(1);
       bool ok = true;
       if (need_w) {
-        ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, e, o0, p0, par_w, nullptr);
+        ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0, par_w, nullptr);
         par_w ^= 1u;
         staged_chunk = kc;
       }
@@ -293,8 +296,8 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
     for (int h = 0; h < 2; ++h) {
       const int og = o0 + out_local + g + 8 * h;
       if (og < v.out_features) {
-        if (v.output_scale) scale[h] = __half2float(reinterpret_cast<const __half*>(v.output_scale)[static_cast<size_t>(e) * v.out_features + og]);
-        if (v.bias) bias[h] = __half2float(reinterpret_cast<const __half*>(v.bias)[static_cast<size_t>(e) * v.out_features + og]);
+        if (v.output_scale) scale[h] = __half2float(reinterpret_cast<const __half*>(v.output_scale)[static_cast<size_t>(expert) * v.out_features + og]);
+        if (v.bias) bias[h] = __half2float(reinterpret_cast<const __half*>(v.bias)[static_cast<size_t>(expert) * v.out_features + og]);
       }
     }
 #pragma unroll
@@ -370,6 +373,8 @@ static int validate_proj(const TrisProjView* v, const char* name, bool need_runt
     TRIS_REQUIRE(v->gmap_sparse_rows == 0 || (v->q_gmap_sparse && v->q_gmap_sparse_prefix), TRIS_ERR_INVALID_ARG,
                  "%s: q_gmap_sparse needs its prefix", name);
   }
+  TRIS_REQUIRE(!(v->gmap_slot && v->expert_slot), TRIS_ERR_INVALID_ARG,
+               "%s: gmap_slot and expert_slot are mutually exclusive", name);
   if (need_runtime)
     TRIS_REQUIRE(v->packed_row_group != nullptr || v->num_groups == 1, TRIS_ERR_INVALID_ARG,
                  "%s: packed_row_group missing (call tris_build_row_groups)", name);

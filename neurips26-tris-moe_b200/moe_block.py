@@ -136,6 +136,74 @@ class TrisSparseMoeBlock(nn.Module):
                 )
         return y.reshape(shape), logits
 
+    def forward_streaming(self, hidden_states: torch.Tensor, manager, block_index: int,
+                          router_logits: Optional[torch.Tensor] = None):
+        """Forward with the expert payloads paged in by a
+        :class:`~.staging.GroupedQGmapCPUStagingManager` (the streaming mode of
+        ``OlmoeModel.forward``, modeling_olmoe.py:1305-1339): the route is built first, the
+        pager for gate/up/down starts on the side stream and overlaps the input-side backbone
+        GEMM; the grouped kernels wait on its event.  Nothing synchronises with the host."""
+        _native.require_cuda(hidden_states, "TrisSparseMoeBlock.forward_streaming")
+        lib = _native.load()
+        shape = hidden_states.shape
+        x = hidden_states.reshape(-1, shape[-1]).contiguous()
+        T, dev = int(x.shape[0]), x.device
+        E, k, H, I = self.num_experts, self.top_k, self.hidden_size, self.intermediate_size
+        R = T * k
+        y = torch.empty_like(x)
+        if T == 0:
+            return y.reshape(shape), x.new_zeros((0, E), dtype=torch.float32)
+        stream = lambda: torch.cuda.current_stream(dev).cuda_stream
+        f16 = torch.float16
+        with torch.cuda.device(dev):
+            if router_logits is None:
+                logits = torch.empty((T, E), dtype=torch.float32, device=dev)
+                _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, T, None, H, self.gate.weight.data_ptr(), E,
+                                                             logits.data_ptr(), 1, stream()), "router")
+            else:
+                logits = router_logits.reshape(T, E).to(torch.float32).contiguous()
+            sel = torch.empty((T, k), dtype=torch.int32, device=dev)
+            wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+            _native.check(lib.tris_router_topk(logits.data_ptr(), T, E, k, int(self.norm_topk_prob), sel.data_ptr(),
+                                               wts.data_ptr(), stream()), "router_topk")
+            buf = torch.empty((4 * R + 3 * E + 6,), dtype=torch.int32, device=dev)
+            perm, tok, slot, rof = (buf[i * R:(i + 1) * R] for i in range(4))
+            ids, seg = buf[4 * R: 4 * R + E], buf[4 * R + E: 4 * R + 2 * E + 1]
+            prob, counts = buf[4 * R + 2 * E + 1: 4 * R + 3 * E + 2], buf[4 * R + 3 * E + 2: 4 * R + 3 * E + 6]
+            _native.check(lib.tris_build_grouped_route(sel.data_ptr(), T, k, E, 4, perm.data_ptr(), tok.data_ptr(),
+                                                       slot.data_ptr(), rof.data_ptr(), ids.data_ptr(), seg.data_ptr(),
+                                                       prob.data_ptr(), counts.data_ptr(), stream()), "route")
+            route = {"expert_ids": ids, "segment_offsets": seg, "counts": counts, "experts": E, "rows": R}
+            paged = manager.page_layer(block_index, route)  # side stream, starts now
+
+            r_gu, r_d = int(self.shared_gate.shape[0]), int(self.shared_down.shape[0])
+            mode_gu, mode_d = (2 if r_gu % 32 == 0 else 0), (2 if r_d % 32 == 0 else 0)
+            hg = torch.empty((T, r_gu), dtype=f16, device=dev)
+            hu = torch.empty((T, r_gu), dtype=f16, device=dev)
+            for sv, out in ((self.shared_gate, hg), (self.shared_up, hu)):
+                _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, T, None, H, sv.data_ptr(), r_gu,
+                                                             out.data_ptr(), mode_gu, stream()), "backbone")
+            rv = _native.TrisRouteView()
+            rv.expert_ids, rv.segment_offsets, rv.num_segments_dev = ids.data_ptr(), seg.data_ptr(), counts.data_ptr()
+            rv.num_segments, rv.num_rows, rv.max_rows_per_segment = min(E, R), R, T
+            rv.row_gather, rv.status_dev, rv.flags = tok.data_ptr(), None, (1 if mode_gu else 0)
+            paged.wait()
+            mlp = torch.empty((R, I), dtype=f16, device=dev)
+            _native.check(lib.tris_grouped_pair_forward(C.byref(paged.views["gate"]), C.byref(paged.views["up"]), C.byref(rv),
+                                                        hg.data_ptr(), hu.data_ptr(), mlp.data_ptr(), None, 1, stream()),
+                          "grouped_pair_forward")
+            hd = torch.empty((R, r_d), dtype=f16, device=dev)
+            _native.check(lib.tris_shared_hidden_forward(mlp.data_ptr(), None, R, None, I, self.shared_down.data_ptr(), r_d,
+                                                         hd.data_ptr(), mode_d, stream()), "down backbone")
+            rv.row_gather, rv.flags = None, (1 if mode_d else 0)
+            down = torch.empty((R, H), dtype=f16, device=dev)
+            _native.check(lib.tris_grouped_forward(C.byref(paged.views["down"]), C.byref(rv), hd.data_ptr(), down.data_ptr(),
+                                                   stream()), "grouped_forward")
+            paged.release()
+            _native.check(lib.tris_combine_routed(down.data_ptr(), rof.data_ptr(), wts.data_ptr(), T, k, H, y.data_ptr(),
+                                                  stream()), "combine")
+        return y.reshape(shape), logits
+
     def forward_grouped_ops(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
         """Same result as :meth:`forward`, composed from the reference-named operators in
         the order of ``_forward_grouped`` (modeling_olmoe.py:916-1044); torch is used only

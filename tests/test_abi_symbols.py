@@ -46,7 +46,7 @@ def test_struct_sizes_match_c_layout(lib):
     """ctypes mirrors of the ABI structs: natural alignment, no packing surprises."""
     import trismoe_b200 as tm
 
-    assert C.sizeof(tm._native.TrisProjView) == 8 * 4 + 14 * 8 + 8 + 8 + 8 + 8
+    assert C.sizeof(tm._native.TrisProjView) == 8 * 4 + 14 * 8 + 8 + 8 + 8 + 8 + 8
     assert C.sizeof(tm._native.TrisRouteView) == 64
     assert tm._native.TrisRouteView.row_gather.offset == 40
 

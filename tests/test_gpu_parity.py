@@ -415,3 +415,44 @@ def test_full_size_properties(tm, olmoe_layer):
     for t in (0, 77):
         y_one, _ = blk(x[t: t + 1].view(1, 1, -1), router_logits=logits[t: t + 1])
         assert torch.allclose(y_one.view(-1).float(), y_all.view(T, -1)[t].float(), atol=2e-3, rtol=2e-3)
+
+
+# ---------------------------------------------------------------------------------------
+# (8) streaming: payloads paged from pinned host memory
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mode,fmt", [("bitmap", "sparse"), ("payload", "sparse"), ("payload", "block_gr")])
+def test_streaming_forward_matches_resident(tm, mode, fmt):
+    from trismoe_b200 import staging, synth
+
+    shape = synth.LayerShape(256, 192, 8, 2, rank=96, group_size=32)
+    blocks, inputs, wants = [], [], []
+    for L in range(3):
+        layer = synth.synth_layer(shape, seed=30 + L, keep_sparse_gmap=True)
+        for name in ("gate", "up", "down"):
+            layer["shared_" + name] = (layer["shared_" + name].float() * 5.0).half()
+            if fmt == "sparse":
+                layer[name]["compact3_use_block_gr"] = False
+        blk = _block_from_layer(tm, shape, layer)
+        T = 5 + 3 * L
+        x = synth.synth_activations(T, shape.hidden_size, seed=L).cuda()
+        logits = synth.synth_router_logits(T, shape.num_experts, seed=9 + L).cuda()
+        want, _ = blk(x.view(1, T, -1), router_logits=logits)
+        blocks.append(blk)
+        inputs.append((x, logits))
+        wants.append(want.clone())
+    resident_before = sum(t.numel() * t.element_size() for b in blocks for p in ("gate", "up", "down")
+                          for t in b._get_grouped_payload(p).values() if isinstance(t, torch.Tensor))
+    manager = staging.GroupedQGmapCPUStagingManager(blocks, mode=mode)
+    assert manager.initialize()
+    resident_after = sum(t.numel() * t.element_size() for b in blocks for p in ("gate", "up", "down")
+                         for t in b._get_grouped_payload(p).values() if isinstance(t, torch.Tensor))
+    assert resident_after < resident_before
+    for rep in range(2):  # second pass reuses the two staging slots
+        for L, blk in enumerate(blocks):
+            x, logits = inputs[L]
+            got, _ = blk.forward_streaming(x.view(1, x.shape[0], -1), manager, L, router_logits=logits)
+            torch.cuda.synchronize()
+            assert torch.equal(got, wants[L]), (mode, fmt, rep, L)
+    report = manager.overlap_report()
+    assert report["layers"] == 6 and report["copy_ms"] > 0
+    assert manager.pipeline_stats["calls"] == 6 and manager.pipeline_stats["slot_reuses"] >= 4
