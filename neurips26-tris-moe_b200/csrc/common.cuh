@@ -40,6 +40,12 @@ struct SkinnyProblem {
 int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather,
                          int n, int k, cudaStream_t stream, bool pdl = false, const int32_t* n_dev = nullptr);
 
+// tcgen05 / TMEM version of the same product (tc_gemm.cu), for row counts that make it a
+// dense contraction.
+bool tc_gemm_applicable(int n, int k, const __half* x, const SkinnyProblem* probs, int num_problems);
+int launch_tc_gemm(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather, int n,
+                   int k, cudaStream_t stream, bool pdl, const int32_t* n_dev, int32_t* status);
+
 // Launch with optional programmatic dependent launch (the kernel may start while its
 // predecessor in the stream drains; it must execute griddepcontrol.wait before touching
 // anything the predecessor writes) and an optional cluster size along z.

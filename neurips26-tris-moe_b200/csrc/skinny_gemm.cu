@@ -137,6 +137,11 @@ int launch_shared_hidden(const SkinnyProblem* probs, int num_problems, const __h
   TRIS_REQUIRE(n >= 0 && k > 0, TRIS_ERR_INVALID_ARG, "shared hidden: bad sizes n=%d k=%d", n, k);
   TRIS_REQUIRE((k & 7) == 0, TRIS_ERR_UNSUPPORTED, "shared hidden: in_features=%d must be a multiple of 8", k);
   if (n == 0) return TRIS_OK;
+  for (int i = 0; i < num_problems; ++i)
+    TRIS_REQUIRE(probs[i].a && probs[i].out && probs[i].m > 0, TRIS_ERR_INVALID_ARG, "shared hidden: bad problem %d", i);
+  // enough rows for a dense contraction: tcgen05 / TMEM tiles
+  if (tc_gemm_applicable(n, k, x, probs, num_problems))
+    return launch_tc_gemm(probs, num_problems, x, row_gather, n, k, stream, pdl, n_dev, nullptr);
   SkinnyArgs args{};
   int mtiles = 0;
   for (int i = 0; i < num_problems; ++i) {

@@ -1,0 +1,288 @@
+// Backbone projection on the 5th-generation tensor cores (tcgen05 + TMEM), used when there
+// are enough activation rows for a dense contraction (prefill, or the down backbone over
+// all routed rows of a decode batch): out[n, m] = sum_k x[n, k] * A[m, k].
+//
+// One CTA computes a 128-output x NTILE-row tile over its share of K.  Operands are staged
+// in shared memory in the K-major no-swizzle ("interleaved") core-matrix layout: 8 rows x
+// 16 bytes per core matrix, all rows of one 8-column K chunk contiguous, so
+//   byte offset(row, k) = (k / 8) * ROWS * 16 + row * 16 + (k % 8) * 2,
+// stride between 8-row groups (SBO) = 128 B, stride between K chunks (LBO) = ROWS * 16 B.
+// A single thread issues tcgen05.mma (M = 128, N = NTILE, K = 16 per instruction) into a
+// TMEM accumulator; completion is tracked with tcgen05.commit on mbarriers, two shared-memory
+// stages deep, so the loads of chunk i+1 overlap the MMAs of chunk i.  The split-K partial
+// tiles of a thread-block cluster are reduced through distributed shared memory.
+// Every mbarrier wait is bounded; a time-out frees the TMEM allocation and reports
+// TRIS_ERR_TIMEOUT through the status word.
+#include <cooperative_groups.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace tris {
+
+constexpr int kTcThreads = 128;
+constexpr int kTcM = 128;   // outputs per tile = TMEM lanes
+constexpr int kTcKChunk = 64;
+
+struct TcGemmArgs {
+  SkinnyProblem prob[3];
+  int32_t num_problems;
+  const __half* x;
+  const int32_t* row_gather;
+  const int32_t* n_dev;
+  int32_t* status;
+  int32_t n;
+  int32_t k;
+  int32_t k_per_cta;  // multiple of kTcKChunk
+};
+
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  // start address [0,14) (>>4), leading byte offset [16,30) (>>4), stride byte offset [32,46) (>>4),
+  // descriptor version 1 at [46,48), layout type 0 (no swizzle) at [61,64)
+  return static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+
+// kind::f16 instruction descriptor: fp16 A and B, both K-major, fp32 accumulate, M x N.
+__device__ __forceinline__ uint32_t umma_idesc_f16(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 lanes x 16 consecutive 32-bit columns of the accumulator: thread t of the warp gets lane
+// (taddr.lane + t), registers = columns.
+__device__ __forceinline__ void tmem_ld_16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Copies a ROWS x 64 fp16 tile (row-major source, 128 B per row) into the core-matrix layout.
+// row_ptr(r) returns the source row (already offset to the chunk's first column) or nullptr
+// for a row that must read as zeros.
+template <int ROWS, typename RowPtr>
+__device__ __forceinline__ void stage_operand(uint8_t* dst, RowPtr row_ptr) {
+  constexpr int kVecs = ROWS * 8;
+  for (int idx = threadIdx.x; idx < kVecs; idx += kTcThreads) {
+    // a warp covers 8 rows x 4 chunks: 64 contiguous source bytes per row, and every 8
+    // consecutive lanes write 128 contiguous shared-memory bytes
+    const int r_lo = idx & 7, c_lo = (idx >> 3) & 3, rest = idx >> 5;
+    const int c = ((rest & 1) << 2) | c_lo, row = ((rest >> 1) << 3) | r_lo;
+    const __half* src = row_ptr(row);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (src) v = *reinterpret_cast<const uint4*>(src + 8 * c);
+    *reinterpret_cast<uint4*>(dst + (c * ROWS + row) * 16) = v;
+  }
+}
+
+template <int NTILE>
+struct alignas(128) TcSmem {
+  uint8_t a[2][kTcM * kTcKChunk * 2];
+  uint8_t b[2][NTILE * kTcKChunk * 2];
+  uint64_t mbar[2];
+  uint32_t tmem_base;
+  int32_t timed_out;
+};
+
+// grid (m tiles over all problems, ceil(n / NTILE), ksplit); cluster (1, 1, ksplit).
+// After the MMAs the stage buffers are reused as the fp32 partial tile [NTILE][128].
+template <int NTILE>
+__global__ void __launch_bounds__(kTcThreads) umma_gemm_kernel(const __grid_constant__ TcGemmArgs args) {
+  extern __shared__ uint4 smem_raw[];
+  auto& sm = *reinterpret_cast<TcSmem<NTILE>*>(smem_raw);
+  cg::cluster_group cluster = cg::this_cluster();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  int tile = blockIdx.x, pi = 0;
+  while (pi + 1 < args.num_problems && tile >= (args.prob[pi].m + kTcM - 1) / kTcM) {
+    tile -= (args.prob[pi].m + kTcM - 1) / kTcM;
+    ++pi;
+  }
+  const SkinnyProblem& pb = args.prob[pi];
+  const int m0 = tile * kTcM;
+  const int n0 = blockIdx.y * NTILE;
+  const int K = args.k;
+  const int kbeg = blockIdx.z * args.k_per_cta;
+  const int kend = min(K, kbeg + args.k_per_cta);
+  const int nchunks = max(0, (kend - kbeg + kTcKChunk - 1) / kTcKChunk);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.mbar[0], 1);
+    mbar_init(&sm.mbar[1], 1);
+    fence_mbar_init();
+    sm.timed_out = 0;
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem_base, NTILE);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  pdl_wait();  // x, row_gather and n_dev come from earlier kernels
+  pdl_launch_dependents();
+  const int n_live = args.n_dev ? min(args.n, *args.n_dev) : args.n;
+  const uint32_t idesc = umma_idesc_f16(kTcM, NTILE);
+
+  uint32_t phase[2] = {0u, 0u};
+  bool ok = true;
+  for (int i = 0; i < nchunks; ++i) {
+    const int s = i & 1;
+    const int k0 = kbeg + i * kTcKChunk;
+    if (i >= 2) {  // the MMAs that read this stage two chunks ago must have finished
+      if (!mbar_wait_bounded(&sm.mbar[s], phase[s])) ok = false;
+      phase[s] ^= 1u;
+    }
+    stage_operand<kTcM>(sm.a[s], [&](int r) -> const __half* {
+      const int m = m0 + r;
+      return (m < pb.m) ? pb.a + static_cast<size_t>(m) * K + k0 : nullptr;
+    });
+    stage_operand<NTILE>(sm.b[s], [&](int r) -> const __half* {
+      const int n = n0 + r;
+      if (n >= n_live) return nullptr;
+      const int src = args.row_gather ? args.row_gather[n] : n;
+      return args.x + static_cast<size_t>(src) * K + k0;
+    });
+    fence_proxy_async();  // generic-proxy stores above -> visible to the tensor core's reads
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      tcgen05_fence_after();
+      const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+#pragma unroll
+      for (int j = 0; j < kTcKChunk / 16; ++j) {
+        const uint64_t da = umma_smem_desc(a_addr + j * 2 * kTcM * 16, kTcM * 16, 128);
+        const uint64_t db = umma_smem_desc(b_addr + j * 2 * NTILE * 16, NTILE * 16, 128);
+        umma_f16_ss(tmem, da, db, idesc, (i > 0 || j > 0) ? 1u : 0u);
+      }
+      umma_commit(&sm.mbar[s]);
+    }
+  }
+  // drain: the last one or two commits
+  for (int i = max(0, nchunks - 2); i < nchunks; ++i) {
+    const int s = i & 1;
+    if (!mbar_wait_bounded(&sm.mbar[s], phase[s])) ok = false;
+    phase[s] ^= 1u;
+  }
+  if (!ok) sm.timed_out = 1;
+  tcgen05_fence_after();
+  __syncthreads();
+  const bool failed = sm.timed_out != 0;
+
+  // accumulator -> fp32 partial tile in shared memory, [NTILE][128] (stage buffers are free now)
+  float* part = reinterpret_cast<float*>(smem_raw);
+  if (!failed && nchunks > 0) {
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+#pragma unroll 1
+    for (int c0 = 0; c0 < NTILE; c0 += 16) {
+      float v[16];
+      tmem_ld_16(tmem + lane_base + c0, v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) part[(c0 + j) * kTcM + warp * 32 + lane] = v[j];
+    }
+  } else {
+    for (int i = threadIdx.x; i < NTILE * kTcM; i += kTcThreads) part[i] = 0.f;
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, NTILE);
+  if (failed && threadIdx.x == 0 && args.status) atomicExch(args.status, TRIS_ERR_TIMEOUT);
+
+  cluster.sync();
+  if (cluster.block_rank() == 0) {
+    const unsigned nblk = cluster.num_blocks();
+    for (int i = threadIdx.x; i < NTILE * kTcM; i += kTcThreads) {
+      float v = part[i];
+      for (unsigned r = 1; r < nblk; ++r) v += cluster.map_shared_rank(part, r)[i];
+      const int n = n0 + i / kTcM, m = m0 + (i % kTcM);
+      if (n < n_live && m < pb.m) {
+        if (pb.out_mode == TRIS_OUT_F32) {
+          static_cast<float*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = v;
+        } else {
+          const int mm = (pb.out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? ((m & ~31) | ((m & 15) << 1) | ((m >> 4) & 1)) : m;
+          static_cast<__half*>(pb.out)[static_cast<size_t>(n) * pb.m + mm] = __float2half_rn(v);
+        }
+      }
+    }
+  }
+  cluster.sync();  // keep every CTA's shared memory alive until rank 0 has read it
+}
+
+template <int NTILE>
+static int launch_umma(const TcGemmArgs& args, int mtiles, int ksplit, cudaStream_t stream, bool pdl) {
+  const size_t smem = std::max(sizeof(TcSmem<NTILE>), static_cast<size_t>(NTILE) * kTcM * 4 + 128);
+  static bool configured[64] = {};
+  int dev = 0;
+  TRIS_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    TRIS_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<NTILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  return check_cuda(launch_kernel(umma_gemm_kernel<NTILE>, dim3(mtiles, ceil_div(args.n, NTILE), ksplit),
+                                  dim3(kTcThreads), smem, stream, pdl, ksplit, args),
+                    "umma_gemm_kernel launch");
+}
+
+// True when the tensor-core path applies: enough rows for a dense contraction, K a multiple
+// of the 64-column chunk, 16-byte aligned rows.
+bool tc_gemm_applicable(int n, int k, const __half* x, const SkinnyProblem* probs, int num_problems) {
+  if (n < 64 || (k % kTcKChunk) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u)) return false;
+  for (int i = 0; i < num_problems; ++i)
+    if (reinterpret_cast<uintptr_t>(probs[i].a) & 15u) return false;
+  return true;
+}
+
+int launch_tc_gemm(const SkinnyProblem* probs, int num_problems, const __half* x, const int32_t* row_gather, int n,
+                   int k, cudaStream_t stream, bool pdl, const int32_t* n_dev, int32_t* status) {
+  TcGemmArgs args{};
+  int mtiles = 0;
+  for (int i = 0; i < num_problems; ++i) {
+    args.prob[i] = probs[i];
+    mtiles += ceil_div(probs[i].m, kTcM);
+  }
+  args.num_problems = num_problems;
+  args.x = x;
+  args.row_gather = row_gather;
+  args.n_dev = n_dev;
+  args.status = status;
+  args.n = n;
+  args.k = k;
+  const int ntile = n <= 64 ? 64 : 128;
+  const int ntiles = ceil_div(n, ntile);
+  int ksplit = 1;
+  while (ksplit < 8 && mtiles * ntiles * ksplit < 148 && k / (ksplit * 2) >= 2 * kTcKChunk) ksplit *= 2;
+  args.k_per_cta = ceil_div(ceil_div(k, ksplit), kTcKChunk) * kTcKChunk;
+  if (ntile == 64) return launch_umma<64>(args, mtiles, ksplit, stream, pdl);
+  return launch_umma<128>(args, mtiles, ksplit, stream, pdl);
+}
+
+}  // namespace tris
