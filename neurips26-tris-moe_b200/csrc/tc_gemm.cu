@@ -88,11 +88,20 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Copies a ROWS x 64 fp16 tile (row-major source, 128 B per row) into the core-matrix layout.
-// row_ptr(r) returns the source row (already offset to the chunk's first column) or nullptr
-// for a row that must read as zeros.
+__device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src, bool valid) {
+  // src-size 0 zero-fills the destination without reading the source
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 16 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Starts the asynchronous copy of a ROWS x 64 fp16 tile (row-major source, 128 B per row) into
+// the core-matrix layout.  row_ptr(r) returns the source row (already offset to the chunk's
+// first column) or nullptr for a row that must read as zeros.
 template <int ROWS, typename RowPtr>
-__device__ __forceinline__ void stage_operand(uint8_t* dst, RowPtr row_ptr) {
+__device__ __forceinline__ void stage_operand_async(uint8_t* dst, const __half* fallback, RowPtr row_ptr) {
   constexpr int kVecs = ROWS * 8;
   for (int idx = threadIdx.x; idx < kVecs; idx += kTcThreads) {
     // a warp covers 8 rows x 4 chunks: 64 contiguous source bytes per row, and every 8
@@ -100,17 +109,17 @@ __device__ __forceinline__ void stage_operand(uint8_t* dst, RowPtr row_ptr) {
     const int r_lo = idx & 7, c_lo = (idx >> 3) & 3, rest = idx >> 5;
     const int c = ((rest & 1) << 2) | c_lo, row = ((rest >> 1) << 3) | r_lo;
     const __half* src = row_ptr(row);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (src) v = *reinterpret_cast<const uint4*>(src + 8 * c);
-    *reinterpret_cast<uint4*>(dst + (c * ROWS + row) * 16) = v;
+    cp_async_16(dst + (c * ROWS + row) * 16, src ? src + 8 * c : fallback, src != nullptr);
   }
 }
 
+constexpr int kTcStages = 4;
+
 template <int NTILE>
 struct alignas(128) TcSmem {
-  uint8_t a[2][kTcM * kTcKChunk * 2];
-  uint8_t b[2][NTILE * kTcKChunk * 2];
-  uint64_t mbar[2];
+  uint8_t a[kTcStages][kTcM * kTcKChunk * 2];
+  uint8_t b[kTcStages][NTILE * kTcKChunk * 2];
+  uint64_t mbar[kTcStages];
   uint32_t tmem_base;
   int32_t timed_out;
 };
@@ -138,8 +147,8 @@ __global__ void __launch_bounds__(kTcThreads) umma_gemm_kernel(const __grid_cons
   const int nchunks = max(0, (kend - kbeg + kTcKChunk - 1) / kTcKChunk);
 
   if (threadIdx.x == 0) {
-    mbar_init(&sm.mbar[0], 1);
-    mbar_init(&sm.mbar[1], 1);
+#pragma unroll
+    for (int i = 0; i < kTcStages; ++i) mbar_init(&sm.mbar[i], 1);
     fence_mbar_init();
     sm.timed_out = 0;
   }
@@ -154,26 +163,33 @@ __global__ void __launch_bounds__(kTcThreads) umma_gemm_kernel(const __grid_cons
   const int n_live = args.n_dev ? min(args.n, *args.n_dev) : args.n;
   const uint32_t idesc = umma_idesc_f16(kTcM, NTILE);
 
-  uint32_t phase[2] = {0u, 0u};
-  bool ok = true;
-  for (int i = 0; i < nchunks; ++i) {
-    const int s = i & 1;
+  auto issue_chunk = [&](int i) {
+    const int s = i % kTcStages;
     const int k0 = kbeg + i * kTcKChunk;
-    if (i >= 2) {  // the MMAs that read this stage two chunks ago must have finished
-      if (!mbar_wait_bounded(&sm.mbar[s], phase[s])) ok = false;
-      phase[s] ^= 1u;
-    }
-    stage_operand<kTcM>(sm.a[s], [&](int r) -> const __half* {
+    stage_operand_async<kTcM>(sm.a[s], pb.a, [&](int r) -> const __half* {
       const int m = m0 + r;
       return (m < pb.m) ? pb.a + static_cast<size_t>(m) * K + k0 : nullptr;
     });
-    stage_operand<NTILE>(sm.b[s], [&](int r) -> const __half* {
+    stage_operand_async<NTILE>(sm.b[s], args.x, [&](int r) -> const __half* {
       const int n = n0 + r;
       if (n >= n_live) return nullptr;
       const int src = args.row_gather ? args.row_gather[n] : n;
       return args.x + static_cast<size_t>(src) * K + k0;
     });
-    fence_proxy_async();  // generic-proxy stores above -> visible to the tensor core's reads
+  };
+
+  // Software pipeline over the K chunks: copies run kTcStages-1 chunks ahead of the MMAs.
+  uint32_t phase_bits = 0u;  // bit s = parity to wait for on mbar[s]
+  bool ok = true;
+#pragma unroll
+  for (int i = 0; i < kTcStages - 1; ++i) {
+    if (i < nchunks) issue_chunk(i);
+    cp_async_commit();
+  }
+  for (int i = 0; i < nchunks; ++i) {
+    const int s = i % kTcStages;
+    cp_async_wait<kTcStages - 2>();  // this thread's copies of chunk i have landed
+    fence_proxy_async();             // ... and are visible to the tensor core's reads
     __syncthreads();
     if (threadIdx.x == 0) {
       tcgen05_fence_after();
@@ -186,12 +202,23 @@ __global__ void __launch_bounds__(kTcThreads) umma_gemm_kernel(const __grid_cons
       }
       umma_commit(&sm.mbar[s]);
     }
+    // refill the stage that chunk i-1 used, once its MMAs have drained
+    const int nxt = i + kTcStages - 1;
+    if (nxt < nchunks) {
+      if (i >= 1) {
+        const int ps = (i - 1) % kTcStages;
+        if (!mbar_wait_bounded(&sm.mbar[ps], (phase_bits >> ps) & 1u)) ok = false;
+        phase_bits ^= 1u << ps;
+      }
+      issue_chunk(nxt);
+    }
+    cp_async_commit();
   }
-  // drain: the last one or two commits
-  for (int i = max(0, nchunks - 2); i < nchunks; ++i) {
-    const int s = i & 1;
-    if (!mbar_wait_bounded(&sm.mbar[s], phase[s])) ok = false;
-    phase[s] ^= 1u;
+  // drain: chunks up to nchunks - kTcStages - 1 were waited for when their stage was refilled
+  for (int c = max(0, nchunks - kTcStages); c < nchunks; ++c) {
+    const int s = c % kTcStages;
+    if (!mbar_wait_bounded(&sm.mbar[s], (phase_bits >> s) & 1u)) ok = false;
+    phase_bits ^= 1u << s;
   }
   if (!ok) sm.timed_out = 1;
   tcgen05_fence_after();
@@ -218,23 +245,41 @@ __global__ void __launch_bounds__(kTcThreads) umma_gemm_kernel(const __grid_cons
   if (failed && threadIdx.x == 0 && args.status) atomicExch(args.status, TRIS_ERR_TIMEOUT);
 
   cluster.sync();
-  if (cluster.block_rank() == 0) {
-    const unsigned nblk = cluster.num_blocks();
-    for (int i = threadIdx.x; i < NTILE * kTcM; i += kTcThreads) {
-      float v = part[i];
-      for (unsigned r = 1; r < nblk; ++r) v += cluster.map_shared_rank(part, r)[i];
-      const int n = n0 + i / kTcM, m = m0 + (i % kTcM);
-      if (n < n_live && m < pb.m) {
+  {
+    // every CTA of the cluster reduces and stores its own slice of the tile; the remote
+    // reads of one element are independent, so they are all in flight together
+    const unsigned nblk = cluster.num_blocks(), rank = cluster.block_rank();
+    constexpr int kVec = NTILE * kTcM / 4;
+    const int per = (kVec + nblk - 1) / nblk;
+    const int v_end = min(kVec, static_cast<int>((rank + 1) * per));
+    const float4* parts[8];
+#pragma unroll
+    for (unsigned r = 0; r < 8; ++r)
+      parts[r] = reinterpret_cast<const float4*>(cluster.map_shared_rank(part, r < nblk ? r : 0));
+    for (int i4 = rank * per + threadIdx.x; i4 < v_end; i4 += kTcThreads) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 v[8];
+#pragma unroll
+      for (unsigned r = 0; r < 8; ++r) v[r] = (r < nblk) ? parts[r][i4] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (unsigned r = 0; r < 8; ++r) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
+      const int n = n0 + (4 * i4) / kTcM, mbase = m0 + (4 * i4) % kTcM;
+      if (n >= n_live) continue;
+      const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int m = mbase + u;
+        if (m >= pb.m) continue;
         if (pb.out_mode == TRIS_OUT_F32) {
-          static_cast<float*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = v;
+          static_cast<float*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = vals[u];
         } else {
           const int mm = (pb.out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? ((m & ~31) | ((m & 15) << 1) | ((m >> 4) & 1)) : m;
-          static_cast<__half*>(pb.out)[static_cast<size_t>(n) * pb.m + mm] = __float2half_rn(v);
+          static_cast<__half*>(pb.out)[static_cast<size_t>(n) * pb.m + mm] = __float2half_rn(vals[u]);
         }
       }
     }
   }
-  cluster.sync();  // keep every CTA's shared memory alive until rank 0 has read it
+  cluster.sync();  // keep every CTA's shared memory alive until its peers have read it
 }
 
 template <int NTILE>
@@ -276,10 +321,10 @@ int launch_tc_gemm(const SkinnyProblem* probs, int num_problems, const __half* x
   args.status = status;
   args.n = n;
   args.k = k;
-  const int ntile = n <= 64 ? 64 : 128;
+  const int ntile = n <= 2048 ? 64 : 128;
   const int ntiles = ceil_div(n, ntile);
   int ksplit = 1;
-  while (ksplit < 8 && mtiles * ntiles * ksplit < 148 && k / (ksplit * 2) >= 2 * kTcKChunk) ksplit *= 2;
+  while (ksplit < 8 && mtiles * ntiles * ksplit < 148 && k / (ksplit * 2) >= 4 * kTcKChunk) ksplit *= 2;
   args.k_per_cta = ceil_div(ceil_div(k, ksplit), kTcKChunk) * kTcKChunk;
   if (ntile == 64) return launch_umma<64>(args, mtiles, ksplit, stream, pdl);
   return launch_umma<128>(args, mtiles, ksplit, stream, pdl);
