@@ -112,38 +112,44 @@ __device__ __forceinline__ uint32_t gr_peek32(const uint32_t* w, int nwords, int
   return __funnelshift_r(lo, hi, bitpos & 31);
 }
 
-// Window of 32 stream bits at `bitpos`, no bounds checks: callers keep bitpos below the
-// end of the block's words and the staging buffer has slack behind every span.
-__device__ __forceinline__ uint32_t gr_peek32_unchecked(const uint32_t* w, int bitpos) {
-  const int wi = bitpos >> 5;
-  return __funnelshift_r(w[wi], w[wi + 1], bitpos & 31);
+__device__ __forceinline__ uint32_t lds_u32(uint32_t smem_addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_addr));
+  return v;
 }
 
-// Decodes `n_ones` codewords starting at (bitpos, flatpos) and calls set(flat) for each
-// one.  The common case (terminating one and remainder inside one 32-bit window) is
-// straight-line code; zero runs of 32 or more and remainders that straddle the window take
-// the rare branches.
+// Decodes `n_ones` codewords of a block staged in shared memory, starting at (bitpos,
+// flatpos), and calls set(flat) for each one.  The loop is a serial dependency chain (the
+// next codeword starts where this one ends), so it is kept to the bare minimum: one
+// shared-memory window load, find-first-set, two adds.  Zero runs of 32 or more and
+// remainders that straddle the 32-bit window take the rare slow branch.  Reads stay inside
+// the block's words plus the two words of slack every staged span has behind it.
 template <typename SetBit>
 __device__ __forceinline__ void gr_decode_run(const uint32_t* w, int nwords, int k, int n_ones, int bitpos,
                                               int flatpos, SetBit set) {
   const int total_bits = nwords << 5;
   const uint32_t kmask = (1u << k) - 1u;
+  const uint32_t base = smem_u32(w);
   for (int n = 0; n < n_ones; ++n) {
-    if (bitpos >= total_bits) return;  // stream ran out: malformed, stop
-    uint32_t v = gr_peek32_unchecked(w, bitpos);
+    const int wi = min(bitpos >> 5, nwords);
+    const uint32_t addr = base + (static_cast<uint32_t>(wi) << 2);
+    uint32_t v = __funnelshift_r(lds_u32(addr), lds_u32(addr + 4), bitpos & 31);
+    int t = __ffs(v) - 1;
     int q = 0;
-    while (v == 0u) {
-      q += 32;
-      bitpos += 32;
-      if (bitpos >= total_bits) return;
-      v = gr_peek32_unchecked(w, bitpos);
-    }
-    const int t = __ffs(v) - 1;
     uint32_t rem = ((v >> t) >> 1) & kmask;
-    if (t + 1 + k > 32) rem = gr_peek32_unchecked(w, bitpos + t + 1) & kmask;
+    if (v == 0u || t + 1 + k > 32) {  // rare
+      while (v == 0u) {
+        q += 32;
+        bitpos += 32;
+        if (bitpos >= total_bits) return;  // stream ran out: malformed, stop
+        v = gr_peek32(w, nwords, bitpos);
+      }
+      t = __ffs(v) - 1;
+      rem = gr_peek32(w, nwords, bitpos + t + 1) & kmask;
+    }
     bitpos += t + 1 + k;
     flatpos += ((q + t) << k) + static_cast<int>(rem);
-    if (flatpos >= TRIS_GR_BLOCK_WORDS * 32) return;
+    if (flatpos >= TRIS_GR_BLOCK_WORDS * 32 || bitpos > total_bits) return;
     set(flatpos);
     ++flatpos;
   }
@@ -198,9 +204,11 @@ __device__ __forceinline__ uint32_t staged_bits_at(const uint32_t* rows, int ow,
 // `e` indexes the bulky E-stacked tensors (sign planes, bitmap data, scale packs: a staging
 // slot when the payload is paged in), `ex` is the expert id and indexes the small tables
 // (c_map, prefixes, packed-row groups, block-GR offsets and meta), which stay resident.
+// Only packed rows [p_lo, p_hi) of the chunk (multiples of 2) are staged: a cluster may split a
+// chunk's K range over its CTAs.
 template <int NPROJ, int NT>
 __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
-                                                    int ex, int o0, int p0) {
+                                                    int ex, int o0, int p0, int p_lo = 0, int p_hi = KC) {
   constexpr int OW = Geom<NPROJ>::OW;
   constexpr int NOB = Geom<NPROJ>::NOB;
   constexpr int SPAN = Geom<NPROJ>::SPAN;
@@ -216,7 +224,7 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
       const TrisProjView& v = views[proj];
       const int pr = proj_packed_rows(v);
       const int wv = min(OW, v.out_features - o0);
-      if (p0 + p < pr && wv > 0)
+      if (p0 + p < pr && wv > 0 && p >= p_lo && p < p_hi)
         bytes += lane_copy(sm.s1 + (proj * KC + p) * OW,
                            reinterpret_cast<const uint32_t*>(v.qweight1) +
                                (static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0,
@@ -246,8 +254,9 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
       if (v.use_block_gr && v.gr_index != nullptr) {
         const int pr = proj_packed_rows(v);
         const int nkb = (pr + 1) >> 1, nob = (v.out_features + 63) >> 6;
-        const int kb = (p0 >> 1) + ((b / NOB) & 3), ob = (o0 >> 6) + (b % NOB);
-        if (kb < nkb && ob < nob) {
+        const int kbl = (b / NOB) & 3;
+        const int kb = (p0 >> 1) + kbl, ob = (o0 >> 6) + (b % NOB);
+        if (kb < nkb && ob < nob && 2 * kbl >= p_lo && 2 * kbl < p_hi) {
           const size_t bi = static_cast<size_t>(e) * nkb * nob + static_cast<size_t>(kb) * nob + ob;
           bytes += lane_copy(sm.gridx + b * 32, v.gr_index + bi * v.gr_substreams, v.gr_substreams, bar);
         }
@@ -268,7 +277,7 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
       const int kb = (p0 >> 1) + kbl, ob0 = o0 >> 6;
       int begins[NOB + 1];
       int metas[NOB];
-      bool ok = v.use_block_gr && v.q_gmap_gr_words != nullptr && kb < nkb;
+      bool ok = v.use_block_gr && v.q_gmap_gr_words != nullptr && kb < nkb && 2 * kbl >= p_lo && 2 * kbl < p_hi;
 #pragma unroll
       for (int j = 0; j < NOB; ++j) metas[j] = 0;
 #pragma unroll
@@ -470,7 +479,8 @@ __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, cons
 // Returns false when a wait timed out.
 template <int NPROJ, int NT>
 __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
-                                                     int ex, int o0, int p0, uint32_t parity, uint32_t* gmap_dump) {
+                                                     int ex, int o0, int p0, uint32_t parity, uint32_t* gmap_dump,
+                                                     int p_lo = 0, int p_hi = KC) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int tid = threadIdx.x;
   bool ok = mbar_wait_bounded(&sm.mbar[0], parity);
@@ -564,6 +574,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
     const int proj = i / (KC * OW);
     const int p = (i / OW) % KC;
     const int o = i % OW;
+    if (p < p_lo || p >= p_hi) continue;
     const TrisProjView& v = views[proj];
     const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
     const uint32_t cwv = info.cw;
@@ -665,6 +676,35 @@ __device__ __forceinline__ void unpack_fragments(const TileSmem<NPROJ, NT>& sm, 
 template <int NPROJ, int NT>
 __device__ __forceinline__ uint4 load_b_fragments(const TileSmem<NPROJ, NT>& sm, int proj, int n, int p, int t) {
   return *reinterpret_cast<const uint4*>(sm.hrows + (proj * NT * 8 + n) * kHiddenRowBytes + p * 64 + t * 16);
+}
+
+// ---- launch arguments shared by the grouped kernels ---------------------------------------
+struct GroupedArgs {
+  TrisProjView proj[2];
+  const __half* hidden[2];
+  __half* out[2];
+  const int32_t* expert_ids;
+  const int32_t* segment_offsets;
+  const int32_t* num_segments_dev;
+  const int32_t* row_gather;
+  int32_t* status;
+  int32_t num_segments;
+  int32_t num_rows;
+  int32_t hidden_interleaved;
+  int32_t weights_before_wait;  // route arrays were final before the predecessor kernel started
+  int32_t ksplit;               // CTAs per cluster sharing one tile: each takes 8/ksplit packed rows of a chunk
+};
+
+enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };
+
+__device__ __forceinline__ void init_stage_barriers(uint64_t* mbar) {
+  if (threadIdx.x == 0) {
+    mbar_init(&mbar[0], 32);
+    mbar_init(&mbar[1], 32);
+    mbar_init(&mbar[2], 32);
+    fence_mbar_init();
+  }
+  __syncthreads();
 }
 
 }  // namespace tris

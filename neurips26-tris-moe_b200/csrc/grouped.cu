@@ -6,6 +6,7 @@
 // memory, then every warp unpacks weights straight into m16n8k16 A fragments and
 // multiplies them with the staged activation rows; no dequantized weight is written
 // anywhere but registers.  fp32 accumulation.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include <algorithm>
@@ -16,7 +17,7 @@ namespace tris { __device__ long long* g_phase_stamps = nullptr; }
 #define TRIS_MARK(k)                                                                                          \
   do {                                                                                                        \
     if (threadIdx.x == 0 && ::tris::g_phase_stamps)                                                           \
-      ::tris::g_phase_stamps[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (k)] = clock64(); \
+      ::tris::g_phase_stamps[((static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (k)] = clock64(); \
   } while (0)
 #define TRIS_SUBMARK(k) TRIS_MARK(k)
 #else
@@ -24,6 +25,8 @@ namespace tris { __device__ long long* g_phase_stamps = nullptr; }
 #endif
 
 #include "compact3_tile.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace tris {
 
@@ -106,15 +109,7 @@ __global__ void build_row_groups_kernel(const int32_t* g_idx, int num_experts, i
 }
 
 // ---- dump kernels -------------------------------------------------------------------------
-__device__ __forceinline__ void init_barriers(uint64_t* mbar) {
-  if (threadIdx.x == 0) {
-    mbar_init(&mbar[0], 32);
-    mbar_init(&mbar[1], 32);
-    mbar_init(&mbar[2], 32);
-    fence_mbar_init();
-  }
-  __syncthreads();
-}
+__device__ __forceinline__ void init_barriers(uint64_t* mbar) { init_stage_barriers(mbar); }
 
 // Second, equally bounded, wait for copies that may still be in flight before a CTA that
 // saw a time-out leaves; then the status word is set.
@@ -175,29 +170,20 @@ __global__ void __launch_bounds__(kThreads) compact3_dump_kernel(TrisProjView v,
 }
 
 // ---- grouped forward ----------------------------------------------------------------------
-struct GroupedArgs {
-  TrisProjView proj[2];
-  const __half* hidden[2];
-  __half* out[2];
-  const int32_t* expert_ids;
-  const int32_t* segment_offsets;
-  const int32_t* num_segments_dev;
-  const int32_t* row_gather;
-  int32_t* status;
-  int32_t num_segments;
-  int32_t num_rows;
-  int32_t hidden_interleaved;
-  int32_t weights_before_wait;  // route arrays were final before the predecessor kernel started
-};
 
-enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };
 
-// grid (ceil(O/OW), num_segments bound)
+// grid (ceil(O/OW), num_segments bound, ksplit); cluster (1, 1, ksplit).  With ksplit > 1 the
+// CTAs of a cluster split every 256-column chunk between them and cluster rank 0 adds the
+// partial tiles (read through distributed shared memory) before the epilogue: small batches
+// have too few (expert, tile) units to fill the GPU otherwise.
 template <int NPROJ, int NT, int EPI>
 __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_kernel(const __grid_constant__ GroupedArgs args) {
   constexpr int OW = Geom<NPROJ>::OW;
   extern __shared__ uint4 smem_raw[];
   auto& sm = *reinterpret_cast<TileSmem<NPROJ, NT>*>(smem_raw);
+  cg::cluster_group cluster = cg::this_cluster();
+  const int ksplit = args.ksplit > 1 ? args.ksplit : 1;
+  const int p_lo = (KC / ksplit) * static_cast<int>(blockIdx.z), p_hi = p_lo + KC / ksplit;
 
   TRIS_MARK(0);
   init_barriers(sm.mbar);
@@ -230,6 +216,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
 
   int staged_chunk = -1;
   uint32_t par_w = 0u, par_h = 0u;
+  bool dead = false;  // a bounded wait ran out: skip the work but keep meeting the cluster barriers
   for (int r0 = row_begin; r0 < row_end; r0 += NT * 8) {
     const int rows = min(NT * 8, row_end - r0);
     const int nt_count = (rows + 7) >> 3;
@@ -242,15 +229,16 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
     for (int kc = 0; kc < num_chunks; ++kc) {
       const int p0 = kc * KC;
       __syncthreads();  // previous consumers of the staging buffers are done
+      if (dead) break;
       const bool need_w = staged_chunk != kc;
       auto row_src = [&](int n) { return args.row_gather ? args.row_gather[r0 + n] : (r0 + n); };
-      if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0);
+      if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0, p_lo, p_hi);
       if (waited) stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, row_src);
       __syncthreads();
       TRIS_MARK(1);
       bool ok = true;
       if (need_w) {
-        ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0, par_w, nullptr);
+        ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0, par_w, nullptr, p_lo, p_hi);
         par_w ^= 1u;
         staged_chunk = kc;
       }
@@ -266,15 +254,16 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       par_h ^= 1u;
       if (__syncthreads_or(!ok)) {
         leave_after_timeout(sm, par_w ^ 1u, par_h ^ 1u, args.status);
-        return;
+        dead = true;
+        break;
       }
       TRIS_MARK(3);
 
       RowScales rs[2];
       int rs_slot = -1;
-      const int p_end = min(KC, pr - p0);
+      const int p_end = min(p_hi, pr - p0);
 #pragma unroll 2
-      for (int p = 0; p < p_end; ++p) {
+      for (int p = p_lo; p < p_end; ++p) {
         uint32_t a[2][4];
         unpack_fragments<NPROJ, NT>(sm, proj, p, out_local, lane, rs, rs_slot, a);
 #pragma unroll
@@ -289,6 +278,28 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
     }
 
     TRIS_MARK(4);
+    if (ksplit > 1) {
+      // partial tiles of the cluster -> rank 0 (the activation rows are dead by now)
+      __syncthreads();
+      float4* part = reinterpret_cast<float4*>(sm.hrows);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+        part[(warp * NT + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+      cluster.sync();
+      if (cluster.block_rank() == 0) {
+        for (int r = 1; r < ksplit; ++r) {
+          const float4* remote = cluster.map_shared_rank(part, r);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const float4 v = remote[(warp * NT + nt) * 32 + lane];
+            acc[nt][0] += v.x; acc[nt][1] += v.y; acc[nt][2] += v.z; acc[nt][3] += v.w;
+          }
+        }
+      }
+      cluster.sync();  // peers keep their shared memory until rank 0 has read it
+      if (cluster.block_rank() != 0) continue;  // next row pass (same trip count in every CTA)
+    }
+    if (dead) continue;
     // epilogue: acc[nt] = {(out g, row 2t), (out g, row 2t+1), (out g+8, row 2t), (out g+8, row 2t+1)}
     const TrisProjView& v = args.proj[proj];
     float scale[2] = {1.f, 1.f}, bias[2] = {0.f, 0.f};
@@ -349,6 +360,10 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
   TRIS_MARK(5);
 }
 
+// tensor-core path for prefill-sized segments (grouped_umma.cu)
+bool grouped_umma_applicable(const GroupedArgs& args, int rows_hint);
+int launch_grouped_umma(const GroupedArgs& args, int nproj, int epi, cudaStream_t stream, bool pdl);
+
 // ---- host launchers -----------------------------------------------------------------------
 static int validate_proj(const TrisProjView* v, const char* name, bool need_runtime) {
   TRIS_REQUIRE(v != nullptr, TRIS_ERR_INVALID_ARG, "%s: null projection view", name);
@@ -392,8 +407,9 @@ static int launch_grouped(const GroupedArgs& args, cudaStream_t stream, bool pdl
     TRIS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  dim3 grid(ceil_div(args.proj[0].out_features, Geom<NPROJ>::OW), args.num_segments);
-  return check_cuda(launch_kernel(kernel, grid, dim3(kThreads), smem, stream, pdl, 1, args),
+  const int ksplit = args.ksplit > 1 ? args.ksplit : 1;
+  dim3 grid(ceil_div(args.proj[0].out_features, Geom<NPROJ>::OW), args.num_segments, ksplit);
+  return check_cuda(launch_kernel(kernel, grid, dim3(kThreads), smem, stream, pdl, ksplit, args),
                     "grouped_compact3_kernel launch");
 }
 
@@ -418,6 +434,18 @@ static int fill_route(GroupedArgs& a, const TrisRouteView* route) {
   a.status = route->status_dev;
   a.hidden_interleaved = (route->flags & TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED) != 0;
   return TRIS_OK;
+}
+
+// CTAs per tile: small batches have few (segment, tile) units, so a cluster splits each
+// unit's K range to put more SMs to work.
+static int pick_ksplit(const TrisProjView* proj, const TrisRouteView* route, int out_per_cta) {
+  // Measured on B200 at decode batch 1 (128 units): splitting K over 4 CTAs shortens the main
+  // loop, but block-GR decode (a per-lane chain of ~12 codewords), the staging round trips and
+  // the two cluster barriers do not shrink, and the layer got slower (54 vs 38 us).  The split
+  // stays available for shapes with long K, where the main loop dominates.
+  const int units = ceil_div(proj->out_features, out_per_cta) * std::max(1, route->num_segments);
+  if (proj->rank >= 2048 && units <= 160) return 2;
+  return 1;
 }
 
 // Rows per activation tile: sized for the typical segment (mean + 4 sigma of a balanced
@@ -512,6 +540,8 @@ int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* ro
   a.hidden[0] = a.hidden[1] = static_cast<const __half*>(hidden_f16);
   a.out[0] = a.out[1] = static_cast<__half*>(out_f16);
   a.weights_before_wait = opts.pdl && opts.weights_before_wait;
+  a.ksplit = pick_ksplit(proj, route, 128);
+  if (grouped_umma_applicable(a, rows_hint(route))) return launch_grouped_umma(a, 1, EPI_STORE, stream, opts.pdl);
   return dispatch_grouped<1, EPI_STORE>(a, rows_hint(route), stream, opts.pdl);
 }
 
@@ -549,7 +579,10 @@ int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjVi
   a.out[0] = static_cast<__half*>(out_a_f16);
   a.out[1] = static_cast<__half*>(out_b_f16);
   a.weights_before_wait = opts.pdl && opts.weights_before_wait;
+  a.ksplit = pick_ksplit(proj_a, route, 64);
   const int max_rows = rows_hint(route);
+  if (grouped_umma_applicable(a, max_rows))
+    return launch_grouped_umma(a, 2, fuse_silu_mul ? EPI_SILU_MUL : EPI_STORE, stream, opts.pdl);
   if (fuse_silu_mul) return dispatch_grouped<2, EPI_SILU_MUL>(a, max_rows, stream, opts.pdl);
   return dispatch_grouped<2, EPI_STORE>(a, max_rows, stream, opts.pdl);
 }

@@ -456,3 +456,54 @@ def test_streaming_forward_matches_resident(tm, mode, fmt):
     report = manager.overlap_report()
     assert report["layers"] == 6 and report["copy_ms"] > 0
     assert manager.pipeline_stats["calls"] == 6 and manager.pipeline_stats["slot_reuses"] >= 4
+
+
+# ---------------------------------------------------------------------------------------
+# (9) prefill-sized segments: tcgen05 / TMEM grouped kernel
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rank,T", [(96, 200), (256, 150), (64, 700)])
+def test_layer_prefill_rows_take_the_tensor_core_path(tm, rank, T):
+    """Few experts, many tokens: ~100+ rows per expert, rank a multiple of 32 -> the grouped
+    kernels run their tcgen05 variant (weights unpacked once per tile into shared memory)."""
+    from trismoe_b200 import synth
+
+    shape = synth.LayerShape(256, 320, 4, 2, rank=rank, group_size=32)
+    layer = synth.synth_layer(shape, seed=rank + T)
+    for name in ("gate", "up", "down"):
+        layer["shared_" + name] = (layer["shared_" + name].float() * 5.0).half()
+    blk = _block_from_layer(tm, shape, layer)
+    weights = {n: [orc.dequantize_expert(to_numpy_payload(layer[n]), e) for e in range(4)] for n in ("gate", "up", "down")}
+    for name in ("gate", "up", "down"):  # the tile unpack of this path is the bit-exact one
+        got = tm.dequantize_grouped_payload(blk._get_grouped_payload(name)).cpu().numpy()
+        _assert_half_bits_equal(got, np.stack(weights[name]))
+    x = synth.synth_activations(T, shape.hidden_size, seed=T)
+    logits = synth.synth_router_logits(T, shape.num_experts, seed=T + 1)
+    shared = {n: layer["shared_" + n].numpy() for n in ("gate", "up", "down")}
+    y, _ = blk(x.cuda().view(1, T, -1), router_logits=logits.cuda())
+    ref = orc.moe_layer_fp32(x.numpy(), logits.numpy(), weights, shared, shape.top_k, shape.norm_topk_prob)
+    max_abs, mean_rel = orc.error_metrics(y.view(T, -1).float().cpu().numpy(), ref)
+    assert np.abs(ref).mean() > 1e-4
+    assert max_abs <= MAX_ABS and mean_rel <= MEAN_REL, (max_abs, mean_rel)
+    # and agrees with the register (mma.sync) path, which the operator API takes for row-major input
+    y2, _ = blk.forward_grouped_ops(x.cuda().view(1, T, -1), router_logits=logits.cuda())
+    max_abs, mean_rel = orc.error_metrics(y2.view(T, -1).float().cpu().numpy(), ref)
+    assert max_abs <= MAX_ABS and mean_rel <= 2 * MEAN_REL, (max_abs, mean_rel)
+
+
+def test_layer_olmoe_shape_prefill_512(tm, olmoe_layer):
+    """Headline shape, 512-token prefill (64 rows per expert on average)."""
+    from trismoe_b200 import synth
+
+    layer, blk = olmoe_layer
+    T = 512
+    x = synth.synth_activations(T, 2048, seed=3).cuda()
+    logits = synth.synth_router_logits(T, 64, seed=4).cuda()
+    y, _ = blk(x.view(1, T, -1), router_logits=logits)
+    y2, _ = blk.forward_grouped_ops(x.view(1, T, -1), router_logits=logits)
+    ref = y2.view(T, -1).float().cpu().numpy()
+    max_abs, mean_rel = orc.error_metrics(y.view(T, -1).float().cpu().numpy(), ref)
+    assert np.abs(ref).mean() > 1e-4 and max_abs <= MAX_ABS and mean_rel <= 2 * MEAN_REL, (max_abs, mean_rel)
+    # a single token of the batch, recomputed alone through the decode kernels
+    for t in (5, 300):
+        y_one, _ = blk(x[t: t + 1].view(1, 1, -1), router_logits=logits[t: t + 1])
+        assert torch.allclose(y_one.view(-1).float(), y.view(T, -1)[t].float(), atol=3e-3, rtol=3e-3)
