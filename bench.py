@@ -326,6 +326,86 @@ def run_ncu_case(args):
         torch.cuda.synchronize()
 
 
+def run_extra(args):
+    """Secondary workloads (not the contract line): prints one JSON object with
+    - prefill of 2048 tokens through OLMoE-shaped layers (tcgen05 grouped path),
+    - a Mixtral-shaped layer (8 experts, top-2, hidden 4096, intermediate 14336): prefill 2048, decode 1/64,
+    - streaming: OLMoE-shaped layers with the payload paged from pinned host memory, decode 1/16,
+      tokens/s and overlapped fraction of the transfer time."""
+    import trismoe_b200 as tm
+    from trismoe_b200 import staging, synth
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    out = {}
+
+    def stack(shape, layers, seed, **kw):
+        blocks = []
+        for l in range(layers):
+            layer = synth.synth_layer(shape, seed=seed + l, **kw)
+            blk = tm.TrisSparseMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
+            blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
+                                      layer["shared_down"], layer["router_weight"], device=device)
+            blocks.append(blk)
+        return blocks
+
+    def time_stack(blocks, T, hidden, steps=10):
+        x = synth.synth_activations(T, hidden, seed=T).to(device)
+
+        def step():
+            for blk in blocks:
+                blk(x.view(1, T, hidden))
+
+        graph = capture(step)
+        ms = time_replays(graph, steps, 3)
+        return {"tokens": T, "us_per_layer": round(ms * 1e3 / len(blocks), 2), "tokens_per_s": round(T / (ms * 1e-3), 1)}
+
+    olmoe = stack(synth.OLMOE, 8, 500)
+    out["olmoe_prefill"] = [time_stack(olmoe, T, 2048) for T in (512, 2048)]
+    flops = lambda shape, T: 2 * T * shape.top_k * shape.rank * (2 * shape.intermediate_size + shape.hidden_size) + \
+        2 * T * shape.hidden_size * 2 * shape.rank + 2 * T * shape.top_k * shape.intermediate_size * shape.rank
+    for rec in out["olmoe_prefill"]:
+        rec["tflops"] = round(flops(synth.OLMOE, rec["tokens"]) / (rec["us_per_layer"] * 1e-6) / 1e12, 2)
+    del olmoe
+    torch.cuda.empty_cache()
+    mixtral = stack(synth.MIXTRAL, 4, 600)
+    out["mixtral_layer"] = [time_stack(mixtral, T, 4096) for T in (1, 64, 2048)]
+    for rec in out["mixtral_layer"]:
+        rec["tflops"] = round(flops(synth.MIXTRAL, rec["tokens"]) / (rec["us_per_layer"] * 1e-6) / 1e12, 2)
+    del mixtral
+    torch.cuda.empty_cache()
+    for mode, fmt_gr in (("bitmap", False), ("payload", True)):
+        blocks = stack(synth.OLMOE, 8, 700, keep_sparse_gmap=not fmt_gr, use_block_gr=fmt_gr)
+        manager = staging.GroupedQGmapCPUStagingManager(blocks, mode=mode)
+        manager.initialize()
+        recs = []
+        for T in (1, 16):
+            x = synth.synth_activations(T, 2048, seed=T).to(device)
+            for _ in range(3):
+                for l, blk in enumerate(blocks):
+                    blk.forward_streaming(x.view(1, T, 2048), manager, l)
+            torch.cuda.synchronize()
+            manager.overlap_report()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            reps = 10
+            for _ in range(reps):
+                for l, blk in enumerate(blocks):
+                    blk.forward_streaming(x.view(1, T, 2048), manager, l)
+            stop.record()
+            torch.cuda.synchronize()
+            ms = start.elapsed_time(stop) / reps
+            rep = manager.overlap_report()
+            recs.append({"tokens": T, "us_per_layer": round(ms * 1e3 / len(blocks), 2), "tokens_per_s": round(T / (ms * 1e-3), 1),
+                         "overlapped_fraction": None if rep["overlapped_fraction"] is None else round(rep["overlapped_fraction"], 3),
+                         "copy_ms_per_layer": round(rep["copy_ms"] / max(1, rep["layers"]), 4),
+                         "staging_buffer_mb": round(manager.buffer_nbytes / 1e6, 1)})
+        out["streaming_" + mode] = recs
+        del blocks, manager
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -334,12 +414,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ncu-case", default=None, choices=["layer", "grouped"],
                     help="run a short untimed launch sequence for a profiler capture and exit")
+    ap.add_argument("--extra", action="store_true", help="run the secondary workloads (prefill, Mixtral shape, streaming)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers for --ncu-case")
     ap.add_argument("--tokens", type=int, default=HEADLINE_TOKENS, help="decode batch for --ncu-case")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.ncu_case:
         return run_ncu_case(args)
+    if args.extra:
+        return run_extra(args)
     if args.impl == "reference":
         run_reference(args)
     else:
