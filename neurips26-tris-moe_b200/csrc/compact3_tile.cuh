@@ -542,15 +542,16 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
       sm.g[block_word_to_tile<NPROJ>(b, wl)] = word;
     }
     __syncthreads();
-    const int sub = views[0].gr_substreams;
+    const int sub = views[0].gr_substreams;  // a power of two
+    const int sub_log2 = 31 - __clz(sub);
     for (int i = tid; i < kBlocksPerChunk * sub; i += kThreads) {
-      const int b = i / sub, j = i - b * sub;
+      const int b = i >> sub_log2, j = i & (sub - 1);
       const int count = sm.binfo[b * 4 + 1];
       const int meta = sm.binfo[b * 4 + 2];
       if (count <= 0 || (meta & TRIS_GR_META_RAW_FLAG)) continue;
       const int k = meta & TRIS_GR_META_K_MASK;
       const int one_count = meta >> TRIS_GR_META_ONE_COUNT_SHIFT;
-      const int per = (one_count + sub - 1) / sub;
+      const int per = (one_count + sub - 1) >> sub_log2;
       const int first = j * per;
       if (per == 0 || first >= one_count) continue;
       const int n_ones = min(per, one_count - first);

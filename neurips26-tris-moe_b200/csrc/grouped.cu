@@ -259,17 +259,38 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       }
       TRIS_MARK(3);
 
+      // Per-lane base addresses; inside the fully unrolled loop every access is base + constant.
+      const int p_end = min(p_hi, pr - p0);
+      const int word0 = proj * KC * OW + out_local + g;
+      const uint32_t* s1_base = sm.s1 + word0;
+      const uint32_t* sel_base = sm.g + word0;
+      const uint4* col_base = sm.coltab + proj * KC * 16 + t;
+      const PackedRowInfo* pinfo = sm.ptab + proj * (KC + 1);
+      const uint8_t* h_base = sm.hrows + (proj * NT * 8 + g) * kHiddenRowBytes + t * 16;
+      const uint2* row_base = sm.rowtab + (proj * OW + out_local + g) * sm.row_stride;
+      const int row_step = 8 * sm.row_stride;
       RowScales rs[2];
       int rs_slot = -1;
-      const int p_end = min(p_hi, pr - p0);
-#pragma unroll 2
-      for (int p = p_lo; p < p_end; ++p) {
+#pragma unroll
+      for (int p = 0; p < KC; ++p) {
+        if (p < p_lo || p >= p_end) continue;  // warp-uniform
+        const PackedRowInfo info = pinfo[p];
+        if (info.gslot != rs_slot) {  // groups span several packed rows
+          rs_slot = info.gslot;
+          rs[0] = broadcast_row_scales(row_base[rs_slot]);
+          rs[1] = broadcast_row_scales(row_base[row_step + rs_slot]);
+        }
+        uint4 ct[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ct[i] = col_base[p * 16 + i * 4];
+        const bool any_salient = info.cw != 0u;
         uint32_t a[2][4];
-        unpack_fragments<NPROJ, NT>(sm, proj, p, out_local, lane, rs, rs_slot, a);
+        unpack_row(s1_base[p * OW], sel_base[p * OW], rs[0], ct, any_salient, t, a[0]);
+        unpack_row(s1_base[p * OW + 8], sel_base[p * OW + 8], rs[1], ct, any_salient, t, a[1]);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           if (nt < nt_count) {
-            const uint4 hv = load_b_fragments<NPROJ, NT>(sm, proj, nt * 8 + g, p, t);
+            const uint4 hv = *reinterpret_cast<const uint4*>(h_base + nt * 8 * kHiddenRowBytes + p * 64);
             mma_m16n8k16(acc[nt], a[0][0], a[1][0], a[0][1], a[1][1], hv.x, hv.y);
             mma_m16n8k16(acc[nt], a[0][2], a[1][2], a[0][3], a[1][3], hv.z, hv.w);
           }
@@ -337,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const float gv = acc[nt][c];
-            acc[nt][c] = gv / (1.f + __expf(-gv)) * uu[c];
+            acc[nt][c] = __fdividef(gv, 1.f + __expf(-gv)) * uu[c];
           }
         }
       }

@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
           const float x = va[j] * scale[0] + bias[0];
           if (EPI == EPI_SILU_MUL) {
             const float u = vb[j] * scale[NPROJ - 1] + bias[NPROJ - 1];
-            args.out[0][static_cast<size_t>(r0 + n) * v0.out_features + og] = __float2half_rn(x / (1.f + __expf(-x)) * u);
+            args.out[0][static_cast<size_t>(r0 + n) * v0.out_features + og] = __float2half_rn(__fdividef(x, 1.f + __expf(-x)) * u);
           } else {
             args.out[0][static_cast<size_t>(r0 + n) * v0.out_features + og] = __float2half_rn(x);
             if (NPROJ == 2)
