@@ -109,6 +109,7 @@ typedef struct TrisRouteView {
   int32_t* status_dev;              /* optional device int32: set to TRIS_ERR_TIMEOUT when a
                                        bounded wait inside a kernel ran out                */
   int32_t flags;                    /* TRIS_ROUTE_* bits                                   */
+  int32_t hidden_row_stride;        /* halves between activation rows; 0 = the projection's rank */
 } TrisRouteView;
 
 /* Activation rows handed to the grouped kernels are "pair-interleaved": inside every group
@@ -201,6 +202,23 @@ int tris_build_grouped_route(const int32_t* selected_experts, int32_t num_tokens
 int tris_router_topk(const float* router_logits, int32_t num_tokens, int32_t num_experts,
                      int32_t top_k, int32_t norm_topk_prob, int32_t* selected_experts,
                      float* routing_weights, void* stream);
+
+/*
+ * Expert-parallel dispatch packing (no reference counterpart: the reference is single-GPU).
+ * Rows of the grouped order are sorted by expert, hence by owner rank (rank g of `world` owns
+ * a contiguous range of experts, sizes differing by at most one).  For every grouped row the
+ * kernel copies its two backbone outputs (hidden_gate[tok], hidden_up[tok], each `rank_gu`
+ * halves) side by side into slot (owner, position among the rows for that owner) of
+ * send_rows [world * capacity, 2*rank_gu], writes the row's expert id into send_ids
+ * [world * capacity] (unused slots = -1), and records combine_index[flat] = that slot for
+ * the flat (token, slot) entry the row came from.  capacity >= rows sent to any one rank
+ * (tokens * top_k always suffices); a row beyond it is dropped and *overflow_dev set to 1.
+ */
+int tris_ep_pack_rows(const void* hidden_gate_f16, const void* hidden_up_f16, int32_t rank_gu,
+                      const int32_t* selected_experts, const int32_t* perm, const int32_t* grouped_token_indices,
+                      int32_t num_rows, int32_t top_k, int32_t num_experts, int32_t world, int32_t capacity,
+                      void* send_rows_f16, int32_t* send_ids, int32_t* combine_index, int32_t* overflow_dev,
+                      void* stream);
 
 /* ---- backbone ---------------------------------------------------------------------- */
 

@@ -41,7 +41,7 @@ class TrisRouteView(C.Structure):
     _fields_ = [
         ("expert_ids", _vp), ("segment_offsets", _vp), ("num_segments_dev", _vp),
         ("num_segments", _i32), ("num_rows", _i32), ("max_rows_per_segment", _i32),
-        ("row_gather", _vp), ("status_dev", _vp), ("flags", _i32),
+        ("row_gather", _vp), ("status_dev", _vp), ("flags", _i32), ("hidden_row_stride", _i32),
     ]
 
 
@@ -68,6 +68,7 @@ SIGNATURES = {
     "tris_build_row_groups": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "tris_compact3_dequantize": (C.c_int, [_P(TrisProjView), _vp, _vp]),
     "tris_build_grouped_route": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tris_ep_pack_rows": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "tris_router_topk": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "tris_shared_hidden_forward": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _vp]),
     "tris_grouped_forward": (C.c_int, [_P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp]),

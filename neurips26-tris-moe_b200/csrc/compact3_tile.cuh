@@ -421,7 +421,7 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
 template <int NPROJ, int NT, typename RowSrc>
 __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, const __half* const* hidden,
                                                    const TrisProjView* views, int p0, int nrows, bool interleaved,
-                                                   RowSrc row_src) {
+                                                   int row_stride, RowSrc row_src) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = views[0].rank;
   const int c0 = 32 * p0;
@@ -436,7 +436,7 @@ __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, cons
         const int src = row_src(n);
         if (src >= 0)
           bytes += lane_copy(reinterpret_cast<uint32_t*>(sm.hrows + (proj * NT * 8 + n) * kHiddenRowBytes),
-                             reinterpret_cast<const uint32_t*>(hidden[proj] + static_cast<size_t>(src) * rank + c0),
+                             reinterpret_cast<const uint32_t*>(hidden[proj] + static_cast<size_t>(src) * row_stride + c0),
                              ncols >> 1, &sm.mbar[2]);
       }
       if (bytes) mbar_arrive_expect_tx(&sm.mbar[2], bytes);
@@ -457,7 +457,7 @@ __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, cons
 #pragma unroll
     for (int u = 0; u < 8; ++u) vals[u] = __ushort_as_half(0);
     if (src >= 0 && col < rank) {
-      const __half* rowp = hidden[proj] + static_cast<size_t>(src) * rank + col;
+      const __half* rowp = hidden[proj] + static_cast<size_t>(src) * row_stride + col;
       if ((rank & 7) == 0 && col + 8 <= rank && (reinterpret_cast<uintptr_t>(rowp) & 15u) == 0) {
         *reinterpret_cast<uint4*>(vals) = *reinterpret_cast<const uint4*>(rowp);
       } else {
@@ -692,6 +692,7 @@ struct GroupedArgs {
   int32_t num_segments;
   int32_t num_rows;
   int32_t hidden_interleaved;
+  int32_t hidden_stride;        // halves between consecutive activation rows (>= rank)
   int32_t weights_before_wait;  // route arrays were final before the predecessor kernel started
   int32_t ksplit;               // CTAs per cluster sharing one tile: each takes 8/ksplit packed rows of a chunk
 };

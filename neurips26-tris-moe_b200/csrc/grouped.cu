@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       const bool need_w = staged_chunk != kc;
       auto row_src = [&](int n) { return args.row_gather ? args.row_gather[r0 + n] : (r0 + n); };
       if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0, p_lo, p_hi);
-      if (waited) stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, row_src);
+      if (waited) stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, args.hidden_stride, row_src);
       __syncthreads();
       TRIS_MARK(1);
       bool ok = true;
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
         pdl_wait();
         pdl_launch_dependents();
         waited = true;
-        stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, row_src);
+        stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, args.hidden_stride, row_src);
         __syncthreads();
       }
       TRIS_MARK(2);
@@ -454,6 +454,7 @@ static int fill_route(GroupedArgs& a, const TrisRouteView* route) {
   a.num_rows = route->num_rows;
   a.status = route->status_dev;
   a.hidden_interleaved = (route->flags & TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED) != 0;
+  a.hidden_stride = route->hidden_row_stride;
   return TRIS_OK;
 }
 
@@ -556,6 +557,8 @@ int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* ro
   if (a.num_segments == 0 || a.num_rows == 0) return TRIS_OK;
   TRIS_REQUIRE(!a.hidden_interleaved || proj->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
                "tris_grouped_forward: pair-interleaved activations need rank % 32 == 0");
+  if (a.hidden_stride <= 0) a.hidden_stride = proj->rank;
+  TRIS_REQUIRE(a.hidden_stride >= proj->rank, TRIS_ERR_INVALID_ARG, "tris_grouped_forward: hidden_row_stride < rank");
   a.proj[0] = *proj;
   a.proj[1] = *proj;
   a.hidden[0] = a.hidden[1] = static_cast<const __half*>(hidden_f16);
@@ -593,6 +596,8 @@ int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjVi
   if (a.num_segments == 0 || a.num_rows == 0) return TRIS_OK;
   TRIS_REQUIRE(!a.hidden_interleaved || proj_a->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
                "tris_grouped_pair_forward: pair-interleaved activations need rank % 32 == 0");
+  if (a.hidden_stride <= 0) a.hidden_stride = proj_a->rank;
+  TRIS_REQUIRE(a.hidden_stride >= proj_a->rank, TRIS_ERR_INVALID_ARG, "tris_grouped_pair_forward: hidden_row_stride < rank");
   a.proj[0] = *proj_a;
   a.proj[1] = *proj_b;
   a.hidden[0] = static_cast<const __half*>(hidden_a_f16);

@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
           stage_operand_async<NB>(b_op + proj * UmmaGeom<NPROJ>::kBBytes + cc * 8 * NB * 16, hid, [&](int n) -> const __half* {
             if (n >= rows) return nullptr;
             const int src = args.row_gather ? args.row_gather[r0 + n] : (r0 + n);
-            return hid + static_cast<size_t>(src) * rank + 64 * cc;
+            return hid + static_cast<size_t>(src) * args.hidden_stride + 64 * cc;
           }, min(8, (rank - 64 * cc) / 8));
         }
       }
@@ -227,7 +227,8 @@ static int launch_umma_grouped(const GroupedArgs& args, cudaStream_t stream, boo
 // most one 256-column chunk.
 bool grouped_umma_applicable(const GroupedArgs& args, int rows_hint) {
   const TrisProjView& v = args.proj[0];
-  return rows_hint > 32 && args.hidden_interleaved && (v.rank % 32) == 0 && v.rank <= 256 && args.ksplit <= 1;
+  return rows_hint > 32 && args.hidden_interleaved && (v.rank % 32) == 0 && v.rank <= 256 && args.ksplit <= 1 &&
+         (args.hidden_stride % 8) == 0;
 }
 
 int launch_grouped_umma(const GroupedArgs& args, int nproj, int epi, cudaStream_t stream, bool pdl) {

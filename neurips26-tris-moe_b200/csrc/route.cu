@@ -2,6 +2,8 @@
 //
 // The route is built entirely on the device and written into arrays padded to the number
 // of experts, so the launch sequence of a layer never waits on the host.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace tris {
@@ -288,9 +290,75 @@ int launch_router_route(const float* logits, int num_tokens, int num_experts, in
                     "build_route_kernel launch");
 }
 
+// Owner rank of an expert under the contiguous partition (sizes differ by at most one).
+__device__ __forceinline__ int ep_owner(int e, int base, int extra) {
+  const int big = extra * (base + 1);
+  return e < big ? e / (base + 1) : extra + (e - big) / max(base, 1);
+}
+
+// grid = rows (one warp-sized group of 16-byte copies per row), 128 threads
+__global__ void __launch_bounds__(128) ep_pack_rows_kernel(
+    const __half* __restrict__ hidden_gate, const __half* __restrict__ hidden_up, int rank_gu,
+    const int32_t* __restrict__ selected, const int32_t* __restrict__ perm, const int32_t* __restrict__ tok,
+    int num_rows, int top_k, int num_experts, int world, int capacity, __half* __restrict__ send_rows,
+    int32_t* __restrict__ send_ids, int32_t* __restrict__ combine_index, int32_t* __restrict__ overflow) {
+  __shared__ int32_t s_first[64];  // first grouped row owned by each rank (world <= 64)
+  const int base = num_experts / world, extra = num_experts % world;
+  // rows are sorted by expert, so the first row of rank d is a lower bound: binary search
+  if (threadIdx.x < world) {
+    const int d = threadIdx.x;
+    int lo = 0, hi = num_rows;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (ep_owner(selected[perm[mid]], base, extra) < d) lo = mid + 1;
+      else hi = mid;
+    }
+    s_first[d] = lo;
+  }
+  __syncthreads();
+  for (int pos = blockIdx.x; pos < world * capacity; pos += gridDim.x) {
+    // slot pos = (owner d, offset): which grouped row, if any, lands here?
+    const int d = pos / capacity, off = pos - d * capacity;
+    const int row = s_first[d] + off;
+    const int row_end = (d + 1 < world) ? s_first[d + 1] : num_rows;
+    const bool used = row < row_end;
+    if (threadIdx.x == 0) {
+      send_ids[pos] = used ? selected[perm[row]] : -1;
+      if (used) combine_index[perm[row]] = pos;
+      if (off == capacity - 1 && row + 1 < row_end) *overflow = 1;  // more rows for this rank than slots
+    }
+    if (!used) continue;
+    const int t = tok[row];
+    const uint4* g = reinterpret_cast<const uint4*>(hidden_gate + static_cast<size_t>(t) * rank_gu);
+    const uint4* u = reinterpret_cast<const uint4*>(hidden_up + static_cast<size_t>(t) * rank_gu);
+    uint4* dst = reinterpret_cast<uint4*>(send_rows + static_cast<size_t>(pos) * 2 * rank_gu);
+    const int vecs = rank_gu >> 3;
+    for (int i = threadIdx.x; i < 2 * vecs; i += blockDim.x) dst[i] = (i < vecs) ? g[i] : u[i - vecs];
+  }
+}
+
 }  // namespace tris
 
 using namespace tris;
+
+extern "C" int tris_ep_pack_rows(const void* hidden_gate_f16, const void* hidden_up_f16, int32_t rank_gu,
+                                 const int32_t* selected_experts, const int32_t* perm,
+                                 const int32_t* grouped_token_indices, int32_t num_rows, int32_t top_k,
+                                 int32_t num_experts, int32_t world, int32_t capacity, void* send_rows_f16,
+                                 int32_t* send_ids, int32_t* combine_index, int32_t* overflow_dev, void* stream) {
+  TRIS_REQUIRE(hidden_gate_f16 && hidden_up_f16 && selected_experts && perm && grouped_token_indices && send_rows_f16 &&
+                   send_ids && combine_index && overflow_dev,
+               TRIS_ERR_INVALID_ARG, "tris_ep_pack_rows: null pointer");
+  TRIS_REQUIRE(rank_gu > 0 && (rank_gu & 7) == 0, TRIS_ERR_UNSUPPORTED, "tris_ep_pack_rows: rank must be a multiple of 8");
+  TRIS_REQUIRE(num_rows >= 0 && top_k > 0 && num_experts > 0 && world >= 1 && world <= 64 && capacity > 0,
+               TRIS_ERR_INVALID_ARG, "tris_ep_pack_rows: bad sizes rows=%d world=%d capacity=%d", num_rows, world, capacity);
+  const int slots = world * capacity;
+  ep_pack_rows_kernel<<<std::min(slots, 4096), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(hidden_gate_f16), static_cast<const __half*>(hidden_up_f16), rank_gu, selected_experts,
+      perm, grouped_token_indices, num_rows, top_k, num_experts, world, capacity, static_cast<__half*>(send_rows_f16),
+      send_ids, combine_index, overflow_dev);
+  return check_cuda(cudaGetLastError(), "ep_pack_rows_kernel launch");
+}
 
 extern "C" int tris_router_topk(const float* router_logits, int32_t num_tokens, int32_t num_experts, int32_t top_k,
                                 int32_t norm_topk_prob, int32_t* selected_experts, float* routing_weights,

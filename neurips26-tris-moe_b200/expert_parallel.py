@@ -126,6 +126,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         self.shared: dict = {}
         self.router_weight: Optional[torch.Tensor] = None
         self.capacity_tokens = 0  # tokens per rank the fixed-capacity exchange is sized for
+        self._overflow = None
 
     def set_capacity(self, max_tokens_per_rank: int) -> "ExpertParallelMoeBlock":
         """Sizes the fixed-capacity exchange: every rank must use the same value, at least the
@@ -165,7 +166,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         return {"perm": perm, "tok": tok, "slot": slot, "row_of_flat": rof, "expert_ids": ids, "segment_offsets": seg,
                 "counts": counts, "_buf": buf, "rows": R, "experts": E, "max_rows": T}
 
-    def _route_view(self, route: dict, row_gather, interleaved: bool) -> TrisRouteView:
+    def _route_view(self, route: dict, row_gather, interleaved: bool, hidden_stride: int = 0) -> TrisRouteView:
         rv = TrisRouteView()
         rv.expert_ids = route["expert_ids"].data_ptr()
         rv.segment_offsets = route["segment_offsets"].data_ptr()
@@ -176,6 +177,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         rv.row_gather = None if row_gather is None else row_gather.data_ptr()
         rv.status_dev = None
         rv.flags = 1 if interleaved else 0
+        rv.hidden_row_stride = int(hidden_stride)
         return rv
 
     def _backbone(self, x: torch.Tensor, sv: torch.Tensor, interleaved: bool, live_rows=None) -> torch.Tensor:
@@ -202,14 +204,15 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         r_gu = int(self.shared["gate"].shape[0])
         r_d = int(self.shared["down"].shape[0])
         inter_gu, inter_d = r_gu % 32 == 0, r_d % 32 == 0
-        hg = recv_hidden[:, :r_gu].contiguous()
-        hu = recv_hidden[:, r_gu:].contiguous()
+        recv_hidden = recv_hidden.contiguous()  # [rows, 2*r_gu]: gate and up backbone outputs side by side
+        hg_ptr = recv_hidden.data_ptr()
+        hu_ptr = hg_ptr + 2 * r_gu
         route = self._route(recv_local_ids.reshape(Rr, 1).contiguous(), self.hi - self.lo)
         route["max_rows"] = rows_hint if rows_hint > 0 else Rr
         va, vb, vd = (proj_view(self.payloads[n]) for n in ("gate", "up", "down"))
         mlp = torch.empty((Rr, self.intermediate_size), dtype=torch.float16, device=dev)
-        rv = self._route_view(route, route["tok"], inter_gu)
-        _native.check(lib.tris_grouped_pair_forward(C.byref(va), C.byref(vb), C.byref(rv), hg.data_ptr(), hu.data_ptr(),
+        rv = self._route_view(route, route["tok"], inter_gu, hidden_stride=2 * r_gu)
+        _native.check(lib.tris_grouped_pair_forward(C.byref(va), C.byref(vb), C.byref(rv), hg_ptr, hu_ptr,
                                                     mlp.data_ptr(), None, 1, stream), "grouped_pair_forward")
         live = route["segment_offsets"][route["experts"]:]  # total routed rows, on the device
         hd = self._backbone(mlp, self.shared["down"], inter_d, live_rows=live)
@@ -249,12 +252,13 @@ class ExpertParallelMoeBlock(torch.nn.Module):
             route = self._route(sel, self.num_experts)
             r_gu = int(self.shared["gate"].shape[0])
             inter = r_gu % 32 == 0
-            hidden = torch.cat([self._backbone(x, self.shared["gate"], inter),
-                                self._backbone(x, self.shared["up"], inter)], dim=1)
-            grouped_hidden = hidden.index_select(0, route["tok"].to(torch.long))
-            grouped_ids = sel.reshape(-1).index_select(0, route["perm"].to(torch.long))
+            hg = self._backbone(x, self.shared["gate"], inter)
+            hu = self._backbone(x, self.shared["up"], inter)
             y = torch.empty_like(x)
             if exact_splits:
+                tok = route["tok"].to(torch.long)
+                grouped_hidden = torch.cat([hg, hu], dim=1).index_select(0, tok)
+                grouped_ids = sel.reshape(-1).index_select(0, route["perm"].to(torch.long))
                 returned = expert_parallel_exchange(grouped_hidden, grouped_ids, self.num_experts, self._local_experts,
                                                     self.group)
                 index = route["row_of_flat"]
@@ -265,37 +269,47 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                 if T > self.capacity_tokens:
                     raise RuntimeError(f"trismoe_b200: batch of {T} tokens exceeds the exchange capacity "
                                        f"{self.capacity_tokens} set with set_capacity()")
-                returned, dest = self._padded_exchange(grouped_hidden, grouped_ids, self.capacity_tokens * self.top_k)
-                index = dest.index_select(0, route["row_of_flat"].to(torch.long)).to(torch.int32)
+                returned, index = self._padded_exchange(hg, hu, sel, route, self.capacity_tokens * self.top_k)
             if T:
                 _native.check(lib.tris_combine_routed(returned.data_ptr(), index.data_ptr(), wts.data_ptr(),
                                                       T, self.top_k, self.hidden_size, y.data_ptr(), stream), "combine")
         return y.reshape(shape), logits
 
-    def _padded_exchange(self, grouped_hidden: torch.Tensor, grouped_ids: torch.Tensor, capacity: int):
-        """Fixed-capacity exchange; every rank must call it with the same ``capacity``.  Returns
-        the result rows laid out [peer, capacity, H] (flattened) and, for every grouped row,
-        its index in that layout."""
-        dev, N = grouped_hidden.device, self.world
-        R, W = int(grouped_hidden.shape[0]), int(grouped_hidden.shape[1])
-        owners = owner_of(grouped_ids, self.num_experts, N)
-        counts = (owners.unsqueeze(1) == torch.arange(N, device=dev).unsqueeze(0)).sum(dim=0)
-        rank_start = torch.cumsum(counts, 0) - counts
-        dest = owners * capacity + (torch.arange(R, device=dev) - rank_start.index_select(0, owners))
-        send_rows = torch.zeros((N * capacity, W), dtype=grouped_hidden.dtype, device=dev)
-        send_ids = torch.full((N * capacity,), -1, dtype=torch.int32, device=dev)
-        send_rows.index_copy_(0, dest, grouped_hidden)
-        send_ids.index_copy_(0, dest, grouped_ids.to(torch.int32))
+    def _padded_exchange(self, hg: torch.Tensor, hu: torch.Tensor, sel: torch.Tensor, route: dict, capacity: int):
+        """Fixed-capacity exchange; every rank must call it with the same ``capacity`` (rows per
+        peer slot).  One kernel packs the routed rows into the [peer, capacity] send layout,
+        three equal-split all-to-alls move rows, expert ids and results; nothing is read back
+        to the host.  Returns the result rows in the send layout and, for every flat
+        (token, slot) entry, the index of its row there."""
+        lib = _native.load()
+        dev, N = hg.device, self.world
+        R, r_gu = int(route["rows"]), int(hg.shape[1])
+        slots = N * capacity
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        send_rows = torch.empty((slots, 2 * r_gu), dtype=torch.float16, device=dev)
+        send_ids = torch.empty((slots,), dtype=torch.int32, device=dev)
+        index = torch.empty((max(R, 1),), dtype=torch.int32, device=dev)
+        if self._overflow is None or self._overflow.device != dev:
+            self._overflow = torch.zeros((1,), dtype=torch.int32, device=dev)
+        _native.check(lib.tris_ep_pack_rows(hg.data_ptr(), hu.data_ptr(), r_gu, sel.data_ptr(), route["perm"].data_ptr(),
+                                            route["tok"].data_ptr(), R, self.top_k, self.num_experts, N, capacity,
+                                            send_rows.data_ptr(), send_ids.data_ptr(), index.data_ptr(),
+                                            self._overflow.data_ptr(), stream), "ep_pack_rows")
         recv_rows = torch.empty_like(send_rows)
         recv_ids = torch.empty_like(send_ids)
         dist.all_to_all_single(recv_rows, send_rows, group=self.group)
         dist.all_to_all_single(recv_ids, send_ids, group=self.group)
-        local_ids = torch.where(recv_ids >= 0, recv_ids - self.lo, recv_ids)
+        local_ids = recv_ids - self.lo  # padding slots (-1) stay negative and are skipped by the route
         expected = max(1, (N * R) // max(1, self.hi - self.lo))  # rows per local expert if routing is balanced
         result = self._local_experts(recv_rows, local_ids, rows_hint=int(expected + 4 * expected ** 0.5))
         back = torch.empty_like(result)
         dist.all_to_all_single(back, result, group=self.group)
-        return back, dest
+        return back, index
+
+    def exchange_overflowed(self) -> bool:
+        """True if any fixed-capacity exchange so far had more rows for a peer than slots
+        (cannot happen with the default capacity of tokens * top_k); reads one device word."""
+        return self._overflow is not None and bool(self._overflow.item())
 
     def _backbone_f32(self, x: torch.Tensor) -> torch.Tensor:
         if self.router_weight is None:
