@@ -396,7 +396,26 @@ def run_extra(args):
             torch.cuda.synchronize()
             ms = start.elapsed_time(stop) / reps
             rep = manager.overlap_report()
+            # the same step as one CUDA graph (kernels on two streams, ordered by events)
+            graph_ms = None
+            try:
+                manager.collect_timings = False
+
+                def step():
+                    for l, blk in enumerate(blocks):
+                        blk.forward_streaming(x.view(1, T, 2048), manager, l)
+
+                graph = capture(step)
+                graph_ms = time_replays(graph, 10, 3)
+                del graph
+            except Exception as exc:  # noqa: BLE001
+                graph_ms = None
+                torch.cuda.synchronize()
+            finally:
+                manager.collect_timings = True
             recs.append({"tokens": T, "us_per_layer": round(ms * 1e3 / len(blocks), 2), "tokens_per_s": round(T / (ms * 1e-3), 1),
+                         "graph_us_per_layer": None if graph_ms is None else round(graph_ms * 1e3 / len(blocks), 2),
+                         "graph_tokens_per_s": None if graph_ms is None else round(T / (graph_ms * 1e-3), 1),
                          "overlapped_fraction": None if rep["overlapped_fraction"] is None else round(rep["overlapped_fraction"], 3),
                          "copy_ms_per_layer": round(rep["copy_ms"] / max(1, rep["layers"]), 4),
                          "staging_buffer_mb": round(manager.buffer_nbytes / 1e6, 1)})

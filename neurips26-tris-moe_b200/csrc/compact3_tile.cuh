@@ -35,6 +35,9 @@
 #ifndef TRIS_SUBMARK
 #define TRIS_SUBMARK(k) do { } while (0)
 #endif
+#ifndef TRIS_MARK_T
+#define TRIS_MARK_T(k, tid) do { } while (0)
+#endif
 
 namespace tris {
 
@@ -120,50 +123,79 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t smem_addr) {
 
 // Decodes `n_ones` codewords of a block staged in shared memory, starting at (bitpos,
 // flatpos), and calls set(flat) for each one.  The loop is a serial dependency chain (the
-// next codeword starts where this one ends), so it is kept to the bare minimum: one
-// shared-memory window load, find-first-set, two adds.  Zero runs of 32 or more and
-// remainders that straddle the 32-bit window take the rare slow branch.  Reads stay inside
-// the block's words plus the two words of slack every staged span has behind it.
+// next codeword starts where this one ends).  The common case runs in a branch-light inner
+// loop: the stream is read through a three-word register window (the 64 bits being parsed
+// plus one word fetched ahead, so no load sits on the chain), a codeword costs a funnel
+// shift, a count of trailing zeros and a few adds, and positions past the block are dropped
+// by predication.  A zero run of 32 or more, or a remainder that straddles the 32-bit view,
+// leaves the inner loop for a general step that also bounds malformed streams.  Reads stay
+// inside the block's words plus three words behind them; every staged span has that much
+// slack (its neighbour's words or the tail of the buffer).
 template <typename SetBit>
 __device__ __forceinline__ void gr_decode_run(const uint32_t* w, int nwords, int k, int n_ones, int bitpos,
                                               int flatpos, SetBit set) {
   const int total_bits = nwords << 5;
   const uint32_t kmask = (1u << k) - 1u;
+  const int k1 = k + 1;
   const uint32_t base = smem_u32(w);
-  for (int n = 0; n < n_ones; ++n) {
-    const int wi = min(bitpos >> 5, nwords);
-    const uint32_t addr = base + (static_cast<uint32_t>(wi) << 2);
-    uint32_t v = __funnelshift_r(lds_u32(addr), lds_u32(addr + 4), bitpos & 31);
-    int t = __ffs(v) - 1;
-    int q = 0;
-    uint32_t rem = ((v >> t) >> 1) & kmask;
-    if (v == 0u || t + 1 + k > 32) {  // rare
-      while (v == 0u) {
-        q += 32;
-        bitpos += 32;
-        if (bitpos >= total_bits) return;  // stream ran out: malformed, stop
-        v = gr_peek32(w, nwords, bitpos);
+  const uint32_t last = base + (static_cast<uint32_t>(nwords) << 2);
+  uint32_t addr = base + (static_cast<uint32_t>(min(bitpos >> 5, nwords)) << 2);
+  uint32_t lo = lds_u32(addr), hi = lds_u32(addr + 4), nx = lds_u32(addr + 8);
+  int sh = bitpos & 31;
+  int n = 0;
+  for (;;) {
+    int t = 0;
+#pragma unroll 2
+    for (; n < n_ones; ++n) {
+      const uint32_t v = __funnelshift_r(lo, hi, sh);
+      t = __clz(__brev(v));  // zero run length; 32 when the view holds no one
+      if (t + k1 > 32) break;
+      const uint32_t rem = __funnelshift_r(v, 0u, t + 1) & kmask;
+      const int pos = flatpos + (t << k) + static_cast<int>(rem);
+      if (pos < TRIS_GR_BLOCK_WORDS * 32) set(pos);
+      flatpos = pos + 1;
+      sh += t + k1;
+      if (sh >= 32) {
+        sh -= 32;
+        lo = hi;
+        hi = nx;
+        addr = min(addr + 4, last);
+        nx = lds_u32(addr + 8);  // needed two words from now: its latency is off the chain
       }
-      t = __ffs(v) - 1;
-      rem = gr_peek32(w, nwords, bitpos + t + 1) & kmask;
     }
-    bitpos += t + 1 + k;
-    flatpos += ((q + t) << k) + static_cast<int>(rem);
-    if (flatpos >= TRIS_GR_BLOCK_WORDS * 32 || bitpos > total_bits) return;
-    set(flatpos);
-    ++flatpos;
+    if (n >= n_ones) return;
+    // general step: long zero run or remainder beyond the 32-bit view
+    bitpos = (static_cast<int>(addr - base) << 3) + sh;
+    int q = 0;
+    uint32_t v = gr_peek32(w, nwords, bitpos);
+    while (v == 0u) {
+      q += 32;
+      bitpos += 32;
+      if (bitpos >= total_bits) return;  // stream ran out: malformed, stop
+      v = gr_peek32(w, nwords, bitpos);
+    }
+    t = __ffs(v) - 1;
+    const uint32_t rem = gr_peek32(w, nwords, bitpos + t + 1) & kmask;
+    bitpos += t + k1;
+    const int pos = flatpos + ((q + t) << k) + static_cast<int>(rem);
+    if (pos >= TRIS_GR_BLOCK_WORDS * 32 || bitpos > total_bits) return;
+    set(pos);
+    flatpos = pos + 1;
+    ++n;
+    addr = base + (static_cast<uint32_t>(min(bitpos >> 5, nwords)) << 2);
+    lo = lds_u32(addr), hi = lds_u32(addr + 4), nx = lds_u32(addr + 8);
+    sh = bitpos & 31;
   }
 }
 
-// Word index inside the chunk planes of flat word `wl` (0..127) of chunk-local block b.
+// The bit planes of a chunk (sign plane, g_map / select plane) are stored block by block, in
+// the block-GR order: chunk-local block b = (proj * 4 + k block) * NOB + out block holds its
+// 128 words [packed row parity][64 outputs] contiguously, so a decoded block needs no index
+// arithmetic and a raw block is a straight copy.
 template <int NPROJ>
-__device__ __forceinline__ int block_word_to_tile(int b, int wl) {
-  constexpr int OW = Geom<NPROJ>::OW;
+__device__ __forceinline__ int plane_index(int proj, int p, int o) {
   constexpr int NOB = Geom<NPROJ>::NOB;
-  const int obl = b % NOB;
-  const int kbl = (b / NOB) & 3;
-  const int proj = b / (NOB * 4);
-  return (proj * KC + 2 * kbl + (wl >> 6)) * OW + obl * 64 + (wl & 63);
+  return ((proj * 4 + (p >> 1)) * NOB + (o >> 6)) * 128 + (p & 1) * 64 + (o & 63);
 }
 
 // ---- bit-plane helpers ----------------------------------------------------------------
@@ -219,15 +251,15 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
     fence_proxy_async();
     uint32_t bytes = 0;
     uint64_t* bar = &sm.mbar[0];
-    if (lane < NPROJ * KC) {  // sign plane rows
-      const int proj = lane / KC, p = lane % KC;
+    if (lane < NPROJ * KC * NOB) {  // sign plane rows, one 64-output piece each (16 lanes)
+      const int obl = lane % NOB, p = (lane / NOB) % KC, proj = lane / (NOB * KC);
       const TrisProjView& v = views[proj];
       const int pr = proj_packed_rows(v);
-      const int wv = min(OW, v.out_features - o0);
+      const int wv = min(64, v.out_features - (o0 + 64 * obl));
       if (p0 + p < pr && wv > 0 && p >= p_lo && p < p_hi)
-        bytes += lane_copy(sm.s1 + (proj * KC + p) * OW,
+        bytes += lane_copy(sm.s1 + plane_index<NPROJ>(proj, p, 64 * obl),
                            reinterpret_cast<const uint32_t*>(v.qweight1) +
-                               (static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0,
+                               (static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0 + 64 * obl,
                            wv, bar);
     } else if (lane < 16 + NPROJ) {  // column scale packs
       const int proj = lane - 16;
@@ -539,7 +571,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
       const bool raw = (sm.binfo[b * 4 + 2] & TRIS_GR_META_RAW_FLAG) != 0;
       uint32_t word = 0u;
       if (raw && wl < sm.binfo[b * 4 + 1]) word = sm.gmraw[sm.binfo[b * 4 + 0] + wl];
-      sm.g[block_word_to_tile<NPROJ>(b, wl)] = word;
+      sm.g[i] = word;
     }
     __syncthreads();
     const int sub = views[0].gr_substreams;  // a power of two
@@ -550,17 +582,16 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
       const int meta = sm.binfo[b * 4 + 2];
       if (count <= 0 || (meta & TRIS_GR_META_RAW_FLAG)) continue;
       const int k = meta & TRIS_GR_META_K_MASK;
-      const int one_count = meta >> TRIS_GR_META_ONE_COUNT_SHIFT;
+      const int one_count = min(meta >> TRIS_GR_META_ONE_COUNT_SHIFT, TRIS_GR_BLOCK_WORDS * 32);  // a block has 4096 bits
       const int per = (one_count + sub - 1) >> sub_log2;
       const int first = j * per;
       if (per == 0 || first >= one_count) continue;
       const int n_ones = min(per, one_count - first);
       const uint32_t packed = sm.gridx[b * 32 + j];
-      uint32_t* gblock = sm.g + block_word_to_tile<NPROJ>(b, 0);  // word wl of the block sits at (wl>>6)*OW + (wl&63)
+      uint32_t* gblock = sm.g + b * 128;
       gr_decode_run(sm.gmraw + sm.binfo[b * 4 + 0], count, k, n_ones, static_cast<int>(packed & 0xFFFFu),
-                    static_cast<int>(packed >> 16), [&](int flat) {
-                      atomicOr(gblock + ((flat >> 11) * OW) + ((flat >> 5) & 63), 1u << (flat & 31));
-                    });
+                    static_cast<int>(packed >> 16),
+                    [&](int flat) { atomicOr(gblock + (flat >> 5), 1u << (flat & 31)); });
     }
     __syncthreads();
     TRIS_SUBMARK(6);
@@ -571,10 +602,12 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
   //   fp16(+-a +- b) = sign1 * fp16(a + (sign1*sign2) b)
   // so a salient weight is again "pick one of two magnitudes, then apply sign1" with
   // magnitudes fp16(a+b) and fp16(a-b).
-  for (int i = tid; i < kTileWords; i += kThreads) {
-    const int proj = i / (KC * OW);
-    const int p = (i / OW) % KC;
-    const int o = i % OW;
+  constexpr int NOB = Geom<NPROJ>::NOB;
+  for (int i = tid; i < kTileWords; i += kThreads) {  // i is a plane index (block-major)
+    const int b = i >> 7, wl = i & 127;
+    const int proj = b / (NOB * 4);
+    const int p = 2 * ((b / NOB) & 3) + (wl >> 6);
+    const int o = (b % NOB) * 64 + (wl & 63);
     if (p < p_lo || p >= p_hi) continue;
     const TrisProjView& v = views[proj];
     const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
@@ -665,7 +698,7 @@ __device__ __forceinline__ void unpack_fragments(const TileSmem<NPROJ, NT>& sm, 
   uint4 ct[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) ct[i] = sm.coltab[((proj * KC + p) * 4 + i) * 4 + t];
-  const int idx = (proj * KC + p) * OW + out_local + g;
+  const int idx = plane_index<NPROJ>(proj, p, out_local + g);
   const uint32_t s1a = sm.s1[idx], s1b = sm.s1[idx + 8];
   const uint32_t sea = sm.g[idx], seb = sm.g[idx + 8];
   const bool any_salient = info.cw != 0u;

@@ -13,15 +13,17 @@
 
 // Development builds (-DTRIS_PHASE_TIMERS) stamp clock64() at phase boundaries of every CTA.
 #ifdef TRIS_PHASE_TIMERS
-namespace tris { __device__ long long* g_phase_stamps = nullptr; }
-#define TRIS_MARK(k)                                                                                          \
+namespace tris { __constant__ long long* g_phase_stamps = nullptr; }
+#define TRIS_MARK_T(k, tid)                                                                                   \
   do {                                                                                                        \
-    if (threadIdx.x == 0 && ::tris::g_phase_stamps)                                                           \
-      ::tris::g_phase_stamps[((static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (k)] = clock64(); \
+    if (threadIdx.x == (tid) && ::tris::g_phase_stamps)                                                       \
+      ::tris::g_phase_stamps[((static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 24 + (k)] = clock64(); \
   } while (0)
+#define TRIS_MARK(k) TRIS_MARK_T(k, 0)
 #define TRIS_SUBMARK(k) TRIS_MARK(k)
 #else
 #define TRIS_MARK(k) do { } while (0)
+#define TRIS_MARK_T(k, tid) do { } while (0)
 #endif
 
 #include "compact3_tile.cuh"
@@ -142,7 +144,8 @@ __global__ void __launch_bounds__(kThreads) compact3_dump_kernel(TrisProjView v,
     for (int i = threadIdx.x; i < kTileWords; i += kThreads) {
       const int p = i / 128, o = i % 128;
       if (p0 + p < pr && o0 + o < v.out_features)
-        dense_out[(static_cast<size_t>(blockIdx.z) * pr + p0 + p) * v.out_features + o0 + o] = static_cast<int32_t>(dump[i]);
+        dense_out[(static_cast<size_t>(blockIdx.z) * pr + p0 + p) * v.out_features + o0 + o] =
+            static_cast<int32_t>(dump[plane_index<1>(0, p, o)]);
     }
   }
   if (weights_out) {
@@ -187,6 +190,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
 
   TRIS_MARK(0);
   init_barriers(sm.mbar);
+  TRIS_MARK(8);
   // Activations come from the predecessor kernel; the route arrays too, unless the caller
   // says they are older, in which case the weight staging below overlaps the predecessor.
   bool waited = false;
@@ -195,15 +199,18 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
     pdl_launch_dependents();
     waited = true;
   }
+  // seg < gridDim.y <= num_segments, the arrays' length: read them before the live count
+  // is known, so that the four loads are in flight together
   const int seg = blockIdx.y;
-  const int nseg = args.num_segments_dev ? min(*args.num_segments_dev, args.num_segments) : args.num_segments;
-  if (seg >= nseg) return;
   const int expert = args.expert_ids[seg];
   const int row_begin = args.segment_offsets[seg];
   const int row_end = min(args.segment_offsets[seg + 1], args.num_rows);
+  const int nseg = args.num_segments_dev ? min(*args.num_segments_dev, args.num_segments) : args.num_segments;
+  if (seg >= nseg) return;
   if (expert < 0 || expert >= args.proj[0].num_experts || row_end <= row_begin) return;
   // row block of the expert inside the payload tensors (a staging slot when they are paged in)
   const int e = args.proj[0].expert_slot ? args.proj[0].expert_slot[expert] : expert;
+  TRIS_MARK(9);
 
   const int o0 = blockIdx.x * OW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -233,7 +240,11 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       const bool need_w = staged_chunk != kc;
       auto row_src = [&](int n) { return args.row_gather ? args.row_gather[r0 + n] : (r0 + n); };
       if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0, p_lo, p_hi);
+      TRIS_MARK(10);
+      TRIS_MARK_T(11, 32);
+      TRIS_MARK_T(12, 96);
       if (waited) stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, args.hidden_stride, row_src);
+      TRIS_MARK_T(13, 64);
       __syncthreads();
       TRIS_MARK(1);
       bool ok = true;
@@ -261,7 +272,8 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
 
       // Per-lane base addresses; inside the fully unrolled loop every access is base + constant.
       const int p_end = min(p_hi, pr - p0);
-      const int word0 = proj * KC * OW + out_local + g;
+      constexpr int NOB = Geom<NPROJ>::NOB;
+      const int word0 = plane_index<NPROJ>(proj, 0, out_local + g);  // packed row p adds a constant
       const uint32_t* s1_base = sm.s1 + word0;
       const uint32_t* sel_base = sm.g + word0;
       const uint4* col_base = sm.coltab + proj * KC * 16 + t;
@@ -285,8 +297,10 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
         for (int i = 0; i < 4; ++i) ct[i] = col_base[p * 16 + i * 4];
         const bool any_salient = info.cw != 0u;
         uint32_t a[2][4];
-        unpack_row(s1_base[p * OW], sel_base[p * OW], rs[0], ct, any_salient, t, a[0]);
-        unpack_row(s1_base[p * OW + 8], sel_base[p * OW + 8], rs[1], ct, any_salient, t, a[1]);
+        constexpr int kRowPair = NOB * 128;  // words between k blocks of the same output block
+        const int poff = (p >> 1) * kRowPair + (p & 1) * 64;
+        unpack_row(s1_base[poff], sel_base[poff], rs[0], ct, any_salient, t, a[0]);
+        unpack_row(s1_base[poff + 8], sel_base[poff + 8], rs[1], ct, any_salient, t, a[1]);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           if (nt < nt_count) {
@@ -338,36 +352,42 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       for (int c = 0; c < 4; ++c) acc[nt][c] = acc[nt][c] * scale[c >> 1] + bias[c >> 1];
 
     if (EPI == EPI_SILU_MUL) {
-      // up warps (proj 1) hand their tile to the gate warps (proj 0) through shared memory
-      __syncthreads();
-      float* xbuf = reinterpret_cast<float*>(sm.hrows);
-      if (proj == 1) {
+      // Warps w (gate) and w+4 (up) hold the two factors of the same 16 outputs.  They split
+      // the row tiles: tile nt is finished by projection (nt & 1), the other warp hands its
+      // values over through shared memory.  Up to 4 tiles the exchange buffer is the staged
+      // bitmap data (dead since the select plane was built) and only the two warps meet, at
+      // a named barrier; the 8-tile variant needs the activation rows' space and a full barrier.
+      constexpr bool kPairBarrier = NT <= 4;
+      static_assert(!kPairBarrier || 4 * NT * 32 * 16 <= sizeof(sm.s2raw) + sizeof(sm.gmraw), "exchange buffer");
+      float* xbuf = reinterpret_cast<float*>(kPairBarrier ? reinterpret_cast<void*>(sm.s2raw) : reinterpret_cast<void*>(sm.hrows));
+      if (!kPairBarrier) __syncthreads();
+      const int pw = warp & 3;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-          if (nt < nt_count)
-            *reinterpret_cast<float4*>(xbuf + (((warp & 3) * NT + nt) * 32 + lane) * 4) =
-                make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
-      }
-      __syncthreads();
-      if (proj == 0) {
+      for (int nt = 0; nt < NT; ++nt)
+        if (nt < nt_count && (nt & 1) != proj)
+          *reinterpret_cast<float4*>(xbuf + ((pw * NT + nt) * 32 + lane) * 4) =
+              make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+      if (kPairBarrier) named_barrier_sync(1 + pw, 64);
+      else __syncthreads();
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          if (nt >= nt_count) break;
-          const float4 u = *reinterpret_cast<const float4*>(xbuf + (((warp & 3) * NT + nt) * 32 + lane) * 4);
-          const float uu[4] = {u.x, u.y, u.z, u.w};
+      for (int nt = 0; nt < NT; ++nt) {
+        if (nt >= nt_count || (nt & 1) != proj) continue;
+        const float4 o = *reinterpret_cast<const float4*>(xbuf + ((pw * NT + nt) * 32 + lane) * 4);
+        const float other[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const float gv = acc[nt][c];
-            acc[nt][c] = __fdividef(gv, 1.f + __expf(-gv)) * uu[c];
-          }
+        for (int c = 0; c < 4; ++c) {
+          const float gv = proj == 0 ? acc[nt][c] : other[c];
+          const float uv = proj == 0 ? other[c] : acc[nt][c];
+          acc[nt][c] = __fdividef(gv, 1.f + __expf(-gv)) * uv;
         }
       }
     }
-    if (EPI == EPI_STORE || proj == 0) {
-      __half* outp = args.out[proj];
+    {
+      __half* outp = args.out[EPI == EPI_SILU_MUL ? 0 : proj];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         if (nt >= nt_count) break;
+        if (EPI == EPI_SILU_MUL && (nt & 1) != proj) continue;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int n = nt * 8 + 2 * t + (c & 1);
@@ -559,6 +579,8 @@ int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* ro
                "tris_grouped_forward: pair-interleaved activations need rank % 32 == 0");
   if (a.hidden_stride <= 0) a.hidden_stride = proj->rank;
   TRIS_REQUIRE(a.hidden_stride >= proj->rank, TRIS_ERR_INVALID_ARG, "tris_grouped_forward: hidden_row_stride < rank");
+  TRIS_REQUIRE(!a.hidden_interleaved || (a.hidden_stride % 2 == 0 && reinterpret_cast<uintptr_t>(hidden_f16) % 4 == 0),
+               TRIS_ERR_INVALID_ARG, "tris_grouped_forward: pair-interleaved activation rows must be 4-byte aligned");
   a.proj[0] = *proj;
   a.proj[1] = *proj;
   a.hidden[0] = a.hidden[1] = static_cast<const __half*>(hidden_f16);
@@ -598,6 +620,9 @@ int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjVi
                "tris_grouped_pair_forward: pair-interleaved activations need rank % 32 == 0");
   if (a.hidden_stride <= 0) a.hidden_stride = proj_a->rank;
   TRIS_REQUIRE(a.hidden_stride >= proj_a->rank, TRIS_ERR_INVALID_ARG, "tris_grouped_pair_forward: hidden_row_stride < rank");
+  TRIS_REQUIRE(!a.hidden_interleaved || (a.hidden_stride % 2 == 0 && reinterpret_cast<uintptr_t>(hidden_a_f16) % 4 == 0 &&
+                                         reinterpret_cast<uintptr_t>(hidden_b_f16) % 4 == 0),
+               TRIS_ERR_INVALID_ARG, "tris_grouped_pair_forward: pair-interleaved activation rows must be 4-byte aligned");
   a.proj[0] = *proj_a;
   a.proj[1] = *proj_b;
   a.hidden[0] = static_cast<const __half*>(hidden_a_f16);

@@ -62,15 +62,6 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src, bool valid) {
-  // src-size 0 zero-fills the destination without reading the source
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 16 : 0)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // Starts the asynchronous copy of a ROWS x 64 fp16 tile (row-major source, 128 B per row) into
 // the core-matrix layout.  row_ptr(r) returns the source row (already offset to the chunk's
 // first column) or nullptr for a row that must read as zeros.

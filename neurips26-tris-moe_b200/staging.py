@@ -93,6 +93,7 @@ class GroupedQGmapCPUStagingManager:
         self._initialized = False
         self.pipeline_stats = {"calls": 0, "chunks": 0, "bytes": 0, "slot_reuses": 0}
         self._timings = []         # (copy_start, copy_end, wait_start, wait_end) events
+        self.collect_timings = True  # set False while capturing the forward into a CUDA graph
 
     @property
     def buffer_nbytes(self) -> int:
@@ -158,10 +159,14 @@ class GroupedQGmapCPUStagingManager:
             self.pipeline_stats["slot_reuses"] += 1
         nseg_bound = min(int(route["experts"]), int(route["rows"]), self.capacity)
         table = self.slot_tables[ring]
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        timed = self.collect_timings
+        start = end = None
+        if timed:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         views = {}
         with torch.cuda.stream(copy):
-            start.record(copy)
+            if timed:
+                start.record(copy)
             for proj in PROJECTIONS:
                 entry = self.entries[(block_index, proj)]
                 jobs = (TrisPageJob * len(entry.host))()
@@ -175,7 +180,8 @@ class GroupedQGmapCPUStagingManager:
                                                     table.data_ptr(), copy.cuda_stream), "page_experts")
                 self.pipeline_stats["chunks"] += 1
                 views[proj] = self._staged_view(entry, ring, proj, table)
-            end.record(copy)
+            if timed:
+                end.record(copy)
             self._paged[ring].record(copy)
         self.pipeline_stats["calls"] += 1
         self._used[ring] = True
@@ -230,11 +236,14 @@ class _PagedLayer:
         if self._waited:
             return
         compute = torch.cuda.current_stream(self.manager.device)
-        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        w0.record(compute)
-        compute.wait_event(self.manager._paged[self.ring])
-        w1.record(compute)
-        self.manager._timings.append((self._copy_start, self._copy_end, w0, w1))
+        if self._copy_start is None:
+            compute.wait_event(self.manager._paged[self.ring])
+        else:
+            w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            w0.record(compute)
+            compute.wait_event(self.manager._paged[self.ring])
+            w1.record(compute)
+            self.manager._timings.append((self._copy_start, self._copy_end, w0, w1))
         self._waited = True
 
     def release(self) -> None:
