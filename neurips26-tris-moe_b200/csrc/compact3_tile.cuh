@@ -232,7 +232,16 @@ __device__ __forceinline__ uint32_t staged_bits_at(const uint32_t* rows, int ow,
 
 // ---- stage 1: issue -------------------------------------------------------------------
 // Called by all threads after a barrier that ended every earlier use of the staging
-// buffers.  Warps 0 and 1 issue the weight copies of chunk (e, o0, p0); warp 3 fills ptab.
+// buffers.  A warp issues its bulk copies one lane after the other (60-70 cycles each),
+// warps issue side by side, and a warp that waits for a table entry stalls with all its
+// lanes.  So every warp gets one kind of work and at most ten copies:
+//   warp 0  sign-plane pieces 0-7, column scale packs      (group A: mbar[0])
+//   warp 4  sign-plane pieces 8-15, row scale packs        (A)
+//   warp 5  block-GR sub-stream index blocks (A); lanes 16+: ptab of projection 0
+//   warp 6  lanes 16+: ptab of projection 1
+//   warp 1  block-GR spans, after reading the block offsets (group B: mbar[1])
+//   warps 2, 3  salient sign rows / sparse g_map rows of projection 0, 1, after the prefixes (B)
+// Lane 0 of every warp arrives on both barriers with its warp's byte counts.
 // `e` indexes the bulky E-stacked tensors (sign planes, bitmap data, scale packs: a staging
 // slot when the payload is paged in), `ex` is the expert id and indexes the small tables
 // (c_map, prefixes, packed-row groups, block-GR offsets and meta), which stay resident.
@@ -244,63 +253,56 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
   constexpr int OW = Geom<NPROJ>::OW;
   constexpr int NOB = Geom<NPROJ>::NOB;
   constexpr int SPAN = Geom<NPROJ>::SPAN;
+  static_assert(NPROJ * KC * NOB == 16 && kBlocksPerChunk == 8 && kWarps == 8 && kSparseRows <= 16, "copy roles");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  if (warp == 0) {
-    // ---- copies whose addresses need nothing but (e, o0, p0) ---------------------------
-    fence_proxy_async();
-    uint32_t bytes = 0;
-    uint64_t* bar = &sm.mbar[0];
-    if (lane < NPROJ * KC * NOB) {  // sign plane rows, one 64-output piece each (16 lanes)
-      const int obl = lane % NOB, p = (lane / NOB) % KC, proj = lane / (NOB * KC);
+  uint64_t* bar_a = &sm.mbar[0];
+  uint64_t* bar_b = &sm.mbar[1];
+  uint32_t bytes_a = 0, bytes_b = 0;
+  if (lane < 16) fence_proxy_async();
+  if (warp == 0 || warp == 4) {
+    if (lane < 8) {  // sign plane: 16 pieces of one packed row x 64 outputs
+      const int piece = 2 * warp + lane;  // warp 0: 0-7, warp 4: 8-15
+      const int obl = piece % NOB, p = (piece / NOB) % KC, proj = piece / (NOB * KC);
       const TrisProjView& v = views[proj];
       const int pr = proj_packed_rows(v);
       const int wv = min(64, v.out_features - (o0 + 64 * obl));
       if (p0 + p < pr && wv > 0 && p >= p_lo && p < p_hi)
-        bytes += lane_copy(sm.s1 + plane_index<NPROJ>(proj, p, 64 * obl),
-                           reinterpret_cast<const uint32_t*>(v.qweight1) +
-                               (static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0 + 64 * obl,
-                           wv, bar);
-    } else if (lane < 16 + NPROJ) {  // column scale packs
-      const int proj = lane - 16;
-      if (proj >= 0) {
-        const TrisProjView& v = views[proj];
+        bytes_a += lane_copy(sm.s1 + plane_index<NPROJ>(proj, p, 64 * obl),
+                             reinterpret_cast<const uint32_t*>(v.qweight1) +
+                                 (static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0 + 64 * obl,
+                             wv, bar_a);
+    } else if (lane < 8 + NPROJ) {
+      const int proj = lane - 8;
+      const TrisProjView& v = views[proj];
+      if (warp == 0) {  // column scale packs
         const int c0 = 32 * p0, c1 = min(v.rank, 32 * (p0 + KC));
         if (c1 > c0)
-          bytes += lane_copy(reinterpret_cast<uint32_t*>(sm.colraw + proj * 256),
-                             reinterpret_cast<const uint32_t*>(v.col_pack3 + static_cast<size_t>(e) * v.rank + c0),
-                             2 * (c1 - c0), bar);
-      }
-    } else if (lane >= 18 && lane < 18 + NPROJ) {  // row scale packs, all groups, when they fit
-      const int proj = lane - 18;
-      const TrisProjView& v = views[proj];
-      const int G = v.num_groups;
-      const int wv = min(OW, v.out_features - o0);
-      if (G * NPROJ * OW <= kRowTabEntries && wv > 0)
-        bytes += lane_copy(reinterpret_cast<uint32_t*>(sm.rowtab + proj * OW * G),
-                           reinterpret_cast<const uint32_t*>(v.row_pack3 + (static_cast<size_t>(e) * v.out_features + o0) * G),
-                           2 * wv * G, bar);
-    } else if (lane >= 20 && lane < 20 + kBlocksPerChunk) {  // block-GR sub-stream index
-      const int b = lane - 20;
-      const TrisProjView& v = views[b / (NOB * 4)];
-      if (v.use_block_gr && v.gr_index != nullptr) {
-        const int pr = proj_packed_rows(v);
-        const int nkb = (pr + 1) >> 1, nob = (v.out_features + 63) >> 6;
-        const int kbl = (b / NOB) & 3;
-        const int kb = (p0 >> 1) + kbl, ob = (o0 >> 6) + (b % NOB);
-        if (kb < nkb && ob < nob && 2 * kbl >= p_lo && 2 * kbl < p_hi) {
-          const size_t bi = static_cast<size_t>(e) * nkb * nob + static_cast<size_t>(kb) * nob + ob;
-          bytes += lane_copy(sm.gridx + b * 32, v.gr_index + bi * v.gr_substreams, v.gr_substreams, bar);
-        }
+          bytes_a += lane_copy(reinterpret_cast<uint32_t*>(sm.colraw + proj * 256),
+                               reinterpret_cast<const uint32_t*>(v.col_pack3 + static_cast<size_t>(e) * v.rank + c0),
+                               2 * (c1 - c0), bar_a);
+      } else {  // row scale packs, all groups, when they fit
+        const int G = v.num_groups;
+        const int wv = min(OW, v.out_features - o0);
+        if (G * NPROJ * OW <= kRowTabEntries && wv > 0)
+          bytes_a += lane_copy(reinterpret_cast<uint32_t*>(sm.rowtab + proj * OW * G),
+                               reinterpret_cast<const uint32_t*>(v.row_pack3 + (static_cast<size_t>(e) * v.out_features + o0) * G),
+                               2 * wv * G, bar_a);
       }
     }
-    if (bytes) mbar_arrive_expect_tx(bar, bytes);
-    else mbar_arrive(bar);
+  } else if (warp == 5 && lane < kBlocksPerChunk) {  // block-GR sub-stream index
+    const int b = lane;
+    const TrisProjView& v = views[b / (NOB * 4)];
+    if (v.use_block_gr && v.gr_index != nullptr) {
+      const int pr = proj_packed_rows(v);
+      const int nkb = (pr + 1) >> 1, nob = (v.out_features + 63) >> 6;
+      const int kbl = (b / NOB) & 3;
+      const int kb = (p0 >> 1) + kbl, ob = (o0 >> 6) + (b % NOB);
+      if (kb < nkb && ob < nob && 2 * kbl >= p_lo && 2 * kbl < p_hi) {
+        const size_t bi = static_cast<size_t>(e) * nkb * nob + static_cast<size_t>(kb) * nob + ob;
+        bytes_a += lane_copy(sm.gridx + b * 32, v.gr_index + bi * v.gr_substreams, v.gr_substreams, bar_a);
+      }
+    }
   } else if (warp == 1) {
-    // ---- copies that need offsets / prefixes -------------------------------------------
-    fence_proxy_async();
-    uint32_t bytes = 0;
-    uint64_t* bar = &sm.mbar[1];
     if (lane < NPROJ * 4) {  // one block-GR span = the NOB blocks of (proj, k block)
       const int proj = lane >> 2, kbl = lane & 3;
       const TrisProjView& v = views[proj];
@@ -360,10 +362,10 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
         if (a1 > total) a1 = abs0 + nwords;
         const int n_al = static_cast<int>(a1 - a0);
         if ((n_al & 3) == 0 && a0 + n_al <= total) {
-          bytes += lane_copy(region, base + a0, n_al, bar);
+          bytes_b += lane_copy(region, base + a0, n_al, bar_b);
         } else {
           const int bulk = (n_al >> 2) << 2;
-          bytes += lane_copy(region, base + a0, bulk, bar);
+          bytes_b += lane_copy(region, base + a0, bulk, bar_b);
           for (int w = bulk; w < n_al; ++w) region[w] = base[a0 + w];
         }
       }
@@ -372,46 +374,43 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
         const int b = lane * NOB + j;
         sm.binfo[b * 4 + 0] = lane * SPAN + shift + (sm.binfo[b * 4 + 0] - first);
       }
-    } else if (lane >= 8 && lane < 8 + NPROJ) {  // salient sign rows
-      const int proj = lane - 8;
-      const TrisProjView& v = views[proj];
-      const int pr = proj_packed_rows(v);
-      const int wv = min(OW, v.out_features - o0);
-      if (v.sign2_rows > 0 && v.qweight2_sparse != nullptr && p0 < pr && wv > 0) {
+    }
+  } else if ((warp == 2 || warp == 3) && warp - 2 < NPROJ && lane < kSparseRows) {
+    // salient sign rows and (streaming format) sparse g_map rows of one projection
+    const int proj = warp - 2, rq = lane;
+    const TrisProjView& v = views[proj];
+    const int pr = proj_packed_rows(v);
+    const int wv = min(OW, v.out_features - o0);
+    if (p0 < pr && wv > 0) {
+      if (v.sign2_rows > 0 && v.qweight2_sparse != nullptr) {
         const int32_t* pre = v.qweight2_sparse_prefix + static_cast<size_t>(ex) * (pr + 1);
         const int r0 = pre[p0], r1 = pre[min(pr, p0 + KC)];
         const int q0 = max(0, r0 >> 5);
         const int q1 = min(min(v.sign2_rows, (r1 + 31) >> 5), q0 + kSparseRows);
-        for (int q = q0; q < q1; ++q)
-          bytes += lane_copy(sm.s2raw + (proj * kSparseRows + (q - q0)) * OW,
-                             reinterpret_cast<const uint32_t*>(v.qweight2_sparse) +
-                                 (static_cast<size_t>(e) * v.sign2_rows + q) * v.out_features + o0,
-                             wv, bar);
+        if (q0 + rq < q1)
+          bytes_b += lane_copy(sm.s2raw + (proj * kSparseRows + rq) * OW,
+                               reinterpret_cast<const uint32_t*>(v.qweight2_sparse) +
+                                   (static_cast<size_t>(e) * v.sign2_rows + q0 + rq) * v.out_features + o0,
+                               wv, bar_b);
       }
-    } else if (lane >= 12 && lane < 12 + NPROJ) {  // sparse g_map rows (streaming format)
-      const int proj = lane - 12;
-      const TrisProjView& v = views[proj];
-      const int pr = proj_packed_rows(v);
-      const int wv = min(OW, v.out_features - o0);
-      if (!v.use_block_gr && v.gmap_sparse_rows > 0 && v.q_gmap_sparse != nullptr && p0 < pr && wv > 0) {
+      if (!v.use_block_gr && v.gmap_sparse_rows > 0 && v.q_gmap_sparse != nullptr) {
         const int32_t* pre = v.q_gmap_sparse_prefix + static_cast<size_t>(ex) * (pr + 1);
         const int r0 = pre[p0], r1 = pre[min(pr, p0 + KC)];
         const int slot = v.gmap_slot ? v.gmap_slot[ex] : e;
         const int q0 = max(0, r0 >> 5);
         const int q1 = min(min(v.gmap_sparse_rows, (r1 + 31) >> 5), q0 + kSparseRows);
-        for (int q = q0; q < q1; ++q)
-          bytes += lane_copy(sm.gmraw + (proj * kSparseRows + (q - q0)) * OW,
-                             reinterpret_cast<const uint32_t*>(v.q_gmap_sparse) +
-                                 (static_cast<size_t>(slot) * v.gmap_sparse_rows + q) * v.out_features + o0,
-                             wv, bar);
+        if (q0 + rq < q1)
+          bytes_b += lane_copy(sm.gmraw + (proj * kSparseRows + rq) * OW,
+                               reinterpret_cast<const uint32_t*>(v.q_gmap_sparse) +
+                                   (static_cast<size_t>(slot) * v.gmap_sparse_rows + q0 + rq) * v.out_features + o0,
+                               wv, bar_b);
       }
     }
-    if (bytes) mbar_arrive_expect_tx(bar, bytes);
-    else mbar_arrive(bar);
-  } else if (warp == 3) {
+  }
+  if (warp >= 5 && warp < 5 + NPROJ && lane >= 16 && lane <= 16 + KC) {
     // ---- per packed row table -----------------------------------------------------------
-    if (lane < NPROJ * 16) {
-      const int proj = lane >> 4, p = lane & 15;
+    {
+      const int proj = warp - 5, p = lane - 16;
       if (p <= KC) {
         const TrisProjView& v = views[proj];
         const int pr = proj_packed_rows(v);
@@ -440,16 +439,26 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
         sm.ptab[proj * (KC + 1) + p] = info;
       }
     }
-    if (lane == 0) {
-      const int G = views[0].num_groups;
-      sm.row_stride = (G * NPROJ * OW <= kRowTabEntries) ? G : KC;
-    }
+  }
+  if (threadIdx.x == 0) {
+    const int G = views[0].num_groups;
+    sm.row_stride = (G * NPROJ * OW <= kRowTabEntries) ? G : KC;
+  }
+  bytes_a = __reduce_add_sync(0xFFFFFFFFu, bytes_a);
+  bytes_b = __reduce_add_sync(0xFFFFFFFFu, bytes_b);
+  if (lane == 0) {
+    if (bytes_a) mbar_arrive_expect_tx(bar_a, bytes_a);
+    else mbar_arrive(bar_a);
+    if (bytes_b) mbar_arrive_expect_tx(bar_b, bytes_b);
+    else mbar_arrive(bar_b);
   }
 }
 
 // Activation rows.  row_src(n) returns the source row of local row n or -1 for padding.
-// `interleaved` activations are copied as they are (one TMA copy per row, issued by warp
-// 2); row-major ones are re-ordered by all threads.  All threads must call.
+// `interleaved` activations are copied as they are, one bulk copy per row; lanes 24-31 of
+// every warp take eight rows per round, so that no warp issues more than a few copies in a
+// row.  Row-major activations are re-ordered by all threads.  Lane 0 of every warp arrives
+// on mbar[2].  All threads must call.
 template <int NPROJ, int NT, typename RowSrc>
 __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, const __half* const* hidden,
                                                    const TrisProjView* views, int p0, int nrows, bool interleaved,
@@ -458,25 +467,24 @@ __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, cons
   const int rank = views[0].rank;
   const int c0 = 32 * p0;
   const int ncols = min(256, rank - c0);
-  const bool tma_rows = interleaved;  // callers pass interleaved only when rank % 32 == 0
-  if (tma_rows) {
-    if (warp == 2) {
-      fence_proxy_async();
-      uint32_t bytes = 0;
-      for (int i = lane; i < NPROJ * nrows; i += 32) {
-        const int proj = i / nrows, n = i - proj * nrows;
-        const int src = row_src(n);
-        if (src >= 0)
-          bytes += lane_copy(reinterpret_cast<uint32_t*>(sm.hrows + (proj * NT * 8 + n) * kHiddenRowBytes),
-                             reinterpret_cast<const uint32_t*>(hidden[proj] + static_cast<size_t>(src) * row_stride + c0),
-                             ncols >> 1, &sm.mbar[2]);
-      }
-      if (bytes) mbar_arrive_expect_tx(&sm.mbar[2], bytes);
-      else mbar_arrive(&sm.mbar[2]);
+  uint32_t bytes = 0;
+  if (interleaved && lane >= 24) {  // callers pass interleaved only when rank % 32 == 0
+    fence_proxy_async();
+    for (int i = warp * 8 + (lane - 24); i < NPROJ * nrows; i += kWarps * 8) {
+      const int proj = i / nrows, n = i - proj * nrows;
+      const int src = row_src(n);
+      if (src >= 0)
+        bytes += lane_copy(reinterpret_cast<uint32_t*>(sm.hrows + (proj * NT * 8 + n) * kHiddenRowBytes),
+                           reinterpret_cast<const uint32_t*>(hidden[proj] + static_cast<size_t>(src) * row_stride + c0),
+                           ncols >> 1, &sm.mbar[2]);
     }
-    return;
   }
-  if (warp == 2) mbar_arrive(&sm.mbar[2]);
+  bytes = __reduce_add_sync(0xFFFFFFFFu, bytes);
+  if (lane == 0) {
+    if (bytes) mbar_arrive_expect_tx(&sm.mbar[2], bytes);
+    else mbar_arrive(&sm.mbar[2]);
+  }
+  if (interleaved) return;
   // row-major activations: 8 columns per item, scattered to their pair-interleaved positions
   const int items = NPROJ * nrows * 32;
   for (int i = threadIdx.x; i < items; i += kThreads) {
@@ -734,9 +742,9 @@ enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };
 
 __device__ __forceinline__ void init_stage_barriers(uint64_t* mbar) {
   if (threadIdx.x == 0) {
-    mbar_init(&mbar[0], 32);
-    mbar_init(&mbar[1], 32);
-    mbar_init(&mbar[2], 32);
+    mbar_init(&mbar[0], kWarps);  // lane 0 of every warp arrives, with its warp's byte count
+    mbar_init(&mbar[1], kWarps);
+    mbar_init(&mbar[2], kWarps);
     fence_mbar_init();
   }
   __syncthreads();
