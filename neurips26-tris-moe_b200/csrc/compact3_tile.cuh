@@ -77,9 +77,9 @@ struct alignas(128) TileSmem {
   uint32_t gridx[kBlocksPerChunk * 32];              // block-GR sub-stream index
   uint4 coltab[NPROJ * KC * 16];                     // [proj][p][i][t] -> {cd2, cnd2, c1_2, c2_2}
   uint32_t g[kTileWords];                            // decoded g_map, then the select plane
-  PackedRowInfo ptab[NPROJ * (KC + 1)];
+  PackedRowInfo ptab[2][NPROJ * (KC + 1)];             // two copies: a pipelined kernel fills one while the other is read
   int32_t binfo[kBlocksPerChunk * 4];                // {word offset in gmraw, count, meta, -}
-  uint64_t mbar[3];                                  // A: table-free copies, B: dependent copies, H: activations
+  uint64_t mbar[3];                                  // W0: all a chunk needs but the sign plane, W1: sign plane + row scales, H: activations
   int32_t row_stride;
 };
 
@@ -231,65 +231,74 @@ __device__ __forceinline__ uint32_t staged_bits_at(const uint32_t* rows, int ow,
 }
 
 // ---- stage 1: issue -------------------------------------------------------------------
-// Called by all threads after a barrier that ended every earlier use of the staging
-// buffers.  A warp issues its bulk copies one lane after the other (60-70 cycles each),
-// warps issue side by side, and a warp that waits for a table entry stalls with all its
-// lanes.  So every warp gets one kind of work and at most ten copies:
-//   warp 0  sign-plane pieces 0-7, column scale packs      (group A: mbar[0])
-//   warp 4  sign-plane pieces 8-15, row scale packs        (A)
-//   warp 5  block-GR sub-stream index blocks (A); lanes 16+: ptab of projection 0
+// Called by all threads after a barrier that ended every earlier use of the buffers it
+// fills.  The copies of chunk (e, o0, p0) form two sets with a barrier each:
+//   W0 (mbar[0])  column scale packs, block-GR sub-stream index and spans, salient sign rows,
+//                 sparse g_map rows, and the table ptab[pt]: all that decode needs
+//   W1 (mbar[1])  sign plane and row scale packs: needed for the select plane and the main loop
+// `parts` selects the sets to issue (bit 0: W0, bit 1: W1): a pipelined caller issues W0 of its
+// next tile while the current tile's sign plane and row scales are still in use.
+// A warp issues its bulk copies one lane after the other (60-70 cycles each), warps issue
+// side by side, and a warp that waits for a table entry stalls with all its lanes.  So every
+// warp gets one kind of work and at most ten copies:
+//   warp 0  sign-plane pieces 0-7 (W1), column scale packs (W0)
+//   warp 4  sign-plane pieces 8-15, row scale packs (W1)
+//   warp 5  block-GR sub-stream index blocks (W0); lanes 16+: ptab of projection 0
 //   warp 6  lanes 16+: ptab of projection 1
-//   warp 1  block-GR spans, after reading the block offsets (group B: mbar[1])
-//   warps 2, 3  salient sign rows / sparse g_map rows of projection 0, 1, after the prefixes (B)
-// Lane 0 of every warp arrives on both barriers with its warp's byte counts.
+//   warp 1  block-GR spans, after reading the block offsets (W0)
+//   warps 2, 3  salient sign rows / sparse g_map rows of projection 0, 1, after the prefixes (W0)
+// Lane 0 of every warp arrives on the barriers of the issued sets with its warp's byte counts.
 // `e` indexes the bulky E-stacked tensors (sign planes, bitmap data, scale packs: a staging
 // slot when the payload is paged in), `ex` is the expert id and indexes the small tables
 // (c_map, prefixes, packed-row groups, block-GR offsets and meta), which stay resident.
 // Only packed rows [p_lo, p_hi) of the chunk (multiples of 2) are staged: a cluster may split a
 // chunk's K range over its CTAs.
+enum { STAGE_W0 = 1, STAGE_W1 = 2, STAGE_ALL = 3 };
 template <int NPROJ, int NT>
 __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
-                                                    int ex, int o0, int p0, int p_lo = 0, int p_hi = KC) {
+                                                    int ex, int o0, int p0, int p_lo = 0, int p_hi = KC,
+                                                    int parts = STAGE_ALL, int pt = 0) {
   constexpr int OW = Geom<NPROJ>::OW;
   constexpr int NOB = Geom<NPROJ>::NOB;
   constexpr int SPAN = Geom<NPROJ>::SPAN;
+  const bool w0 = (parts & STAGE_W0) != 0, w1 = (parts & STAGE_W1) != 0;
   static_assert(NPROJ * KC * NOB == 16 && kBlocksPerChunk == 8 && kWarps == 8 && kSparseRows <= 16, "copy roles");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint64_t* bar_a = &sm.mbar[0];
-  uint64_t* bar_b = &sm.mbar[1];
-  uint32_t bytes_a = 0, bytes_b = 0;
+  uint64_t* bar_0 = &sm.mbar[0];
+  uint64_t* bar_1 = &sm.mbar[1];
+  uint32_t bytes_0 = 0, bytes_1 = 0;
   if (lane < 16) fence_proxy_async();
   if (warp == 0 || warp == 4) {
-    if (lane < 8) {  // sign plane: 16 pieces of one packed row x 64 outputs
+    if (lane < 8 && w1) {  // sign plane: 16 pieces of one packed row x 64 outputs
       const int piece = 2 * warp + lane;  // warp 0: 0-7, warp 4: 8-15
       const int obl = piece % NOB, p = (piece / NOB) % KC, proj = piece / (NOB * KC);
       const TrisProjView& v = views[proj];
       const int pr = proj_packed_rows(v);
       const int wv = min(64, v.out_features - (o0 + 64 * obl));
       if (p0 + p < pr && wv > 0 && p >= p_lo && p < p_hi)
-        bytes_a += lane_copy(sm.s1 + plane_index<NPROJ>(proj, p, 64 * obl),
+        bytes_1 += lane_copy(sm.s1 + plane_index<NPROJ>(proj, p, 64 * obl),
                              reinterpret_cast<const uint32_t*>(v.qweight1) +
                                  (static_cast<size_t>(e) * pr + p0 + p) * v.out_features + o0 + 64 * obl,
-                             wv, bar_a);
-    } else if (lane < 8 + NPROJ) {
+                             wv, bar_1);
+    } else if (lane >= 8 && lane < 8 + NPROJ) {
       const int proj = lane - 8;
       const TrisProjView& v = views[proj];
       if (warp == 0) {  // column scale packs
         const int c0 = 32 * p0, c1 = min(v.rank, 32 * (p0 + KC));
-        if (c1 > c0)
-          bytes_a += lane_copy(reinterpret_cast<uint32_t*>(sm.colraw + proj * 256),
+        if (c1 > c0 && w0)
+          bytes_0 += lane_copy(reinterpret_cast<uint32_t*>(sm.colraw + proj * 256),
                                reinterpret_cast<const uint32_t*>(v.col_pack3 + static_cast<size_t>(e) * v.rank + c0),
-                               2 * (c1 - c0), bar_a);
-      } else {  // row scale packs, all groups, when they fit
+                               2 * (c1 - c0), bar_0);
+      } else if (w1) {  // row scale packs, all groups, when they fit
         const int G = v.num_groups;
         const int wv = min(OW, v.out_features - o0);
         if (G * NPROJ * OW <= kRowTabEntries && wv > 0)
-          bytes_a += lane_copy(reinterpret_cast<uint32_t*>(sm.rowtab + proj * OW * G),
+          bytes_1 += lane_copy(reinterpret_cast<uint32_t*>(sm.rowtab + proj * OW * G),
                                reinterpret_cast<const uint32_t*>(v.row_pack3 + (static_cast<size_t>(e) * v.out_features + o0) * G),
-                               2 * wv * G, bar_a);
+                               2 * wv * G, bar_1);
       }
     }
-  } else if (warp == 5 && lane < kBlocksPerChunk) {  // block-GR sub-stream index
+  } else if (warp == 5 && lane < kBlocksPerChunk && w0) {  // block-GR sub-stream index
     const int b = lane;
     const TrisProjView& v = views[b / (NOB * 4)];
     if (v.use_block_gr && v.gr_index != nullptr) {
@@ -299,11 +308,11 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
       const int kb = (p0 >> 1) + kbl, ob = (o0 >> 6) + (b % NOB);
       if (kb < nkb && ob < nob && 2 * kbl >= p_lo && 2 * kbl < p_hi) {
         const size_t bi = static_cast<size_t>(e) * nkb * nob + static_cast<size_t>(kb) * nob + ob;
-        bytes_a += lane_copy(sm.gridx + b * 32, v.gr_index + bi * v.gr_substreams, v.gr_substreams, bar_a);
+        bytes_0 += lane_copy(sm.gridx + b * 32, v.gr_index + bi * v.gr_substreams, v.gr_substreams, bar_0);
       }
     }
   } else if (warp == 1) {
-    if (lane < NPROJ * 4) {  // one block-GR span = the NOB blocks of (proj, k block)
+    if (lane < NPROJ * 4 && w0) {  // one block-GR span = the NOB blocks of (proj, k block)
       const int proj = lane >> 2, kbl = lane & 3;
       const TrisProjView& v = views[proj];
       const int pr = proj_packed_rows(v);
@@ -362,10 +371,10 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
         if (a1 > total) a1 = abs0 + nwords;
         const int n_al = static_cast<int>(a1 - a0);
         if ((n_al & 3) == 0 && a0 + n_al <= total) {
-          bytes_b += lane_copy(region, base + a0, n_al, bar_b);
+          bytes_0 += lane_copy(region, base + a0, n_al, bar_0);
         } else {
           const int bulk = (n_al >> 2) << 2;
-          bytes_b += lane_copy(region, base + a0, bulk, bar_b);
+          bytes_0 += lane_copy(region, base + a0, bulk, bar_0);
           for (int w = bulk; w < n_al; ++w) region[w] = base[a0 + w];
         }
       }
@@ -375,7 +384,7 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
         sm.binfo[b * 4 + 0] = lane * SPAN + shift + (sm.binfo[b * 4 + 0] - first);
       }
     }
-  } else if ((warp == 2 || warp == 3) && warp - 2 < NPROJ && lane < kSparseRows) {
+  } else if ((warp == 2 || warp == 3) && warp - 2 < NPROJ && lane < kSparseRows && w0) {
     // salient sign rows and (streaming format) sparse g_map rows of one projection
     const int proj = warp - 2, rq = lane;
     const TrisProjView& v = views[proj];
@@ -388,10 +397,10 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
         const int q0 = max(0, r0 >> 5);
         const int q1 = min(min(v.sign2_rows, (r1 + 31) >> 5), q0 + kSparseRows);
         if (q0 + rq < q1)
-          bytes_b += lane_copy(sm.s2raw + (proj * kSparseRows + rq) * OW,
+          bytes_0 += lane_copy(sm.s2raw + (proj * kSparseRows + rq) * OW,
                                reinterpret_cast<const uint32_t*>(v.qweight2_sparse) +
                                    (static_cast<size_t>(e) * v.sign2_rows + q0 + rq) * v.out_features + o0,
-                               wv, bar_b);
+                               wv, bar_0);
       }
       if (!v.use_block_gr && v.gmap_sparse_rows > 0 && v.q_gmap_sparse != nullptr) {
         const int32_t* pre = v.q_gmap_sparse_prefix + static_cast<size_t>(ex) * (pr + 1);
@@ -400,14 +409,14 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
         const int q0 = max(0, r0 >> 5);
         const int q1 = min(min(v.gmap_sparse_rows, (r1 + 31) >> 5), q0 + kSparseRows);
         if (q0 + rq < q1)
-          bytes_b += lane_copy(sm.gmraw + (proj * kSparseRows + rq) * OW,
+          bytes_0 += lane_copy(sm.gmraw + (proj * kSparseRows + rq) * OW,
                                reinterpret_cast<const uint32_t*>(v.q_gmap_sparse) +
                                    (static_cast<size_t>(slot) * v.gmap_sparse_rows + q0 + rq) * v.out_features + o0,
-                               wv, bar_b);
+                               wv, bar_0);
       }
     }
   }
-  if (warp >= 5 && warp < 5 + NPROJ && lane >= 16 && lane <= 16 + KC) {
+  if (warp >= 5 && warp < 5 + NPROJ && lane >= 16 && lane <= 16 + KC && w0) {
     // ---- per packed row table -----------------------------------------------------------
     {
       const int proj = warp - 5, p = lane - 16;
@@ -436,21 +445,25 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
             info.gslot = all_groups ? min(max(grp, 0), v.num_groups - 1) : (p < KC ? p : 0);
           }
         }
-        sm.ptab[proj * (KC + 1) + p] = info;
+        sm.ptab[pt][proj * (KC + 1) + p] = info;
       }
     }
   }
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && w0) {
     const int G = views[0].num_groups;
     sm.row_stride = (G * NPROJ * OW <= kRowTabEntries) ? G : KC;
   }
-  bytes_a = __reduce_add_sync(0xFFFFFFFFu, bytes_a);
-  bytes_b = __reduce_add_sync(0xFFFFFFFFu, bytes_b);
+  bytes_0 = __reduce_add_sync(0xFFFFFFFFu, bytes_0);
+  bytes_1 = __reduce_add_sync(0xFFFFFFFFu, bytes_1);
   if (lane == 0) {
-    if (bytes_a) mbar_arrive_expect_tx(bar_a, bytes_a);
-    else mbar_arrive(bar_a);
-    if (bytes_b) mbar_arrive_expect_tx(bar_b, bytes_b);
-    else mbar_arrive(bar_b);
+    if (w0) {
+      if (bytes_0) mbar_arrive_expect_tx(bar_0, bytes_0);
+      else mbar_arrive(bar_0);
+    }
+    if (w1) {
+      if (bytes_1) mbar_arrive_expect_tx(bar_1, bytes_1);
+      else mbar_arrive(bar_1);
+    }
   }
 }
 
@@ -514,16 +527,17 @@ __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, cons
 }
 
 // ---- stage 2: decode + tables ---------------------------------------------------------
-// All threads.  Waits for the weight copies, expands the block-GR blocks into sm.g (and
-// optionally hands the dense g_map words to `dump`), builds select plane and column table.
-// Returns false when a wait timed out.
+// All threads.  Waits for copy set W0 (phase parity0 of mbar[0]), builds the column table
+// from ptab[pt] and expands the block-GR blocks into sm.g; then waits for W1 (parity1 of
+// mbar[1]) and builds the select plane (optionally handing the dense g_map words to
+// `gmap_dump`).  Returns false when a wait timed out.
 template <int NPROJ, int NT>
 __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
-                                                     int ex, int o0, int p0, uint32_t parity, uint32_t* gmap_dump,
-                                                     int p_lo = 0, int p_hi = KC) {
+                                                     int ex, int o0, int p0, uint32_t parity0, uint32_t parity1,
+                                                     uint32_t* gmap_dump, int p_lo = 0, int p_hi = KC, int pt = 0) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int tid = threadIdx.x;
-  bool ok = mbar_wait_bounded(&sm.mbar[0], parity);
+  bool ok = mbar_wait_bounded(&sm.mbar[0], parity0);
 
   // column table: pairs (4t+i, 4t+i+16); scales a column does not use are zeroed so that
   // one fused multiply-add serves salient and non-salient halves alike
@@ -533,7 +547,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
     const int ii = (i >> 2) & 3;
     const int t = i & 3;
     const TrisProjView& v = views[proj];
-    const uint32_t cwv = sm.ptab[proj * (KC + 1) + p].cw;
+    const uint32_t cwv = sm.ptab[pt][proj * (KC + 1) + p].cw;
     const int ja = 4 * t + ii, jb = ja + 16;
     const int ca = 32 * (p0 + p) + ja, cb = ca + 16;
     uint2 pa = make_uint2(0u, 0u), pb = make_uint2(0u, 0u);
@@ -569,7 +583,6 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
     }
   }
 
-  ok = mbar_wait_bounded(&sm.mbar[1], parity) && ok;
   TRIS_SUBMARK(7);
   const bool gr = views[0].use_block_gr != 0;
   if (gr) {
@@ -605,6 +618,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
     TRIS_SUBMARK(6);
   }
 
+  ok = mbar_wait_bounded(&sm.mbar[1], parity1) && ok;  // the sign plane
   // select plane: for a non-salient column the g_map bit (1 -> "d" scale pair, CU:736-737);
   // for a salient column XNOR(sign1, sign2), because
   //   fp16(+-a +- b) = sign1 * fp16(a + (sign1*sign2) b)
@@ -618,7 +632,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
     const int o = (b % NOB) * 64 + (wl & 63);
     if (p < p_lo || p >= p_hi) continue;
     const TrisProjView& v = views[proj];
-    const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
+    const PackedRowInfo info = sm.ptab[pt][proj * (KC + 1) + p];
     const uint32_t cwv = info.cw;
     const uint32_t s1 = sm.s1[i];
     uint32_t s2 = 0u;
@@ -695,7 +709,7 @@ __device__ __forceinline__ void unpack_fragments(const TileSmem<NPROJ, NT>& sm, 
                                                  int lane, RowScales (&rs)[2], int& rs_slot, uint32_t (&a)[2][4]) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int g = lane >> 2, t = lane & 3;
-  const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
+  const PackedRowInfo info = sm.ptab[0][proj * (KC + 1) + p];
   if (info.gslot != rs_slot) {  // warp-uniform; groups span several packed rows
     rs_slot = info.gslot;
     const int stride = sm.row_stride;

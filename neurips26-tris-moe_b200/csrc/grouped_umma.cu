@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
       __syncthreads();
       stage_issue_weights<1, 1>(stage, &args.proj[proj], e, expert, o0, 0);
       __syncthreads();
-      ok = stage_finish_weights<1, 1>(stage, &args.proj[proj], e, expert, o0, 0, static_cast<uint32_t>(proj & 1), nullptr) && ok;
+      ok = stage_finish_weights<1, 1>(stage, &args.proj[proj], e, expert, o0, 0, static_cast<uint32_t>(proj & 1), static_cast<uint32_t>(proj & 1), nullptr) && ok;
       __syncthreads();
       uint8_t* a_dst = a_op + proj * UmmaGeom<NPROJ>::kABytes;
       RowScales rs[2];
