@@ -77,7 +77,7 @@ struct alignas(128) TileSmem {
   uint32_t gridx[kBlocksPerChunk * 32];              // block-GR sub-stream index
   uint4 coltab[NPROJ * KC * 16];                     // [proj][p][i][t] -> {cd2, cnd2, c1_2, c2_2}
   uint32_t g[kTileWords];                            // decoded g_map, then the select plane
-  PackedRowInfo ptab[2][NPROJ * (KC + 1)];             // two copies: a pipelined kernel fills one while the other is read
+  PackedRowInfo ptab[NPROJ * (KC + 1)];
   int32_t binfo[kBlocksPerChunk * 4];                // {word offset in gmraw, count, meta, -}
   uint64_t mbar[3];                                  // W0: all a chunk needs but the sign plane, W1: sign plane + row scales, H: activations
   int32_t row_stride;
@@ -234,10 +234,9 @@ __device__ __forceinline__ uint32_t staged_bits_at(const uint32_t* rows, int ow,
 // Called by all threads after a barrier that ended every earlier use of the buffers it
 // fills.  The copies of chunk (e, o0, p0) form two sets with a barrier each:
 //   W0 (mbar[0])  column scale packs, block-GR sub-stream index and spans, salient sign rows,
-//                 sparse g_map rows, and the table ptab[pt]: all that decode needs
+//                 sparse g_map rows, and the table ptab: all that decode needs
 //   W1 (mbar[1])  sign plane and row scale packs: needed for the select plane and the main loop
-// `parts` selects the sets to issue (bit 0: W0, bit 1: W1): a pipelined caller issues W0 of its
-// next tile while the current tile's sign plane and row scales are still in use.
+// `parts` selects the sets to issue (bit 0: W0, bit 1: W1).
 // A warp issues its bulk copies one lane after the other (60-70 cycles each), warps issue
 // side by side, and a warp that waits for a table entry stalls with all its lanes.  So every
 // warp gets one kind of work and at most ten copies:
@@ -257,7 +256,7 @@ enum { STAGE_W0 = 1, STAGE_W1 = 2, STAGE_ALL = 3 };
 template <int NPROJ, int NT>
 __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
                                                     int ex, int o0, int p0, int p_lo = 0, int p_hi = KC,
-                                                    int parts = STAGE_ALL, int pt = 0) {
+                                                    int parts = STAGE_ALL) {
   constexpr int OW = Geom<NPROJ>::OW;
   constexpr int NOB = Geom<NPROJ>::NOB;
   constexpr int SPAN = Geom<NPROJ>::SPAN;
@@ -445,7 +444,7 @@ __device__ __forceinline__ void stage_issue_weights(TileSmem<NPROJ, NT>& sm, con
             info.gslot = all_groups ? min(max(grp, 0), v.num_groups - 1) : (p < KC ? p : 0);
           }
         }
-        sm.ptab[pt][proj * (KC + 1) + p] = info;
+        sm.ptab[proj * (KC + 1) + p] = info;
       }
     }
   }
@@ -528,13 +527,13 @@ __device__ __forceinline__ void stage_issue_hidden(TileSmem<NPROJ, NT>& sm, cons
 
 // ---- stage 2: decode + tables ---------------------------------------------------------
 // All threads.  Waits for copy set W0 (phase parity0 of mbar[0]), builds the column table
-// from ptab[pt] and expands the block-GR blocks into sm.g; then waits for W1 (parity1 of
+// and expands the block-GR blocks into sm.g; then waits for W1 (parity1 of
 // mbar[1]) and builds the select plane (optionally handing the dense g_map words to
 // `gmap_dump`).  Returns false when a wait timed out.
 template <int NPROJ, int NT>
 __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, const TrisProjView* views, int e,
                                                      int ex, int o0, int p0, uint32_t parity0, uint32_t parity1,
-                                                     uint32_t* gmap_dump, int p_lo = 0, int p_hi = KC, int pt = 0) {
+                                                     uint32_t* gmap_dump, int p_lo = 0, int p_hi = KC) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int tid = threadIdx.x;
   bool ok = mbar_wait_bounded(&sm.mbar[0], parity0);
@@ -547,7 +546,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
     const int ii = (i >> 2) & 3;
     const int t = i & 3;
     const TrisProjView& v = views[proj];
-    const uint32_t cwv = sm.ptab[pt][proj * (KC + 1) + p].cw;
+    const uint32_t cwv = sm.ptab[proj * (KC + 1) + p].cw;
     const int ja = 4 * t + ii, jb = ja + 16;
     const int ca = 32 * (p0 + p) + ja, cb = ca + 16;
     uint2 pa = make_uint2(0u, 0u), pb = make_uint2(0u, 0u);
@@ -632,7 +631,7 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
     const int o = (b % NOB) * 64 + (wl & 63);
     if (p < p_lo || p >= p_hi) continue;
     const TrisProjView& v = views[proj];
-    const PackedRowInfo info = sm.ptab[pt][proj * (KC + 1) + p];
+    const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
     const uint32_t cwv = info.cw;
     const uint32_t s1 = sm.s1[i];
     uint32_t s2 = 0u;
@@ -709,7 +708,7 @@ __device__ __forceinline__ void unpack_fragments(const TileSmem<NPROJ, NT>& sm, 
                                                  int lane, RowScales (&rs)[2], int& rs_slot, uint32_t (&a)[2][4]) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int g = lane >> 2, t = lane & 3;
-  const PackedRowInfo info = sm.ptab[0][proj * (KC + 1) + p];
+  const PackedRowInfo info = sm.ptab[proj * (KC + 1) + p];
   if (info.gslot != rs_slot) {  // warp-uniform; groups span several packed rows
     rs_slot = info.gslot;
     const int stride = sm.row_stride;

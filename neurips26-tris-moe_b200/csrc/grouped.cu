@@ -10,7 +10,6 @@
 #include <math.h>
 
 #include <algorithm>
-#include <cstddef>
 
 // Development builds (-DTRIS_PHASE_TIMERS) stamp clock64() at phase boundaries of every CTA.
 #ifdef TRIS_PHASE_TIMERS
@@ -180,7 +179,7 @@ __global__ void __launch_bounds__(kThreads) compact3_dump_kernel(TrisProjView v,
 // The warp's 16 outputs (lane (g, t): outputs g and g+8, column pairs 4t+i / 4t+i+16) against
 // up to NT tiles of 8 activation rows; packed rows [p_lo, p_end) of the chunk.
 template <int NPROJ, int NT>
-__device__ __forceinline__ void main_chunk(const TileSmem<NPROJ, NT>& sm, int pt, int proj, int out_local, int lane,
+__device__ __forceinline__ void main_chunk(const TileSmem<NPROJ, NT>& sm, int proj, int out_local, int lane,
                                            int nt_count, int p_lo, int p_end, float (&acc)[NT][4]) {
   constexpr int OW = Geom<NPROJ>::OW;
   const int g = lane >> 2, t = lane & 3;
@@ -190,18 +189,13 @@ __device__ __forceinline__ void main_chunk(const TileSmem<NPROJ, NT>& sm, int pt
   const uint32_t* s1_base = sm.s1 + word0;
   const uint32_t* sel_base = sm.g + word0;
   const uint4* col_base = sm.coltab + proj * KC * 16 + t;
-  const PackedRowInfo* pinfo = sm.ptab[pt] + proj * (KC + 1);
+  const PackedRowInfo* pinfo = sm.ptab + proj * (KC + 1);
   const uint8_t* h_base = sm.hrows + (proj * NT * 8 + g) * kHiddenRowBytes + t * 16;
   const uint2* row_base = sm.rowtab + (proj * OW + out_local + g) * sm.row_stride;
   const int row_step = 8 * sm.row_stride;
   RowScales rs[2];
   int rs_slot = -1;
-#ifdef TRIS_MAIN_UNROLL
-  constexpr int kMainUnroll = TRIS_MAIN_UNROLL;
-#else
-  constexpr int kMainUnroll = KC;
-#endif
-#pragma unroll kMainUnroll
+#pragma unroll
   for (int p = 0; p < KC; ++p) {
     if (p < p_lo || p >= p_end) continue;  // warp-uniform
     const PackedRowInfo info = pinfo[p];
@@ -392,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       }
       TRIS_MARK(3);
 
-      main_chunk<NPROJ, NT>(sm, 0, proj, out_local, lane, nt_count, p_lo, min(p_hi, pr - p0), acc);
+      main_chunk<NPROJ, NT>(sm, proj, out_local, lane, nt_count, p_lo, min(p_hi, pr - p0), acc);
     }
 
     TRIS_MARK(4);
@@ -428,157 +422,6 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
     }
   }
   TRIS_MARK(5);
-}
-
-// ---- pipelined variant: persistent CTAs, copies of the next tile behind the current one -----
-// One (segment, output tile) unit of work.
-struct TileItem {
-  int expert, e, row_begin, row_end, o0;
-  bool valid;
-};
-
-__device__ __forceinline__ TileItem fetch_item(const GroupedArgs& args, int item, int tiles, int ow) {
-  TileItem it;
-  const int seg = item / tiles;
-  it.o0 = (item - seg * tiles) * ow;
-  it.expert = args.expert_ids[seg];
-  it.row_begin = args.segment_offsets[seg];
-  it.row_end = min(args.segment_offsets[seg + 1], args.num_rows);
-  it.valid = it.expert >= 0 && it.expert < args.proj[0].num_experts && it.row_end > it.row_begin;
-  // row block of the expert inside the payload tensors (a staging slot when they are paged in)
-  it.e = (it.valid && args.proj[0].expert_slot) ? args.proj[0].expert_slot[it.expert] : it.expert;
-  return it;
-}
-
-// For projections of at most 256 columns (one chunk).  grid = min(units, CTAs the GPU holds);
-// CTA b takes units b, b + gridDim.x, ...  A unit alone is a chain of latencies (route entry ->
-// table entries -> bulk copies -> decode -> main loop), and CTAs that start together wait
-// together; so every CTA keeps its next unit's copies in flight behind the current unit's work:
-//   decode(i) | issue W0(i+1) | main(i) | issue W1(i+1), rows(i+1) | epilogue(i) | decode(i+1) ...
-// W0 (bitmap data, column scales, tables) lands in staging buffers that are dead once the
-// select plane of unit i is built; W1 (sign plane, row scales) and the activation rows replace
-// buffers the main loop of unit i has finished with.  Only ptab exists twice.
-template <int NPROJ, int NT, int EPI>
-__global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_pipelined_kernel(const __grid_constant__ GroupedArgs args) {
-  constexpr int OW = Geom<NPROJ>::OW;
-  extern __shared__ uint4 smem_raw[];
-  auto& sm = *reinterpret_cast<TileSmem<NPROJ, NT>*>(smem_raw);
-  init_barriers(sm.mbar);
-  // Activations come from the predecessor kernel; the route arrays too, unless the caller
-  // says they are older, in which case the first unit's weight staging overlaps the predecessor.
-  bool waited = false;
-  if (!args.weights_before_wait) {
-    pdl_wait();
-    pdl_launch_dependents();
-    waited = true;
-  }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int proj = (NPROJ == 2) ? (warp >> 2) : 0;
-  const int out_local = (NPROJ == 2) ? (warp & 3) * 16 : warp * 16;
-  const int pr = proj_packed_rows(args.proj[0]);  // <= KC
-  const bool interleaved = args.hidden_interleaved != 0;
-  const int tiles = (args.proj[0].out_features + OW - 1) / OW;
-  const int nseg = args.num_segments_dev ? min(*args.num_segments_dev, args.num_segments) : args.num_segments;
-  const int total = nseg * tiles;
-  const int stride = static_cast<int>(gridDim.x);
-  auto next_valid = [&](int from, TileItem& out) {
-    for (int i = from; i < total; i += stride) {
-      out = fetch_item(args, i, tiles, OW);
-      if (out.valid) return i;
-    }
-    return -1;
-  };
-  auto issue_rows = [&](const TileItem& it, int r0) {
-    const int rows = min(NT * 8, it.row_end - r0);
-    auto row_src = [&](int n) { return args.row_gather ? args.row_gather[r0 + n] : (r0 + n); };
-    stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, 0, rows, interleaved, args.hidden_stride, row_src);
-  };
-
-  TileItem cur;
-  int item = next_valid(static_cast<int>(blockIdx.x), cur);
-  if (item < 0) return;
-  uint32_t par0 = 0u, par1 = 0u, parh = 0u;
-  int pt = 0;
-  stage_issue_weights<NPROJ, NT>(sm, args.proj, cur.e, cur.expert, cur.o0, 0, 0, KC, STAGE_ALL, pt);
-  if (!waited) {
-    pdl_wait();
-    pdl_launch_dependents();
-    waited = true;
-  }
-  issue_rows(cur, cur.row_begin);
-  bool in0 = true, in1 = true, inh = true;  // copies in flight on mbar[0], mbar[1], mbar[2]
-
-  for (;;) {
-    TileItem nxt;
-    const int nitem = next_valid(item + stride, nxt);  // its loads are in flight during the decode
-    __syncthreads();  // ptab[pt] and the block table of this unit are visible
-    bool ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, cur.e, cur.expert, cur.o0, 0, par0, par1, nullptr, 0, KC, pt);
-    par0 ^= 1u;
-    par1 ^= 1u;
-    in0 = in1 = false;
-    if (__syncthreads_or(!ok)) {  // also: select plane and tables complete, staging buffers dead
-      if (inh) mbar_wait_bounded(&sm.mbar[2], parh);
-      if (threadIdx.x == 0 && args.status) atomicExch(args.status, TRIS_ERR_TIMEOUT);
-      return;
-    }
-    if (nitem >= 0) {
-      stage_issue_weights<NPROJ, NT>(sm, args.proj, nxt.e, nxt.expert, nxt.o0, 0, 0, KC, STAGE_W0, pt ^ 1);
-      in0 = true;
-    }
-    for (int r0 = cur.row_begin; r0 < cur.row_end; r0 += NT * 8) {
-      const int rows = min(NT * 8, cur.row_end - r0);
-      const int nt_count = (rows + 7) >> 3;
-      const bool last = r0 + NT * 8 >= cur.row_end;
-      float acc[NT][4];
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
-      ok = mbar_wait_bounded(&sm.mbar[2], parh);
-      parh ^= 1u;
-      inh = false;
-      if (__syncthreads_or(!ok)) {  // also publishes re-ordered row-major activations
-        if (in0) mbar_wait_bounded(&sm.mbar[0], par0);
-        if (threadIdx.x == 0 && args.status) atomicExch(args.status, TRIS_ERR_TIMEOUT);
-        return;
-      }
-      main_chunk<NPROJ, NT>(sm, pt, proj, out_local, lane, nt_count, 0, pr, acc);
-      __syncthreads();  // all warps are done with the activation rows (after the last pass: with
-                        // the sign plane, the select plane, the tables and the row scales too)
-      // The SiLU exchange needs 4*NT*512 bytes nobody touches: after the last pass the column
-      // table and select plane (8 KB, enough up to 4 tiles), otherwise the activation rows,
-      // which then must be exchanged through before the next rows are copied over them.
-      using Smem = TileSmem<NPROJ, NT>;
-      static_assert(EPI != EPI_SILU_MUL || (offsetof(Smem, g) == offsetof(Smem, coltab) + sizeof(sm.coltab) &&
-                                            sizeof(sm.coltab) + sizeof(sm.g) >= 4 * 4 * 32 * 16),
-                    "column table and select plane form the exchange buffer");
-      const bool early_issue = EPI == EPI_STORE || (last && NT <= 4);
-      auto issue_following = [&]() {
-        if (!last) {
-          issue_rows(cur, r0 + NT * 8);
-          inh = true;
-        } else if (nitem >= 0) {
-          stage_issue_weights<NPROJ, NT>(sm, args.proj, nxt.e, nxt.expert, nxt.o0, 0, 0, KC, STAGE_W1, pt ^ 1);
-          issue_rows(nxt, nxt.row_begin);
-          in1 = inh = true;
-        }
-      };
-      if (early_issue) {
-        issue_following();
-        finish_rows<NPROJ, NT, EPI>(args, reinterpret_cast<float*>(sm.coltab), true, proj, out_local, warp, lane, cur.expert,
-                                    cur.o0, r0, rows, nt_count, acc);
-      } else {
-        finish_rows<NPROJ, NT, EPI>(args, reinterpret_cast<float*>(sm.hrows), true, proj, out_local, warp, lane, cur.expert,
-                                    cur.o0, r0, rows, nt_count, acc);
-        __syncthreads();  // the exchange buffer has been read
-        issue_following();
-      }
-    }
-    if (nitem < 0) break;
-    cur = nxt;
-    item = nitem;
-    pt ^= 1;
-  }
 }
 
 // tensor-core path for prefill-sized segments (grouped_umma.cu)
@@ -634,44 +477,9 @@ static int launch_grouped(const GroupedArgs& args, cudaStream_t stream, bool pdl
                     "grouped_compact3_kernel launch");
 }
 
-// CTAs of `kernel` one SM holds at this shared-memory size, times the SM count (cached per device).
-template <typename Kernel>
-static int resident_ctas(Kernel kernel, size_t smem, int dev) {
-  int per_sm = 0, sms = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) != cudaSuccess) return 0;
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-  return per_sm * sms;
-}
-
-template <int NPROJ, int NT, int EPI>
-static int launch_grouped_pipelined(const GroupedArgs& args, cudaStream_t stream, bool pdl) {
-  const size_t smem = sizeof(TileSmem<NPROJ, NT>);
-  auto kernel = grouped_compact3_pipelined_kernel<NPROJ, NT, EPI>;
-  static int resident[64] = {};  // per instantiation, per device; 0 = not configured yet
-  int dev = 0;
-  TRIS_CUDA(cudaGetDevice(&dev));
-  TRIS_REQUIRE(dev >= 0 && dev < 64, TRIS_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  if (resident[dev] == 0) {
-    TRIS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    const int r = resident_ctas(kernel, smem, dev);
-    TRIS_REQUIRE(r > 0, TRIS_ERR_CUDA, "occupancy query failed for the pipelined grouped kernel");
-    resident[dev] = r;
-  }
-  const int units = ceil_div(args.proj[0].out_features, Geom<NPROJ>::OW) * args.num_segments;
-  dim3 grid(std::max(1, std::min(units, resident[dev])));
-  return check_cuda(launch_kernel(kernel, grid, dim3(kThreads), smem, stream, pdl, 1, args),
-                    "grouped_compact3_pipelined_kernel launch");
-}
-
 template <int NPROJ, int EPI>
 static int dispatch_grouped(const GroupedArgs& args, int max_rows, cudaStream_t stream, bool pdl) {
   // one 256-column chunk and no K split: persistent CTAs that prefetch their next tile
-  if ((args.proj[0].rank + 31) / 32 <= KC && args.ksplit <= 1) {
-    if (max_rows <= 8) return launch_grouped_pipelined<NPROJ, 1, EPI>(args, stream, pdl);
-    if (max_rows <= 16) return launch_grouped_pipelined<NPROJ, 2, EPI>(args, stream, pdl);
-    if (max_rows <= 32) return launch_grouped_pipelined<NPROJ, 4, EPI>(args, stream, pdl);
-    return launch_grouped_pipelined<NPROJ, 8, EPI>(args, stream, pdl);
-  }
   if (max_rows <= 8) return launch_grouped<NPROJ, 1, EPI>(args, stream, pdl);
   if (max_rows <= 16) return launch_grouped<NPROJ, 2, EPI>(args, stream, pdl);
   if (max_rows <= 32) return launch_grouped<NPROJ, 4, EPI>(args, stream, pdl);
