@@ -405,9 +405,7 @@ def run_extra(args):
                     for l, blk in enumerate(blocks):
                         blk.forward_streaming(x.view(1, T, 2048), manager, l)
 
-                # relaxed: the pager looks up the device alias of its pinned source (a driver query,
-                # not a stream operation) while the capture is open
-                graph = capture(step, error_mode="relaxed")
+                graph = capture(step)
                 graph_ms = time_replays(graph, 10, 3)
                 del graph
             except Exception as exc:  # noqa: BLE001

@@ -94,6 +94,14 @@ class GroupedQGmapCPUStagingManager:
         self.pipeline_stats = {"calls": 0, "chunks": 0, "bytes": 0, "slot_reuses": 0}
         self._timings = []         # (copy_start, copy_end, wait_start, wait_end) events
         self.collect_timings = True  # set False while capturing the forward into a CUDA graph
+        # A stream that is being captured may not wait for an event recorded outside the
+        # capture.  Slot uses are therefore stamped with an epoch that changes whenever a
+        # capture starts or ends; a pager only waits for "consumed" events of its own epoch
+        # (work of an earlier epoch is ordered before it by the stream itself: the caller
+        # captures, and replays, on the stream the earlier work ran on or has synchronised).
+        self._epoch = 0
+        self._capturing = False
+        self._consumed_epoch = []
 
     @property
     def buffer_nbytes(self) -> int:
@@ -132,6 +140,7 @@ class GroupedQGmapCPUStagingManager:
             self._paged.append(torch.cuda.Event())
             self._consumed.append(torch.cuda.Event())
             self._used.append(False)
+            self._consumed_epoch.append(-1)
         self._copy_stream = torch.cuda.Stream(device=self.device)
         self.capacity = cap
         # drop the device copies: from here on the tensors exist only in pinned host memory
@@ -154,7 +163,11 @@ class GroupedQGmapCPUStagingManager:
         compute = torch.cuda.current_stream(self.device)
         copy = self._copy_stream
         copy.wait_stream(compute)  # the route must be final before the pager reads it
-        if self._used[ring]:
+        capturing = bool(torch.cuda.is_current_stream_capturing())
+        if capturing != self._capturing:
+            self._capturing = capturing
+            self._epoch += 1
+        if self._used[ring] and self._consumed_epoch[ring] == self._epoch:
             copy.wait_event(self._consumed[ring])
             self.pipeline_stats["slot_reuses"] += 1
         nseg_bound = min(int(route["experts"]), int(route["rows"]), self.capacity)
@@ -249,6 +262,7 @@ class _PagedLayer:
     def release(self) -> None:
         """Marks the staging slots free once the kernels enqueued so far have consumed them."""
         self.manager._consumed[self.ring].record(torch.cuda.current_stream(self.manager.device))
+        self.manager._consumed_epoch[self.ring] = self.manager._epoch
 
 
 def maybe_create_grouped_qgmap_cpu_staging_manager(moe_blocks, mode: str = "bitmap", **kw):

@@ -396,6 +396,46 @@ def test_layer_olmoe_shape_decode_batches(tm, olmoe_layer, T):
     assert max_abs <= MAX_ABS and mean_rel <= MEAN_REL, (max_abs, mean_rel)
 
 
+_SHAPE_CACHE = {}
+
+
+@pytest.mark.parametrize("shape_name,T", [("MIXTRAL", 1), ("MIXTRAL", 64), ("QWEN35", 1), ("QWEN35", 16)])
+def test_layer_other_baseline_shapes(tm, shape_name, T):
+    """Mixtral-shaped (8 experts, top-2, hidden 4096, intermediate 14336) and Qwen3.5-shaped (256
+    experts, top-8, hidden 2048, intermediate 512) layers at their decode batches: dequantized
+    weights of a sample of the routed experts bit-exact against the oracle, output against the
+    fp32 oracle built from the weights of all routed experts."""
+    from trismoe_b200 import synth
+
+    shape = getattr(synth, shape_name)
+    if shape_name not in _SHAPE_CACHE:
+        _SHAPE_CACHE.clear()  # one full-size layer at a time
+        layer = synth.synth_layer(shape, seed=77)
+        _SHAPE_CACHE[shape_name] = (layer, _block_from_layer(tm, shape, layer))
+    layer, blk = _SHAPE_CACHE[shape_name]
+    x = synth.synth_activations(T, shape.hidden_size, seed=3 + T)
+    logits = synth.synth_router_logits(T, shape.num_experts, seed=11 + T)
+    sel, _ = orc.router_topk(logits.numpy(), shape.top_k, shape.norm_topk_prob)
+    active = sorted(set(int(e) for e in sel.reshape(-1)))
+    check = active[:: max(1, len(active) // 3)]
+    weights = {}
+    for name in ("gate", "up", "down"):
+        npp = to_numpy_payload(layer[name])
+        got = tm.dequantize_grouped_payload(blk._get_grouped_payload(name))
+        weights[name] = {}
+        for e in active:
+            if e in check:
+                _assert_half_bits_equal(got[e].cpu().numpy(), orc.dequantize_expert(npp, e))
+            weights[name][e] = got[e].cpu().numpy()
+        del got
+    shared = {n: layer["shared_" + n].numpy() for n in ("gate", "up", "down")}
+    y, _ = blk(x.cuda().view(1, T, -1), router_logits=logits.cuda())
+    ref = orc.moe_layer_fp32(x.numpy(), logits.numpy(), weights, shared, shape.top_k, shape.norm_topk_prob)
+    max_abs, mean_rel = orc.error_metrics(y.view(T, -1).float().cpu().numpy(), ref)
+    assert np.abs(ref).mean() > 1e-4
+    assert max_abs <= MAX_ABS and mean_rel <= MEAN_REL, (max_abs, mean_rel)
+
+
 def test_full_size_properties(tm, olmoe_layer):
     """Size-independent properties at the headline size: GR decode of every block of every
     expert round-trips to the dense map it was encoded from; a token's output does not
@@ -456,6 +496,28 @@ def test_streaming_forward_matches_resident(tm, mode, fmt):
     report = manager.overlap_report()
     assert report["layers"] == 6 and report["copy_ms"] > 0
     assert manager.pipeline_stats["calls"] == 6 and manager.pipeline_stats["slot_reuses"] >= 4
+    # the same three-layer step as one CUDA graph: pager and compute streams, no host decisions
+    manager.collect_timings = False
+    outs = []
+
+    def step():
+        outs.clear()
+        for L, blk in enumerate(blocks):
+            x, logits = inputs[L]
+            outs.append(blk.forward_streaming(x.view(1, x.shape[0], -1), manager, L, router_logits=logits)[0])
+
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(2):
+        for o in outs:
+            o.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for L in range(3):
+            assert torch.equal(outs[L], wants[L]), (mode, fmt, "graph", L)
+    manager.collect_timings = True
 
 
 # ---------------------------------------------------------------------------------------
