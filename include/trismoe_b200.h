@@ -30,7 +30,7 @@ extern "C" {
 
 /* Mirrors TRIS_COMPACT3_KERNEL_ABI_VERSION (CPP:1138-1139); the payload layout is ABI 2. */
 #define TRIS_COMPACT3_KERNEL_ABI_VERSION 2
-#define TRIS_B200_ABI_VERSION 1
+#define TRIS_B200_ABI_VERSION 2
 
 enum {
   TRIS_OK = 0,
@@ -110,6 +110,10 @@ typedef struct TrisRouteView {
                                        bounded wait inside a kernel ran out                */
   int32_t flags;                    /* TRIS_ROUTE_* bits                                   */
   int32_t hidden_row_stride;        /* halves between activation rows; 0 = the projection's rank */
+  const int32_t* out_row_scatter;   /* optional [R]: output row of each grouped row (default: the
+                                       grouped row itself); no reference counterpart - lets a
+                                       caller get results back in its own row order without a
+                                       second pass                                          */
 } TrisRouteView;
 
 /* Activation rows handed to the grouped kernels are "pair-interleaved": inside every group
@@ -209,16 +213,19 @@ int tris_router_topk(const float* router_logits, int32_t num_tokens, int32_t num
  * a contiguous range of experts, sizes differing by at most one).  For every grouped row the
  * kernel copies its two backbone outputs (hidden_gate[tok], hidden_up[tok], each `rank_gu`
  * halves) side by side into slot (owner, position among the rows for that owner) of
- * send_rows [world * capacity, 2*rank_gu], writes the row's expert id into send_ids
- * [world * capacity] (unused slots = -1), and records combine_index[flat] = that slot for
- * the flat (token, slot) entry the row came from.  capacity >= rows sent to any one rank
- * (tokens * top_k always suffices); a row beyond it is dropped and *overflow_dev set to 1.
+ * send_rows [world * capacity, send_row_stride] (send_row_stride halves per slot, a multiple of
+ * 8, >= 2*rank_gu).  The row's expert id (unused slots: -1) is written as an int32 right behind
+ * the two activation rows when send_row_stride >= 2*rank_gu + 8 (so that one exchange moves
+ * rows and ids together), and into send_ids [world * capacity] when that is not NULL.
+ * combine_index[flat] = the slot of the flat (token, slot) entry the row came from.
+ * capacity >= rows sent to any one rank (tokens * top_k always suffices); a row beyond it is
+ * dropped and *overflow_dev set to 1.
  */
 int tris_ep_pack_rows(const void* hidden_gate_f16, const void* hidden_up_f16, int32_t rank_gu,
                       const int32_t* selected_experts, const int32_t* perm, const int32_t* grouped_token_indices,
                       int32_t num_rows, int32_t top_k, int32_t num_experts, int32_t world, int32_t capacity,
-                      void* send_rows_f16, int32_t* send_ids, int32_t* combine_index, int32_t* overflow_dev,
-                      void* stream);
+                      void* send_rows_f16, int32_t send_row_stride, int32_t* send_ids, int32_t* combine_index,
+                      int32_t* overflow_dev, void* stream);
 
 /* ---- backbone ---------------------------------------------------------------------- */
 

@@ -37,11 +37,15 @@ class TrisPageJob(C.Structure):
     _fields_ = [("host_src", _vp), ("dst", _vp), ("bytes_per_expert", C.c_int64)]
 
 
+ABI_VERSION = 2  # TRIS_B200_ABI_VERSION of include/trismoe_b200.h
+
+
 class TrisRouteView(C.Structure):
     _fields_ = [
         ("expert_ids", _vp), ("segment_offsets", _vp), ("num_segments_dev", _vp),
         ("num_segments", _i32), ("num_rows", _i32), ("max_rows_per_segment", _i32),
         ("row_gather", _vp), ("status_dev", _vp), ("flags", _i32), ("hidden_row_stride", _i32),
+        ("out_row_scatter", _vp),
     ]
 
 
@@ -68,7 +72,7 @@ SIGNATURES = {
     "tris_build_row_groups": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "tris_compact3_dequantize": (C.c_int, [_P(TrisProjView), _vp, _vp]),
     "tris_build_grouped_route": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "tris_ep_pack_rows": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "tris_ep_pack_rows": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
     "tris_router_topk": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "tris_shared_hidden_forward": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _vp]),
     "tris_grouped_forward": (C.c_int, [_P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp]),
@@ -101,6 +105,9 @@ def load():
         fn.argtypes = argtypes
     if lib.tris_compact3_kernel_abi_version() != 2:
         raise RuntimeError("trismoe_b200: compact3 payload ABI mismatch")
+    if lib.tris_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"trismoe_b200: the library has struct/entry-point ABI {lib.tris_abi_version()}, this "
+                           f"package was written for {ABI_VERSION}; rebuild it (python build.py --force)")
     _lib = lib
     return lib
 

@@ -742,6 +742,7 @@ struct GroupedArgs {
   const int32_t* segment_offsets;
   const int32_t* num_segments_dev;
   const int32_t* row_gather;
+  const int32_t* out_scatter;  // output row of each grouped row, or null
   int32_t* status;
   int32_t num_segments;
   int32_t num_rows;

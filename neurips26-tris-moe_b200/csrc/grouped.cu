@@ -285,8 +285,10 @@ __device__ __forceinline__ void finish_rows(const GroupedArgs& args, float* xbuf
       for (int c = 0; c < 4; ++c) {
         const int n = nt * 8 + 2 * t + (c & 1);
         const int og = o0 + out_local + g + 8 * (c >> 1);
-        if (n < rows && og < v.out_features)
-          outp[static_cast<size_t>(r0 + n) * v.out_features + og] = __float2half_rn(acc[nt][c]);
+        if (n < rows && og < v.out_features) {
+          const int orow = args.out_scatter ? args.out_scatter[r0 + n] : r0 + n;
+          if (orow >= 0) outp[static_cast<size_t>(orow) * v.out_features + og] = __float2half_rn(acc[nt][c]);
+        }
       }
     }
   }
@@ -494,6 +496,7 @@ static int fill_route(GroupedArgs& a, const TrisRouteView* route) {
   a.segment_offsets = route->segment_offsets;
   a.num_segments_dev = route->num_segments_dev;
   a.row_gather = route->row_gather;
+  a.out_scatter = route->out_row_scatter;
   a.num_segments = route->num_segments;
   a.num_rows = route->num_rows;
   a.status = route->status_dev;

@@ -228,7 +228,7 @@ static int launch_umma_grouped(const GroupedArgs& args, cudaStream_t stream, boo
 bool grouped_umma_applicable(const GroupedArgs& args, int rows_hint) {
   const TrisProjView& v = args.proj[0];
   return rows_hint > 32 && args.hidden_interleaved && (v.rank % 32) == 0 && v.rank <= 256 && args.ksplit <= 1 &&
-         (args.hidden_stride % 8) == 0;
+         (args.hidden_stride % 8) == 0 && args.out_scatter == nullptr;
 }
 
 int launch_grouped_umma(const GroupedArgs& args, int nproj, int epi, cudaStream_t stream, bool pdl) {

@@ -301,7 +301,8 @@ __global__ void __launch_bounds__(128) ep_pack_rows_kernel(
     const __half* __restrict__ hidden_gate, const __half* __restrict__ hidden_up, int rank_gu,
     const int32_t* __restrict__ selected, const int32_t* __restrict__ perm, const int32_t* __restrict__ tok,
     int num_rows, int top_k, int num_experts, int world, int capacity, __half* __restrict__ send_rows,
-    int32_t* __restrict__ send_ids, int32_t* __restrict__ combine_index, int32_t* __restrict__ overflow) {
+    int send_row_stride, int32_t* __restrict__ send_ids, int32_t* __restrict__ combine_index,
+    int32_t* __restrict__ overflow) {
   __shared__ int32_t s_first[64];  // first grouped row owned by each rank (world <= 64)
   const int base = num_experts / world, extra = num_experts % world;
   // rows are sorted by expert, so the first row of rank d is a lower bound: binary search
@@ -323,7 +324,10 @@ __global__ void __launch_bounds__(128) ep_pack_rows_kernel(
     const int row_end = (d + 1 < world) ? s_first[d + 1] : num_rows;
     const bool used = row < row_end;
     if (threadIdx.x == 0) {
-      send_ids[pos] = used ? selected[perm[row]] : -1;
+      const int32_t id = used ? selected[perm[row]] : -1;
+      if (send_ids) send_ids[pos] = id;
+      if (send_row_stride >= 2 * rank_gu + 8)
+        *reinterpret_cast<int32_t*>(send_rows + static_cast<size_t>(pos) * send_row_stride + 2 * rank_gu) = id;
       if (used) combine_index[perm[row]] = pos;
       if (off == capacity - 1 && row + 1 < row_end) *overflow = 1;  // more rows for this rank than slots
     }
@@ -331,7 +335,7 @@ __global__ void __launch_bounds__(128) ep_pack_rows_kernel(
     const int t = tok[row];
     const uint4* g = reinterpret_cast<const uint4*>(hidden_gate + static_cast<size_t>(t) * rank_gu);
     const uint4* u = reinterpret_cast<const uint4*>(hidden_up + static_cast<size_t>(t) * rank_gu);
-    uint4* dst = reinterpret_cast<uint4*>(send_rows + static_cast<size_t>(pos) * 2 * rank_gu);
+    uint4* dst = reinterpret_cast<uint4*>(send_rows + static_cast<size_t>(pos) * send_row_stride);
     const int vecs = rank_gu >> 3;
     for (int i = threadIdx.x; i < 2 * vecs; i += blockDim.x) dst[i] = (i < vecs) ? g[i] : u[i - vecs];
   }
@@ -345,10 +349,15 @@ extern "C" int tris_ep_pack_rows(const void* hidden_gate_f16, const void* hidden
                                  const int32_t* selected_experts, const int32_t* perm,
                                  const int32_t* grouped_token_indices, int32_t num_rows, int32_t top_k,
                                  int32_t num_experts, int32_t world, int32_t capacity, void* send_rows_f16,
-                                 int32_t* send_ids, int32_t* combine_index, int32_t* overflow_dev, void* stream) {
+                                 int32_t send_row_stride, int32_t* send_ids, int32_t* combine_index,
+                                 int32_t* overflow_dev, void* stream) {
   TRIS_REQUIRE(hidden_gate_f16 && hidden_up_f16 && selected_experts && perm && grouped_token_indices && send_rows_f16 &&
-                   send_ids && combine_index && overflow_dev,
+                   combine_index && overflow_dev,
                TRIS_ERR_INVALID_ARG, "tris_ep_pack_rows: null pointer");
+  TRIS_REQUIRE(send_row_stride >= 2 * rank_gu && (send_row_stride & 7) == 0, TRIS_ERR_INVALID_ARG,
+               "tris_ep_pack_rows: send_row_stride %d must be a multiple of 8 and >= 2*rank", send_row_stride);
+  TRIS_REQUIRE(send_ids != nullptr || send_row_stride >= 2 * rank_gu + 8, TRIS_ERR_INVALID_ARG,
+               "tris_ep_pack_rows: no place for the expert ids (send_ids NULL and no room behind the rows)");
   TRIS_REQUIRE(rank_gu > 0 && (rank_gu & 7) == 0, TRIS_ERR_UNSUPPORTED, "tris_ep_pack_rows: rank must be a multiple of 8");
   TRIS_REQUIRE(num_rows >= 0 && top_k > 0 && num_experts > 0 && world >= 1 && world <= 64 && capacity > 0,
                TRIS_ERR_INVALID_ARG, "tris_ep_pack_rows: bad sizes rows=%d world=%d capacity=%d", num_rows, world, capacity);
@@ -356,7 +365,7 @@ extern "C" int tris_ep_pack_rows(const void* hidden_gate_f16, const void* hidden
   ep_pack_rows_kernel<<<std::min(slots, 4096), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half*>(hidden_gate_f16), static_cast<const __half*>(hidden_up_f16), rank_gu, selected_experts,
       perm, grouped_token_indices, num_rows, top_k, num_experts, world, capacity, static_cast<__half*>(send_rows_f16),
-      send_ids, combine_index, overflow_dev);
+      send_row_stride, send_ids, combine_index, overflow_dev);
   return check_cuda(cudaGetLastError(), "ep_pack_rows_kernel launch");
 }
 

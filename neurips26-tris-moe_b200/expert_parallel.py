@@ -38,6 +38,16 @@ _SHARD_KEYS = ("qweight1", "qweight2_sparse", "qweight2_sparse_prefix", "q_gmap_
                "output_scale", "bias")
 
 
+def balanced_rows_per_peer(tokens_per_rank: int, top_k: int, world: int, sigmas: float = 6.0) -> int:
+    """Rows one rank sends to one peer when every expert is equally likely: the binomial mean
+    ``tokens * top_k / world`` plus ``sigmas`` standard deviations, rounded up to a multiple of 8
+    and capped at the worst case ``tokens * top_k``."""
+    rows = tokens_per_rank * top_k
+    p = 1.0 / max(1, world)
+    bound = rows * p + sigmas * (rows * p * (1.0 - p)) ** 0.5
+    return int(min(rows, -(-int(bound + 1) // 8) * 8))
+
+
 def expert_range(num_experts: int, rank: int, world: int):
     """Experts owned by ``rank``: contiguous, sizes differ by at most one."""
     base, extra = divmod(num_experts, world)
@@ -126,13 +136,19 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         self.shared: dict = {}
         self.router_weight: Optional[torch.Tensor] = None
         self.capacity_tokens = 0  # tokens per rank the fixed-capacity exchange is sized for
+        self.capacity_rows = 0    # rows per peer slot
         self._overflow = None
 
-    def set_capacity(self, max_tokens_per_rank: int) -> "ExpertParallelMoeBlock":
-        """Sizes the fixed-capacity exchange: every rank must use the same value, at least the
-        largest per-rank batch (each peer slot holds ``max_tokens_per_rank * top_k`` rows, the
-        worst case, so no routed row can be dropped)."""
+    def set_capacity(self, max_tokens_per_rank: int, rows_per_peer: Optional[int] = None) -> "ExpertParallelMoeBlock":
+        """Sizes the fixed-capacity exchange; every rank must pass the same values.
+        ``max_tokens_per_rank`` is the largest per-rank batch.  ``rows_per_peer`` is the number of
+        routed rows a rank can send to one peer per step: the default, ``max_tokens_per_rank *
+        top_k``, is the worst case and can never overflow; a smaller value moves less padding
+        (:func:`balanced_rows_per_peer` gives mean + 6 sigma of balanced routing) and drops the
+        rows beyond it - :meth:`exchange_overflowed` tells whether that ever happened."""
         self.capacity_tokens = int(max_tokens_per_rank)
+        worst = self.capacity_tokens * self.top_k
+        self.capacity_rows = worst if rows_per_peer is None else max(1, min(worst, int(rows_per_peer)))
         return self
 
     def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate, shared_up, shared_down,
@@ -193,37 +209,38 @@ class ExpertParallelMoeBlock(torch.nn.Module):
 
     def _local_experts(self, recv_hidden: torch.Tensor, recv_local_ids: torch.Tensor, rows_hint: int = 0) -> torch.Tensor:
         """gate/up -> SiLU*mul -> down for the rows this rank received; returns [rows, H] in the
-        received order."""
+        received order.  ``recv_hidden`` is [rows, >= 2*r]: gate and up backbone outputs side by
+        side at the start of every row (anything behind them is skipped through the row stride).
+        Rows with a negative id are padding: they are in no segment and their output rows are
+        never written."""
         lib = _native.load()
         dev = recv_hidden.device
         Rr = int(recv_hidden.shape[0])
-        out = torch.empty((Rr, self.hidden_size), dtype=torch.float16, device=dev)
+        down = torch.empty((Rr, self.hidden_size), dtype=torch.float16, device=dev)
         if Rr == 0:
-            return out
+            return down
         stream = torch.cuda.current_stream(dev).cuda_stream
         r_gu = int(self.shared["gate"].shape[0])
         r_d = int(self.shared["down"].shape[0])
         inter_gu, inter_d = r_gu % 32 == 0, r_d % 32 == 0
-        recv_hidden = recv_hidden.contiguous()  # [rows, 2*r_gu]: gate and up backbone outputs side by side
+        recv_hidden = recv_hidden.contiguous()
+        stride = int(recv_hidden.shape[1])
         hg_ptr = recv_hidden.data_ptr()
         hu_ptr = hg_ptr + 2 * r_gu
         route = self._route(recv_local_ids.reshape(Rr, 1).contiguous(), self.hi - self.lo)
         route["max_rows"] = rows_hint if rows_hint > 0 else Rr
         va, vb, vd = (proj_view(self.payloads[n]) for n in ("gate", "up", "down"))
         mlp = torch.empty((Rr, self.intermediate_size), dtype=torch.float16, device=dev)
-        rv = self._route_view(route, route["tok"], inter_gu, hidden_stride=2 * r_gu)
+        rv = self._route_view(route, route["tok"], inter_gu, hidden_stride=stride)
         _native.check(lib.tris_grouped_pair_forward(C.byref(va), C.byref(vb), C.byref(rv), hg_ptr, hu_ptr,
                                                     mlp.data_ptr(), None, 1, stream), "grouped_pair_forward")
         live = route["segment_offsets"][route["experts"]:]  # total routed rows, on the device
         hd = self._backbone(mlp, self.shared["down"], inter_d, live_rows=live)
-        down = torch.empty((Rr, self.hidden_size), dtype=torch.float16, device=dev)
         rv = self._route_view(route, None, inter_d)
+        rv.out_row_scatter = route["tok"].data_ptr()  # grouped row -> the slot it was received in
         _native.check(lib.tris_grouped_forward(C.byref(vd), C.byref(rv), hd.data_ptr(), down.data_ptr(), stream),
                       "grouped_forward")
-        ones = torch.ones((Rr,), dtype=torch.float32, device=dev)
-        _native.check(lib.tris_combine_routed(down.data_ptr(), route["row_of_flat"].data_ptr(), ones.data_ptr(), Rr, 1,
-                                              self.hidden_size, out.data_ptr(), stream), "ungroup")
-        return out
+        return down
 
     def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None, exact_splits: bool = False):
         """``hidden_states`` are this rank's tokens ``[..., H]`` fp16; returns
@@ -269,7 +286,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                 if T > self.capacity_tokens:
                     raise RuntimeError(f"trismoe_b200: batch of {T} tokens exceeds the exchange capacity "
                                        f"{self.capacity_tokens} set with set_capacity()")
-                returned, index = self._padded_exchange(hg, hu, sel, route, self.capacity_tokens * self.top_k)
+                returned, index = self._padded_exchange(hg, hu, sel, route, self.capacity_rows)
             if T:
                 _native.check(lib.tris_combine_routed(returned.data_ptr(), index.data_ptr(), wts.data_ptr(),
                                                       T, self.top_k, self.hidden_size, y.data_ptr(), stream), "combine")
@@ -277,28 +294,28 @@ class ExpertParallelMoeBlock(torch.nn.Module):
 
     def _padded_exchange(self, hg: torch.Tensor, hu: torch.Tensor, sel: torch.Tensor, route: dict, capacity: int):
         """Fixed-capacity exchange; every rank must call it with the same ``capacity`` (rows per
-        peer slot).  One kernel packs the routed rows into the [peer, capacity] send layout,
-        three equal-split all-to-alls move rows, expert ids and results; nothing is read back
-        to the host.  Returns the result rows in the send layout and, for every flat
-        (token, slot) entry, the index of its row there."""
+        peer slot).  One kernel packs the routed rows - two backbone outputs and, behind them, the
+        expert id - into the [peer, capacity] send layout; one equal-split all-to-all moves them,
+        one brings the results back; nothing is read back to the host.  Returns the result rows in
+        the send layout and, for every flat (token, slot) entry, the index of its row there (a
+        dropped row keeps index -1 and contributes nothing)."""
         lib = _native.load()
         dev, N = hg.device, self.world
         R, r_gu = int(route["rows"]), int(hg.shape[1])
         slots = N * capacity
+        stride = 2 * r_gu + 8  # halves per slot: gate row, up row, 16 bytes that start with the expert id
         stream = torch.cuda.current_stream(dev).cuda_stream
-        send_rows = torch.empty((slots, 2 * r_gu), dtype=torch.float16, device=dev)
-        send_ids = torch.empty((slots,), dtype=torch.int32, device=dev)
-        index = torch.empty((max(R, 1),), dtype=torch.int32, device=dev)
+        send_rows = torch.empty((slots, stride), dtype=torch.float16, device=dev)
+        index = torch.full((max(R, 1),), -1, dtype=torch.int32, device=dev)
         if self._overflow is None or self._overflow.device != dev:
             self._overflow = torch.zeros((1,), dtype=torch.int32, device=dev)
         _native.check(lib.tris_ep_pack_rows(hg.data_ptr(), hu.data_ptr(), r_gu, sel.data_ptr(), route["perm"].data_ptr(),
                                             route["tok"].data_ptr(), R, self.top_k, self.num_experts, N, capacity,
-                                            send_rows.data_ptr(), send_ids.data_ptr(), index.data_ptr(),
+                                            send_rows.data_ptr(), stride, None, index.data_ptr(),
                                             self._overflow.data_ptr(), stream), "ep_pack_rows")
         recv_rows = torch.empty_like(send_rows)
-        recv_ids = torch.empty_like(send_ids)
         dist.all_to_all_single(recv_rows, send_rows, group=self.group)
-        dist.all_to_all_single(recv_ids, send_ids, group=self.group)
+        recv_ids = recv_rows.view(torch.int32)[:, r_gu]  # the int32 right behind the 2*r_gu halves
         local_ids = recv_ids - self.lo  # padding slots (-1) stay negative and are skipped by the route
         expected = max(1, (N * R) // max(1, self.hi - self.lo))  # rows per local expert if routing is balanced
         result = self._local_experts(recv_rows, local_ids, rows_hint=int(expected + 4 * expected ** 0.5))
@@ -340,7 +357,7 @@ def run_bench(args, rank: int, world: int, device) -> None:
         blk = ExpertParallelMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
         blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
                                   layer["shared_down"], layer["router_weight"], device=device)
-        blocks.append(blk.set_capacity(T))
+        blocks.append(blk.set_capacity(T, balanced_rows_per_peer(T, shape.top_k, world)))
     x = synth.synth_activations(T, shape.hidden_size, seed=1000 + rank).to(device)
     x_host = x.cpu().pin_memory()
     y_host = torch.empty_like(x_host).pin_memory()
@@ -402,6 +419,8 @@ def run_bench(args, rank: int, world: int, device) -> None:
             y_host.copy_(step(xd).view(T, -1), non_blocking=True)
 
     e2e_ms = timed(e2e, args.steps, args.warmup)
+    overflowed = torch.tensor([int(any(b.exchange_overflowed() for b in blocks))], device=device)
+    dist.all_reduce(overflowed, op=dist.ReduceOp.MAX)
     if rank == 0:
         clocks = sampler.stop()
         total = T * world
@@ -412,6 +431,7 @@ def run_bench(args, rank: int, world: int, device) -> None:
             "config": {"workload": "OLMoE-shaped 16-layer MoE stack, decode batch 128 per GPU, experts sharded over the "
                                    "GPUs (expert parallel), NCCL all-to-all dispatch and combine",
                        "tokens_per_step": total, "layers": layers, "parallelism": f"ep{world}", "launch_mode": mode,
+                       "exchange_rows_per_peer": blocks[0].capacity_rows, "exchange_overflowed": bool(overflowed.item()),
                        "cold_cache": "16 distinct layer payloads per rank"},
             "e2e": {"value": round(total / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": T * 2048 * 2,
                     "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},

@@ -297,6 +297,14 @@ def _route_view(route: dict, num_rows: int, keep: list) -> TrisRouteView:
     rv.row_gather = None
     rv.status_dev = None
     rv.flags = 0
+    # extension of the route dict (no reference counterpart): "_out_row_scatter" [R] int32 sends the
+    # result of grouped row i to output row scatter[i] (a negative entry drops it)
+    scatter = route.get("_out_row_scatter")
+    if isinstance(scatter, torch.Tensor):
+        if scatter.dtype != torch.int32 or not scatter.is_contiguous():
+            scatter = scatter.to(torch.int32).contiguous()
+        keep.append(scatter)
+        rv.out_row_scatter = scatter.data_ptr()
     return rv
 
 

@@ -53,6 +53,24 @@ def _worker(rank, world, port, out):
                 err = (got.float() - want.float()).abs()
                 ok = ok and bool(torch.isfinite(got.float()).all()) and \
                     float(err.max()) <= 2e-3 * max(1.0, float(want.float().abs().max()))
+        ok = ok and not blk.exchange_overflowed()
+        # a slot count below the worst case: 9 tokens * top-2 = 18 rows, 14 slots per peer here
+        # (mean 9 + 6 sigma = 21.7 is capped by the worst case, so the test picks its own value);
+        # whatever is dropped must be reported, and nothing else may change
+        T = 9
+        blk.set_capacity(9, rows_per_peer=14)
+        x = synth.synth_activations(T, shape.hidden_size, seed=100 + rank).to(dev)
+        logits = synth.synth_router_logits(T, shape.num_experts, seed=105 + rank).to(dev)
+        want, _ = full(x.view(1, T, -1), router_logits=logits)
+        got, _ = blk(x.view(1, T, -1), router_logits=logits)
+        torch.cuda.synchronize()
+        sel = torch.topk(torch.softmax(logits.float(), 1), shape.top_k, -1)[1]
+        to_peer = [int(((sel // (shape.num_experts // world)) == d).sum()) for d in range(world)]
+        dropped = any(n > 14 for n in to_peer)
+        ok = ok and (blk.exchange_overflowed() == dropped)
+        if not dropped:
+            err = (got.float() - want.float()).abs()
+            ok = ok and float(err.max()) <= 2e-3 * max(1.0, float(want.float().abs().max()))
         out[rank] = ok
     finally:
         dist.destroy_process_group()

@@ -288,6 +288,13 @@ def test_grouped_forward_from_segment_lengths_and_bad_args(tm, small_layer):
     ref = _grouped_reference(weights["down"], h, route)
     max_abs, mean_rel = orc.error_metrics(out.float().cpu().numpy(), ref)
     assert max_abs <= MAX_ABS and mean_rel <= MEAN_REL
+    # results sent to caller-chosen output rows: the same numbers, permuted
+    scatter = torch.from_numpy(rng.permutation(R).astype(np.int32)).cuda()
+    troute = {"expert_ids": torch.tensor([0, 2, 3], dtype=torch.int32, device="cuda"),
+              "segment_offsets": torch.tensor([0, 2, 7, 8], dtype=torch.int32, device="cuda"),
+              "_out_row_scatter": scatter}
+    out2 = tm.run_grouped_structured_expert_forward(p, torch.from_numpy(h).cuda(), None, troute)
+    assert torch.equal(out2[scatter.long()], out)
     # reference behaviour: wrong dtype / wrong rank -> None, not an exception
     assert tm.run_grouped_structured_expert_forward(p, torch.zeros((R, r), device="cuda"), None, lengths) is None
     assert tm.run_grouped_structured_expert_forward(p, torch.zeros((R, r + 8), dtype=torch.float16, device="cuda"), None, lengths) is None
