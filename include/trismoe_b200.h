@@ -227,6 +227,46 @@ int tris_ep_pack_rows(const void* hidden_gate_f16, const void* hidden_up_f16, in
                       void* send_rows_f16, int32_t send_row_stride, int32_t* send_ids, int32_t* combine_index,
                       int32_t* overflow_dev, void* stream);
 
+/*
+ * Expert-parallel exchange over peer memory (no reference counterpart; no collective library
+ * call).  Every rank owns a receive buffer [world * capacity, row_stride] fp16 for routed rows,
+ * a result buffer [world * capacity, hidden] fp16 and two int32[world] counter arrays (zeroed
+ * once), all mapped into every peer (CUDA IPC or the like; the caller sets that up and passes
+ * device arrays of the world's pointers, its own included).
+ *
+ * tris_ep_dispatch_peer  = tris_ep_pack_rows writing slot (owner d, off) straight into rank d's
+ *                          receive buffer at slot (my_rank, off), expert id behind the two
+ *                          activation rows, then adding 1 per CTA to counter my_rank of every
+ *                          peer's dispatch counters.
+ * tris_ep_return_peer    sends block s of `results` (received-slot order; rows whose received id
+ *                          is negative are skipped) to block my_rank of rank s's result buffer and
+ *                          bumps every peer's return counters the same way.
+ * tris_ep_wait           one CTA: waits until all `world` counters have reached
+ *                          (*step_dev + 1) * tris_ep_signal_increment(), then increments
+ *                          *step_dev (a device int32, zeroed once).  Gives up after ~2 s and
+ *                          writes TRIS_ERR_TIMEOUT to *status_dev.  Counters only grow, so the
+ *                          sequence can be replayed from a CUDA graph; every rank must run the
+ *                          same number of steps.
+ */
+int tris_ep_signal_increment(void);
+/* Lets kernels on the current device use memory of `peer_device` (cudaDeviceEnablePeerAccess;
+   "already enabled" is success).  TRIS_ERR_UNSUPPORTED when the devices have no P2P path. */
+int tris_ep_enable_peer_access(int32_t peer_device);
+/* Maps an allocation another process exported (the 64 bytes of its cudaIpcMemHandle_t) into the
+   current device's context; *base_out = the allocation's base address in this process.  One open
+   per allocation and process; tris_ep_close_peer_memory unmaps it. */
+int tris_ep_open_peer_memory(const void* ipc_handle_64, void** base_out);
+int tris_ep_close_peer_memory(void* base);
+int tris_ep_dispatch_peer(const void* hidden_gate_f16, const void* hidden_up_f16, int32_t rank_gu,
+                          const int32_t* selected_experts, const int32_t* perm, const int32_t* grouped_token_indices,
+                          int32_t num_rows, int32_t num_experts, int32_t world, int32_t my_rank, int32_t capacity,
+                          void* const* peer_recv_rows_dev, int32_t row_stride, int32_t* combine_index,
+                          int32_t* overflow_dev, int32_t* const* peer_flags_dev, void* stream);
+int tris_ep_return_peer(const void* results_f16, const void* recv_rows_f16, int32_t row_stride, int32_t rank_gu,
+                        int32_t hidden_size, int32_t world, int32_t my_rank, int32_t capacity,
+                        void* const* peer_back_dev, int32_t* const* peer_flags_dev, void* stream);
+int tris_ep_wait(const int32_t* flags_dev, int32_t* step_dev, int32_t world, int32_t* status_dev, void* stream);
+
 /* ---- backbone ---------------------------------------------------------------------- */
 
 /*

@@ -73,6 +73,13 @@ SIGNATURES = {
     "tris_compact3_dequantize": (C.c_int, [_P(TrisProjView), _vp, _vp]),
     "tris_build_grouped_route": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tris_ep_pack_rows": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
+    "tris_ep_signal_increment": (C.c_int, []),
+    "tris_ep_enable_peer_access": (C.c_int, [_i32]),
+    "tris_ep_open_peer_memory": (C.c_int, [_vp, _P(_vp)]),
+    "tris_ep_close_peer_memory": (C.c_int, [_vp]),
+    "tris_ep_dispatch_peer": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
+    "tris_ep_return_peer": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "tris_ep_wait": (C.c_int, [_vp, _vp, _i32, _vp, _vp]),
     "tris_router_topk": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "tris_shared_hidden_forward": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _vp]),
     "tris_grouped_forward": (C.c_int, [_P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp]),

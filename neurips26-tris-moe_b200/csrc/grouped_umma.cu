@@ -185,15 +185,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
         for (int j = 0; j < 16; ++j) {
           const int n = c0 + j;
           if (n >= rows || og >= v0.out_features) continue;
+          const int orow = args.out_scatter ? args.out_scatter[r0 + n] : r0 + n;  // same address for the warp
+          if (orow < 0) continue;
+          const size_t oi = static_cast<size_t>(orow) * v0.out_features + og;
           const float x = va[j] * scale[0] + bias[0];
           if (EPI == EPI_SILU_MUL) {
             const float u = vb[j] * scale[NPROJ - 1] + bias[NPROJ - 1];
-            args.out[0][static_cast<size_t>(r0 + n) * v0.out_features + og] = __float2half_rn(__fdividef(x, 1.f + __expf(-x)) * u);
+            args.out[0][oi] = __float2half_rn(__fdividef(x, 1.f + __expf(-x)) * u);
           } else {
-            args.out[0][static_cast<size_t>(r0 + n) * v0.out_features + og] = __float2half_rn(x);
-            if (NPROJ == 2)
-              args.out[1][static_cast<size_t>(r0 + n) * v0.out_features + og] =
-                  __float2half_rn(vb[j] * scale[NPROJ - 1] + bias[NPROJ - 1]);
+            args.out[0][oi] = __float2half_rn(x);
+            if (NPROJ == 2) args.out[1][oi] = __float2half_rn(vb[j] * scale[NPROJ - 1] + bias[NPROJ - 1]);
           }
         }
       }
@@ -228,7 +229,7 @@ static int launch_umma_grouped(const GroupedArgs& args, cudaStream_t stream, boo
 bool grouped_umma_applicable(const GroupedArgs& args, int rows_hint) {
   const TrisProjView& v = args.proj[0];
   return rows_hint > 32 && args.hidden_interleaved && (v.rank % 32) == 0 && v.rank <= 256 && args.ksplit <= 1 &&
-         (args.hidden_stride % 8) == 0 && args.out_scatter == nullptr;
+         (args.hidden_stride % 8) == 0;
 }
 
 int launch_grouped_umma(const GroupedArgs& args, int nproj, int epi, cudaStream_t stream, bool pdl) {

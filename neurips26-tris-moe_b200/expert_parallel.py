@@ -121,6 +121,70 @@ def expert_parallel_exchange(hidden_grouped: torch.Tensor, grouped_expert_ids: t
     return plan.combine(result)
 
 
+class PeerExchangeBuffers:
+    """Receive buffer, result buffer and counters of one block, mapped into every rank of the
+    group through CUDA IPC, plus the device tables of everybody's pointers that the exchange
+    kernels take (``tris_ep_dispatch_peer`` / ``tris_ep_return_peer`` / ``tris_ep_wait``).
+
+    Building one is a collective call (handles are gathered over the process group).  All ranks
+    must live on one node with a P2P path between their GPUs."""
+
+    _opened: dict = {}  # (peer device, IPC handle) -> base address in this process; one open per allocation
+
+    @staticmethod
+    def _export(t: torch.Tensor):
+        """(IPC handle of the allocation holding ``t``, byte offset of ``t`` in it)."""
+        shared = t.untyped_storage()._share_cuda_()
+        handle, offset = bytes(shared[1]), int(shared[3])
+        if len(handle) > 64:  # torch prefixes the 64-byte cudaIpcMemHandle_t with a version and a kind byte
+            if handle[-65:-64] == b"e":
+                raise RuntimeError("trismoe_b200: peer exchange needs cudaMalloc-backed tensors (expandable "
+                                   "segments of the caching allocator cannot be exported with cudaIpcGetMemHandle)")
+            handle = handle[-64:]
+        return handle, offset + t.storage_offset() * t.element_size()
+
+    def __init__(self, group, device: torch.device, slots: int, row_stride: int, hidden_size: int):
+        lib = _native.load()
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.device = device
+        self.recv = torch.zeros((slots, row_stride), dtype=torch.float16, device=device)
+        self.back = torch.zeros((slots, hidden_size), dtype=torch.float16, device=device)
+        self.flags = torch.zeros((2, 64), dtype=torch.int32, device=device)  # [0] dispatch, [1] return counters
+        self.steps = torch.zeros((2,), dtype=torch.int32, device=device)
+        self.status = torch.zeros((1,), dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        mine = (device.index, [self._export(t) for t in (self.recv, self.back, self.flags)])
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, mine, group=group)
+        recv_ptrs, back_ptrs, dflag_ptrs, rflag_ptrs = [], [], [], []
+        with torch.cuda.device(device):  # the mappings belong to the device whose kernels use them
+            for r, (peer_dev, exported) in enumerate(gathered):
+                if r == self.rank:
+                    ptrs = [t.data_ptr() for t in (self.recv, self.back, self.flags)]
+                else:
+                    _native.check(lib.tris_ep_enable_peer_access(int(peer_dev)), "enable_peer_access")
+                    ptrs = []
+                    for handle, offset in exported:
+                        key = (device.index, int(peer_dev), handle)
+                        if key not in self._opened:
+                            base = C.c_void_p()
+                            _native.check(lib.tris_ep_open_peer_memory(handle, C.byref(base)), "open_peer_memory")
+                            self._opened[key] = int(base.value)
+                        ptrs.append(self._opened[key] + offset)
+                recv_ptrs.append(ptrs[0])
+                back_ptrs.append(ptrs[1])
+                dflag_ptrs.append(ptrs[2])
+                rflag_ptrs.append(ptrs[2] + 64 * 4)
+        table = lambda ptrs: torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self.recv_ptrs, self.back_ptrs = table(recv_ptrs), table(back_ptrs)
+        self.dflag_ptrs, self.rflag_ptrs = table(dflag_ptrs), table(rflag_ptrs)
+        dist.barrier(group=group)  # nobody signals before everybody has mapped everything
+
+    def timed_out(self) -> bool:
+        """True if a bounded wait for a peer ever ran out (reads one device word)."""
+        return bool(self.status.item())
+
+
 class ExpertParallelMoeBlock(torch.nn.Module):
     """MoE block whose experts are sharded over the ranks of ``group`` (one process per GPU)."""
 
@@ -138,6 +202,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         self.capacity_tokens = 0  # tokens per rank the fixed-capacity exchange is sized for
         self.capacity_rows = 0    # rows per peer slot
         self._overflow = None
+        self._peer: Optional[PeerExchangeBuffers] = None  # set by use_peer_exchange()
 
     def set_capacity(self, max_tokens_per_rank: int, rows_per_peer: Optional[int] = None) -> "ExpertParallelMoeBlock":
         """Sizes the fixed-capacity exchange; every rank must pass the same values.
@@ -149,6 +214,17 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         self.capacity_tokens = int(max_tokens_per_rank)
         worst = self.capacity_tokens * self.top_k
         self.capacity_rows = worst if rows_per_peer is None else max(1, min(worst, int(rows_per_peer)))
+        return self
+
+    def use_peer_exchange(self) -> "ExpertParallelMoeBlock":
+        """Switches the fixed-capacity exchange from NCCL all-to-all to kernels that write into
+        the peers' buffers over NVLink (one node, P2P-capable GPUs).  Collective: every rank calls
+        it, after :meth:`set_capacity` and :meth:`load_grouped_payloads`."""
+        if self.capacity_rows <= 0 or not self.shared:
+            raise RuntimeError("trismoe_b200: call set_capacity() and load_grouped_payloads() before use_peer_exchange()")
+        r_gu = int(self.shared["gate"].shape[0])
+        dev = self.shared["gate"].device
+        self._peer = PeerExchangeBuffers(self.group, dev, self.world * self.capacity_rows, 2 * r_gu + 8, self.hidden_size)
         return self
 
     def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate, shared_up, shared_down,
@@ -286,7 +362,8 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                 if T > self.capacity_tokens:
                     raise RuntimeError(f"trismoe_b200: batch of {T} tokens exceeds the exchange capacity "
                                        f"{self.capacity_tokens} set with set_capacity()")
-                returned, index = self._padded_exchange(hg, hu, sel, route, self.capacity_rows)
+                exchange = self._peer_exchange if self._peer is not None else self._padded_exchange
+                returned, index = exchange(hg, hu, sel, route, self.capacity_rows)
             if T:
                 _native.check(lib.tris_combine_routed(returned.data_ptr(), index.data_ptr(), wts.data_ptr(),
                                                       T, self.top_k, self.hidden_size, y.data_ptr(), stream), "combine")
@@ -323,6 +400,40 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         dist.all_to_all_single(back, result, group=self.group)
         return back, index
 
+    def _peer_exchange(self, hg: torch.Tensor, hu: torch.Tensor, sel: torch.Tensor, route: dict, capacity: int):
+        """The fixed-capacity exchange without a collective call: the dispatch kernel writes every
+        routed row into its owner's receive buffer over NVLink and bumps the owner's counters, a
+        one-CTA kernel waits for all peers' rows, the local experts run on them, a second kernel
+        sends the result rows back the same way.  Same results and layout as
+        :meth:`_padded_exchange`."""
+        lib = _native.load()
+        pb = self._peer
+        dev, N = hg.device, self.world
+        R, r_gu = int(route["rows"]), int(hg.shape[1])
+        stride = 2 * r_gu + 8
+        if capacity * N != pb.recv.shape[0] or stride != pb.recv.shape[1]:
+            raise RuntimeError("trismoe_b200: exchange sizes changed after use_peer_exchange(); call it again on every rank")
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        index = torch.full((max(R, 1),), -1, dtype=torch.int32, device=dev)
+        if self._overflow is None or self._overflow.device != dev:
+            self._overflow = torch.zeros((1,), dtype=torch.int32, device=dev)
+        _native.check(lib.tris_ep_dispatch_peer(hg.data_ptr(), hu.data_ptr(), r_gu, sel.data_ptr(), route["perm"].data_ptr(),
+                                                route["tok"].data_ptr(), R, self.num_experts, N, self.rank, capacity,
+                                                pb.recv_ptrs.data_ptr(), stride, index.data_ptr(),
+                                                self._overflow.data_ptr(), pb.dflag_ptrs.data_ptr(), stream), "ep_dispatch_peer")
+        _native.check(lib.tris_ep_wait(pb.flags[0].data_ptr(), pb.steps[0:].data_ptr(), N, pb.status.data_ptr(), stream),
+                      "ep_wait (rows)")
+        recv_ids = pb.recv.view(torch.int32)[:, r_gu]
+        local_ids = recv_ids - self.lo
+        expected = max(1, (N * R) // max(1, self.hi - self.lo))
+        result = self._local_experts(pb.recv, local_ids, rows_hint=int(expected + 4 * expected ** 0.5))
+        _native.check(lib.tris_ep_return_peer(result.data_ptr(), pb.recv.data_ptr(), stride, r_gu, self.hidden_size, N,
+                                              self.rank, capacity, pb.back_ptrs.data_ptr(), pb.rflag_ptrs.data_ptr(),
+                                              stream), "ep_return_peer")
+        _native.check(lib.tris_ep_wait(pb.flags[1].data_ptr(), pb.steps[1:].data_ptr(), N, pb.status.data_ptr(), stream),
+                      "ep_wait (results)")
+        return pb.back, index
+
     def exchange_overflowed(self) -> bool:
         """True if any fixed-capacity exchange so far had more rows for a peer than slots
         (cannot happen with the default capacity of tokens * top_k); reads one device word."""
@@ -358,6 +469,23 @@ def run_bench(args, rank: int, world: int, device) -> None:
         blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
                                   layer["shared_down"], layer["router_weight"], device=device)
         blocks.append(blk.set_capacity(T, balanced_rows_per_peer(T, shape.top_k, world)))
+    # exchange through peer memory unless TRIS_EP_EXCHANGE=nccl or the mapping cannot be set up
+    exchange = "nccl all-to-all"
+    if os.environ.get("TRIS_EP_EXCHANGE", "peer") != "nccl":
+        try:
+            for blk in blocks:
+                blk.use_peer_exchange()
+            exchange = "peer memory (NVLink stores + counters)"
+        except Exception as exc:  # noqa: BLE001
+            for blk in blocks:
+                blk._peer = None
+            exchange = f"nccl all-to-all (peer mapping failed: {type(exc).__name__})"
+    agree = [None] * world
+    dist.all_gather_object(agree, exchange)
+    if any(a != exchange for a in agree):  # all ranks or none
+        for blk in blocks:
+            blk._peer = None
+        exchange = "nccl all-to-all (peer mapping failed on a rank)"
     x = synth.synth_activations(T, shape.hidden_size, seed=1000 + rank).to(device)
     x_host = x.cpu().pin_memory()
     y_host = torch.empty_like(x_host).pin_memory()
@@ -421,6 +549,8 @@ def run_bench(args, rank: int, world: int, device) -> None:
     e2e_ms = timed(e2e, args.steps, args.warmup)
     overflowed = torch.tensor([int(any(b.exchange_overflowed() for b in blocks))], device=device)
     dist.all_reduce(overflowed, op=dist.ReduceOp.MAX)
+    timed_out = torch.tensor([int(any(b._peer is not None and b._peer.timed_out() for b in blocks))], device=device)
+    dist.all_reduce(timed_out, op=dist.ReduceOp.MAX)
     if rank == 0:
         clocks = sampler.stop()
         total = T * world
@@ -429,9 +559,10 @@ def run_bench(args, rank: int, world: int, device) -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "OLMoE-shaped 16-layer MoE stack, decode batch 128 per GPU, experts sharded over the "
-                                   "GPUs (expert parallel), NCCL all-to-all dispatch and combine",
+                                   "GPUs (expert parallel), dispatch and combine over NVLink",
                        "tokens_per_step": total, "layers": layers, "parallelism": f"ep{world}", "launch_mode": mode,
-                       "exchange_rows_per_peer": blocks[0].capacity_rows, "exchange_overflowed": bool(overflowed.item()),
+                       "exchange": exchange, "exchange_rows_per_peer": blocks[0].capacity_rows,
+                       "exchange_overflowed": bool(overflowed.item()), "exchange_timed_out": bool(timed_out.item()),
                        "cold_cache": "16 distinct layer payloads per rank"},
             "e2e": {"value": round(total / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": T * 2048 * 2,
                     "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},

@@ -53,7 +53,29 @@ def _worker(rank, world, port, out):
                 err = (got.float() - want.float()).abs()
                 ok = ok and bool(torch.isfinite(got.float()).all()) and \
                     float(err.max()) <= 2e-3 * max(1.0, float(want.float().abs().max()))
+        # prefill-sized batch: ~100 rows per local expert, so the tensor-core grouped kernels run
+        # on the received rows (strided activations in, scattered rows out)
+        T = 200
+        blk.set_capacity(T)
+        x = synth.synth_activations(T, shape.hidden_size, seed=50 + rank).to(dev)
+        logits = synth.synth_router_logits(T, shape.num_experts, seed=55 + rank).to(dev)
+        want, _ = full(x.view(1, T, -1), router_logits=logits)
+        got, _ = blk(x.view(1, T, -1), router_logits=logits)
+        torch.cuda.synchronize()
+        err = (got.float() - want.float()).abs()
+        ok = ok and float(err.max()) <= 2e-3 * max(1.0, float(want.float().abs().max()))
         ok = ok and not blk.exchange_overflowed()
+        # the same exchange through peer memory (kernels write into the peers' buffers over NVLink,
+        # counters instead of a collective): bit-equal results, several steps in a row
+        got_nccl = got.clone()
+        blk.use_peer_exchange()
+        for _ in range(3):
+            got_peer, _ = blk(x.view(1, T, -1), router_logits=logits)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(got_peer, got_nccl)
+        ok = ok and not blk._peer.timed_out()
+        dist.barrier()
+        blk._peer = None  # back to the all-to-all path for the rest of the test
         # a slot count below the worst case: 9 tokens * top-2 = 18 rows, 14 slots per peer here
         # (mean 9 + 6 sigma = 21.7 is capped by the worst case, so the test picks its own value);
         # whatever is dropped must be reported, and nothing else may change
