@@ -128,7 +128,11 @@ def run_ours(args):
     if world > 1:
         from trismoe_b200 import expert_parallel
 
-        return expert_parallel.run_bench(args, rank, world, device)
+        try:
+            return expert_parallel.run_bench(args, rank, world, device)
+        finally:
+            dist.barrier()
+            dist.destroy_process_group()
 
     blocks, infos = build_stack(device)
     peak, peak_kind = measured_hbm_peak()

@@ -566,7 +566,9 @@ def run_bench(args, rank: int, world: int, device) -> None:
                        "cold_cache": "16 distinct layer payloads per rank"},
             "e2e": {"value": round(total / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": T * 2048 * 2,
                     "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},
-            "gpu_launches": args.steps * layers * 12,
+            # per layer: router GEMM, top-k, route, two backbones, dispatch, wait, route of the received rows,
+            # gate/up, down backbone, down, return, wait, combine (the all-to-all path has 2 fewer)
+            "gpu_launches": args.steps * layers * (14 if blocks[0]._peer is not None else 12),
             "roofline": None, "cpu_baseline": None, "clocks": clocks,
         }))
     dist.barrier()

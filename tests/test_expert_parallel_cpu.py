@@ -92,3 +92,75 @@ def test_partition_and_payload_sharding(lib):
     assert torch.equal(torch.cat([p["qweight1"] for p in parts]), full["qweight1"])
     assert torch.equal(torch.cat([p["q_gmap_gr_offsets"] for p in parts]), full["q_gmap_gr_offsets"])
     assert parts[0]["compact3_use_block_gr"] is True
+
+
+def test_balanced_rows_per_peer_bounds():
+    import trismoe_b200  # noqa: F401
+    from trismoe_b200 import expert_parallel as ep
+
+    for tokens, k, world in [(128, 8, 2), (128, 8, 8), (1, 8, 4), (9, 2, 2), (4096, 2, 8)]:
+        rows = tokens * k
+        c = ep.balanced_rows_per_peer(tokens, k, world)
+        assert c <= rows and (c % 8 == 0 or c == rows)
+        assert c >= min(rows, rows / world)          # never below the mean
+    assert ep.balanced_rows_per_peer(128, 8, 2) == 616   # 512 + 6 * 16 = 608 -> next multiple of 8 above it
+    assert ep.balanced_rows_per_peer(128, 8, 1) == 1024  # one rank: everything stays
+
+
+@pytest.mark.parametrize("world,num_experts,top_k,tokens,capacity", [
+    (2, 8, 2, [9, 5], 18),
+    (3, 7, 3, [4, 0, 6], 18),   # uneven expert split, a rank without tokens
+    (4, 64, 8, [16, 16, 16, 16], 56),  # fewer slots than the worst case (128): nothing overflows at this seed
+])
+def test_fixed_capacity_slot_layout(world, num_experts, top_k, tokens, capacity):
+    """The slot arithmetic of the fixed-capacity exchange (tris_ep_pack_rows /
+    tris_ep_dispatch_peer / tris_ep_return_peer), all ranks emulated in one process: rank s puts
+    row `off` of its rows for owner d into slot (s, off) of d's receive buffer, d answers into
+    slot (d, off) of s's result buffer, and combine_index[flat] = d * capacity + off finds it."""
+    import trismoe_b200  # noqa: F401
+    from trismoe_b200 import expert_parallel as ep
+
+    rng = np.random.default_rng(7)
+    recv = [np.full((world * capacity, 3), np.nan) for _ in range(world)]       # [value, expert id, unused]
+    recv_id = [np.full((world * capacity,), -1, np.int64) for _ in range(world)]
+    back = [np.full((world * capacity,), np.nan) for _ in range(world)]
+    routes, values, indexes, overflow = [], [], [], False
+    for s in range(world):
+        T = tokens[s]
+        sel = np.stack([rng.choice(num_experts, size=top_k, replace=False) for _ in range(T)]).astype(np.int64) \
+            if T else np.zeros((0, top_k), np.int64)
+        route = orc.build_route(sel, num_experts)
+        gid = route["grouped_expert_ids"].astype(np.int64)
+        val = rng.standard_normal(T * top_k)           # one number per flat (token, slot) entry
+        owner = ep.owner_of(torch.from_numpy(gid), num_experts, world).numpy() if gid.size else gid
+        first = np.searchsorted(owner, np.arange(world), side="left")
+        index = np.full((T * top_k,), -1, np.int64)
+        for d in range(world):
+            end = first[d + 1] if d + 1 < world else gid.size
+            overflow |= (end - first[d]) > capacity
+            for off in range(capacity):
+                row = first[d] + off
+                if row < end:
+                    flat = route["perm"][row]
+                    recv[d][s * capacity + off, 0] = val[flat]
+                    recv_id[d][s * capacity + off] = gid[row]
+                    index[flat] = d * capacity + off
+                else:
+                    recv_id[d][s * capacity + off] = -1
+        routes.append(sel)
+        values.append(val)
+        indexes.append(index)
+    assert not overflow
+    for d in range(world):  # every rank processes what it received and sends it back
+        lo, hi = ep.expert_range(num_experts, d, world)
+        for pos in range(world * capacity):
+            e = recv_id[d][pos]
+            if e < 0:
+                continue
+            assert lo <= e < hi
+            s, off = divmod(pos, capacity)
+            back[s][d * capacity + off] = recv[d][pos, 0] * (e + 1)
+    for s in range(world):
+        sel = routes[s].reshape(-1)
+        got = back[s][indexes[s]] if sel.size else np.zeros((0,))
+        assert np.array_equal(got, values[s] * (sel + 1))
