@@ -576,3 +576,36 @@ def test_layer_olmoe_shape_prefill_512(tm, olmoe_layer):
     for t in (5, 300):
         y_one, _ = blk(x[t: t + 1].view(1, 1, -1), router_logits=logits[t: t + 1])
         assert torch.allclose(y_one.view(-1).float(), y.view(T, -1)[t].float(), atol=3e-3, rtol=3e-3)
+
+
+# ---------------------------------------------------------------------------------------
+# (10) expert-parallel exchange: a wait for a peer that never signals ends by itself
+# ---------------------------------------------------------------------------------------
+def test_peer_wait_times_out_and_reports(tm):
+    """tris_ep_wait with counters nobody bumps: the one-CTA wait gives up after about two
+    seconds, writes TRIS_ERR_TIMEOUT to the status word and still advances the step; with the
+    counters at their target it returns at once and leaves the status alone.  The context stays
+    usable (the next launches run)."""
+    import time
+
+    lib = tm._native.load()
+    inc = lib.tris_ep_signal_increment()
+    assert inc > 0
+    flags = torch.zeros((64,), dtype=torch.int32, device="cuda")
+    step = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    t0 = time.perf_counter()
+    tm._native.check(lib.tris_ep_wait(flags.data_ptr(), step.data_ptr(), 2, status.data_ptr(), stream), "ep_wait")
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 1.0 < waited < 10.0, waited
+    assert int(status.item()) == 6 and int(step.item()) == 1  # TRIS_ERR_TIMEOUT
+    status.zero_()
+    flags[:2] = 2 * inc  # both peers have signalled step 2
+    t0 = time.perf_counter()
+    tm._native.check(lib.tris_ep_wait(flags.data_ptr(), step.data_ptr(), 2, status.data_ptr(), stream), "ep_wait")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    assert int(status.item()) == 0 and int(step.item()) == 2
+    assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0
