@@ -48,6 +48,9 @@ FALLBACK_HBM_GBS = 6650.0
 LAUNCHES_PER_LAYER = 7  # backbone+router GEMM, top-k, route, gate/up, down backbone, down, combine
 
 
+NCU_DRAM_BYTES_PER_LAUNCH = {"pair": 11729920, "down": 10625024}  # batch 128, 64 active experts
+
+
 def measured_hbm_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -203,7 +206,10 @@ def run_ours(args):
         "bound": "hbm", "kernel": f"grouped_compact3_kernel ({'gate/up dual + SiLU*mul' if dom == 'pair' else 'down'})",
         "achieved": round(kern[dom]["gbs"], 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
         "frac": round(kern[dom]["gbs"] / peak, 4), "frac_of_nominal_8TBs": round(kern[dom]["gbs"] / NOMINAL_HBM_GBS, 4),
-        "traffic": None, "us_per_launch": round(kern[dom]["us_per_launch"], 2),
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
+        # ncu capture summarised in profiles/grouped_compact3_olmoe_decode128.md (not measured in this run)
+        "traffic": NCU_DRAM_BYTES_PER_LAUNCH[dom], "traffic_source": "ncu capture, see profiles/",
+        "us_per_launch": round(kern[dom]["us_per_launch"], 2),
         "algorithmic_bytes_per_launch": int(kern[dom]["bytes_per_launch"]),
         "other_kernels": {n: {k: round(v, 2) for k, v in d.items()} for n, d in kern.items() if n != dom},
         "whole_layer": {"gbs": round(head["layer_gbs"], 1), "frac": round(head["layer_gbs"] / peak, 4),

@@ -270,6 +270,19 @@ int tris_ep_wait(const int32_t* flags_dev, int32_t* step_dev, int32_t world, int
 /* ---- backbone ---------------------------------------------------------------------- */
 
 /*
+ * PackedQuantMatrix4bit.dequantize (QL:2756-2784): the shared backbone of real checkpoints is a
+ * GPTQ-style 4-bit matrix - qweight [ceil(cols/8), rows] int32 (nibble j of word [i, r] = input
+ * column 8i+j of output row r), qzeros [num_groups, ceil(rows/8)] int32 (zero points minus one,
+ * packed along rows), scales [num_groups, rows] fp16, g_idx [cols] int32.  Writes
+ * weight[r, c] = fp16((q - zero) * scale) as fp16 [rows, cols], bit for bit what the reference
+ * hands to F.linear; run it once at load time and use the result as shared_sv.
+ */
+int tris_packed4_dequantize(const int32_t* qweight, const int32_t* qzeros, const void* scales_f16,
+                            const int32_t* g_idx, int32_t rows, int32_t cols, int32_t num_groups,
+                            void* weight_f16, void* stream);
+
+
+/*
  * hidden = x . shared_sv^T (QuantLinear.compute_shared_hidden fp16 branch, QL:4454-4502):
  * x [N, in] fp16 (rows optionally gathered through row_gather), shared_sv [r, in] fp16,
  * out [N, r] in the layout named by out_mode (TRIS_OUT_*).  num_rows_dev (optional device

@@ -24,6 +24,7 @@ from .qlinear_grouped import (  # noqa: F401
     compute_shared_hidden,
     decode_block_gr_gmap,
     dequantize_grouped_payload,
+    dequantize_packed_4bit,
     prepare_grouped_payload,
     run_grouped_structured_expert_forward,
     run_grouped_structured_expert_pair_forward,
@@ -43,6 +44,7 @@ __all__ = [
     "decode_block_gr_gmap",
     "dense_gmap_words",
     "dequantize_grouped_payload",
+    "dequantize_packed_4bit",
     "pack_bool_matrix",
     "pack_bool_vector",
     "pack_half4_words",

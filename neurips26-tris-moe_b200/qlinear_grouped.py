@@ -458,16 +458,55 @@ def compute_shared_hidden(x: torch.Tensor, shared_sv: torch.Tensor) -> torch.Ten
     return out.reshape(x.shape[:-1] + (rank,))
 
 
+def dequantize_packed_4bit(payload: dict, device) -> torch.Tensor:
+    """fp16 matrix ``[rows, cols]`` of a 4-bit packed matrix payload (keys ``qweight``, ``qzeros``,
+    ``scales``, ``g_idx`` and optionally ``rows``/``cols``), bit for bit what
+    ``PackedQuantMatrix4bit.dequantize`` (qlinear_cuda.py:2756-2784) computes in fp16; built by
+    a CUDA kernel on ``device``."""
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError("trismoe_b200: the 4-bit backbone is expanded on a CUDA device (there is no CPU fallback)")
+    lib = _native.load()
+    as_int = lambda v: int(v.item()) if isinstance(v, torch.Tensor) else (None if v is None else int(v))
+    qweight = payload["qweight"].to(dev, torch.int32).contiguous()
+    qzeros = payload["qzeros"].to(dev, torch.int32).contiguous()
+    scales = payload["scales"].to(dev, torch.float16).contiguous()
+    g_idx = payload["g_idx"].to(dev, torch.int32).contiguous()
+    rows, cols = as_int(payload.get("rows")), as_int(payload.get("cols"))
+    rows = int(scales.shape[1]) if rows is None else rows
+    cols = int(g_idx.numel()) if cols is None else cols
+    groups = int(scales.shape[0])
+    if qweight.shape != ((cols + 7) // 8, rows) or qzeros.shape != (groups, (rows + 7) // 8) or g_idx.numel() != cols:
+        raise RuntimeError(f"trismoe_b200: inconsistent 4-bit matrix payload: qweight {tuple(qweight.shape)}, qzeros "
+                           f"{tuple(qzeros.shape)}, scales {tuple(scales.shape)}, g_idx {g_idx.numel()}, rows {rows}, cols {cols}")
+    out = torch.empty((rows, cols), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        _native.check(lib.tris_packed4_dequantize(qweight.data_ptr(), qzeros.data_ptr(), scales.data_ptr(), g_idx.data_ptr(),
+                                                  rows, cols, groups, out.data_ptr(),
+                                                  torch.cuda.current_stream(dev).cuda_stream), "packed4_dequantize")
+    return out
+
+
 class ExpertSharedMatrix(torch.nn.Module):
     """Holder of one shared input-side backbone ``shared_sv [r, in]`` fp16
-    (``ExpertSharedMatrix``, qlinear_cuda.py:2787-2968; the 4-bit packed form is not covered)."""
+    (``ExpertSharedMatrix``, qlinear_cuda.py:2787-2968).  ``set_shared_sv`` takes the fp16 matrix
+    or, as real checkpoints store it, the 4-bit packed payload dict (``qweight``, ``qzeros``,
+    ``scales``, ``g_idx``, ``rows``, ``cols``; qlinear_cuda.py:2937-2945), which is expanded to
+    fp16 once on the GPU (the fp16 copy is what every forward uses)."""
 
     def __init__(self, weight_dtype=torch.float16):
         super().__init__()
         self.register_buffer("shared_sv", torch.zeros((0, 0), dtype=weight_dtype))
+        self.shared_sv_quant = None  # the packed payload, when the matrix was given in 4 bits
 
-    def set_shared_sv(self, payload):
+    def set_shared_sv(self, payload, device=None):
+        if isinstance(payload, dict) and "qweight" in payload:
+            dev = torch.device(device) if device is not None else payload["qweight"].device
+            self.shared_sv_quant = {k: v for k, v in payload.items()}
+            self.shared_sv = dequantize_packed_4bit(payload, dev)
+            return self
         tensor = payload if isinstance(payload, torch.Tensor) else payload["shared_sv"]
+        self.shared_sv_quant = None
         self.shared_sv = tensor.to(dtype=torch.float16).contiguous()
         return self
 

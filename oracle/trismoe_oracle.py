@@ -250,3 +250,22 @@ def canonical_half_bits(a: np.ndarray) -> np.ndarray:
     """uint16 bit patterns with -0 folded onto +0 (the reference's accumulation into a zero
     matrix never yields -0, a product that underflows with a minus sign does)."""
     return (np.asarray(a, dtype=np.float16) + np.float16(0)).view(np.uint16)
+
+
+def dequantize_packed4(qweight: np.ndarray, qzeros: np.ndarray, scales: np.ndarray, g_idx: np.ndarray,
+                       rows: int, cols: int) -> np.ndarray:
+    """fp16 matrix [rows, cols] of a 4-bit packed backbone, as PackedQuantMatrix4bit.dequantize
+    computes it in fp16 (qlinear_cuda.py:2756-2784): qweight [ceil(cols/8), rows] int32 holds the
+    nibbles of input columns 8i..8i+7 of output row r (nibble j at bits 4j); qzeros
+    [groups, ceil(rows/8)] int32 holds zero points minus one, packed the same way along rows;
+    scales [groups, rows] fp16; g_idx [cols] the group of every input column.
+    weight[r, c] = fp16((q - zero) * scale), q - zero exact, one rounding in the product."""
+    shifts = (np.arange(8, dtype=np.int64) * 4).reshape(1, 1, 8)
+    qz = qzeros.astype(np.int64) & 0xFFFFFFFF
+    zeros = ((qz[:, :, None] >> shifts) & 0xF).reshape(qz.shape[0], -1)[:, :rows] + 1          # [groups, rows]
+    qw = qweight.astype(np.int64) & 0xFFFFFFFF
+    intweight = ((qw[:, :, None] >> shifts) & 0xF).transpose(0, 2, 1).reshape(-1, qw.shape[1])[:cols]  # [cols, rows]
+    g = g_idx.astype(np.int64)
+    diff = (intweight - zeros[g]).astype(np.float16)                                           # exact: |q - z| <= 16
+    weight = (diff.astype(np.float32) * scales.astype(np.float16)[g].astype(np.float32)).astype(np.float16)
+    return np.ascontiguousarray(weight.T)

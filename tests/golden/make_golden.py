@@ -8,7 +8,8 @@ Reference code exercised (paths inside the TriS-MoE tree):
   utils/pack_utils.py: build_compact3_packed_payload                      (payload tensors)
   qlinear_cuda.py: QuantLinear.pack_expert, _restore_dense_bool_matrix_from_sparse,
                    _pack_block_gr_gmap_tensor, _dequantize_compact3_matrix,
-                   ExpertSharedMatrix.set_shared_sv, build_grouped_route (torch branch)
+                   ExpertSharedMatrix.set_shared_sv, build_grouped_route (torch branch),
+                   PackedQuantMatrix4bit.set_quantized / dequantize                 (4-bit backbone)
   modeling_olmoe.py: OlmoeSparseMoeBlock.forward -> _forward_expert_loop  (fp16 CPU layer output)
 The `import auto_gptq` package init needs `accelerate`, which is absent, so the needed
 sub-packages are registered as empty namespace modules first.
@@ -200,6 +201,28 @@ def case_layer(QL, MO, PU):
     save("moe_layer_small.npz", out)
 
 
+def case_backbone4(QL):
+    """4-bit packed backbones through PackedQuantMatrix4bit.dequantize (fp16, CPU)."""
+    rng = np.random.default_rng(44)
+    out = {}
+    for tag, rows, cols, group in (("pc", 80, 200, 0), ("g64", 64, 256, 64), ("perm", 40, 96, 32)):
+        groups = 1 if group == 0 else math.ceil(cols / group)
+        qweight = rng.integers(-2**31, 2**31, size=(math.ceil(cols / 8), rows), dtype=np.int64).astype(np.int32)
+        qzeros = rng.integers(-2**31, 2**31, size=(groups, math.ceil(rows / 8)), dtype=np.int64).astype(np.int32)
+        scales = np.abs(rng.normal(0, 0.01, size=(groups, rows))).astype(np.float16)
+        g_idx = np.zeros(cols, np.int32) if group == 0 else (np.arange(cols) // group).astype(np.int32)
+        if tag == "perm":
+            g_idx = rng.permutation(g_idx)   # act-order style: groups not contiguous in the column order
+        m = QL.PackedQuantMatrix4bit(weight_dtype=torch.float16)
+        m.set_quantized(torch.from_numpy(qweight), torch.from_numpy(qzeros), torch.from_numpy(scales),
+                        torch.from_numpy(g_idx), rows, cols)
+        w = m.dequantize(torch.device("cpu"), torch.float16)
+        assert tuple(w.shape) == (rows, cols)
+        out.update({f"{tag}_qweight": qweight, f"{tag}_qzeros": qzeros, f"{tag}_scales": scales, f"{tag}_g_idx": g_idx,
+                    f"{tag}_dims": np.array([rows, cols, groups], np.int64), f"{tag}_weight_f16": w.numpy()})
+    save("backbone4.npz", out)
+
+
 def main():
     torch.manual_seed(0)
     QL, MO, PU = load_reference()
@@ -209,6 +232,7 @@ def main():
                     unit_cols=True)
     case_gr_sweep(QL)
     case_layer(QL, MO, PU)
+    case_backbone4(QL)
 
 
 if __name__ == "__main__":

@@ -609,3 +609,30 @@ def test_peer_wait_times_out_and_reports(tm):
     assert time.perf_counter() - t0 < 1.0
     assert int(status.item()) == 0 and int(step.item()) == 2
     assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0
+
+
+# ---------------------------------------------------------------------------------------
+# (11) 4-bit packed backbone
+# ---------------------------------------------------------------------------------------
+def test_packed4_backbone_bit_exact_and_used_by_the_backbone_gemm(tm):
+    """tris_packed4_dequantize against the reference's PackedQuantMatrix4bit.dequantize outputs
+    (bit-exact), and ExpertSharedMatrix fed with the packed payload gives the backbone GEMM the
+    same matrix as the fp16 path."""
+    z = load_golden("backbone4.npz")
+    for tag in ("pc", "g64", "perm"):
+        rows, cols, _ = (int(v) for v in z[f"{tag}_dims"])
+        payload = {"qweight": torch.from_numpy(z[f"{tag}_qweight"].copy()), "qzeros": torch.from_numpy(z[f"{tag}_qzeros"].copy()),
+                   "scales": torch.from_numpy(z[f"{tag}_scales"].copy()), "g_idx": torch.from_numpy(z[f"{tag}_g_idx"].copy()),
+                   "rows": torch.tensor(rows), "cols": torch.tensor(cols)}
+        w = tm.dequantize_packed_4bit(payload, "cuda")
+        _assert_half_bits_equal(w.cpu().numpy(), z[f"{tag}_weight_f16"])
+        holder = tm.ExpertSharedMatrix().set_shared_sv(payload, device="cuda")
+        assert holder.shared_sv_quant is not None and torch.equal(holder.shared_sv, w)
+        x = torch.randn((5, cols), device="cuda").half()
+        got = holder.compute_shared_hidden(x).float().cpu().numpy()
+        ref = x.float().cpu().numpy() @ z[f"{tag}_weight_f16"].astype(np.float32).T
+        assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
+    with pytest.raises(RuntimeError, match="inconsistent"):
+        bad = dict(payload)
+        bad["qzeros"] = payload["qzeros"][:, :-1]
+        tm.dequantize_packed_4bit(bad, "cuda")

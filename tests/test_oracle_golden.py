@@ -150,3 +150,14 @@ def test_synth_payload_round_trip(lib):
             assert np.array_equal(orc.unpack_rows(dense, 80), orc.restore_sparse(npp["q_gmap_sparse"][e], ~sal, O))
         w = orc.dequantize_expert(npp, 0)
         assert np.isfinite(w.astype(np.float32)).all() and np.abs(w.astype(np.float32)).mean() > 1e-3
+
+
+def test_packed4_backbone_matches_reference_dequantize():
+    """4-bit packed backbone: the oracle against PackedQuantMatrix4bit.dequantize outputs
+    (per-channel single group, 64-column groups, permuted group index)."""
+    z = load_golden("backbone4.npz")
+    for tag in ("pc", "g64", "perm"):
+        rows, cols, _ = (int(v) for v in z[f"{tag}_dims"])
+        w = orc.dequantize_packed4(z[f"{tag}_qweight"], z[f"{tag}_qzeros"], z[f"{tag}_scales"], z[f"{tag}_g_idx"], rows, cols)
+        assert w.shape == (rows, cols)
+        assert np.array_equal(w.view(np.uint16), z[f"{tag}_weight_f16"].view(np.uint16)), tag
