@@ -59,8 +59,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}")
-    with open(os.path.join(CSRC, "build.log"), "w") as fh:
-        fh.write("\n".join(log))
+    with open(os.path.join(CSRC, "build.log"), "w") as fh:  # registers / spills / shared memory per kernel
+        fh.write("\n".join(line for line in "\n".join(log).split("\n") if "Compile time" not in line))
     if verbose:
         print("\n".join(log))
     return LIB
