@@ -324,6 +324,15 @@ int tris_combine_routed(const void* down_out_f16, const int32_t* row_of_flat,
                         const float* routing_weights, int32_t num_tokens, int32_t top_k,
                         int32_t hidden_size, void* final_f16, void* stream);
 
+/*
+ * Rows per expert segment (the launch's upper estimate) above which the grouped entry points use
+ * their tcgen05/TMEM kernel instead of the register kernel; returns the previous value.  The
+ * default (2048) lies above the range in which the register kernel measured faster on B200; the
+ * tests lower it to exercise the tensor-core kernel.  Process-wide; no reference counterpart
+ * (the reference decides per call in run_grouped_structured_expert_forward, QL:2187-2229).
+ */
+int tris_set_grouped_tc_min_rows(int32_t rows);
+
 /* ---- streaming ----------------------------------------------------------------------- */
 
 /* One tensor to page: expert e's block of `bytes_per_expert` bytes (a multiple of 16) is

@@ -15,6 +15,7 @@
 // eight consecutive K positions, i.e. one 16-byte core-matrix row, so the unpack writes its
 // fragments with two 128-bit stores per packed row.  Needs rank % 32 == 0 and rank <= 256.
 #include <algorithm>
+#include <atomic>
 
 #include "compact3_tile.cuh"
 #include "umma.cuh"
@@ -224,12 +225,19 @@ static int launch_umma_grouped(const GroupedArgs& args, cudaStream_t stream, boo
   return check_cuda(launch_kernel(kernel, grid, dim3(kThreads), smem, stream, pdl, 1, args), "grouped_umma_kernel launch");
 }
 
+// Rows per segment above which the launchers pick this kernel.  Measured on B200 (OLMoE- and
+// Mixtral-shaped layers, 256 to 4096 prefill tokens, up to ~1000 rows per expert): the register
+// path (eight 8-row tiles per pass, two CTAs per SM, weights re-unpacked every pass) is faster
+// throughout - 220 vs 298 us per layer at 512 tokens, 616 vs 661 at 2048 (OLMoE), 1872 vs 1935 at
+// 4096 (Mixtral) - because this kernel holds a whole SM (192 KB of shared memory) while its
+// decode-and-unpack phase runs on eight warps.  So the default sits above the measured range.
+static std::atomic<int> g_tc_min_rows{2048};
+
 // Dense-contraction path: activations must be pair-interleaved, rank a multiple of 32 and at
 // most one 256-column chunk.
 bool grouped_umma_applicable(const GroupedArgs& args, int rows_hint) {
   const TrisProjView& v = args.proj[0];
-  // up to 64 rows per segment the register path (one pass of eight 8-row tiles) measured faster
-  return rows_hint > 64 && args.hidden_interleaved && (v.rank % 32) == 0 && v.rank <= 256 && args.ksplit <= 1 &&
+  return rows_hint > g_tc_min_rows.load(std::memory_order_relaxed) && args.hidden_interleaved && (v.rank % 32) == 0 && v.rank <= 256 && args.ksplit <= 1 &&
          (args.hidden_stride % 8) == 0;
 }
 
@@ -240,3 +248,7 @@ int launch_grouped_umma(const GroupedArgs& args, int nproj, int epi, cudaStream_
 }
 
 }  // namespace tris
+
+extern "C" int tris_set_grouped_tc_min_rows(int32_t rows) {
+  return tris::g_tc_min_rows.exchange(rows < 0 ? 0 : rows, std::memory_order_relaxed);
+}

@@ -57,6 +57,7 @@ def _worker(rank, world, port, out):
         # on the received rows (strided activations in, scattered rows out)
         T = 200
         blk.set_capacity(T)
+        previous_tc_rows = tm._native.load().tris_set_grouped_tc_min_rows(64)
         x = synth.synth_activations(T, shape.hidden_size, seed=50 + rank).to(dev)
         logits = synth.synth_router_logits(T, shape.num_experts, seed=55 + rank).to(dev)
         want, _ = full(x.view(1, T, -1), router_logits=logits)
@@ -76,6 +77,7 @@ def _worker(rank, world, port, out):
         ok = ok and not blk._peer.timed_out()
         dist.barrier()
         blk._peer = None  # back to the all-to-all path for the rest of the test
+        tm._native.load().tris_set_grouped_tc_min_rows(previous_tc_rows)
         # a slot count below the worst case: 9 tokens * top-2 = 18 rows, 14 slots per peer here
         # (mean 9 + 6 sigma = 21.7 is capped by the worst case, so the test picks its own value);
         # whatever is dropped must be reported, and nothing else may change

@@ -530,8 +530,18 @@ def test_streaming_forward_matches_resident(tm, mode, fmt):
 # ---------------------------------------------------------------------------------------
 # (9) prefill-sized segments: tcgen05 / TMEM grouped kernel
 # ---------------------------------------------------------------------------------------
+@pytest.fixture
+def tensor_core_from_64_rows(tm):
+    """The launchers pick the tcgen05 kernel above a row count whose default lies beyond these
+    tests' sizes; lower it so that the tensor-core kernel is what runs, and put it back."""
+    lib = tm._native.load()
+    previous = lib.tris_set_grouped_tc_min_rows(64)
+    yield
+    lib.tris_set_grouped_tc_min_rows(previous)
+
+
 @pytest.mark.parametrize("rank,T", [(96, 200), (256, 150), (64, 700)])
-def test_layer_prefill_rows_take_the_tensor_core_path(tm, rank, T):
+def test_layer_prefill_rows_take_the_tensor_core_path(tm, tensor_core_from_64_rows, rank, T):
     """Few experts, many tokens: ~100+ rows per expert, rank a multiple of 32 -> the grouped
     kernels run their tcgen05 variant (weights unpacked once per tile into shared memory)."""
     from trismoe_b200 import synth
@@ -559,7 +569,8 @@ def test_layer_prefill_rows_take_the_tensor_core_path(tm, rank, T):
     assert max_abs <= MAX_ABS and mean_rel <= 2 * MEAN_REL, (max_abs, mean_rel)
 
 
-def test_layer_olmoe_shape_prefill_512(tm, olmoe_layer):
+@pytest.mark.parametrize("kernel", ["register", "tensor_core"])
+def test_layer_olmoe_shape_prefill_512(tm, olmoe_layer, kernel):
     """Headline shape, 512-token prefill (64 rows per expert on average)."""
     from trismoe_b200 import synth
 
@@ -567,7 +578,13 @@ def test_layer_olmoe_shape_prefill_512(tm, olmoe_layer):
     T = 512
     x = synth.synth_activations(T, 2048, seed=3).cuda()
     logits = synth.synth_router_logits(T, 64, seed=4).cuda()
-    y, _ = blk(x.view(1, T, -1), router_logits=logits)
+    lib = tm._native.load()
+    previous = lib.tris_set_grouped_tc_min_rows(64 if kernel == "tensor_core" else 1 << 20)
+    try:
+        y, _ = blk(x.view(1, T, -1), router_logits=logits)
+        torch.cuda.synchronize()
+    finally:
+        lib.tris_set_grouped_tc_min_rows(previous)
     y2, _ = blk.forward_grouped_ops(x.view(1, T, -1), router_logits=logits)
     ref = y2.view(T, -1).float().cpu().numpy()
     max_abs, mean_rel = orc.error_metrics(y.view(T, -1).float().cpu().numpy(), ref)
