@@ -447,7 +447,13 @@ def main():
     ap.add_argument("--extra", action="store_true", help="run the secondary workloads (prefill, Mixtral shape, streaming)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers for --ncu-case")
     ap.add_argument("--tokens", type=int, default=HEADLINE_TOKENS, help="decode batch for --ncu-case")
+    ap.add_argument("--tc-min-rows", type=int, default=None,
+                    help="rows per expert segment above which the tcgen05 grouped kernel is used (library default 2048)")
     args = ap.parse_args()
+    if args.tc_min_rows is not None and args.impl == "ours":
+        import trismoe_b200 as tm
+
+        tm._native.load().tris_set_grouped_tc_min_rows(int(args.tc_min_rows))
     args.warmup = max(args.warmup, 3)
     if args.ncu_case:
         return run_ncu_case(args)
