@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory by running the TriS-MoE reference's own
-Python code on CPU.  Needs the reference tree (default /root/reference, override with
-TRIS_REFERENCE_ROOT); the fixtures it writes are committed so that the tests never need it.
+Python code on CPU.  Needs a checkout of the reference tree (TRIS_REFERENCE_ROOT points at
+it); the fixtures it writes are committed so that the tests never need it.
 
-    python tests/golden/make_golden.py
+    TRIS_REFERENCE_ROOT=<path to the TriS-MoE tree> python tests/golden/make_golden.py
 
 Reference code exercised (paths inside the TriS-MoE tree):
   utils/pack_utils.py: build_compact3_packed_payload                      (payload tensors)
@@ -23,10 +23,12 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("TRIS_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("TRIS_REFERENCE_ROOT", "")
 
 
 def load_reference():
+    if not REF or not os.path.isdir(REF):
+        raise SystemExit("set TRIS_REFERENCE_ROOT to a checkout of the TriS-MoE reference tree")
     sys.path.insert(0, REF)
     base = os.path.join(REF, "AutoGPTQ", "auto_gptq")
     for name, sub in [("auto_gptq", ""), ("auto_gptq.nn_modules", "nn_modules"),
