@@ -85,19 +85,61 @@ __global__ void __launch_bounds__(kTcThreads) umma_gemm_kernel(const __grid_cons
   const int n_live = args.n_dev ? min(args.n, *args.n_dev) : args.n;
   const uint32_t idesc = umma_idesc_f16(kTcM, NTILE);
 
+  // Every thread copies the same (row, 16-byte column) pieces of every K chunk: work out their
+  // source rows and shared-memory offsets once, so that a chunk costs one add and one cp.async
+  // per piece (address arithmetic per piece per chunk used to dominate this kernel).
+  constexpr int kAPieces = kTcM * 8 / kTcThreads, kBPieces = NTILE * 8 / kTcThreads;
+  static_assert(kTcM * 8 % kTcThreads == 0 && NTILE * 8 % kTcThreads == 0, "pieces per thread");
+  const __half* a_src[kAPieces];
+  const __half* b_src[kBPieces];
+  uint32_t a_off[kAPieces], b_off[kBPieces];
+  uint32_t a_live = 0u, b_live = 0u;
+  auto piece = [](int idx, int rows, int& row, int& c) {
+    // a warp covers 8 rows x 4 chunks: 64 contiguous source bytes per row, and every 8
+    // consecutive lanes write 128 contiguous shared-memory bytes
+    const int r_lo = idx & 7, c_lo = (idx >> 3) & 3, rest = idx >> 5;
+    c = ((rest & 1) << 2) | c_lo;
+    row = ((rest >> 1) << 3) | r_lo;
+    (void)rows;
+  };
+#pragma unroll
+  for (int it = 0; it < kAPieces; ++it) {
+    int row, c;
+    piece(threadIdx.x + it * kTcThreads, kTcM, row, c);
+    const int m = m0 + row;
+    a_off[it] = static_cast<uint32_t>((c * kTcM + row) * 16);
+    a_src[it] = pb.a;
+    if (m < pb.m) {
+      a_src[it] = pb.a + static_cast<size_t>(m) * K + kbeg + 8 * c;
+      a_live |= 1u << it;
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < kBPieces; ++it) {
+    int row, c;
+    piece(threadIdx.x + it * kTcThreads, NTILE, row, c);
+    const int n = n0 + row;
+    b_off[it] = static_cast<uint32_t>((c * NTILE + row) * 16);
+    b_src[it] = args.x;
+    if (n < n_live) {
+      const int src = args.row_gather ? args.row_gather[n] : n;
+      b_src[it] = args.x + static_cast<size_t>(src) * K + kbeg + 8 * c;
+      b_live |= 1u << it;
+    }
+  }
   auto issue_chunk = [&](int i) {
     const int s = i % kTcStages;
-    const int k0 = kbeg + i * kTcKChunk;
-    stage_operand_async<kTcM>(sm.a[s], pb.a, [&](int r) -> const __half* {
-      const int m = m0 + r;
-      return (m < pb.m) ? pb.a + static_cast<size_t>(m) * K + k0 : nullptr;
-    });
-    stage_operand_async<NTILE>(sm.b[s], args.x, [&](int r) -> const __half* {
-      const int n = n0 + r;
-      if (n >= n_live) return nullptr;
-      const int src = args.row_gather ? args.row_gather[n] : n;
-      return args.x + static_cast<size_t>(src) * K + k0;
-    });
+    const int koff = i * kTcKChunk;  // halves from the start of this CTA's K range
+#pragma unroll
+    for (int it = 0; it < kAPieces; ++it) {
+      const bool live = (a_live >> it) & 1u;
+      cp_async_16(sm.a[s] + a_off[it], live ? a_src[it] + koff : a_src[it], live);
+    }
+#pragma unroll
+    for (int it = 0; it < kBPieces; ++it) {
+      const bool live = (b_live >> it) & 1u;
+      cp_async_16(sm.b[s] + b_off[it], live ? b_src[it] + koff : b_src[it], live);
+    }
   };
 
   // Software pipeline over the K chunks: copies run kTcStages-1 chunks ahead of the MMAs.
