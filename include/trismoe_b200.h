@@ -293,6 +293,18 @@ int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_gather, int
                                const void* shared_sv_f16, int32_t rank, void* out, int32_t out_mode,
                                void* stream);
 
+/*
+ * The three products that share the block's input rows, in one launch: hidden_gate =
+ * x * shared_gate^T, hidden_up = x * shared_up^T (each [num_rows, rank] fp16, TRIS_OUT_F16 or
+ * TRIS_OUT_F16_PAIR_INTERLEAVED) and, when router_weight_f16 is given, router_logits =
+ * x * router_weight^T as fp32 [num_rows, num_experts] (the router nn.Linear of MO:1052 and the
+ * two compute_shared_hidden calls of MO:944-953, which the reference runs as three GEMMs).
+ */
+int tris_input_projections(const void* x_f16, int32_t num_rows, int32_t in_features, const void* shared_gate_f16,
+                           const void* shared_up_f16, int32_t rank, const void* router_weight_f16,
+                           int32_t num_experts, void* hidden_gate, void* hidden_up, int32_t hidden_out_mode,
+                           float* router_logits_f32, void* stream);
+
 /* ---- grouped expert kernels -------------------------------------------------------- */
 
 /*

@@ -81,6 +81,7 @@ SIGNATURES = {
     "tris_ep_return_peer": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "tris_ep_wait": (C.c_int, [_vp, _vp, _i32, _vp, _vp]),
     "tris_router_topk": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "tris_input_projections": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i32, _vp, _vp]),
     "tris_packed4_dequantize": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "tris_shared_hidden_forward": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _vp]),
     "tris_grouped_forward": (C.c_int, [_P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp]),

@@ -188,3 +188,29 @@ extern "C" int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_
   return launch_shared_hidden(&pb, 1, static_cast<const __half*>(x_f16), row_gather, num_rows, in_features,
                               static_cast<cudaStream_t>(stream), false, num_rows_dev);
 }
+
+// Both input-side backbones and the router logits in one pass over x (what the layer entry
+// point does internally): three matrices that share the activation rows.
+extern "C" int tris_input_projections(const void* x_f16, int32_t num_rows, int32_t in_features,
+                                      const void* shared_gate_f16, const void* shared_up_f16, int32_t rank,
+                                      const void* router_weight_f16, int32_t num_experts, void* hidden_gate,
+                                      void* hidden_up, int32_t hidden_out_mode, float* router_logits_f32,
+                                      void* stream) {
+  TRIS_REQUIRE(x_f16 && shared_gate_f16 && shared_up_f16 && hidden_gate && hidden_up, TRIS_ERR_INVALID_ARG,
+               "tris_input_projections: null pointer");
+  TRIS_REQUIRE(rank > 0 && num_rows >= 0 && in_features > 0, TRIS_ERR_INVALID_ARG,
+               "tris_input_projections: bad sizes rows=%d in=%d rank=%d", num_rows, in_features, rank);
+  TRIS_REQUIRE((router_weight_f16 == nullptr) == (router_logits_f32 == nullptr) && (!router_weight_f16 || num_experts > 0),
+               TRIS_ERR_INVALID_ARG, "tris_input_projections: router weight and logits go together");
+  TRIS_REQUIRE(hidden_out_mode == TRIS_OUT_F16 || (hidden_out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED && rank % 32 == 0),
+               TRIS_ERR_INVALID_ARG, "tris_input_projections: out_mode %d (pair-interleaved needs rank %% 32 == 0)",
+               hidden_out_mode);
+  if (num_rows == 0) return TRIS_OK;
+  SkinnyProblem probs[3] = {
+      {static_cast<const __half*>(shared_gate_f16), hidden_gate, rank, hidden_out_mode},
+      {static_cast<const __half*>(shared_up_f16), hidden_up, rank, hidden_out_mode},
+      {static_cast<const __half*>(router_weight_f16), router_logits_f32, num_experts, TRIS_OUT_F32},
+  };
+  return launch_shared_hidden(probs, router_weight_f16 ? 3 : 2, static_cast<const __half*>(x_f16), nullptr, num_rows,
+                              in_features, static_cast<cudaStream_t>(stream), false, nullptr);
+}

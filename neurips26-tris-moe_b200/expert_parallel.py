@@ -334,8 +334,21 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         T, dev = int(x.shape[0]), x.device
         stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
-            if router_logits is None:
-                router_logits = self._backbone_f32(x)
+            r_gu = int(self.shared["gate"].shape[0])
+            inter = r_gu % 32 == 0
+            hg = torch.empty((T, r_gu), dtype=torch.float16, device=dev)
+            hu = torch.empty((T, r_gu), dtype=torch.float16, device=dev)
+            own_logits = router_logits is None
+            if own_logits:
+                if self.router_weight is None:
+                    raise RuntimeError("trismoe_b200: no router weight was loaded and no router_logits were given")
+                router_logits = torch.empty((T, self.num_experts), dtype=torch.float32, device=dev)
+            # both backbones (and the router, unless the caller brought logits) in one pass over x
+            if T:
+                _native.check(lib.tris_input_projections(
+                    x.data_ptr(), T, int(x.shape[1]), self.shared["gate"].data_ptr(), self.shared["up"].data_ptr(), r_gu,
+                    self.router_weight.data_ptr() if own_logits else None, self.num_experts, hg.data_ptr(), hu.data_ptr(),
+                    2 if inter else 0, router_logits.data_ptr() if own_logits else None, stream), "input_projections")
             logits = router_logits.reshape(T, self.num_experts).to(torch.float32).contiguous()
             sel = torch.empty((T, self.top_k), dtype=torch.int32, device=dev)
             wts = torch.empty((T, self.top_k), dtype=torch.float32, device=dev)
@@ -343,10 +356,6 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                 _native.check(lib.tris_router_topk(logits.data_ptr(), T, self.num_experts, self.top_k,
                                                    int(self.norm_topk_prob), sel.data_ptr(), wts.data_ptr(), stream), "router_topk")
             route = self._route(sel, self.num_experts)
-            r_gu = int(self.shared["gate"].shape[0])
-            inter = r_gu % 32 == 0
-            hg = self._backbone(x, self.shared["gate"], inter)
-            hu = self._backbone(x, self.shared["up"], inter)
             y = torch.empty_like(x)
             if exact_splits:
                 tok = route["tok"].to(torch.long)
@@ -439,21 +448,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         (cannot happen with the default capacity of tokens * top_k); reads one device word."""
         return self._overflow is not None and bool(self._overflow.item())
 
-    def _backbone_f32(self, x: torch.Tensor) -> torch.Tensor:
-        if self.router_weight is None:
-            raise RuntimeError("trismoe_b200: no router weight loaded and no router_logits given")
-        lib = _native.load()
-        out = torch.empty((x.shape[0], self.num_experts), dtype=torch.float32, device=x.device)
-        if x.shape[0]:
-            _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, int(x.shape[0]), None, int(x.shape[1]),
-                                                         self.router_weight.data_ptr(), self.num_experts, out.data_ptr(), 1,
-                                                         torch.cuda.current_stream(x.device).cuda_stream), "router")
-        return out
 
-
-# ---------------------------------------------------------------------------------------
-# benchmark leg for N > 1 (called by bench.py under torchrun)
-# ---------------------------------------------------------------------------------------
 def run_bench(args, rank: int, world: int, device) -> None:
     """Weak scaling: every rank decodes its own batch of 128 tokens through 16 layers whose
     experts are sharded over the ranks.  Timed on the device (CUDA events), max over ranks."""

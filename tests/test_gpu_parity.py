@@ -653,3 +653,36 @@ def test_packed4_backbone_bit_exact_and_used_by_the_backbone_gemm(tm):
         bad = dict(payload)
         bad["qzeros"] = payload["qzeros"][:, :-1]
         tm.dequantize_packed_4bit(bad, "cuda")
+
+
+def test_input_projections_match_the_single_products(tm):
+    """tris_input_projections (both backbones and the router logits in one launch) against
+    three tris_shared_hidden_forward calls, decode-sized (mma.sync) and prefill-sized (tcgen05 +
+    TMA) batches."""
+    lib = tm._native.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    H, r, E = 512, 96, 24
+    g = torch.Generator().manual_seed(3)
+    sg, su = (torch.randn((r, H), generator=g) * 0.05).half().cuda(), (torch.randn((r, H), generator=g) * 0.05).half().cuda()
+    rw = (torch.randn((E, H), generator=g) * 0.05).half().cuda()
+    for T in (3, 200):
+        x = torch.randn((T, H), generator=g).half().cuda()
+        hg, hu = torch.empty((T, r), dtype=torch.float16, device="cuda"), torch.empty((T, r), dtype=torch.float16, device="cuda")
+        lg = torch.empty((T, E), dtype=torch.float32, device="cuda")
+        tm._native.check(lib.tris_input_projections(x.data_ptr(), T, H, sg.data_ptr(), su.data_ptr(), r, rw.data_ptr(), E,
+                                                    hg.data_ptr(), hu.data_ptr(), 2, lg.data_ptr(), stream), "input_projections")
+        want = []
+        for w, m, mode, dt in ((sg, r, 2, torch.float16), (su, r, 2, torch.float16), (rw, E, 1, torch.float32)):
+            o = torch.empty((T, m), dtype=dt, device="cuda")
+            tm._native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, T, None, H, w.data_ptr(), m, o.data_ptr(), mode,
+                                                            stream), "shared_hidden")
+            want.append(o)
+        torch.cuda.synchronize()
+        assert torch.equal(hg, want[0]) and torch.equal(hu, want[1]) and torch.equal(lg, want[2]), T
+        ref = x.float() @ rw.float().T
+        assert float((lg - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
+    # without a router: two products, the logits pointer must be absent too
+    tm._native.check(lib.tris_input_projections(x.data_ptr(), T, H, sg.data_ptr(), su.data_ptr(), r, None, 0,
+                                                hg.data_ptr(), hu.data_ptr(), 0, None, stream), "input_projections")
+    assert lib.tris_input_projections(x.data_ptr(), T, H, sg.data_ptr(), su.data_ptr(), r, rw.data_ptr(), E,
+                                      hg.data_ptr(), hu.data_ptr(), 0, None, stream) == 1
