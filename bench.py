@@ -166,6 +166,16 @@ def run_ours(args):
         del graph
     T = HEADLINE_TOKENS
     head = results[T]
+    # the same batch through ONE layer 16 times: its ~22 MB payload stays in the 126 MB L2
+    x = synth.synth_activations(T, 2048, seed=T).to(device)
+
+    def warm_step():
+        for _ in range(LAYERS):
+            blocks[0](x.view(1, T, 2048))
+
+    graph = capture(warm_step)
+    l2_resident_us = time_replays(graph, max(10, args.steps // 2), args.warmup) * 1e3 / LAYERS
+    del graph
 
     # ---- dominant kernel alone: grouped gate/up (SiLU*mul epilogue) and grouped down ----------
     x = synth.synth_activations(T, 2048, seed=T).to(device)
@@ -255,6 +265,8 @@ def run_ours(args):
         "gpu_launches": args.steps * LAYERS * LAUNCHES_PER_LAYER,
         "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
         "sweep": {str(t): {k: round(v, 3) for k, v in r.items()} for t, r in results.items()},
+        "l2_resident": {"tokens": T, "us_per_layer": round(l2_resident_us, 3),
+                        "note": "one layer replayed 16 times (payload stays in L2); the headline uses 16 distinct layers"},
     }
     print(json.dumps(out))
 
