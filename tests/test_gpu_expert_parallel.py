@@ -66,6 +66,13 @@ def _worker(rank, world, port, out):
         err = (got.float() - want.float()).abs()
         ok = ok and float(err.max()) <= 2e-3 * max(1.0, float(want.float().abs().max()))
         ok = ok and not blk.exchange_overflowed()
+        # ... and with the register kernels on the same rows (several 64-row passes per expert)
+        tm._native.load().tris_set_grouped_tc_min_rows(1 << 20)
+        got_reg, _ = blk(x.view(1, T, -1), router_logits=logits)
+        torch.cuda.synchronize()
+        tm._native.load().tris_set_grouped_tc_min_rows(64)
+        err = (got_reg.float() - want.float()).abs()
+        ok = ok and float(err.max()) <= 2e-3 * max(1.0, float(want.float().abs().max()))
         # the same exchange through peer memory (kernels write into the peers' buffers over NVLink,
         # counters instead of a collective): bit-equal results, several steps in a row
         got_nccl = got.clone()

@@ -295,6 +295,21 @@ def test_grouped_forward_from_segment_lengths_and_bad_args(tm, small_layer):
               "_out_row_scatter": scatter}
     out2 = tm.run_grouped_structured_expert_forward(p, torch.from_numpy(h).cuda(), None, troute)
     assert torch.equal(out2[scatter.long()], out)
+    # long segments (several passes of the 64-row variant) with scattered output rows
+    big = [150, 0, 0, 70, 0, 9]
+    Rb = sum(big)
+    hb = torch.from_numpy(rng.standard_normal((Rb, r)).astype(np.float16)).cuda()
+    plain = tm.run_grouped_structured_expert_forward(p, hb, None, big)
+    sc = torch.from_numpy(rng.permutation(Rb).astype(np.int32)).cuda()
+    broute = {"expert_ids": torch.tensor([0, 3, 5], dtype=torch.int32, device="cuda"),
+              "segment_offsets": torch.tensor([0, 150, 220, 229], dtype=torch.int32, device="cuda"),
+              "_max_rows_per_segment": 150, "_out_row_scatter": sc}
+    scattered = tm.run_grouped_structured_expert_forward(p, hb, None, broute)
+    assert torch.equal(scattered[sc.long()], plain)
+    refb = _grouped_reference(weights["down"], hb.cpu().numpy(), {"expert_ids": np.array([0, 3, 5]),
+                                                                  "segment_offsets": np.array([0, 150, 220, 229])})
+    max_abs, mean_rel = orc.error_metrics(plain.float().cpu().numpy(), refb)
+    assert max_abs <= MAX_ABS and mean_rel <= MEAN_REL
     # reference behaviour: wrong dtype / wrong rank -> None, not an exception
     assert tm.run_grouped_structured_expert_forward(p, torch.zeros((R, r), device="cuda"), None, lengths) is None
     assert tm.run_grouped_structured_expert_forward(p, torch.zeros((R, r + 8), dtype=torch.float16, device="cuda"), None, lengths) is None
