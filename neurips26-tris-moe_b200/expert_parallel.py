@@ -1,22 +1,29 @@
 """Expert-parallel MoE block: experts sharded over the GPUs of one node, tokens local to each
-rank, routed rows exchanged with NCCL all-to-all over NVLink.
+rank, routed rows exchanged over NVLink.
 
 The reference is single-GPU (``grouped_payload_sidecar.py:867-868`` enforces one device), so
 this module has no counterpart there; it composes the same operators as
 ``OlmoeSparseMoeBlock._forward_grouped`` (``modeling_olmoe.py:916-1044``) around two exchanges:
 
-    rank-local:  router -> route (rows sorted by expert, hence by owner rank)
-                 input-side backbones on the local tokens (replicated fp16 matrices)
-    dispatch:    all-to-all of [rows, 2*r] backbone outputs + one int32 expert id per row
+    rank-local:  both input-side backbones and the router in one launch, top-k, route (rows
+                 sorted by expert, hence by owner rank)
+    dispatch:    every routed row as [2*r backbone outputs | int32 expert id] to its owner
                  (2*r = 512 halves per row instead of the 2048-wide activation)
     owner rank:  route over the received rows, grouped gate/up + SiLU*mul, down backbone,
-                 grouped down
-    combine:     all-to-all of [rows, H] results back to the token's rank, weighted gather
+                 grouped down writing each result to the slot its row arrived in
+    combine:     [rows, H] results back to the token's rank, weighted gather
 
-Rank ``g`` of ``N`` owns experts ``[g*E/N, (g+1)*E/N)``.  Exact split sizes are exchanged first
-(one small all-to-all and a host read), so no row is dropped and no padding crosses NVLink.
-The communication plan is plain torch and runs on CPU tensors with the gloo backend, which is
-how it is tested without GPUs; the expert computation is a callable.
+Rank ``g`` of ``N`` owns experts ``[g*E/N, (g+1)*E/N)``.  Three ways to move the rows:
+
+* exact splits (:func:`expert_parallel_exchange`): counts exchanged first (a small all-to-all
+  and a host read), then ``all_to_all_single`` with exactly the routed rows.  Plain torch; runs
+  on CPU tensors with the gloo backend, which is how the plan is tested without GPUs.
+* fixed capacity over NCCL (:meth:`ExpertParallelMoeBlock._padded_exchange`): every rank sends
+  the same number of slots to every peer, nothing is read back to the host, the step can be
+  captured in a CUDA graph.
+* fixed capacity over peer memory (:meth:`ExpertParallelMoeBlock.use_peer_exchange`): same slot
+  layout, but the dispatch and return kernels store straight into the peers' buffers and bump
+  counters the receiver waits on; no collective call.
 """
 from __future__ import annotations
 
