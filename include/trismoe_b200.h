@@ -30,7 +30,7 @@ extern "C" {
 
 /* Mirrors TRIS_COMPACT3_KERNEL_ABI_VERSION (CPP:1138-1139); the payload layout is ABI 2. */
 #define TRIS_COMPACT3_KERNEL_ABI_VERSION 2
-#define TRIS_B200_ABI_VERSION 2
+#define TRIS_B200_ABI_VERSION 3
 
 enum {
   TRIS_OK = 0,
@@ -92,6 +92,18 @@ typedef struct TrisProjView {
      gmap_slot overrides it) is a staging buffer in which expert e occupies row block
      expert_slot[e]: the layout tris_page_experts fills from pinned host memory. */
   const int32_t* expert_slot;
+  /* Tile-major records built at load time by tris_tile_records_plan / _build (NULL when absent):
+     per (expert, 64 outputs, 256 columns) one contiguous piece holding everything a CTA needs
+     of that tile, so that it arrives with a single bulk copy, plus per (expert, 256 columns)
+     a record of finished column-scale tables.  When present, the grouped entry points and the
+     two dump entry points read the records instead of the tensors above. */
+  const void* tile_records;
+  const uint32_t* tile_desc;             /* [records + 1][2]: {offset / 16, bytes}                */
+  const void* col_records;               /* [E, chunks] x col_record_bytes                        */
+  int32_t col_record_bytes;
+  int32_t max_record_bytes;              /* largest tile record of this projection                */
+  int32_t max_sal_words;                 /* salient words per column record                       */
+  int32_t reserved0;
 } TrisProjView;
 
 /*
@@ -120,10 +132,16 @@ typedef struct TrisRouteView {
    of 32 columns, column j sits at position 2*(j%16) + j/16 (what tris_shared_hidden_forward
    writes with out_mode = TRIS_OUT_F16_PAIR_INTERLEAVED).  Needs rank % 32 == 0. */
 #define TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED 1
+/* Activation rows in "lane order", the order the tile-record kernels consume: inside every group
+   of 32 columns, column j sits at 8*(j%4) + 2*s + j/16 with s = 1, 3, 0, 2 for (j/4)%4 = 0..3
+   (what tris_shared_hidden_forward writes with out_mode = TRIS_OUT_F16_LANE_ORDER).  Needs
+   rank % 32 == 0 and a projection with tile records. */
+#define TRIS_ROUTE_HIDDEN_LANE_ORDER 2
 
 #define TRIS_OUT_F16 0
 #define TRIS_OUT_F32 1
 #define TRIS_OUT_F16_PAIR_INTERLEAVED 2
+#define TRIS_OUT_F16_LANE_ORDER 3
 
 /* ---- library / errors -------------------------------------------------------------- */
 
@@ -180,6 +198,25 @@ int tris_build_row_groups(const int32_t* g_idx, int32_t num_experts, int32_t ran
  * tile staging and register unpack code as the grouped kernels.
  */
 int tris_compact3_dequantize(const TrisProjView* proj, void* weights_out_f16, void* stream);
+
+/* ---- tile records ------------------------------------------------------------------ */
+
+/*
+ * Load-time repack of a block-GR projection into tile-major records (no reference counterpart:
+ * the reference kernels gather each tile from the E-stacked planes on every launch,
+ * CU:5382-5586).  Sequence: tris_tile_record_count -> allocate desc [count + 1][2] uint32 and a
+ * device int64[4] -> tris_tile_records_plan (fills desc; info = {total record bytes, largest
+ * record, salient words per column record, 0}) -> read info, allocate `total` bytes of records
+ * and tris_col_record_bytes(proj, salient words) of column records (both 16-byte aligned) ->
+ * tris_tile_records_build -> set the tile_* fields of the view.  The view passed in needs the
+ * sub-stream index (32 sub-streams) and packed_row_group.  The records repeat, re-arranged, what
+ * the E-stacked tensors hold; the byte total is DRAM traffic of the kernels, not algorithmic bytes.
+ */
+int64_t tris_tile_record_count(const TrisProjView* proj);
+int64_t tris_col_record_bytes(const TrisProjView* proj, int32_t max_sal_words);
+int tris_tile_records_plan(const TrisProjView* proj, uint32_t* desc_out, int64_t* info_out, void* stream);
+int tris_tile_records_build(const TrisProjView* proj, const uint32_t* desc, void* records_out,
+                            void* col_records_out, int32_t max_sal_words, void* stream);
 
 /* ---- route ------------------------------------------------------------------------- */
 
@@ -328,6 +365,18 @@ int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisProjView* pr
                               int32_t fuse_silu_mul, void* stream);
 
 /*
+ * The activation layout (TRIS_OUT_F16, TRIS_OUT_F16_PAIR_INTERLEAVED or TRIS_OUT_F16_LANE_ORDER) the
+ * grouped entry points read fastest for these projections (proj_b may be NULL) and a route of
+ * num_rows rows in num_segments segments of at most max_rows_per_segment rows: lane order for
+ * projections with tile records in the decode regime, pair-interleaved otherwise, row-major for
+ * ranks that are not a multiple of 32.  Ask the backbone GEMM for that out_mode and set the
+ * matching TRIS_ROUTE_HIDDEN_* flag.  No reference counterpart (the reference kernels read
+ * row-major activations only).
+ */
+int tris_grouped_hidden_layout(const TrisProjView* proj_a, const TrisProjView* proj_b, int32_t num_rows,
+                               int32_t num_segments, int32_t max_rows_per_segment);
+
+/*
  * final[T, H] fp16 = sum over slots of routing_weights[t, s] * down_out[row_of_flat[t*k+s]]
  * (the index_add_ of MO:1038-1043, as a deterministic gather in fp32).  A negative row index
  * contributes nothing.
@@ -362,7 +411,12 @@ typedef struct TrisPageJob {
  * job from pinned host memory into slot s of the job's staging buffer and records
  * slot_table[expert] = s.  The copy is a kernel that reads host memory directly, driven by
  * the device-side route, so the host never learns which experts are active and nothing
- * synchronises; run it on a side stream and order it with events.  slot_table is [E] int32.
+ * synchronises; run it on a side stream and order it with events.  slot_table is [E] int32; every
+ * entry is first reset to -1, so an expert beyond the num_segments slots (a batch that activates
+ * more experts than the caller sized its staging buffers for) is left "not paged": the grouped
+ * kernels then skip its segment and set the route's status word to TRIS_ERR_WORKSPACE instead of
+ * reading another expert's bytes.  (The reference pages such a batch in chunks, SC:1047-1136; here
+ * the caller sizes the buffers for the experts a batch can activate, or gets the error.)
  */
 int tris_page_experts(const TrisPageJob* jobs, int32_t num_jobs, const int32_t* expert_ids,
                       const int32_t* num_segments_dev, int32_t num_segments, int32_t num_experts,
@@ -386,6 +440,18 @@ typedef struct TrisMoeLayerView {
 } TrisMoeLayerView;
 
 size_t tris_moe_layer_workspace_bytes(const TrisMoeLayerView* layer, int32_t num_tokens);
+
+/*
+ * Status word of the kernels a layer entry point launched: 0, or TRIS_ERR_TIMEOUT when a bounded
+ * wait inside one of them ran out (that CTA skipped its stores, so the output rows it owned are
+ * stale).  The word lives at byte 8 of the caller's workspace - zero the first 16 bytes of a
+ * workspace once, when it is allocated - and is sticky: the kernels only ever set it, so one read
+ * covers every call since the last clear.  Pass the workspace given to tris_moe_layer_forward, or
+ * NULL for the built-in scratch of tris_moe_layer_forward_static on the current device.  Reads the
+ * word back on `stream` and synchronises that stream; clear != 0 resets a non-zero word.  Stands in
+ * for the C++ exception a failed TORCH_CHECK raises in the reference extension (CU:49-54).
+ */
+int tris_moe_layer_last_status(void* workspace, int32_t clear, void* stream, int32_t* status_out);
 
 /*
  * OlmoeSparseMoeBlock.forward -> _forward_grouped (MO:1046-1105, MO:916-1044) as one

@@ -17,6 +17,9 @@ from .formats import (  # noqa: F401
     stack_expert_payloads,
 )
 from .qlinear_grouped import (  # noqa: F401
+    HIDDEN_LANE_ORDER,
+    HIDDEN_PAIR_INTERLEAVED,
+    HIDDEN_ROW_MAJOR,
     TRIS_COMPACT3_KERNEL_ABI_VERSION,
     ExpertSharedMatrix,
     build_grouped_precomputed_payload,
@@ -33,6 +36,9 @@ from .moe_block import TrisSparseMoeBlock  # noqa: F401
 from . import clocks, expert_parallel, synth  # noqa: F401
 
 __all__ = [
+    "HIDDEN_LANE_ORDER",
+    "HIDDEN_PAIR_INTERLEAVED",
+    "HIDDEN_ROW_MAJOR",
     "TRIS_COMPACT3_KERNEL_ABI_VERSION",
     "ExpertSharedMatrix",
     "TrisSparseMoeBlock",

@@ -30,6 +30,8 @@ class TrisProjView(C.Structure):
         ("c_map", _vp), ("g_idx", _vp), ("col_pack3", _vp), ("row_pack3", _vp),
         ("output_scale", _vp), ("bias", _vp),
         ("gr_index", _vp), ("gr_substreams", _i32), ("packed_row_group", _vp), ("gmap_slot", _vp), ("expert_slot", _vp),
+        ("tile_records", _vp), ("tile_desc", _vp), ("col_records", _vp),
+        ("col_record_bytes", _i32), ("max_record_bytes", _i32), ("max_sal_words", _i32), ("reserved0", _i32),
     ]
 
 
@@ -37,7 +39,7 @@ class TrisPageJob(C.Structure):
     _fields_ = [("host_src", _vp), ("dst", _vp), ("bytes_per_expert", C.c_int64)]
 
 
-ABI_VERSION = 2  # TRIS_B200_ABI_VERSION of include/trismoe_b200.h
+ABI_VERSION = 3  # TRIS_B200_ABI_VERSION of include/trismoe_b200.h
 
 
 class TrisRouteView(C.Structure):
@@ -71,6 +73,10 @@ SIGNATURES = {
     "tris_block_gr_decode": (C.c_int, [_P(TrisProjView), _vp, _vp]),
     "tris_build_row_groups": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "tris_compact3_dequantize": (C.c_int, [_P(TrisProjView), _vp, _vp]),
+    "tris_tile_record_count": (C.c_int64, [_P(TrisProjView)]),
+    "tris_col_record_bytes": (C.c_int64, [_P(TrisProjView), _i32]),
+    "tris_tile_records_plan": (C.c_int, [_P(TrisProjView), _vp, _vp, _vp]),
+    "tris_tile_records_build": (C.c_int, [_P(TrisProjView), _vp, _vp, _vp, _i32, _vp]),
     "tris_build_grouped_route": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tris_ep_pack_rows": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
     "tris_ep_signal_increment": (C.c_int, []),
@@ -86,10 +92,12 @@ SIGNATURES = {
     "tris_shared_hidden_forward": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _vp]),
     "tris_grouped_forward": (C.c_int, [_P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp]),
     "tris_grouped_pair_forward": (C.c_int, [_P(TrisProjView), _P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp, _vp, _i32, _vp]),
+    "tris_grouped_hidden_layout": (C.c_int, [_P(TrisProjView), _P(TrisProjView), _i32, _i32, _i32]),
     "tris_set_grouped_tc_min_rows": (C.c_int, [_i32]),
     "tris_combine_routed": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "tris_page_experts": (C.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _vp]),
     "tris_moe_layer_workspace_bytes": (C.c_size_t, [_P(TrisMoeLayerView), _i32]),
+    "tris_moe_layer_last_status": (C.c_int, [_vp, _i32, _vp, _P(_i32)]),
     "tris_moe_layer_forward": (C.c_int, [_P(TrisMoeLayerView), _vp, _vp, _i32, _vp, _vp, _vp, C.c_size_t, _vp]),
     "tris_moe_layer_forward_static": (C.c_int, [_P(TrisMoeLayerView), _vp, _vp, _i32, _vp, _vp, _vp]),
 }

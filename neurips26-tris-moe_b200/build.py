@@ -14,8 +14,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libtrismoe_b200.so")
-SOURCES = ["grouped.cu", "skinny_gemm.cu", "route.cu", "layer.cu", "paging.cu", "tc_gemm.cu", "grouped_umma.cu", "ep_peer.cu", "packed4.cu", "abi.cpp"]
-HEADERS = ["common.cuh", "compact3_tile.cuh", "umma.cuh", os.path.join("..", "..", "include", "trismoe_b200.h")]
+LAST_LOG = ""
+SOURCES = ["grouped.cu", "grouped_tiled.cu", "tile_records.cu", "skinny_gemm.cu", "route.cu", "layer.cu", "paging.cu", "tc_gemm.cu", "grouped_umma.cu", "ep_peer.cu", "packed4.cu", "abi.cpp"]
+HEADERS = ["common.cuh", "compact3_tile.cuh", "tile_records.cuh", "umma.cuh", os.path.join("..", "..", "include", "trismoe_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
@@ -59,8 +60,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}")
-    with open(os.path.join(CSRC, "build.log"), "w") as fh:  # registers / spills / shared memory per kernel
-        fh.write("\n".join(line for line in "\n".join(log).split("\n") if "Compile time" not in line))
+    global LAST_LOG  # registers / spills / shared memory per kernel (-Xptxas -v), for callers that want it
+    LAST_LOG = "\n".join(line for line in "\n".join(log).split("\n") if "Compile time" not in line)
     if verbose:
         print("\n".join(log))
     return LIB

@@ -7,7 +7,7 @@
 
 #include "../../include/trismoe_b200.h"
 
-static_assert(sizeof(TrisProjView) == 184, "TrisProjView layout is part of the ABI");
+static_assert(sizeof(TrisProjView) == 224, "TrisProjView layout is part of the ABI");
 static_assert(sizeof(TrisRouteView) == 72, "TrisRouteView layout is part of the ABI");
 
 namespace tris {
@@ -29,6 +29,21 @@ int check_cuda(cudaError_t err, const char* what);
   } while (0)
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Position (in halves) of column j of a 32-column group in "lane order" (TRIS_OUT_F16_LANE_ORDER,
+// TRIS_ROUTE_HIDDEN_LANE_ORDER): lane t of a warp finds its eight columns t+8, t+24, t, t+16, t+12,
+// t+28, t+4, t+20 in 16 consecutive bytes.
+__host__ __device__ inline int lane_order_pos(int j) {
+  const int t = j & 3, q = (j >> 2) & 3, h = (j >> 4) & 1;
+  const int slot = (0x2031 >> (4 * q)) & 3;  // q = 0, 1, 2, 3 -> 1, 3, 0, 2
+  return 8 * t + 2 * slot + h;
+}
+// Column position of output m in the layout `out_mode` names (TRIS_OUT_F16_*).
+__host__ __device__ inline int out_mode_pos(int m, int out_mode) {
+  if (out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) return (m & ~31) | ((m & 15) << 1) | ((m >> 4) & 1);
+  if (out_mode == TRIS_OUT_F16_LANE_ORDER) return (m & ~31) | lane_order_pos(m & 31);
+  return m;
+}
 
 // One matrix of the shared skinny GEMM (skinny_gemm.cu): out[n, m] = x[n, :] . a[m, :].
 struct SkinnyProblem {
@@ -86,6 +101,16 @@ int grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* route, c
 int grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjView* proj_b, const TrisRouteView* route,
                               const void* hidden_a_f16, const void* hidden_b_f16, void* out_a_f16, void* out_b_f16,
                               int fuse_silu_mul, cudaStream_t stream, LaunchOpts opts);
+// Tile-record path (grouped_tiled.cu).  mode: 0 single projection, 1 gate/up pair, 2 pair with SiLU * mul.
+bool proj_has_tile_records(const TrisProjView& v);
+int launch_grouped_tiled(const TrisProjView* proj_a, const TrisProjView* proj_b, const TrisRouteView* route,
+                         const void* hidden_a, const void* hidden_b, void* out_a, void* out_b, int mode, int max_rows,
+                         cudaStream_t stream, LaunchOpts opts);
+// Rows per segment (the launch's estimate, route_rows_hint) above which the grouped entry points
+// leave the decode-regime kernels for the tcgen05 kernel (tris_set_grouped_tc_min_rows).
+int grouped_tc_min_rows();
+int route_rows_hint(const TrisRouteView* route);
+int launch_tiled_dump(const TrisProjView* proj, int32_t* dense_out, void* weights_out, cudaStream_t stream);
 int combine_routed_impl(const void* down_out_f16, const int32_t* row_of_flat, const float* routing_weights,
                         int num_tokens, int top_k, int hidden_size, void* final_f16, cudaStream_t stream, bool pdl);
 int launch_router_route(const float* logits, int num_tokens, int num_experts, int top_k, int norm, int m_tile,

@@ -32,13 +32,6 @@
 #pragma once
 #include "common.cuh"
 
-#ifndef TRIS_SUBMARK
-#define TRIS_SUBMARK(k) do { } while (0)
-#endif
-#ifndef TRIS_MARK_T
-#define TRIS_MARK_T(k, tid) do { } while (0)
-#endif
-
 namespace tris {
 
 constexpr int kThreads = 256;
@@ -582,7 +575,6 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
     }
   }
 
-  TRIS_SUBMARK(7);
   const bool gr = views[0].use_block_gr != 0;
   if (gr) {
     // zero the blocks (raw blocks are copied verbatim)
@@ -614,7 +606,6 @@ __device__ __forceinline__ bool stage_finish_weights(TileSmem<NPROJ, NT>& sm, co
                     [&](int flat) { atomicOr(gblock + (flat >> 5), 1u << (flat & 31)); });
     }
     __syncthreads();
-    TRIS_SUBMARK(6);
   }
 
   ok = mbar_wait_bounded(&sm.mbar[1], parity1) && ok;  // the sign plane

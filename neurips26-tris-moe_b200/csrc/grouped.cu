@@ -11,21 +11,6 @@
 
 #include <algorithm>
 
-// Development builds (-DTRIS_PHASE_TIMERS) stamp clock64() at phase boundaries of every CTA.
-#ifdef TRIS_PHASE_TIMERS
-namespace tris { __constant__ long long* g_phase_stamps = nullptr; }
-#define TRIS_MARK_T(k, tid)                                                                                   \
-  do {                                                                                                        \
-    if (threadIdx.x == (tid) && ::tris::g_phase_stamps)                                                       \
-      ::tris::g_phase_stamps[((static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 24 + (k)] = clock64(); \
-  } while (0)
-#define TRIS_MARK(k) TRIS_MARK_T(k, 0)
-#define TRIS_SUBMARK(k) TRIS_MARK(k)
-#else
-#define TRIS_MARK(k) do { } while (0)
-#define TRIS_MARK_T(k, tid) do { } while (0)
-#endif
-
 #include "compact3_tile.cuh"
 
 namespace cg = cooperative_groups;
@@ -307,9 +292,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
   const int ksplit = args.ksplit > 1 ? args.ksplit : 1;
   const int p_lo = (KC / ksplit) * static_cast<int>(blockIdx.z), p_hi = p_lo + KC / ksplit;
 
-  TRIS_MARK(0);
   init_barriers(sm.mbar);
-  TRIS_MARK(8);
   // Activations come from the predecessor kernel; the route arrays too, unless the caller
   // says they are older, in which case the weight staging below overlaps the predecessor.
   bool waited = false;
@@ -329,7 +312,12 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
   if (expert < 0 || expert >= args.proj[0].num_experts || row_end <= row_begin) return;
   // row block of the expert inside the payload tensors (a staging slot when they are paged in)
   const int e = args.proj[0].expert_slot ? args.proj[0].expert_slot[expert] : expert;
-  TRIS_MARK(9);
+  // A paged payload whose expert was not brought in (more active experts than staging slots): the
+  // slot table says -1.  Report it and store nothing rather than read another expert's bytes.
+  if (e < 0 || (args.proj[0].gmap_slot && args.proj[0].gmap_slot[expert] < 0)) {
+    if (threadIdx.x == 0 && args.status) atomicExch(args.status, TRIS_ERR_WORKSPACE);
+    return;
+  }
 
   const int o0 = blockIdx.x * OW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -358,13 +346,8 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       const bool need_w = staged_chunk != kc;
       auto row_src = [&](int n) { return args.row_gather ? args.row_gather[r0 + n] : (r0 + n); };
       if (need_w) stage_issue_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0, p_lo, p_hi);
-      TRIS_MARK(10);
-      TRIS_MARK_T(11, 32);
-      TRIS_MARK_T(12, 96);
       if (waited) stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, args.hidden_stride, row_src);
-      TRIS_MARK_T(13, 64);
       __syncthreads();
-      TRIS_MARK(1);
       bool ok = true;
       if (need_w) {
         ok = stage_finish_weights<NPROJ, NT>(sm, args.proj, e, expert, o0, p0, par_w, par_w, nullptr, p_lo, p_hi);
@@ -378,7 +361,6 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
         stage_issue_hidden<NPROJ, NT>(sm, args.hidden, args.proj, p0, rows, interleaved, args.hidden_stride, row_src);
         __syncthreads();
       }
-      TRIS_MARK(2);
       ok = mbar_wait_bounded(&sm.mbar[2], par_h) && ok;
       par_h ^= 1u;
       if (__syncthreads_or(!ok)) {
@@ -386,12 +368,10 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
         dead = true;
         break;
       }
-      TRIS_MARK(3);
 
       main_chunk<NPROJ, NT>(sm, proj, out_local, lane, nt_count, p_lo, min(p_hi, pr - p0), acc);
     }
 
-    TRIS_MARK(4);
     if (ksplit > 1) {
       // partial tiles of the cluster -> rank 0 (the activation rows are dead by now)
       __syncthreads();
@@ -423,7 +403,6 @@ __global__ void __launch_bounds__(kThreads, (NT <= 4) ? 3 : 2) grouped_compact3_
       finish_rows<NPROJ, NT, EPI>(args, xbuf, kPairBarrier, proj, out_local, warp, lane, expert, o0, r0, rows, nt_count, acc);
     }
   }
-  TRIS_MARK(5);
 }
 
 // tensor-core path for prefill-sized segments (grouped_umma.cu)
@@ -517,9 +496,14 @@ static int pick_ksplit(const TrisProjView* proj, const TrisRouteView* route, int
   return 1;
 }
 
+// Rows per segment (the launch's estimate) up to which the tile-record kernel is used; beyond it
+// the prefill-sized kernels take over.
+static int tiled_max_rows() { return grouped_tc_min_rows(); }
+
 // Rows per activation tile: sized for the typical segment (mean + 4 sigma of a balanced
 // router), never above the caller's bound; longer segments take several passes.
-static int rows_hint(const TrisRouteView* route) {
+static int rows_hint(const TrisRouteView* route) { return route_rows_hint(route); }
+int route_rows_hint(const TrisRouteView* route) {
   const int bound = route->max_rows_per_segment > 0 ? route->max_rows_per_segment : route->num_rows;
   if (route->num_segments <= 0) return bound;
   const double mean = static_cast<double>(route->num_rows) / route->num_segments;
@@ -572,6 +556,7 @@ extern "C" int tris_block_gr_decode(const TrisProjView* proj, int32_t* dense_out
   int st = validate_proj(proj, "tris_block_gr_decode", true);
   if (st != TRIS_OK) return st;
   TRIS_REQUIRE(proj->use_block_gr && dense_out, TRIS_ERR_INVALID_ARG, "tris_block_gr_decode: needs a block-GR payload and an output");
+  if (proj_has_tile_records(*proj)) return launch_tiled_dump(proj, dense_out, nullptr, static_cast<cudaStream_t>(stream));
   const int pr = (proj->rank + 31) / 32;
   dim3 grid(ceil_div(proj->out_features, 128), ceil_div(pr, KC), proj->num_experts);
   const size_t smem = sizeof(TileSmem<1, 1>);
@@ -584,6 +569,7 @@ extern "C" int tris_compact3_dequantize(const TrisProjView* proj, void* weights_
   int st = validate_proj(proj, "tris_compact3_dequantize", true);
   if (st != TRIS_OK) return st;
   TRIS_REQUIRE(weights_out_f16, TRIS_ERR_INVALID_ARG, "tris_compact3_dequantize: null output");
+  if (proj_has_tile_records(*proj)) return launch_tiled_dump(proj, nullptr, weights_out_f16, static_cast<cudaStream_t>(stream));
   const int pr = (proj->rank + 31) / 32;
   dim3 grid(ceil_div(proj->out_features, 128), ceil_div(pr, KC), proj->num_experts);
   const size_t smem = sizeof(TileSmem<1, 1>);
@@ -602,6 +588,11 @@ int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* ro
   st = fill_route(a, route);
   if (st != TRIS_OK) return st;
   if (a.num_segments == 0 || a.num_rows == 0) return TRIS_OK;
+  const bool lane_order = (route->flags & TRIS_ROUTE_HIDDEN_LANE_ORDER) != 0;
+  TRIS_REQUIRE(!lane_order || (proj_has_tile_records(*proj) && !a.hidden_interleaved), TRIS_ERR_INVALID_ARG,
+               "tris_grouped_forward: lane-order activations need a projection with tile records");
+  if (proj_has_tile_records(*proj) && !a.hidden_interleaved && (lane_order || rows_hint(route) <= tiled_max_rows()))
+    return launch_grouped_tiled(proj, nullptr, route, hidden_f16, nullptr, out_f16, nullptr, 0, rows_hint(route), stream, opts);
   TRIS_REQUIRE(!a.hidden_interleaved || proj->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
                "tris_grouped_forward: pair-interleaved activations need rank % 32 == 0");
   if (a.hidden_stride <= 0) a.hidden_stride = proj->rank;
@@ -616,6 +607,17 @@ int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* ro
   a.ksplit = pick_ksplit(proj, route, 128);
   if (grouped_umma_applicable(a, rows_hint(route))) return launch_grouped_umma(a, 1, EPI_STORE, stream, opts.pdl);
   return dispatch_grouped<1, EPI_STORE>(a, rows_hint(route), stream, opts.pdl);
+}
+
+extern "C" int tris_grouped_hidden_layout(const TrisProjView* proj_a, const TrisProjView* proj_b, int32_t num_rows,
+                                          int32_t num_segments, int32_t max_rows_per_segment) {
+  if (proj_a == nullptr || proj_a->rank % 32 != 0) return TRIS_OUT_F16;
+  TrisRouteView route{};
+  route.num_rows = num_rows;
+  route.num_segments = num_segments;
+  route.max_rows_per_segment = max_rows_per_segment;
+  const bool records = proj_has_tile_records(*proj_a) && (proj_b == nullptr || proj_has_tile_records(*proj_b));
+  return (records && route_rows_hint(&route) <= grouped_tc_min_rows()) ? TRIS_OUT_F16_LANE_ORDER : TRIS_OUT_F16_PAIR_INTERLEAVED;
 }
 
 extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
@@ -643,6 +645,13 @@ int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjVi
   st = fill_route(a, route);
   if (st != TRIS_OK) return st;
   if (a.num_segments == 0 || a.num_rows == 0) return TRIS_OK;
+  const bool lane_order = (route->flags & TRIS_ROUTE_HIDDEN_LANE_ORDER) != 0;
+  const bool records = proj_has_tile_records(*proj_a) && proj_has_tile_records(*proj_b);
+  TRIS_REQUIRE(!lane_order || (records && !a.hidden_interleaved), TRIS_ERR_INVALID_ARG,
+               "tris_grouped_pair_forward: lane-order activations need projections with tile records");
+  if (records && !a.hidden_interleaved && (lane_order || rows_hint(route) <= tiled_max_rows()))
+    return launch_grouped_tiled(proj_a, proj_b, route, hidden_a_f16, hidden_b_f16, out_a_f16, out_b_f16, fuse_silu_mul ? 2 : 1,
+                                rows_hint(route), stream, opts);
   TRIS_REQUIRE(!a.hidden_interleaved || proj_a->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
                "tris_grouped_pair_forward: pair-interleaved activations need rank % 32 == 0");
   if (a.hidden_stride <= 0) a.hidden_stride = proj_a->rank;
@@ -673,8 +682,3 @@ extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisP
                                    fuse_silu_mul, static_cast<cudaStream_t>(stream), LaunchOpts{});
 }
 
-#ifdef TRIS_PHASE_TIMERS
-extern "C" int tris_debug_set_phase_stamps(long long* stamps) {
-  return check_cuda(cudaMemcpyToSymbol(tris::g_phase_stamps, &stamps, sizeof(stamps)), "set phase stamps");
-}
-#endif

@@ -77,7 +77,13 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
     row_begin = args.segment_offsets[seg];
     row_end = min(args.segment_offsets[seg + 1], args.num_rows);
   }
-  const bool live = expert >= 0 && expert < args.proj[0].num_experts && row_end > row_begin;
+  bool live = expert >= 0 && expert < args.proj[0].num_experts && row_end > row_begin;
+  bool unpaged = false;  // a paged payload whose expert has no staging slot (the slot table says -1)
+  if (live && ((args.proj[0].expert_slot && args.proj[0].expert_slot[expert] < 0) ||
+               (args.proj[0].gmap_slot && args.proj[0].gmap_slot[expert] < 0))) {
+    live = false;
+    unpaged = true;
+  }
   const int o0 = blockIdx.x * kTcM;
   const int rank = args.proj[0].rank;
   const int pr = proj_packed_rows(args.proj[0]);
@@ -112,7 +118,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
     pdl_wait();
     pdl_launch_dependents();
   }
-  __syncthreads();  // the staging structure is dead from here on: its memory becomes the B operand
+  // Every thread ran its own bounded waits in phase 1: make the verdict CTA-uniform before any
+  // branch that contains barriers (this barrier also ends the life of the staging structure,
+  // whose memory becomes the B operand).
+  ok = !__syncthreads_or(!ok);
   if (threadIdx.x == 0) {
     mbar_inval(&stage.mbar[0]);
     mbar_inval(&stage.mbar[1]);
@@ -169,9 +178,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
         umma_commit(mma_bar);
       }
       if (!mbar_wait_bounded(mma_bar, parity)) ok = false;
-      parity ^= 1u;
       tcgen05_fence_after();
-      if (__syncthreads_or(!ok)) break;
+      if (__syncthreads_or(!ok)) {
+        // the MMAs may still be in flight: give them one more bounded wait before TMEM is released
+        mbar_wait_bounded(mma_bar, parity);
+        ok = false;
+        break;
+      }
+      parity ^= 1u;
 
       // epilogue: this warp reads TMEM lanes [32*quad, +32) (outputs) and half of the row columns
       const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
@@ -208,6 +222,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, NPROJ * NB);
   if (*flag && threadIdx.x == 0 && args.status) atomicExch(args.status, TRIS_ERR_TIMEOUT);
+  if (unpaged && threadIdx.x == 0 && args.status) atomicExch(args.status, TRIS_ERR_WORKSPACE);
 }
 
 template <int NPROJ, int EPI>
@@ -232,6 +247,8 @@ static int launch_umma_grouped(const GroupedArgs& args, cudaStream_t stream, boo
 // 4096 (Mixtral) - because this kernel holds a whole SM (192 KB of shared memory) while its
 // decode-and-unpack phase runs on eight warps.  So the default sits above the measured range.
 static std::atomic<int> g_tc_min_rows{2048};
+
+int grouped_tc_min_rows() { return g_tc_min_rows.load(std::memory_order_relaxed); }
 
 // Dense-contraction path: activations must be pair-interleaved, rank a multiple of 32 and at
 // most one 256-column chunk.

@@ -41,6 +41,7 @@ static LayerWorkspace carve(const TrisMoeLayerView* L, int T, char* base) {
   };
   const size_t R = static_cast<size_t>(T) * L->top_k;
   const size_t E = L->num_experts;
+  w.counts = reinterpret_cast<int32_t*>(take(16));  // {segments, problem tiles, status, -}: first, so the status word is at a fixed offset
   w.logits = reinterpret_cast<float*>(take(sizeof(float) * T * E));
   w.selected = reinterpret_cast<int32_t*>(take(4 * R));
   w.weights = reinterpret_cast<float*>(take(4 * R));
@@ -51,7 +52,6 @@ static LayerWorkspace carve(const TrisMoeLayerView* L, int T, char* base) {
   w.expert_ids = reinterpret_cast<int32_t*>(take(4 * E));
   w.segment_offsets = reinterpret_cast<int32_t*>(take(4 * (E + 1)));
   w.problem_offsets = reinterpret_cast<int32_t*>(take(4 * (E + 1)));
-  w.counts = reinterpret_cast<int32_t*>(take(16));  // {segments, problem tiles, status, -}
   w.hidden_gate = reinterpret_cast<__half*>(take(2 * static_cast<size_t>(T) * L->gate.rank));
   w.hidden_up = reinterpret_cast<__half*>(take(2 * static_cast<size_t>(T) * L->up.rank));
   w.mlp = reinterpret_cast<__half*>(take(2 * R * L->intermediate_size));
@@ -107,8 +107,21 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
   // Launch order.  With logits given, router + route run first, so that the grouped
   // gate/up kernel can stage its weights while the backbone GEMM is still running
   // (programmatic dependent launch); otherwise the logits come out of the backbone GEMM.
-  const int gu_mode = (layer->gate.rank % 32 == 0) ? TRIS_OUT_F16_PAIR_INTERLEAVED : TRIS_OUT_F16;
-  const int down_mode = (layer->down.rank % 32 == 0) ? TRIS_OUT_F16_PAIR_INTERLEAVED : TRIS_OUT_F16;
+  // Activation layout between the backbone GEMMs and the grouped kernels: lane order for the
+  // tile-record kernels, pair-interleaved for the plane-staging kernels, row-major for odd ranks.
+  TrisRouteView route{};
+  route.num_segments = std::min(layer->num_experts, R);
+  route.num_rows = R;
+  route.max_rows_per_segment = T;  // top-k experts of a token are distinct
+  auto hidden_mode = [&](const TrisProjView& a, const TrisProjView& b) {
+    return tris_grouped_hidden_layout(&a, &b, route.num_rows, route.num_segments, route.max_rows_per_segment);
+  };
+  auto route_flags = [](int mode) {
+    return mode == TRIS_OUT_F16_LANE_ORDER ? TRIS_ROUTE_HIDDEN_LANE_ORDER
+                                           : (mode == TRIS_OUT_F16_PAIR_INTERLEAVED ? TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED : 0);
+  };
+  const int gu_mode = hidden_mode(layer->gate, layer->up);
+  const int down_mode = hidden_mode(layer->down, layer->down);
   SkinnyProblem probs[3];
   int np = 0;
   probs[np++] = {static_cast<const __half*>(layer->shared_gate), w.hidden_gate, layer->gate.rank, gu_mode};
@@ -140,18 +153,14 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
     if (st != TRIS_OK) return st;
   }
 
-  TrisRouteView route{};
   route.expert_ids = w.expert_ids;
   route.segment_offsets = w.segment_offsets;
   route.num_segments_dev = w.counts;
-  route.num_segments = std::min(layer->num_experts, R);
-  route.num_rows = R;
-  route.max_rows_per_segment = T;  // top-k experts of a token are distinct
   route.status_dev = w.counts + 2;
 
   // gate/up + SiLU*mul; rows read the per-token backbone outputs through tok[]
   route.row_gather = w.tok;
-  route.flags = (gu_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED : 0;
+  route.flags = route_flags(gu_mode);
   LaunchOpts opts;
   opts.pdl = true;
   opts.weights_before_wait = logits_given;
@@ -165,7 +174,7 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
 
   // grouped down: the route is older than the GEMM before it, so weights stage early
   route.row_gather = nullptr;
-  route.flags = (down_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? TRIS_ROUTE_HIDDEN_PAIR_INTERLEAVED : 0;
+  route.flags = route_flags(down_mode);
   opts.weights_before_wait = true;
   st = grouped_forward_impl(&layer->down, &route, w.hidden_down, w.down_out, s, opts);
   if (st != TRIS_OK) return st;
@@ -213,9 +222,36 @@ extern "C" int tris_moe_layer_forward_static(const TrisMoeLayerView* layer, cons
     scratch = g_static_scratch_ptr[dev];
   }
   // The array keeps whatever the previous call left.  Everything the launch sequence reads it
-  // writes first, except the status/count words, which are cleared here.
+  // writes first, except the two count words, which are cleared here; the status word behind
+  // them is sticky (it starts at zero with the array and only tris_moe_layer_last_status clears it).
   LayerWorkspace w = carve(layer, num_tokens, static_cast<char*>(scratch));
-  TRIS_CUDA(cudaMemsetAsync(w.counts, 0, 16, static_cast<cudaStream_t>(stream)));
+  TRIS_CUDA(cudaMemsetAsync(w.counts, 0, 8, static_cast<cudaStream_t>(stream)));
   return tris_moe_layer_forward(layer, x_f16, router_logits, num_tokens, y_f16, router_logits_out, scratch,
                                 TRIS_STATIC_SCRATCH_BYTES, stream);
+}
+
+// Offset of the sticky status word inside a layer workspace (and inside the built-in scratch array).
+static constexpr size_t kStatusWordOffset = 8;
+
+extern "C" int tris_moe_layer_last_status(void* workspace, int32_t clear, void* stream, int32_t* status_out) {
+  TRIS_REQUIRE(status_out != nullptr, TRIS_ERR_INVALID_ARG, "tris_moe_layer_last_status: null output");
+  char* base = static_cast<char*>(workspace);
+  if (base == nullptr) {  // the built-in scratch of tris_moe_layer_forward_static on the current device
+    int dev = -1;
+    TRIS_CUDA(cudaGetDevice(&dev));
+    TRIS_REQUIRE(dev >= 0 && dev < 64, TRIS_ERR_UNSUPPORTED, "tris_moe_layer_last_status: device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {  // never used on this device: nothing can have been reported
+      *status_out = TRIS_OK;
+      return TRIS_OK;
+    }
+    base = static_cast<char*>(g_static_scratch_ptr[dev]);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int32_t word = 0;
+  TRIS_CUDA(cudaMemcpyAsync(&word, base + kStatusWordOffset, sizeof(word), cudaMemcpyDeviceToHost, s));
+  TRIS_CUDA(cudaStreamSynchronize(s));
+  if (clear && word != 0) TRIS_CUDA(cudaMemsetAsync(base + kStatusWordOffset, 0, sizeof(word), s));
+  *status_out = word;
+  return TRIS_OK;
 }

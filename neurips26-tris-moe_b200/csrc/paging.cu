@@ -75,6 +75,9 @@ extern "C" int tris_page_experts(const TrisPageJob* jobs, int32_t num_jobs, cons
   args.num_segments = num_segments;
   args.num_experts = num_experts;
   args.slot_table = slot_table;
+  // Experts that get no slot (more live segments than num_segments) must not keep a stale entry:
+  // the grouped kernels treat -1 as "not paged in", store nothing and report TRIS_ERR_WORKSPACE.
+  TRIS_CUDA(cudaMemsetAsync(slot_table, 0xFF, sizeof(int32_t) * static_cast<size_t>(num_experts), static_cast<cudaStream_t>(stream)));
   const int chunks = static_cast<int>(std::min<long long>(16, std::max<long long>(1, max_bytes / (256 * 16 * 4))));
   page_experts_kernel<<<dim3(chunks, num_segments, num_jobs), 256, 0, static_cast<cudaStream_t>(stream)>>>(args);
   return check_cuda(cudaGetLastError(), "page_experts_kernel launch");

@@ -112,9 +112,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const __gri
         if (pb.out_mode == TRIS_OUT_F32) {
           static_cast<float*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = v;
         } else {
-          // pair-interleaved: column j of a 32-column group goes to 2*(j%16) + j/16
-          const int mm = (pb.out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED)
-                             ? ((m & ~31) | ((m & 15) << 1) | ((m >> 4) & 1)) : m;
+          const int mm = out_mode_pos(m, pb.out_mode);
           static_cast<__half*>(pb.out)[static_cast<size_t>(n) * pb.m + mm] = __float2half_rn(v);
         }
       }
@@ -180,10 +178,10 @@ extern "C" int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_
                                           void* stream) {
   TRIS_REQUIRE(x_f16 && shared_sv_f16 && out, TRIS_ERR_INVALID_ARG, "tris_shared_hidden_forward: null pointer");
   TRIS_REQUIRE(rank > 0, TRIS_ERR_INVALID_ARG, "tris_shared_hidden_forward: rank=%d", rank);
-  TRIS_REQUIRE(out_mode >= TRIS_OUT_F16 && out_mode <= TRIS_OUT_F16_PAIR_INTERLEAVED, TRIS_ERR_INVALID_ARG,
+  TRIS_REQUIRE(out_mode >= TRIS_OUT_F16 && out_mode <= TRIS_OUT_F16_LANE_ORDER, TRIS_ERR_INVALID_ARG,
                "tris_shared_hidden_forward: unknown out_mode %d", out_mode);
-  TRIS_REQUIRE(out_mode != TRIS_OUT_F16_PAIR_INTERLEAVED || rank % 32 == 0, TRIS_ERR_INVALID_ARG,
-               "tris_shared_hidden_forward: the pair-interleaved layout needs rank % 32 == 0");
+  TRIS_REQUIRE((out_mode != TRIS_OUT_F16_PAIR_INTERLEAVED && out_mode != TRIS_OUT_F16_LANE_ORDER) || rank % 32 == 0,
+               TRIS_ERR_INVALID_ARG, "tris_shared_hidden_forward: the permuted layouts need rank % 32 == 0");
   SkinnyProblem pb{static_cast<const __half*>(shared_sv_f16), out, rank, out_mode};
   return launch_shared_hidden(&pb, 1, static_cast<const __half*>(x_f16), row_gather, num_rows, in_features,
                               static_cast<cudaStream_t>(stream), false, num_rows_dev);
@@ -202,8 +200,9 @@ extern "C" int tris_input_projections(const void* x_f16, int32_t num_rows, int32
                "tris_input_projections: bad sizes rows=%d in=%d rank=%d", num_rows, in_features, rank);
   TRIS_REQUIRE((router_weight_f16 == nullptr) == (router_logits_f32 == nullptr) && (!router_weight_f16 || num_experts > 0),
                TRIS_ERR_INVALID_ARG, "tris_input_projections: router weight and logits go together");
-  TRIS_REQUIRE(hidden_out_mode == TRIS_OUT_F16 || (hidden_out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED && rank % 32 == 0),
-               TRIS_ERR_INVALID_ARG, "tris_input_projections: out_mode %d (pair-interleaved needs rank %% 32 == 0)",
+  TRIS_REQUIRE(hidden_out_mode == TRIS_OUT_F16 ||
+                   ((hidden_out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED || hidden_out_mode == TRIS_OUT_F16_LANE_ORDER) && rank % 32 == 0),
+               TRIS_ERR_INVALID_ARG, "tris_input_projections: out_mode %d (the permuted layouts need rank %% 32 == 0)",
                hidden_out_mode);
   if (num_rows == 0) return TRIS_OK;
   SkinnyProblem probs[3] = {

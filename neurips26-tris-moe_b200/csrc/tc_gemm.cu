@@ -102,7 +102,7 @@ __device__ __forceinline__ void tc_gemm_epilogue(const TcGemmArgs& args, const S
         if (pb.out_mode == TRIS_OUT_F32) {
           static_cast<float*>(pb.out)[static_cast<size_t>(n) * pb.m + m] = vals[u];
         } else {
-          const int mm = (pb.out_mode == TRIS_OUT_F16_PAIR_INTERLEAVED) ? ((m & ~31) | ((m & 15) << 1) | ((m >> 4) & 1)) : m;
+          const int mm = out_mode_pos(m, pb.out_mode);
           static_cast<__half*>(pb.out)[static_cast<size_t>(n) * pb.m + mm] = __float2half_rn(vals[u]);
         }
       }

@@ -38,7 +38,7 @@ import torch.distributed as dist
 
 from . import _native
 from ._native import TrisRouteView
-from .qlinear_grouped import prepare_grouped_payload, proj_view
+from .qlinear_grouped import HIDDEN_LAYOUT_ROUTE_FLAG, grouped_hidden_layout, prepare_grouped_payload, proj_view
 
 _SHARD_KEYS = ("qweight1", "qweight2_sparse", "qweight2_sparse_prefix", "q_gmap_sparse", "q_gmap_sparse_prefix",
                "q_gmap_gr_words", "q_gmap_gr_offsets", "q_gmap_gr_meta", "c_map", "g_idx", "col_pack3", "row_pack3",
@@ -209,6 +209,8 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         self.capacity_tokens = 0  # tokens per rank the fixed-capacity exchange is sized for
         self.capacity_rows = 0    # rows per peer slot
         self._overflow = None
+        self._step_layouts = None
+        self._kernel_status = None  # sticky status word of the grouped kernels (TRIS_ERR_TIMEOUT)
         self._peer: Optional[PeerExchangeBuffers] = None  # set by use_peer_exchange()
 
     def set_capacity(self, max_tokens_per_rank: int, rows_per_peer: Optional[int] = None) -> "ExpertParallelMoeBlock":
@@ -265,7 +267,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         return {"perm": perm, "tok": tok, "slot": slot, "row_of_flat": rof, "expert_ids": ids, "segment_offsets": seg,
                 "counts": counts, "_buf": buf, "rows": R, "experts": E, "max_rows": T}
 
-    def _route_view(self, route: dict, row_gather, interleaved: bool, hidden_stride: int = 0) -> TrisRouteView:
+    def _route_view(self, route: dict, row_gather, layout: int, hidden_stride: int = 0) -> TrisRouteView:
         rv = TrisRouteView()
         rv.expert_ids = route["expert_ids"].data_ptr()
         rv.segment_offsets = route["segment_offsets"].data_ptr()
@@ -274,23 +276,37 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         rv.num_rows = route["rows"]
         rv.max_rows_per_segment = route["max_rows"]
         rv.row_gather = None if row_gather is None else row_gather.data_ptr()
-        rv.status_dev = None
-        rv.flags = 1 if interleaved else 0
+        if self._kernel_status is None or self._kernel_status.device != route["expert_ids"].device:
+            self._kernel_status = torch.zeros((1,), dtype=torch.int32, device=route["expert_ids"].device)
+        rv.status_dev = self._kernel_status.data_ptr()
+        rv.flags = HIDDEN_LAYOUT_ROUTE_FLAG[int(layout)]
         rv.hidden_row_stride = int(hidden_stride)
         return rv
 
-    def _backbone(self, x: torch.Tensor, sv: torch.Tensor, interleaved: bool, live_rows=None) -> torch.Tensor:
+    def _backbone(self, x: torch.Tensor, sv: torch.Tensor, layout: int, live_rows=None) -> torch.Tensor:
         lib = _native.load()
         out = torch.empty((x.shape[0], sv.shape[0]), dtype=torch.float16, device=x.device)
         if x.shape[0]:
             _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, int(x.shape[0]),
                                                          None if live_rows is None else live_rows.data_ptr(),
                                                          int(x.shape[1]), sv.data_ptr(),
-                                                         int(sv.shape[0]), out.data_ptr(), 2 if interleaved else 0,
+                                                         int(sv.shape[0]), out.data_ptr(), int(layout),
                                                          torch.cuda.current_stream(x.device).cuda_stream), "shared_hidden")
         return out
 
-    def _local_experts(self, recv_hidden: torch.Tensor, recv_local_ids: torch.Tensor, rows_hint: int = 0) -> torch.Tensor:
+    def _hidden_layouts(self, tokens: int):
+        """Column orders (gate/up rows, down rows) every rank uses for a step of ``tokens`` tokens per
+        rank: derived from sizes all ranks share (the exchange capacity when one is set), because the
+        sender's backbone GEMM writes the rows the owner's grouped kernels read."""
+        per_rank = self.capacity_tokens if self.capacity_tokens > 0 else int(tokens)
+        rows = max(1, per_rank * self.top_k)  # rows a rank receives when routing is balanced
+        local = max(1, self.hi - self.lo)
+        gu = grouped_hidden_layout(self.payloads["gate"], self.payloads["up"], rows, min(local, rows), per_rank * self.world)
+        d = grouped_hidden_layout(self.payloads["down"], None, rows, min(local, rows), per_rank * self.world)
+        return gu, d
+
+    def _local_experts(self, recv_hidden: torch.Tensor, recv_local_ids: torch.Tensor, rows_hint: int = 0,
+                       layouts=None) -> torch.Tensor:
         """gate/up -> SiLU*mul -> down for the rows this rank received; returns [rows, H] in the
         received order.  ``recv_hidden`` is [rows, >= 2*r]: gate and up backbone outputs side by
         side at the start of every row (anything behind them is skipped through the row stride).
@@ -305,7 +321,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         stream = torch.cuda.current_stream(dev).cuda_stream
         r_gu = int(self.shared["gate"].shape[0])
         r_d = int(self.shared["down"].shape[0])
-        inter_gu, inter_d = r_gu % 32 == 0, r_d % 32 == 0
+        inter_gu, inter_d = layouts if layouts is not None else self._hidden_layouts(0)
         recv_hidden = recv_hidden.contiguous()
         stride = int(recv_hidden.shape[1])
         hg_ptr = recv_hidden.data_ptr()
@@ -342,7 +358,8 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
             r_gu = int(self.shared["gate"].shape[0])
-            inter = r_gu % 32 == 0
+            layouts = self._hidden_layouts(T)
+            self._step_layouts = layouts
             hg = torch.empty((T, r_gu), dtype=torch.float16, device=dev)
             hu = torch.empty((T, r_gu), dtype=torch.float16, device=dev)
             own_logits = router_logits is None
@@ -355,7 +372,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                 _native.check(lib.tris_input_projections(
                     x.data_ptr(), T, int(x.shape[1]), self.shared["gate"].data_ptr(), self.shared["up"].data_ptr(), r_gu,
                     self.router_weight.data_ptr() if own_logits else None, self.num_experts, hg.data_ptr(), hu.data_ptr(),
-                    2 if inter else 0, router_logits.data_ptr() if own_logits else None, stream), "input_projections")
+                    int(layouts[0]), router_logits.data_ptr() if own_logits else None, stream), "input_projections")
             logits = router_logits.reshape(T, self.num_experts).to(torch.float32).contiguous()
             sel = torch.empty((T, self.top_k), dtype=torch.int32, device=dev)
             wts = torch.empty((T, self.top_k), dtype=torch.float32, device=dev)
@@ -368,8 +385,8 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                 tok = route["tok"].to(torch.long)
                 grouped_hidden = torch.cat([hg, hu], dim=1).index_select(0, tok)
                 grouped_ids = sel.reshape(-1).index_select(0, route["perm"].to(torch.long))
-                returned = expert_parallel_exchange(grouped_hidden, grouped_ids, self.num_experts, self._local_experts,
-                                                    self.group)
+                returned = expert_parallel_exchange(grouped_hidden, grouped_ids, self.num_experts,
+                                                    lambda rows, ids: self._local_experts(rows, ids, layouts=layouts), self.group)
                 index = route["row_of_flat"]
             else:
                 if self.capacity_tokens <= 0:
@@ -411,7 +428,8 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         recv_ids = recv_rows.view(torch.int32)[:, r_gu]  # the int32 right behind the 2*r_gu halves
         local_ids = recv_ids - self.lo  # padding slots (-1) stay negative and are skipped by the route
         expected = max(1, (N * R) // max(1, self.hi - self.lo))  # rows per local expert if routing is balanced
-        result = self._local_experts(recv_rows, local_ids, rows_hint=int(expected + 4 * expected ** 0.5))
+        result = self._local_experts(recv_rows, local_ids, rows_hint=int(expected + 4 * expected ** 0.5),
+                                     layouts=self._step_layouts)
         back = torch.empty_like(result)
         dist.all_to_all_single(back, result, group=self.group)
         return back, index
@@ -442,13 +460,24 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         recv_ids = pb.recv.view(torch.int32)[:, r_gu]
         local_ids = recv_ids - self.lo
         expected = max(1, (N * R) // max(1, self.hi - self.lo))
-        result = self._local_experts(pb.recv, local_ids, rows_hint=int(expected + 4 * expected ** 0.5))
+        result = self._local_experts(pb.recv, local_ids, rows_hint=int(expected + 4 * expected ** 0.5),
+                                     layouts=self._step_layouts)
         _native.check(lib.tris_ep_return_peer(result.data_ptr(), pb.recv.data_ptr(), stride, r_gu, self.hidden_size, N,
                                               self.rank, capacity, pb.back_ptrs.data_ptr(), pb.rflag_ptrs.data_ptr(),
                                               stream), "ep_return_peer")
         _native.check(lib.tris_ep_wait(pb.flags[1].data_ptr(), pb.steps[1:].data_ptr(), N, pb.status.data_ptr(), stream),
                       "ep_wait (results)")
         return pb.back, index
+
+    def kernel_status(self, clear: bool = True) -> int:
+        """0, or TRIS_ERR_TIMEOUT (6) if a bounded wait inside a grouped kernel ran out since the last
+        clear (its CTA skipped its stores); reads one device word."""
+        if self._kernel_status is None:
+            return 0
+        word = int(self._kernel_status.item())
+        if clear and word:
+            self._kernel_status.zero_()
+        return word
 
     def exchange_overflowed(self) -> bool:
         """True if any fixed-capacity exchange so far had more rows for a peer than slots

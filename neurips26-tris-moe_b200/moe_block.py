@@ -51,6 +51,7 @@ class TrisSparseMoeBlock(nn.Module):
         self._grouped_payload_cache: dict = {}
         self._layer_view: Optional[TrisMoeLayerView] = None
         self._workspace: Optional[torch.Tensor] = None
+        self._status_word: Optional[torch.Tensor] = None  # status of the kernels forward_streaming launches
 
     # -- loading ---------------------------------------------------------------------------
     def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate: torch.Tensor,
@@ -102,8 +103,41 @@ class TrisSparseMoeBlock(nn.Module):
         if need == 0 and num_tokens > 0:
             raise RuntimeError("trismoe_b200: invalid layer view (workspace size query failed)")
         if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
+            if self._workspace is not None:
+                self.raise_on_kernel_status()  # do not lose a report with the old buffer
             self._workspace = torch.empty((need,), dtype=torch.uint8, device=device)
+            self._workspace[:16].zero_()  # count words and the sticky status word
         return self._workspace
+
+    def last_kernel_status(self, clear: bool = True) -> int:
+        """Status word of every kernel :meth:`forward` launched since the last clear: 0, or 6
+        (``TRIS_ERR_TIMEOUT``) when a bounded device-side wait ran out and a CTA skipped its stores.
+        Synchronises the current stream; call it where the host waits for the GPU anyway (end of a
+        decode step, before results are handed on)."""
+        streamed = 0
+        if self._status_word is not None:
+            streamed = int(self._status_word.item())
+            if clear and streamed:
+                self._status_word.zero_()
+        if self._workspace is None:
+            return streamed
+        lib = _native.load()
+        dev = self._workspace.device
+        word = C.c_int32(0)
+        with torch.cuda.device(dev):
+            _native.check(lib.tris_moe_layer_last_status(self._workspace.data_ptr(), int(bool(clear)),
+                                                         torch.cuda.current_stream(dev).cuda_stream, C.byref(word)),
+                          "moe_layer_last_status")
+        return int(word.value) or streamed
+
+    def raise_on_kernel_status(self) -> None:
+        """Raises ``RuntimeError`` if a kernel reported a time-out since the last check (the outputs
+        of those calls are not trustworthy); the reference surfaces kernel failures as exceptions too."""
+        status = self.last_kernel_status(clear=True)
+        if status != 0:
+            raise RuntimeError(f"trismoe_b200: a grouped kernel reported {_native.STATUS_NAMES.get(status, status)} "
+                               "(TRIS_ERR_TIMEOUT: a bounded wait on a copy ran out; TRIS_ERR_WORKSPACE: a streamed batch activated "
+                               "more experts than the staging manager has slots for; output rows of that launch are stale)")
 
     # -- forward ---------------------------------------------------------------------------
     def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
@@ -186,7 +220,9 @@ class TrisSparseMoeBlock(nn.Module):
             rv = _native.TrisRouteView()
             rv.expert_ids, rv.segment_offsets, rv.num_segments_dev = ids.data_ptr(), seg.data_ptr(), counts.data_ptr()
             rv.num_segments, rv.num_rows, rv.max_rows_per_segment = min(E, R), R, T
-            rv.row_gather, rv.status_dev, rv.flags = tok.data_ptr(), None, (1 if mode_gu else 0)
+            if self._status_word is None or self._status_word.device != dev:
+                self._status_word = torch.zeros((1,), dtype=torch.int32, device=dev)
+            rv.row_gather, rv.status_dev, rv.flags = tok.data_ptr(), self._status_word.data_ptr(), (1 if mode_gu else 0)
             paged.wait()
             mlp = torch.empty((R, I), dtype=f16, device=dev)
             _native.check(lib.tris_grouped_pair_forward(C.byref(paged.views["gate"]), C.byref(paged.views["up"]), C.byref(rv),

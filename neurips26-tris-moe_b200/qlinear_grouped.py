@@ -27,6 +27,8 @@ from .formats import stack_expert_payloads
 TRIS_COMPACT3_KERNEL_ABI_VERSION = 2
 GROUPED_SEGMENT_M_TILE = 4
 DEFAULT_GR_SUBSTREAMS = 32
+# column orders of activation rows (TRIS_OUT_F16 / _PAIR_INTERLEAVED / _LANE_ORDER of the C header)
+HIDDEN_ROW_MAJOR, HIDDEN_PAIR_INTERLEAVED, HIDDEN_LANE_ORDER = 0, 2, 3
 
 
 def _stream_ptr(device) -> int:
@@ -39,6 +41,37 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return t.data_ptr()
 
 
+def _payload_flag(payload: dict, key: str, default: bool = False) -> bool:
+    """Boolean payload entry that may be a Python bool or a 0-dim / 1-element tensor, as sidecars
+    store scalars (``_payload_flag``, qlinear_cuda.py:310-316)."""
+    value = payload.get(key, default)
+    if isinstance(value, torch.Tensor):
+        if value.numel() == 0:
+            return default
+        return bool(value.reshape(-1)[0].item())
+    return bool(value)
+
+
+def _payload_has_output_scale(payload: dict) -> bool:
+    """``_payload_has_output_scale`` (qlinear_cuda.py:318-321): the flag when the payload carries one,
+    otherwise derived from the tensor (anything but exact ones is a real scale)."""
+    if "has_output_scale" in payload:
+        return _payload_flag(payload, "has_output_scale", False)
+    scale = payload.get("output_scale")
+    if not isinstance(scale, torch.Tensor) or scale.numel() == 0:
+        return False
+    return not bool(torch.all(scale == 1).item())
+
+
+def _payload_has_bias(payload: dict) -> bool:
+    """The ``has_bias`` flag when present; a payload without the key has a bias exactly when it
+    carries a non-empty bias tensor (build_grouped_precomputed_payload, qlinear_cuda.py:1543-1553)."""
+    if "has_bias" in payload:
+        return _payload_flag(payload, "has_bias", False)
+    bias = payload.get("bias")
+    return isinstance(bias, torch.Tensor) and bias.numel() > 0
+
+
 def _ensure(t: torch.Tensor, dtype, device) -> torch.Tensor:
     if t.dtype != dtype or t.device != device or not t.is_contiguous():
         t = t.to(device=device, dtype=dtype).contiguous()
@@ -48,12 +81,16 @@ def _ensure(t: torch.Tensor, dtype, device) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------
 # payloads
 # ---------------------------------------------------------------------------------------
-def prepare_grouped_payload(payload: dict, device=None, gr_substreams: int = DEFAULT_GR_SUBSTREAMS) -> dict:
+def prepare_grouped_payload(payload: dict, device=None, gr_substreams: int = DEFAULT_GR_SUBSTREAMS,
+                            tile_records: bool = True) -> dict:
     """Moves an E-stacked payload to ``device`` and derives what the kernels need beyond the
     reference tensors: the per-packed-row group table (validating ``g_idx`` as
     ``prepare_compact3_k64_groups`` does, qlinear_cuda.py:364-407) and, for block-GR
-    payloads, the sub-stream index (validating offsets/meta).  Runs once at load time and
-    synchronises to read the validation status.  Idempotent."""
+    payloads, the sub-stream index (validating offsets/meta) and the tile-major records the
+    grouped kernels read (one contiguous piece per expert, 64 outputs and 256 columns, so a
+    tile arrives with one bulk copy; ``tile_records=False`` skips them and the kernels gather
+    the tile from the E-stacked tensors).  Runs once at load time and synchronises to read the
+    validation status.  Idempotent."""
     if payload.get("_tris_prepared") and (device is None or payload["qweight1"].device == torch.device(device)):
         return payload
     lib = _native.load()
@@ -89,7 +126,7 @@ def prepare_grouped_payload(payload: dict, device=None, gr_substreams: int = DEF
         )
         payload["_tris_packed_row_group"] = groups
         payload["_tris_dims"] = (E, O, rank, G)
-        use_gr = bool(payload.get("compact3_use_block_gr", False)) and payload["q_gmap_gr_offsets"].numel() > 0
+        use_gr = _payload_flag(payload, "compact3_use_block_gr", False) and payload["q_gmap_gr_offsets"].numel() > 0
         payload["_tris_gr_index"] = None
         payload["_tris_gr_substreams"] = 0
         if use_gr:
@@ -105,18 +142,45 @@ def prepare_grouped_payload(payload: dict, device=None, gr_substreams: int = DEF
             )
             payload["_tris_gr_index"] = index
     st = status.cpu().tolist()
+    for key in ("_tris_tile_records", "_tris_tile_desc", "_tris_col_records"):
+        payload[key] = None
+    payload["_tris_tile_meta"] = (0, 0, 0)
     if st[0] != 0:
         raise RuntimeError("trismoe_b200: g_idx is not constant inside every 32-column word (unsupported layout)")
     if st[1] != 0:
         raise RuntimeError("trismoe_b200: corrupt block-GR stream (offsets/meta/bit stream failed validation)")
+    if use_gr and tile_records and int(gr_substreams) == 32:
+        _build_tile_records(payload, lib, dev)
     payload["_tris_prepared"] = True
     payload["_tris_view"] = _build_view(payload, need_index=True)
     return payload
 
 
+def _build_tile_records(payload: dict, lib, dev) -> None:
+    """Plans and fills the tile-major records of a block-GR payload (``tris_tile_records_plan`` /
+    ``tris_tile_records_build``) into tensors kept in the payload dict."""
+    view = _build_view(payload, need_index=True)
+    stream = _stream_ptr(dev)
+    with torch.cuda.device(dev):
+        count = int(lib.tris_tile_record_count(C.byref(view)))
+        desc = torch.empty((count + 1, 2), dtype=torch.int32, device=dev)
+        info = torch.zeros((4,), dtype=torch.int64, device=dev)
+        _native.check(lib.tris_tile_records_plan(C.byref(view), desc.data_ptr(), info.data_ptr(), stream), "tile_records_plan")
+        total, max_rec, max_sal, _ = (int(v) for v in info.cpu().tolist())
+        col_total = int(lib.tris_col_record_bytes(C.byref(view), max_sal))
+        records = torch.empty((max(total, 16),), dtype=torch.uint8, device=dev)
+        cols = torch.empty((max(col_total, 16),), dtype=torch.uint8, device=dev)
+        _native.check(lib.tris_tile_records_build(C.byref(view), desc.data_ptr(), records.data_ptr(), cols.data_ptr(),
+                                                  max_sal, stream), "tile_records_build")
+    payload["_tris_tile_records"] = records
+    payload["_tris_tile_desc"] = desc
+    payload["_tris_col_records"] = cols
+    payload["_tris_tile_meta"] = (64 + 1024 + 256 * max_sal, max_rec, max_sal)
+
+
 def _build_view(payload: dict, need_index: bool) -> TrisProjView:
     E, O, rank, G = payload["_tris_dims"]
-    use_gr = bool(payload.get("compact3_use_block_gr", False)) and payload["q_gmap_gr_offsets"].numel() > 0
+    use_gr = _payload_flag(payload, "compact3_use_block_gr", False) and payload["q_gmap_gr_offsets"].numel() > 0
     v = TrisProjView()
     v.num_experts, v.out_features, v.rank, v.num_groups = E, O, rank, G
     v.sign2_rows = int(payload["qweight2_sparse"].shape[1]) if payload["qweight2_sparse"].dim() == 3 else 0
@@ -136,15 +200,34 @@ def _build_view(payload: dict, need_index: bool) -> TrisProjView:
     v.g_idx = _ptr(payload["g_idx"])
     v.col_pack3 = _ptr(payload["col_pack3"])
     v.row_pack3 = _ptr(payload["row_pack3"])
-    has_scale = bool(payload.get("has_output_scale", False))
-    v.output_scale = _ptr(payload.get("output_scale")) if has_scale else None
-    v.bias = _ptr(payload.get("bias")) if payload.get("has_bias", False) else None
+    v.output_scale = _ptr(payload.get("output_scale")) if _payload_has_output_scale(payload) else None
+    v.bias = _ptr(payload.get("bias")) if _payload_has_bias(payload) else None
     v.gr_index = _ptr(payload.get("_tris_gr_index")) if need_index else None
     v.gr_substreams = int(payload.get("_tris_gr_substreams", 0))
     v.packed_row_group = _ptr(payload["_tris_packed_row_group"])
     slot = payload.get("_tris_gmap_slot")
     v.gmap_slot = _ptr(slot) if isinstance(slot, torch.Tensor) else None
+    if need_index and isinstance(payload.get("_tris_tile_records"), torch.Tensor):
+        v.tile_records = payload["_tris_tile_records"].data_ptr()
+        v.tile_desc = payload["_tris_tile_desc"].data_ptr()
+        v.col_records = payload["_tris_col_records"].data_ptr()
+        v.col_record_bytes, v.max_record_bytes, v.max_sal_words = payload["_tris_tile_meta"]
     return v
+
+
+def grouped_hidden_layout(payload_a: dict, payload_b: Optional[dict], num_rows: int, num_segments: int,
+                          max_rows_per_segment: int) -> int:
+    """Column order (``HIDDEN_*``) in which the grouped operators read activation rows fastest for
+    these payloads and a route of that size (``tris_grouped_hidden_layout``): pass it to
+    ``compute_shared_hidden(..., layout=...)`` and as ``route["_hidden_layout"]``."""
+    lib = _native.load()
+    va = proj_view(payload_a)
+    vb = proj_view(payload_b) if payload_b is not None else None
+    return int(lib.tris_grouped_hidden_layout(C.byref(va), None if vb is None else C.byref(vb), int(num_rows),
+                                              int(num_segments), int(max_rows_per_segment)))
+
+
+HIDDEN_LAYOUT_ROUTE_FLAG = {0: 0, 2: 1, 3: 2}  # HIDDEN_* -> TRIS_ROUTE_HIDDEN_* bit
 
 
 def proj_view(payload: dict) -> TrisProjView:
@@ -297,6 +380,17 @@ def _route_view(route: dict, num_rows: int, keep: list) -> TrisRouteView:
     rv.row_gather = None
     rv.status_dev = None
     rv.flags = 0
+    # extensions of the route dict (no reference counterpart): "_row_gather" [R] int32 makes grouped
+    # row i read activation row gather[i] (so the caller need not index_select the backbone output),
+    # "_hidden_layout" names the column order of the activation rows (HIDDEN_ROW_MAJOR by default;
+    # HIDDEN_LANE_ORDER / HIDDEN_PAIR_INTERLEAVED = what compute_shared_hidden(..., layout=...) wrote)
+    gather = route.get("_row_gather")
+    if isinstance(gather, torch.Tensor):
+        if gather.dtype != torch.int32 or not gather.is_contiguous():
+            gather = gather.to(torch.int32).contiguous()
+        keep.append(gather)
+        rv.row_gather = gather.data_ptr()
+    rv.flags = HIDDEN_LAYOUT_ROUTE_FLAG[int(route.get("_hidden_layout", HIDDEN_ROW_MAJOR))]
     # extension of the route dict (no reference counterpart): "_out_row_scatter" [R] int32 sends the
     # result of grouped row i to output row scatter[i] (a negative entry drops it)
     scatter = route.get("_out_row_scatter")
@@ -347,7 +441,7 @@ def run_grouped_structured_expert_forward(
     if route is None:
         return None
     tok = route.get("grouped_token_indices")
-    if tok is not None and tok.numel() not in (0, hidden_grouped.size(0)):
+    if tok is not None and tok.numel() not in (0, hidden_grouped.size(0)) and route.get("_row_gather") is None:
         return None
     payload = payload_or_modules if isinstance(payload_or_modules, dict) else build_grouped_precomputed_payload(
         payload_or_modules, hidden_grouped.device, hidden_grouped.dtype)
@@ -361,7 +455,7 @@ def run_grouped_structured_expert_forward(
     if hidden_grouped.size(1) != rank:
         return None
     hidden = hidden_grouped.contiguous()
-    R = int(hidden.size(0))
+    R = int(route["_row_gather"].numel()) if isinstance(route.get("_row_gather"), torch.Tensor) else int(hidden.size(0))
     out = torch.empty((R, O), dtype=torch.float16, device=hidden.device)
     if R == 0:
         return out
@@ -415,7 +509,7 @@ def run_grouped_structured_expert_pair_forward(
     if hidden_grouped_a.size(1) != rank:
         return None, None
     ha, hb = hidden_grouped_a.contiguous(), hidden_grouped_b.contiguous()
-    R = int(ha.size(0))
+    R = int(route["_row_gather"].numel()) if isinstance(route.get("_row_gather"), torch.Tensor) else int(ha.size(0))
     out_a = torch.empty((R, O), dtype=torch.float16, device=dev)
     out_b = None if fuse_silu_mul else torch.empty((R, O), dtype=torch.float16, device=dev)
     if R == 0:
@@ -435,9 +529,12 @@ def run_grouped_structured_expert_pair_forward(
 # ---------------------------------------------------------------------------------------
 # backbone
 # ---------------------------------------------------------------------------------------
-def compute_shared_hidden(x: torch.Tensor, shared_sv: torch.Tensor) -> torch.Tensor:
+def compute_shared_hidden(x: torch.Tensor, shared_sv: torch.Tensor, layout: int = HIDDEN_ROW_MAJOR) -> torch.Tensor:
     """``hidden = x @ shared_sv.T`` in fp16 with fp32 accumulation
-    (``QuantLinear.compute_shared_hidden`` fp16 branch, qlinear_cuda.py:4454-4502)."""
+    (``QuantLinear.compute_shared_hidden`` fp16 branch, qlinear_cuda.py:4454-4502).  ``layout``
+    (an addition) picks the column order of the result: row-major like the reference, or one of
+    the permuted orders the grouped kernels consume without re-ordering (pass the same value as
+    ``route["_hidden_layout"]``)."""
     _native.require_cuda(x, "compute_shared_hidden")
     if x.dtype != torch.float16 or shared_sv.dtype != torch.float16:
         raise RuntimeError("trismoe_b200 compute_shared_hidden: fp16 activations and backbone required")
@@ -452,7 +549,7 @@ def compute_shared_hidden(x: torch.Tensor, shared_sv: torch.Tensor) -> torch.Ten
         with torch.cuda.device(x.device):
             _native.check(
                 lib.tris_shared_hidden_forward(x2.data_ptr(), None, int(x2.shape[0]), None, in_features, sv.data_ptr(), rank,
-                                               out.data_ptr(), 0, _stream_ptr(x.device)),
+                                               out.data_ptr(), int(layout), _stream_ptr(x.device)),
                 "shared_hidden_forward",
             )
     return out.reshape(x.shape[:-1] + (rank,))

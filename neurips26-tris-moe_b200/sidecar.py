@@ -16,6 +16,7 @@ from typing import Dict, Optional
 import torch
 
 GROUPED_PAYLOAD_SIDECAR_BASENAME = "grouped_runtime_payload.safetensors"
+GROUPED_PAYLOAD_METADATA = {"format": "olmoe_grouped_runtime_payload_v1"}  # standalone sidecar (grouped_payload_sidecar.py:20)
 GROUPED_PAYLOAD_EMBEDDED_METADATA_KEY = "olmoe_grouped_runtime_payload"
 GROUPED_PAYLOAD_DEPLOYMENT_ONLY_METADATA_KEY = "olmoe_deployment_only"
 GROUPED_PRECOMPUTED_KEYS = ("gate", "up", "down")
@@ -64,8 +65,12 @@ def _encode(name: str, value) -> Optional[torch.Tensor]:
     return None  # not part of the on-disk format (derived indexes, python lists)
 
 
-def save_grouped_payloads_to_sidecar(path: str, layers: Dict[str, Dict[str, dict]], metadata: Optional[dict] = None) -> int:
-    """Writes ``{layer_prefix: {cache_key: payload}}``; returns the number of tensors."""
+def save_grouped_payloads_to_sidecar(path: str, layers: Dict[str, Dict[str, dict]], metadata: Optional[dict] = None,
+                                     embedded: bool = False, deployment_only: bool = False) -> int:
+    """Writes ``{layer_prefix: {cache_key: payload}}``; returns the number of tensors.  Metadata as
+    the reference writes it (grouped_payload_sidecar.py:438-446, 532-550): a standalone sidecar
+    carries ``format = olmoe_grouped_runtime_payload_v1``; a file that also holds the model state
+    (``embedded``) carries ``format = pt`` plus the embedded / deployment-only markers."""
     from safetensors.torch import save_file
 
     tensors = {}
@@ -77,8 +82,14 @@ def save_grouped_payloads_to_sidecar(path: str, layers: Dict[str, Dict[str, dict
                 t = _encode(name, value)
                 if t is not None:
                     tensors[payload_tensor_name(prefix, cache_key, name)] = t
-    meta = {GROUPED_PAYLOAD_EMBEDDED_METADATA_KEY: "v1", GROUPED_PAYLOAD_DEPLOYMENT_ONLY_METADATA_KEY: "v1"}
-    meta.update({k: str(v) for k, v in (metadata or {}).items()})
+    meta = {str(k): str(v) for k, v in (metadata or {}).items()}
+    if embedded:
+        meta["format"] = "pt"
+        meta[GROUPED_PAYLOAD_EMBEDDED_METADATA_KEY] = "v1"
+        if deployment_only:
+            meta[GROUPED_PAYLOAD_DEPLOYMENT_ONLY_METADATA_KEY] = "v1"
+    else:
+        meta.update(GROUPED_PAYLOAD_METADATA)
     save_file(tensors, path, metadata=meta)
     return len(tensors)
 
@@ -89,7 +100,11 @@ def sidecar_has_grouped_payloads(path: str) -> bool:
     if not path or not os.path.exists(path):
         return False
     with safe_open(path, framework="pt", device="cpu") as fh:
-        return (fh.metadata() or {}).get(GROUPED_PAYLOAD_EMBEDDED_METADATA_KEY) == "v1"
+        meta = fh.metadata() or {}
+        if meta.get(GROUPED_PAYLOAD_EMBEDDED_METADATA_KEY) == "v1" or meta.get("format") == GROUPED_PAYLOAD_METADATA["format"]:
+            return True
+        # the reference loader does not look at metadata at all: any payload tensor name counts
+        return any(split_payload_tensor_name(key) is not None for key in fh.keys())
 
 
 def load_grouped_payload_from_sidecar(path: str, prefix: str, cache_key: str, device="cpu",
@@ -120,9 +135,7 @@ def load_grouped_payload_from_sidecar(path: str, prefix: str, cache_key: str, de
             out[name] = bool(t.reshape(-1)[0].item())
         elif name in _INT_SCALARS and t.numel() == 1:
             out[name] = int(t.reshape(-1)[0].item())
-        elif name == "bias" and t.numel() == 0:
-            out[name] = None
-        else:
+        else:  # an absent tensor (None when written) comes back empty, as the reference loader returns it
             out[name] = (t.to(device=device, dtype=dtype) if t.is_floating_point() else t.to(device=device)).contiguous()
     scale = out.get("output_scale")
     if out.get("is_compact3") and isinstance(scale, torch.Tensor) and scale.numel() and bool(torch.all(scale == 0)):

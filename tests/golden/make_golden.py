@@ -11,6 +11,8 @@ Reference code exercised (paths inside the TriS-MoE tree):
                    ExpertSharedMatrix.set_shared_sv, build_grouped_route (torch branch),
                    PackedQuantMatrix4bit.set_quantized / dequantize                 (4-bit backbone)
   modeling_olmoe.py: OlmoeSparseMoeBlock.forward -> _forward_expert_loop  (fp16 CPU layer output)
+  grouped_payload_sidecar.py: save_grouped_payload_sidecar, load_grouped_payload_from_sidecar
+                   (a sidecar file written by the reference and what its own loader returns from it)
 The `import auto_gptq` package init needs `accelerate`, which is absent, so the needed
 sub-packages are registered as empty namespace modules first.
 """
@@ -201,6 +203,36 @@ def case_layer(QL, MO, PU):
     # token index of each grouped row is well defined only as a multiset per segment
     out["ref_route_grouped_token_indices"] = route["grouped_token_indices"].numpy()
     save("moe_layer_small.npz", out)
+    case_sidecar(block)
+
+
+def case_sidecar(block):
+    """The block above written to a standalone sidecar by the reference's own writer, plus what the
+    reference's own loader returns from that file (python scalars and tensors per payload key)."""
+    import auto_gptq.modeling_tris_moe.grouped_payload_sidecar as SC
+
+    model = types.SimpleNamespace(layers=[types.SimpleNamespace(mlp=block)])
+    path = os.path.join(HERE, "ref_sidecar.safetensors")
+    SC.save_grouped_payload_sidecar(model, path)
+    loaded = {}
+    for key in ("gate", "up", "down", "gate_ns", "up_ns", "down_ns"):
+        payload = SC.load_grouped_payload_from_sidecar(path, "model.layers.0.mlp", key, torch.device("cpu"), torch.float16)
+        assert payload is not None, key
+        for name, value in payload.items():
+            if name.startswith("_"):
+                continue
+            if isinstance(value, torch.Tensor):
+                loaded[f"{key}/{name}"] = value.numpy()
+            elif isinstance(value, bool):
+                loaded[f"{key}/{name}@bool"] = np.array([value])
+            elif isinstance(value, int):
+                loaded[f"{key}/{name}@int"] = np.array([value], np.int64)
+            elif value is None:
+                loaded[f"{key}/{name}@none"] = np.zeros(0, np.int8)
+            else:
+                raise TypeError((key, name, type(value)))
+    save("ref_sidecar_loaded.npz", loaded)
+    print(f"  ref_sidecar.safetensors: {os.path.getsize(path) / 1024:.1f} KiB")
 
 
 def case_backbone4(QL):

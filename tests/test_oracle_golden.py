@@ -161,3 +161,50 @@ def test_packed4_backbone_matches_reference_dequantize():
         w = orc.dequantize_packed4(z[f"{tag}_qweight"], z[f"{tag}_qzeros"], z[f"{tag}_scales"], z[f"{tag}_g_idx"], rows, cols)
         assert w.shape == (rows, cols)
         assert np.array_equal(w.view(np.uint16), z[f"{tag}_weight_f16"].view(np.uint16)), tag
+
+
+# ---------------------------------------------------------------------------------------
+# the timed CPU reference arm (oracle/cpu_reference_path.py) pinned to the same fixtures
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["proj_ragged.npz", "proj_r256.npz"])
+def test_cpu_reference_port_dequant_bit_exact_vs_reference(lib, name):
+    """The torch-CPU port that bench.py times reproduces the reference's
+    _dequantize_compact3_matrix weights bit for bit (modulo the sign of zero)."""
+    import cpu_reference_path as cpu
+    import trismoe_b200 as tm
+
+    z = load_golden(name)
+    E, O, r, _ = (int(v) for v in z["dims"])
+    stacked = tm.stack_expert_payloads([golden_expert_payload(z, f"ref{e}") for e in range(E)], use_block_gr=False)
+    for e in range(E):
+        w = cpu.dequantize_expert(stacked, e).numpy()
+        assert w.shape == (O, r)
+        assert np.array_equal(orc.canonical_half_bits(w), orc.canonical_half_bits(z[f"ref{e}_weight_f16"])), e
+
+
+def test_cpu_reference_port_block_matches_reference_block(lib):
+    """...and its MoE block reproduces the output of the reference's own OlmoeSparseMoeBlock
+    on CPU (moe_layer_small.npz: ref_y_f16), same routing, fp16 round-off apart."""
+    import cpu_reference_path as cpu
+    import trismoe_b200 as tm
+
+    z = load_golden("moe_layer_small.npz")
+    E, k, H, I, r, group, T = (int(v) for v in z["dims"])
+    layer = {}
+    for name in ("gate", "up", "down"):
+        layer[name] = tm.stack_expert_payloads([golden_expert_payload(z, f"{name}{e}") for e in range(E)], use_block_gr=False)
+        layer["shared_" + name] = torch.from_numpy(z["shared_" + name].copy())
+    layer["router_weight"] = torch.from_numpy(z["router_weight"].copy())
+    x = torch.from_numpy(z["x"].copy())
+    y = cpu.moe_block_forward(x, layer, k, True).numpy()
+    ref = z["ref_y_f16"]
+    assert y.shape == ref.shape and np.abs(ref.astype(np.float32)).mean() > 1e-3
+    # same tensor-op sequence as the reference: equal up to the accumulation order of index_add_ / F.linear
+    max_abs, mean_rel = orc.error_metrics(y, ref)
+    assert max_abs <= 4e-3 and mean_rel <= 1e-3, (max_abs, mean_rel)
+    # the fp32 oracle sees both at the same distance
+    logits = z["ref_router_logits_f16"].astype(np.float32)
+    _, _, weights, shared = _layer_from_golden(z)
+    y32 = orc.moe_layer_fp32(z["x"], logits, weights, shared, k, True)
+    max_abs, mean_rel = orc.error_metrics(y, y32)
+    assert max_abs <= 2e-2 and mean_rel <= 5e-3, (max_abs, mean_rel)

@@ -13,12 +13,9 @@ import numpy as np
 import pytest
 import torch
 
-import trismoe_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
-MAX_ABS = 2e-2
-MEAN_REL = 1e-3
 
 
 def _make_block(tm):
@@ -64,8 +61,9 @@ def test_static_scratch_entry_matches_workspace_entry(lib):
         got = _call(lib, tm, blk, x, logits, static=True)
         assert torch.isfinite(got.float()).all()
         assert want.float().abs().mean().item() > 1e-4
-        max_abs, mean_rel = orc.error_metrics(got.float().cpu().numpy(), want.float().cpu().numpy())
-        assert max_abs <= MAX_ABS and mean_rel <= MEAN_REL, (call, max_abs, mean_rel)
+        # Both entries run the identical launch sequence, so the outputs must be bit-identical: a
+        # read of stale scratch from the previous call could otherwise hide inside a tolerance.
+        assert torch.equal(got, want), call
 
 
 def test_static_scratch_entry_rejects_oversized_batches(lib):
