@@ -48,7 +48,32 @@ FALLBACK_HBM_GBS = 6650.0
 LAUNCHES_PER_LAYER = 7  # backbone+router GEMM, top-k, route, gate/up, down backbone, down, combine
 
 
-NCU_DRAM_BYTES_PER_LAUNCH = {"pair": 11729920, "down": 10625024}  # batch 128, 64 active experts
+KERNEL_SOURCES = ("grouped_tiled.cu", "tile_records.cuh", "tile_records.cu")  # what the dominant kernel is built from
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "grouped_tiled_traffic.json")
+
+
+def kernel_source_hash():
+    import hashlib
+
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, "neurips26-tris-moe_b200", "csrc", name), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
+def measured_traffic(kernel):
+    """DRAM bytes per launch of the grouped kernels from the last ncu capture, recorded in
+    profiles/grouped_tiled_traffic.json together with a hash of the kernel sources it was taken
+    on; None once the sources have changed since (a stale figure is worse than none)."""
+    try:
+        with open(TRAFFIC_FILE) as fh:
+            rec = json.load(fh)
+    except Exception:
+        return None, "no capture on record"
+    if rec.get("source_hash") != kernel_source_hash():
+        return None, f"capture {rec.get('source_hash')} is older than the kernel sources"
+    return rec.get("dram_bytes_per_launch", {}).get(kernel), rec.get("command", "ncu capture, see profiles/")
 
 
 def measured_hbm_peak():
@@ -88,17 +113,24 @@ def layer_algorithmic_bytes(info, active_experts, tokens):
     return per_proj, sum(per_proj.values()) + backbone + router + act
 
 
-def time_replays(graph, steps, warmup):
+REPEATS = 5
+
+
+def time_replays(graph, steps, warmup, repeats=REPEATS):
+    """Median over `repeats` timings of `steps` back-to-back replays (CUDA events), ms per step."""
     for _ in range(warmup):
         graph.replay()
     torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        graph.replay()
-    stop.record()
-    torch.cuda.synchronize()
-    return start.elapsed_time(stop) / steps
+    samples = []
+    for _ in range(repeats):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        samples.append(start.elapsed_time(stop) / steps)
+    return statistics.median(samples)
 
 
 def capture(fn, error_mode="global"):
@@ -216,12 +248,12 @@ def run_ours(args):
         del graph
     dom = max(kern, key=lambda n: kern[n]["us_per_launch"])
     roofline = {
-        "bound": "hbm", "kernel": f"grouped_compact3_kernel ({'gate/up dual + SiLU*mul' if dom == 'pair' else 'down'})",
+        "bound": "hbm", "kernel": f"grouped_tiled_persistent_kernel ({'gate/up dual + SiLU*mul' if dom == 'pair' else 'down'})",
         "achieved": round(kern[dom]["gbs"], 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
         "frac": round(kern[dom]["gbs"] / peak, 4), "frac_of_nominal_8TBs": round(kern[dom]["gbs"] / NOMINAL_HBM_GBS, 4),
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
-        # ncu capture summarised in profiles/grouped_compact3_olmoe_decode128.md (not measured in this run)
-        "traffic": NCU_DRAM_BYTES_PER_LAUNCH[dom], "traffic_source": "ncu capture, see profiles/",
+        # ncu capture on record (not measured in this run); null when the kernel sources changed since
+        "traffic": measured_traffic(dom)[0], "traffic_source": measured_traffic(dom)[1],
         "us_per_launch": round(kern[dom]["us_per_launch"], 2),
         "algorithmic_bytes_per_launch": int(kern[dom]["bytes_per_launch"]),
         "other_kernels": {n: {k: round(v, 2) for k, v in d.items()} for n, d in kern.items() if n != dom},
@@ -264,7 +296,8 @@ def run_ours(args):
                    "parallelism": "single GPU"},
         "e2e": {"value": round(T / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": T * 2048 * 2,
                 "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},
-        "gpu_launches": args.steps * LAYERS * LAUNCHES_PER_LAYER,
+        "gpu_launches": args.steps * REPEATS * LAYERS * LAUNCHES_PER_LAYER,
+        "timing": f"median of {REPEATS} repeats of {args.steps} graph replays (CUDA events)",
         "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
         "sweep": {str(t): {k: round(v, 3) for k, v in r.items()} for t, r in results.items()},
         "l2_resident": {"tokens": T, "us_per_layer": round(l2_resident_us, 3),

@@ -33,7 +33,7 @@ from .qlinear_grouped import (  # noqa: F401
     run_grouped_structured_expert_pair_forward,
 )
 from .moe_block import TrisSparseMoeBlock  # noqa: F401
-from . import clocks, expert_parallel, synth  # noqa: F401
+from . import clocks, envflags, expert_parallel, synth  # noqa: F401
 
 __all__ = [
     "HIDDEN_LANE_ORDER",

@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 from torch import nn
 
-from . import _native
+from . import _native, envflags
 from ._native import TrisMoeLayerView
 from .qlinear_grouped import (
     build_grouped_route,
@@ -145,6 +145,8 @@ class TrisSparseMoeBlock(nn.Module):
         ``OlmoeSparseMoeBlock.forward`` (modeling_olmoe.py:1046-1105).  ``router_logits``
         (fp32 ``[T, E]``) may be passed in to skip the router linear."""
         _native.require_cuda(hidden_states, "TrisSparseMoeBlock.forward")
+        if not envflags.grouped_experts_enabled():  # TRIS_GROUPED_EXPERTS=0: operator by operator
+            return self.forward_grouped_ops(hidden_states, router_logits)
         if hidden_states.dtype != torch.float16:
             raise RuntimeError(f"trismoe_b200: grouped expert kernels require float16 hidden states, got {hidden_states.dtype}")
         lib = _native.load()

@@ -20,7 +20,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from . import _native
+from . import _native, envflags
 from ._native import TrisProjView, TrisRouteView
 from .formats import stack_expert_payloads
 
@@ -70,6 +70,19 @@ def _payload_has_bias(payload: dict) -> bool:
         return _payload_flag(payload, "has_bias", False)
     bias = payload.get("bias")
     return isinstance(bias, torch.Tensor) and bias.numel() > 0
+
+
+def _use_block_gr(payload: dict) -> bool:
+    """Which g_map encoding the kernels read: the block-GR streams when the payload has them and
+    ``TRIS_COMPACT3_BLOCK_GR`` is not switched off (``_compact3_block_gr_enabled``,
+    qlinear_cuda.py:235-240); with the switch off, the sparse planes if the payload still has them."""
+    offsets = payload.get("q_gmap_gr_offsets")
+    has_gr = _payload_flag(payload, "compact3_use_block_gr", False) and isinstance(offsets, torch.Tensor) and offsets.numel() > 0
+    if has_gr and not envflags.compact3_block_gr_enabled():
+        sparse = payload.get("q_gmap_sparse")
+        if isinstance(sparse, torch.Tensor) and sparse.numel() > 0:
+            return False
+    return has_gr
 
 
 def _ensure(t: torch.Tensor, dtype, device) -> torch.Tensor:
@@ -126,7 +139,7 @@ def prepare_grouped_payload(payload: dict, device=None, gr_substreams: int = DEF
         )
         payload["_tris_packed_row_group"] = groups
         payload["_tris_dims"] = (E, O, rank, G)
-        use_gr = _payload_flag(payload, "compact3_use_block_gr", False) and payload["q_gmap_gr_offsets"].numel() > 0
+        use_gr = _use_block_gr(payload)
         payload["_tris_gr_index"] = None
         payload["_tris_gr_substreams"] = 0
         if use_gr:
@@ -180,7 +193,7 @@ def _build_tile_records(payload: dict, lib, dev) -> None:
 
 def _build_view(payload: dict, need_index: bool) -> TrisProjView:
     E, O, rank, G = payload["_tris_dims"]
-    use_gr = _payload_flag(payload, "compact3_use_block_gr", False) and payload["q_gmap_gr_offsets"].numel() > 0
+    use_gr = _use_block_gr(payload)
     v = TrisProjView()
     v.num_experts, v.out_features, v.rank, v.num_groups = E, O, rank, G
     v.sign2_rows = int(payload["qweight2_sparse"].shape[1]) if payload["qweight2_sparse"].dim() == 3 else 0
@@ -432,28 +445,28 @@ def run_grouped_structured_expert_forward(
     null-space compensation, which must be rank 0 here."""
     _native.require_cuda(hidden_grouped, "run_grouped_structured_expert_forward")
     if hidden_grouped.dtype != torch.float16:
-        return None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_forward", "hidden_grouped must be float16")
     if x_grouped is not None and (x_grouped.device != hidden_grouped.device or x_grouped.dtype != hidden_grouped.dtype):
-        return None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_forward", "x_grouped device/dtype mismatch")
     if hidden_grouped.dim() != 2 or (x_grouped is not None and (x_grouped.dim() != 2 or x_grouped.size(0) != hidden_grouped.size(0))):
-        return None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_forward", "hidden_grouped / x_grouped shape mismatch")
     route = _coerce_grouped_route(grouped_route_or_segment_lengths, hidden_grouped.device, expert_ids=expert_ids)
     if route is None:
-        return None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_forward", "invalid route or segment lengths")
     tok = route.get("grouped_token_indices")
     if tok is not None and tok.numel() not in (0, hidden_grouped.size(0)) and route.get("_row_gather") is None:
-        return None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_forward", "route size does not match hidden_grouped")
     payload = payload_or_modules if isinstance(payload_or_modules, dict) else build_grouped_precomputed_payload(
         payload_or_modules, hidden_grouped.device, hidden_grouped.dtype)
     if payload is None:
-        return None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_forward", "no grouped payload")
     if not _ns_payload_is_noop(ns_payload):
         raise RuntimeError("trismoe_b200: null-space compensation of rank > 0 is not supported by this build")
     lib = _native.load()
     view = proj_view(payload)
     E, O, rank, _ = payload["_tris_dims"]
     if hidden_grouped.size(1) != rank:
-        return None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_forward", "hidden width does not match the payload rank")
     hidden = hidden_grouped.contiguous()
     R = int(route["_row_gather"].numel()) if isinstance(route.get("_row_gather"), torch.Tensor) else int(hidden.size(0))
     out = torch.empty((R, O), dtype=torch.float16, device=hidden.device)
@@ -488,26 +501,26 @@ def run_grouped_structured_expert_pair_forward(
     returns ``(silu(out_a) * out_b, None)`` computed in fp32 inside the kernel."""
     _native.require_cuda(hidden_grouped_a, "run_grouped_structured_expert_pair_forward")
     if hidden_grouped_a.dtype != torch.float16 or hidden_grouped_b.dtype != torch.float16:
-        return None, None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_pair_forward", "hidden states must be float16"), None
     if hidden_grouped_a.dim() != 2 or hidden_grouped_b.shape != hidden_grouped_a.shape:
-        return None, None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_pair_forward", "hidden_grouped_a / hidden_grouped_b shape mismatch"), None
     if hidden_grouped_b.device != hidden_grouped_a.device:
-        return None, None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_pair_forward", "hidden states on different devices"), None
     route = _coerce_grouped_route(grouped_route_or_segment_lengths, hidden_grouped_a.device, expert_ids=expert_ids)
     if route is None:
-        return None, None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_pair_forward", "invalid route or segment lengths"), None
     dev, dt = hidden_grouped_a.device, hidden_grouped_a.dtype
     pa = payload_or_modules_a if isinstance(payload_or_modules_a, dict) else build_grouped_precomputed_payload(payload_or_modules_a, dev, dt)
     pb = payload_or_modules_b if isinstance(payload_or_modules_b, dict) else build_grouped_precomputed_payload(payload_or_modules_b, dev, dt)
     if pa is None or pb is None:
-        return None, None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_pair_forward", "no grouped payload"), None
     if not (_ns_payload_is_noop(ns_payload_a) and _ns_payload_is_noop(ns_payload_b)):
         raise RuntimeError("trismoe_b200: null-space compensation of rank > 0 is not supported by this build")
     lib = _native.load()
     va, vb = proj_view(pa), proj_view(pb)
     _, O, rank, _ = pa["_tris_dims"]
     if hidden_grouped_a.size(1) != rank:
-        return None, None
+        return envflags.return_or_raise_none("run_grouped_structured_expert_pair_forward", "hidden width does not match the payload rank"), None
     ha, hb = hidden_grouped_a.contiguous(), hidden_grouped_b.contiguous()
     R = int(route["_row_gather"].numel()) if isinstance(route.get("_row_gather"), torch.Tensor) else int(ha.size(0))
     out_a = torch.empty((R, O), dtype=torch.float16, device=dev)

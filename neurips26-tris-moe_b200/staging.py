@@ -71,6 +71,15 @@ class _Entry:
             self.block_bytes[key] = per
 
 
+def staging_requested() -> bool:
+    """True when the host asks for the streaming mode through ``TRIS_GROUPED_QGMAP_CPU_STAGING`` (or
+    the reference's per-family names; ``_grouped_qgmap_cpu_staging_enabled``,
+    grouped_payload_sidecar.py:147-152)."""
+    from . import envflags
+
+    return envflags.grouped_qgmap_cpu_staging_enabled()
+
+
 class GroupedQGmapCPUStagingManager:
     """Pages expert payloads of the registered MoE blocks from pinned host memory."""
 
