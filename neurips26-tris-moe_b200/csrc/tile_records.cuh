@@ -285,8 +285,26 @@ __device__ __forceinline__ void gr_decode_block(const uint8_t* rec, int b, uint3
 }
 
 // ---- register unpack --------------------------------------------------------------------------
-// Masks of one half2: PRMT in sign-replicate mode spreads bit 15 over the low half and bit 31
-// over the high half (selector 0xBB99), or bits 7 / 23 (selector 0xAA88).
+// The integer ALU pipe (PRMT, LOP3, shifts) issues at half the rate of the FMA pipe (IMAD, HMUL2),
+// and the unpack is almost all bit work, so it is written to spread over both:
+//   * the two per-word shifts are multiplications by a per-lane power of two (IMAD);
+//   * the sign needs only bits 15 / 31 of a half2, which the shifted word already holds for the
+//     (t+8, t+24) and (t+12, t+28) pairs; for the other two pairs one more multiplication by 256
+//     moves bits 7 / 23 up.  No mask is built for the sign;
+//   * the g_map select does need half-wide masks: PRMT in sign-replicate mode spreads bit 15 over
+//     the low half and bit 31 over the high half (selector 0xBB99), or bits 7 / 23 (0xAA88).
+struct LaneShifts {
+  uint32_t mul_a, mul_b;  // 1 << (7 - t), 1 << (3 - t)
+};
+__device__ __forceinline__ LaneShifts lane_shifts(int t) {
+  LaneShifts ls;
+  ls.mul_a = 1u << (7 - t);
+  ls.mul_b = 1u << (3 - t);
+  // keep the compiler from turning the multiplications back into (ALU pipe) shifts
+  asm("" : "+r"(ls.mul_a));
+  asm("" : "+r"(ls.mul_b));
+  return ls;
+}
 __device__ __forceinline__ uint32_t mask_hi(uint32_t w) { return prmt(w, 0u, 0xBB99u); }
 __device__ __forceinline__ uint32_t mask_lo(uint32_t w) { return prmt(w, 0u, 0xAA88u); }
 
@@ -295,8 +313,8 @@ __device__ __forceinline__ uint32_t lop3_select(uint32_t a, uint32_t b, uint32_t
   asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(d) : "r"(m), "r"(a), "r"(b));  // m ? a : b
   return d;
 }
-// v ^ (~ms & 0x80008000): plane bit 1 -> +, 0 -> - (QL:4213)
-__device__ __forceinline__ uint32_t apply_sign(uint32_t v, uint32_t ms) { return v ^ (~ms & 0x80008000u); }
+// v ^ (~w & 0x80008000): sign-plane bit (at 15 / 31 of w) 1 -> +, 0 -> - (QL:4213)
+__device__ __forceinline__ uint32_t flip_by_bits(uint32_t v, uint32_t w) { return v ^ (~w & 0x80008000u); }
 
 // Non-salient weights of one packed row for one output: the lane's four column pairs as half2
 // bit patterns a[0..3] (pair order of lane_pair_col).  Exact arithmetic of
@@ -304,18 +322,20 @@ __device__ __forceinline__ uint32_t apply_sign(uint32_t v, uint32_t ms) { return
 // ct = {cd(0), cn(0), cd(1), cn(1)}, {cd(2), cn(2), cd(3), cn(3)}: column scales of the d / nd
 // kinds per pair, zero at salient columns.
 __device__ __forceinline__ void unpack_row_ns(uint32_t s1, uint32_t gm, __half2 rd, __half2 rn, const uint4& c01,
-                                              const uint4& c23, int t, uint32_t (&a)[4]) {
-  const uint32_t sA = s1 << (7 - t), sB = s1 << (3 - t);
-  const uint32_t gA = gm << (7 - t), gB = gm << (3 - t);
+                                              const uint4& c23, const LaneShifts& ls, uint32_t (&a)[4]) {
+  const uint32_t sA = s1 * ls.mul_a, sB = s1 * ls.mul_b;
+  const uint32_t gA = gm * ls.mul_a, gB = gm * ls.mul_b;
   const uint32_t cd[4] = {c01.x, c01.z, c23.x, c23.z};
   const uint32_t cn[4] = {c01.y, c01.w, c23.y, c23.w};
-  const uint32_t ms[4] = {mask_hi(sA), mask_lo(sA), mask_hi(sB), mask_lo(sB)};
+  uint32_t up8 = 256u;
+  asm("" : "+r"(up8));
+  const uint32_t sg[4] = {sA, sA * up8, sB, sB * up8};
   const uint32_t mg[4] = {mask_hi(gA), mask_lo(gA), mask_hi(gB), mask_lo(gB)};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const uint32_t vd = h2_as_u32(__hmul2_rn(u32_as_h2(cd[i]), rd));
     const uint32_t vn = h2_as_u32(__hmul2_rn(u32_as_h2(cn[i]), rn));
-    a[i] = apply_sign(lop3_select(vd, vn, mg[i]), ms[i]);  // g_map bit 1 -> "d" pair (CU:736-737)
+    a[i] = flip_by_bits(lop3_select(vd, vn, mg[i]), sg[i]);  // g_map bit 1 -> "d" pair (CU:736-737)
   }
 }
 
@@ -323,17 +343,19 @@ __device__ __forceinline__ void unpack_row_ns(uint32_t s1, uint32_t gm, __half2 
 // sc = {c1(0), c2(0), c1(1), c2(1)}, {c1(2), c2(2), c1(3), c2(3)}; r1 / r2 hold the row scales
 // of the word's two halves (slots 0-15 in the low half, 16-31 in the high half).
 __device__ __forceinline__ void unpack_row_sal(uint32_t w1, uint32_t w2, __half2 r1, __half2 r2, const uint4& c01,
-                                               const uint4& c23, int t, uint32_t (&a)[4]) {
-  const uint32_t s1A = w1 << (7 - t), s1B = w1 << (3 - t);
-  const uint32_t s2A = w2 << (7 - t), s2B = w2 << (3 - t);
+                                               const uint4& c23, const LaneShifts& ls, uint32_t (&a)[4]) {
+  const uint32_t s1A = w1 * ls.mul_a, s1B = w1 * ls.mul_b;
+  const uint32_t s2A = w2 * ls.mul_a, s2B = w2 * ls.mul_b;
   const uint32_t c1[4] = {c01.x, c01.z, c23.x, c23.z};
   const uint32_t c2[4] = {c01.y, c01.w, c23.y, c23.w};
-  const uint32_t m1[4] = {mask_hi(s1A), mask_lo(s1A), mask_hi(s1B), mask_lo(s1B)};
-  const uint32_t m2[4] = {mask_hi(s2A), mask_lo(s2A), mask_hi(s2B), mask_lo(s2B)};
+  uint32_t up8 = 256u;
+  asm("" : "+r"(up8));
+  const uint32_t g1[4] = {s1A, s1A * up8, s1B, s1B * up8};
+  const uint32_t g2[4] = {s2A, s2A * up8, s2B, s2B * up8};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const uint32_t p1 = apply_sign(h2_as_u32(__hmul2_rn(u32_as_h2(c1[i]), r1)), m1[i]);
-    const uint32_t p2 = apply_sign(h2_as_u32(__hmul2_rn(u32_as_h2(c2[i]), r2)), m2[i]);
+    const uint32_t p1 = flip_by_bits(h2_as_u32(__hmul2_rn(u32_as_h2(c1[i]), r1)), g1[i]);
+    const uint32_t p2 = flip_by_bits(h2_as_u32(__hmul2_rn(u32_as_h2(c2[i]), r2)), g2[i]);
     a[i] = h2_as_u32(__hadd2_rn(u32_as_h2(p1), u32_as_h2(p2)));
   }
 }
@@ -373,12 +395,13 @@ __device__ __forceinline__ RowScalesNs load_row_scales_ns(const StagedTile& st, 
 __device__ __forceinline__ void unpack_fragments_ns(const StagedTile& st, int p, int out_local, int lane,
                                                     const RowScalesNs& rs, uint32_t (&a)[2][4]) {
   const int g = lane >> 2, t = lane & 3;
+  const LaneShifts ls = lane_shifts(t);
   const uint4* ct = reinterpret_cast<const uint4*>(st.col + kColHdrBytes) + (p * 4 + t) * 2;
   const uint4 c01 = ct[0], c23 = ct[1];
   const uint32_t* s1 = reinterpret_cast<const uint32_t*>(st.rec + kHdrBytes) + p * kTileOut + out_local + g;
   const uint32_t* gm = st.gmap + p * kTileOut + out_local + g;
-  unpack_row_ns(s1[0], gm[0], rs.rd[0], rs.rn[0], c01, c23, t, a[0]);
-  unpack_row_ns(s1[8], gm[8], rs.rd[1], rs.rn[1], c01, c23, t, a[1]);
+  unpack_row_ns(s1[0], gm[0], rs.rd[0], rs.rn[0], c01, c23, ls, a[0]);
+  unpack_row_ns(s1[8], gm[8], rs.rd[1], rs.rn[1], c01, c23, ls, a[1]);
 }
 
 __device__ __forceinline__ void unpack_fragments_sal(const StagedTile& st, int q, int out_local, int lane,
@@ -395,8 +418,9 @@ __device__ __forceinline__ void unpack_fragments_sal(const StagedTile& st, int q
   const uint4 c01 = sc[0], c23 = sc[1];
   const uint32_t* w1 = reinterpret_cast<const uint32_t*>(st.rec + hdr->off_ss1) + q * kTileOut + out_local + g;
   const uint32_t* w2 = reinterpret_cast<const uint32_t*>(st.rec + hdr->off_ss2) + q * kTileOut + out_local + g;
-  unpack_row_sal(w1[0], w2[0], r1[0], r2[0], c01, c23, t, a[0]);
-  unpack_row_sal(w1[8], w2[8], r1[1], r2[1], c01, c23, t, a[1]);
+  const LaneShifts ls = lane_shifts(t);
+  unpack_row_sal(w1[0], w2[0], r1[0], r2[0], c01, c23, ls, a[0]);
+  unpack_row_sal(w1[8], w2[8], r1[1], r2[1], c01, c23, ls, a[1]);
 }
 
 }  // namespace tr
