@@ -126,6 +126,11 @@ typedef struct TrisRouteView {
                                        grouped row itself); no reference counterpart - lets a
                                        caller get results back in its own row order without a
                                        second pass                                          */
+  const void* hidden_col_scale;     /* optional fp16 [rank]: every activation row is multiplied by it,
+                                       rounded to fp16, while it is staged - the input scale
+                                       vector of an ordinary compact3 linear with ns_mode == 1
+                                       (compact3_linear_forward, has_input_scale, CU:2176-2200).
+                                       Row-major activations and a projection with tile records only */
 } TrisRouteView;
 
 /* Activation rows handed to the grouped kernels are "pair-interleaved": inside every group
@@ -163,6 +168,13 @@ const char* tris_last_error(void);
 int tris_block_gr_encode_host(const int32_t* dense_words, int32_t packed_rows, int32_t out_features,
                               int32_t force_raw, int32_t* words_out, int64_t words_capacity,
                               int32_t* offsets_out, int32_t* meta_out, int64_t* num_words);
+
+/* The same with the Rice parameter searched in [k_min, k_max] only (k_min == k_max fixes it): the
+   --blockgr-k / --blockgr-k-min / --blockgr-k-max options of the reference exporter
+   (pack_block_gr_gmap_tensor(fixed_k, k_min, k_max), RW:252-347; bounds RW:227-250). */
+int tris_block_gr_encode_host_k(const int32_t* dense_words, int32_t packed_rows, int32_t out_features,
+                                int32_t force_raw, int32_t k_min, int32_t k_max, int32_t* words_out,
+                                int64_t words_capacity, int32_t* offsets_out, int32_t* meta_out, int64_t* num_words);
 
 /* Bytes of the derived sub-stream index for a projection. */
 size_t tris_block_gr_index_bytes(int32_t num_experts, int32_t packed_rows, int32_t out_features,

@@ -33,9 +33,17 @@ from .qlinear_grouped import (  # noqa: F401
     run_grouped_structured_expert_pair_forward,
 )
 from .moe_block import TrisSparseMoeBlock  # noqa: F401
+from .compact3_linear import (  # noqa: F401
+    Compact3Linear,
+    run_compact3_gate_up_forward,
+    run_compact3_qkv_forward,
+)
 from . import clocks, envflags, expert_parallel, synth  # noqa: F401
 
 __all__ = [
+    "Compact3Linear",
+    "run_compact3_gate_up_forward",
+    "run_compact3_qkv_forward",
     "HIDDEN_LANE_ORDER",
     "HIDDEN_PAIR_INTERLEAVED",
     "HIDDEN_ROW_MAJOR",

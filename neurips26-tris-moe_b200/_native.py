@@ -47,7 +47,7 @@ class TrisRouteView(C.Structure):
         ("expert_ids", _vp), ("segment_offsets", _vp), ("num_segments_dev", _vp),
         ("num_segments", _i32), ("num_rows", _i32), ("max_rows_per_segment", _i32),
         ("row_gather", _vp), ("status_dev", _vp), ("flags", _i32), ("hidden_row_stride", _i32),
-        ("out_row_scatter", _vp),
+        ("out_row_scatter", _vp), ("hidden_col_scale", _vp),
     ]
 
 
@@ -68,6 +68,7 @@ SIGNATURES = {
     "tris_status_string": (C.c_char_p, [C.c_int]),
     "tris_last_error": (C.c_char_p, []),
     "tris_block_gr_encode_host": (C.c_int, [_vp, _i32, _i32, _i32, _vp, C.c_int64, _vp, _vp, _P(C.c_int64)]),
+    "tris_block_gr_encode_host_k": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, C.c_int64, _vp, _vp, _P(C.c_int64)]),
     "tris_block_gr_index_bytes": (C.c_size_t, [_i32, _i32, _i32, _i32]),
     "tris_block_gr_build_index": (C.c_int, [_P(TrisProjView), _vp, _i32, _vp, _vp]),
     "tris_block_gr_decode": (C.c_int, [_P(TrisProjView), _vp, _vp]),

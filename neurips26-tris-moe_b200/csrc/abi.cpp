@@ -95,8 +95,19 @@ struct BitWriter {
 extern "C" int tris_block_gr_encode_host(const int32_t* dense_words, int32_t packed_rows, int32_t out_features,
                                          int32_t force_raw, int32_t* words_out, int64_t words_capacity,
                                          int32_t* offsets_out, int32_t* meta_out, int64_t* num_words) {
+  return tris_block_gr_encode_host_k(dense_words, packed_rows, out_features, force_raw, 0, TRIS_GR_MAX_K, words_out,
+                                     words_capacity, offsets_out, meta_out, num_words);
+}
+
+extern "C" int tris_block_gr_encode_host_k(const int32_t* dense_words, int32_t packed_rows, int32_t out_features,
+                                           int32_t force_raw, int32_t k_min, int32_t k_max, int32_t* words_out,
+                                           int64_t words_capacity, int32_t* offsets_out, int32_t* meta_out,
+                                           int64_t* num_words) {
   if (!dense_words || !words_out || !offsets_out || !meta_out || !num_words)
     return tris::fail(TRIS_ERR_INVALID_ARG, "tris_block_gr_encode_host: null pointer");
+  if (k_min < 0 || k_max > TRIS_GR_MAX_K || k_min > k_max)
+    return tris::fail(TRIS_ERR_INVALID_ARG, "tris_block_gr_encode_host: k range [%d, %d] outside [0, %d]", k_min, k_max,
+                      TRIS_GR_MAX_K);
   if (packed_rows < 0 || out_features < 0)
     return tris::fail(TRIS_ERR_INVALID_ARG, "tris_block_gr_encode_host: negative dims");
   const int nkb = (packed_rows + TRIS_GR_BLOCK_PACKED_ROWS - 1) / TRIS_GR_BLOCK_PACKED_ROWS;
@@ -132,7 +143,7 @@ extern "C" int tris_block_gr_encode_host(const int32_t* dense_words, int32_t pac
       int best_k = 0;
       int64_t best_bits = static_cast<int64_t>(TRIS_GR_BLOCK_WORDS) * 32 + 1;
       bool have = false;
-      for (int k = 0; k <= TRIS_GR_MAX_K; ++k) {
+      for (int k = k_min; k <= k_max; ++k) {
         int64_t bits = 0;
         for (int r : runs) bits += (r >> k) + 1 + k;
         if (bits < best_bits) {

@@ -591,7 +591,10 @@ int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* ro
   const bool lane_order = (route->flags & TRIS_ROUTE_HIDDEN_LANE_ORDER) != 0;
   TRIS_REQUIRE(!lane_order || (proj_has_tile_records(*proj) && !a.hidden_interleaved), TRIS_ERR_INVALID_ARG,
                "tris_grouped_forward: lane-order activations need a projection with tile records");
-  if (proj_has_tile_records(*proj) && !a.hidden_interleaved && (lane_order || rows_hint(route) <= tiled_max_rows()))
+  const bool col_scaled = route->hidden_col_scale != nullptr;
+  TRIS_REQUIRE(!col_scaled || (proj_has_tile_records(*proj) && !a.hidden_interleaved && !lane_order), TRIS_ERR_UNSUPPORTED,
+               "tris_grouped_forward: hidden_col_scale needs tile records and row-major activations");
+  if (proj_has_tile_records(*proj) && !a.hidden_interleaved && (lane_order || col_scaled || rows_hint(route) <= tiled_max_rows()))
     return launch_grouped_tiled(proj, nullptr, route, hidden_f16, nullptr, out_f16, nullptr, 0, rows_hint(route), stream, opts);
   TRIS_REQUIRE(!a.hidden_interleaved || proj->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
                "tris_grouped_forward: pair-interleaved activations need rank % 32 == 0");
@@ -649,7 +652,10 @@ int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjVi
   const bool records = proj_has_tile_records(*proj_a) && proj_has_tile_records(*proj_b);
   TRIS_REQUIRE(!lane_order || (records && !a.hidden_interleaved), TRIS_ERR_INVALID_ARG,
                "tris_grouped_pair_forward: lane-order activations need projections with tile records");
-  if (records && !a.hidden_interleaved && (lane_order || rows_hint(route) <= tiled_max_rows()))
+  const bool col_scaled = route->hidden_col_scale != nullptr;
+  TRIS_REQUIRE(!col_scaled || (records && !a.hidden_interleaved && !lane_order), TRIS_ERR_UNSUPPORTED,
+               "tris_grouped_pair_forward: hidden_col_scale needs tile records and row-major activations");
+  if (records && !a.hidden_interleaved && (lane_order || col_scaled || rows_hint(route) <= tiled_max_rows()))
     return launch_grouped_tiled(proj_a, proj_b, route, hidden_a_f16, hidden_b_f16, out_a_f16, out_b_f16, fuse_silu_mul ? 2 : 1,
                                 rows_hint(route), stream, opts);
   TRIS_REQUIRE(!a.hidden_interleaved || proj_a->rank % 32 == 0, TRIS_ERR_INVALID_ARG,

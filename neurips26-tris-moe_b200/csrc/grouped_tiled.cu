@@ -55,6 +55,7 @@ struct TiledArgs {
   int32_t rec_slot_bytes;       // shared-memory bytes reserved per tile record (16 bytes of slack included)
   int32_t col_slot_bytes;
   int32_t sal_slots;            // salient words reserved per activation set
+  const __half* col_scale;      // optional [rank]: activation rows are multiplied by it while staged (row-major rows only)
 };
 
 // Shared-memory carve-up: [mbarriers 64][stages x (2 records + NH column records)][2 g_map planes]
@@ -115,7 +116,8 @@ __device__ __forceinline__ void issue_record(const TrisProjView& v, int expert, 
 // rows are re-ordered by all threads.  Lane 0 of every warp arrives on `bar`.
 template <int NT, int NH, typename RowSrc>
 __device__ __forceinline__ void issue_hidden(uint8_t* hrows, const __half* const* hidden, int rank, int p0, int nrows,
-                                             bool lane_order, int row_stride, uint64_t* bar, RowSrc row_src) {
+                                             bool lane_order, int row_stride, uint64_t* bar, RowSrc row_src,
+                                             const __half* col_scale = nullptr) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c0 = 32 * p0;
   const int ncols = min(256, rank - c0);
@@ -152,6 +154,11 @@ __device__ __forceinline__ void issue_hidden(uint8_t* hrows, const __half* const
       } else {
         for (int u = 0; u < 8 && col + u < rank; ++u) vals[u] = rowp[u];
       }
+    }
+    if (col_scale && src >= 0) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (col + u < rank) vals[u] = __hmul(vals[u], col_scale[col + u]);
     }
     __half* dst = reinterpret_cast<__half*>(hrows + (set * NT * 8 + n) * kHiddenRowBytes);
 #pragma unroll
@@ -422,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 3) grouped_tiled_kernel(const __grid
         }
         reinterpret_cast<uint4*>(gmap_base)[tid] = make_uint4(0u, 0u, 0u, 0u);  // 256 threads x 16 B = both planes
       }
-      if (waited) issue_hidden<NT, NH>(hrows, args.hidden, rank, p0, rows, lane_order, args.hidden_stride, &mbar[1], row_src);
+      if (waited) issue_hidden<NT, NH>(hrows, args.hidden, rank, p0, rows, lane_order, args.hidden_stride, &mbar[1], row_src, args.col_scale);
       bool ok = true;
       if (need_w) {
         __syncthreads();  // planes zeroed
@@ -435,7 +442,7 @@ __global__ void __launch_bounds__(kThreads, 3) grouped_tiled_kernel(const __grid
         pdl_wait();
         pdl_launch_dependents();
         waited = true;
-        issue_hidden<NT, NH>(hrows, args.hidden, rank, p0, rows, lane_order, args.hidden_stride, &mbar[1], row_src);
+        issue_hidden<NT, NH>(hrows, args.hidden, rank, p0, rows, lane_order, args.hidden_stride, &mbar[1], row_src, args.col_scale);
       }
       ok = mbar_wait_bounded(&mbar[1], par_h) && ok;
       par_h ^= 1u;
@@ -558,7 +565,7 @@ __global__ void __launch_bounds__(kThreads, 3) grouped_tiled_persistent_kernel(c
     int r0 = cur.row_begin;
     int rows = live ? min(NT * 8, cur.row_end - r0) : 0;
     auto row_src = [&](int n) { return args.row_gather ? args.row_gather[r0 + n] : (r0 + n); };
-    if (waited && live) issue_hidden<NT, NH>(hrows, args.hidden, rank, 0, rows, lane_order, args.hidden_stride, &mbar[2], row_src);
+    if (waited && live) issue_hidden<NT, NH>(hrows, args.hidden, rank, 0, rows, lane_order, args.hidden_stride, &mbar[2], row_src, args.col_scale);
     __syncthreads();  // planes zeroed
     bool ok = mbar_wait_bounded(&mbar[stage], (it >> 1) & 1);
     if (ok && live && tile_valid) gr_decode_block(st.rec, og, const_cast<uint32_t*>(st.gmap), lane);
@@ -566,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 3) grouped_tiled_persistent_kernel(c
       pdl_wait();
       pdl_launch_dependents();
       waited = true;
-      if (live) issue_hidden<NT, NH>(hrows, args.hidden, rank, 0, rows, lane_order, args.hidden_stride, &mbar[2], row_src);
+      if (live) issue_hidden<NT, NH>(hrows, args.hidden, rank, 0, rows, lane_order, args.hidden_stride, &mbar[2], row_src, args.col_scale);
     }
     for (; live;) {
       const int nt_count = (rows + 7) >> 3;
@@ -590,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 3) grouped_tiled_persistent_kernel(c
       if (r0 >= cur.row_end) break;
       rows = min(NT * 8, cur.row_end - r0);
       __syncthreads();  // the stores have read the scratch: the activation rows can be refilled
-      issue_hidden<NT, NH>(hrows, args.hidden, rank, 0, rows, lane_order, args.hidden_stride, &mbar[2], row_src);
+      issue_hidden<NT, NH>(hrows, args.hidden, rank, 0, rows, lane_order, args.hidden_stride, &mbar[2], row_src, args.col_scale);
     }
     if (__syncthreads_or(dead || !ok)) {
       if (u + G < total) mbar_wait_bounded(&mbar[stage ^ 1], ((it + 1) >> 1) & 1);  // the prefetch in flight
@@ -792,6 +799,9 @@ int launch_grouped_tiled(const TrisProjView* proj_a, const TrisProjView* proj_b,
   a.rec_slot_bytes = rec_slot_bytes_for(std::max(a.proj[0].max_record_bytes, a.proj[1].max_record_bytes));
   a.col_slot_bytes = std::max(a.proj[0].col_record_bytes, a.proj[1].col_record_bytes);
   a.sal_slots = std::max(1, std::max(a.proj[0].max_sal_words, a.proj[1].max_sal_words));
+  a.col_scale = static_cast<const __half*>(route->hidden_col_scale);
+  TRIS_REQUIRE(a.col_scale == nullptr || !a.hidden_lane_order, TRIS_ERR_INVALID_ARG,
+               "grouped (tile records): hidden_col_scale needs row-major activation rows");
   TRIS_REQUIRE(!a.hidden_lane_order || proj_a->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
                "grouped (tile records): lane-order activations need rank %% 32 == 0");
   TRIS_REQUIRE(a.hidden_stride >= proj_a->rank, TRIS_ERR_INVALID_ARG, "grouped (tile records): hidden_row_stride < rank");

@@ -147,11 +147,13 @@ def build_compact3_packed_payload(
     }
 
 
-def block_gr_encode(dense_words: torch.Tensor, force_raw: bool = False):
+def block_gr_encode(dense_words: torch.Tensor, force_raw: bool = False, k_min: int = 0, k_max: int = 7):
     """Block Golomb-Rice code of a dense packed g_map ``[pr, O]`` int32.
 
     Returns ``(words, offsets, meta)`` int32 CPU tensors exactly as
-    ``QuantLinear._pack_block_gr_gmap_tensor`` (qlinear_cuda.py:3793-3859) would.
+    ``QuantLinear._pack_block_gr_gmap_tensor`` (qlinear_cuda.py:3793-3859) would; ``k_min`` /
+    ``k_max`` bound the per-block search of the Rice parameter as the reference exporter's
+    ``pack_block_gr_gmap_tensor(fixed_k, k_min, k_max)`` does (tools/rewrite_runtime_min_checkpoint.py:252-347).
     """
     dense = dense_words.detach().to("cpu", torch.int32).contiguous()
     if dense.numel() == 0:
@@ -164,8 +166,8 @@ def block_gr_encode(dense_words: torch.Tensor, force_raw: bool = False):
     meta = torch.empty((nblk,), dtype=torch.int32)
     count = C.c_int64(0)
     lib = _native.load()
-    st = lib.tris_block_gr_encode_host(
-        dense.data_ptr(), pr, out, int(bool(force_raw)), words.data_ptr(), words.numel(),
+    st = lib.tris_block_gr_encode_host_k(
+        dense.data_ptr(), pr, out, int(bool(force_raw)), int(k_min), int(k_max), words.data_ptr(), words.numel(),
         offsets.data_ptr(), meta.data_ptr(), C.byref(count),
     )
     _native.check(st, "block_gr_encode")

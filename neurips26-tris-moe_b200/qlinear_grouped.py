@@ -129,6 +129,10 @@ def prepare_grouped_payload(payload: dict, device=None, gr_substreams: int = DEF
     G = int(row_pack.shape[2]) if row_pack.dim() == 3 else 1
     if pr != math.ceil(rank / 32) or tuple(payload["col_pack3"].shape) != (E, rank) or tuple(row_pack.shape[:2]) != (E, O):
         raise RuntimeError("trismoe_b200: inconsistent compact3 payload shapes")
+    if payload.get("_tris_derived_from_checkpoint") and _adopt_stored_derived(payload, dev, E, pr, O, rank, G):
+        payload["_tris_prepared"] = True
+        payload["_tris_view"] = _build_view(payload, need_index=True)
+        return payload
     status = torch.zeros((2,), dtype=i32, device=dev)
     stream = _stream_ptr(dev)
     with torch.cuda.device(dev):
@@ -167,6 +171,36 @@ def prepare_grouped_payload(payload: dict, device=None, gr_substreams: int = DEF
     payload["_tris_prepared"] = True
     payload["_tris_view"] = _build_view(payload, need_index=True)
     return payload
+
+
+def _adopt_stored_derived(payload: dict, dev, E: int, pr: int, O: int, rank: int, G: int) -> bool:
+    """Uses the derived tensors a checkpoint exporter stored next to the payload (sub-stream index,
+    packed-row groups, tile records) instead of rebuilding them; False when their shapes do not fit
+    this payload (then they are dropped and everything is rebuilt and re-validated)."""
+    nblk = math.ceil(pr / 2) * math.ceil(O / 64)
+    count = E * math.ceil(O / 64) * math.ceil(pr / 8)
+    idx, grp, rec, desc, col = (payload.get(k) for k in ("_tris_gr_index", "_tris_packed_row_group", "_tris_tile_records",
+                                                        "_tris_tile_desc", "_tris_col_records"))
+    meta = payload.get("_tris_tile_meta")
+    ok = all(isinstance(t, torch.Tensor) for t in (idx, grp, rec, desc, col)) and isinstance(meta, tuple) and len(meta) == 3
+    ok = ok and tuple(idx.shape) == (E, nblk, 32) and tuple(grp.shape) == (E, pr) and tuple(desc.shape) == (count + 1, 2)
+    ok = ok and col.numel() == E * math.ceil(pr / 8) * int(meta[0]) and rec.dtype == torch.uint8 and col.dtype == torch.uint8
+    if ok:
+        last = desc[count - 1].to(torch.int64)
+        ok = int((last[0] & 0xFFFFFFFF) * 16 + (last[1] & 0xFFFFFFFF)) <= rec.numel()
+    if not ok:
+        for k in ("_tris_gr_index", "_tris_packed_row_group", "_tris_tile_records", "_tris_tile_desc", "_tris_col_records",
+                  "_tris_tile_meta", "_tris_derived_from_checkpoint"):
+            payload.pop(k, None)
+        return False
+    payload["_tris_gr_index"] = idx.to(dev, torch.int32).contiguous()
+    payload["_tris_packed_row_group"] = grp.to(dev, torch.int32).contiguous()
+    payload["_tris_tile_records"] = rec.to(dev).contiguous()
+    payload["_tris_tile_desc"] = desc.to(dev, torch.int32).contiguous()
+    payload["_tris_col_records"] = col.to(dev).contiguous()
+    payload["_tris_gr_substreams"] = 32
+    payload["_tris_dims"] = (E, O, rank, G)
+    return True
 
 
 def _build_tile_records(payload: dict, lib, dev) -> None:
@@ -404,6 +438,12 @@ def _route_view(route: dict, num_rows: int, keep: list) -> TrisRouteView:
         keep.append(gather)
         rv.row_gather = gather.data_ptr()
     rv.flags = HIDDEN_LAYOUT_ROUTE_FLAG[int(route.get("_hidden_layout", HIDDEN_ROW_MAJOR))]
+    scale = route.get("_hidden_col_scale")  # fp16 [rank]: the input scale vector of an ordinary compact3 linear
+    if isinstance(scale, torch.Tensor):
+        if scale.dtype != torch.float16 or not scale.is_contiguous():
+            scale = scale.to(torch.float16).contiguous()
+        keep.append(scale)
+        rv.hidden_col_scale = scale.data_ptr()
     # extension of the route dict (no reference counterpart): "_out_row_scatter" [R] int32 sends the
     # result of grouped row i to output row scatter[i] (a negative entry drops it)
     scatter = route.get("_out_row_scatter")

@@ -129,6 +129,13 @@ def load_grouped_payload_from_sidecar(path: str, prefix: str, cache_key: str, de
             payload[name] = fh.get_tensor(key)
     if not payload:
         return None
+    return _decode_payload(payload, device=device, dtype=dtype)
+
+
+def _decode_payload(payload: Dict[str, torch.Tensor], device="cpu", dtype: torch.dtype = torch.float16) -> dict:
+    """Stored tensors of one payload -> the runtime dict: one-element scalars become python values
+    (grouped_payload_sidecar.py:282-303), floating tensors get ``dtype``, an all-zero compact3
+    ``output_scale`` is repaired to ones (:264-279)."""
     out = {}
     for name, t in payload.items():
         if name in _BOOL_SCALARS and t.numel() == 1:

@@ -48,7 +48,7 @@ def test_struct_sizes_match_c_layout(lib):
 
     assert C.sizeof(tm._native.TrisProjView) == 224  # static_assert in csrc/common.cuh
     assert tm._native.TrisProjView.tile_records.offset == 184
-    assert C.sizeof(tm._native.TrisRouteView) == 72
+    assert C.sizeof(tm._native.TrisRouteView) == 80
     assert tm._native.TrisRouteView.row_gather.offset == 40
     assert tm._native.TrisRouteView.out_row_scatter.offset == 64
 

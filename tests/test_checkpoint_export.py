@@ -1,0 +1,98 @@
+"""CPU tests of the block-GR exporter and the layer-batched loader against the sidecar the
+reference wrote (tests/golden/ref_sidecar.safetensors): its payloads carry the sparse g_map planes
+AND the block-GR streams the reference's own encoder made from them, so the exporter must
+reproduce those streams bit for bit from the sparse planes alone."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import trismoe_oracle as orc
+from helpers import GOLDEN
+
+
+def _load_all(path):
+    from safetensors import safe_open
+
+    with safe_open(path, framework="pt", device="cpu") as fh:
+        return {k: fh.get_tensor(k) for k in fh.keys()}, dict(fh.metadata() or {})
+
+
+def test_exporter_reproduces_the_reference_streams(lib):
+    from trismoe_b200 import checkpoint_export as ce
+
+    tensors, _ = _load_all(os.path.join(GOLDEN, "ref_sidecar.safetensors"))
+    want = {k: v.clone() for k, v in tensors.items() if ".q_gmap_gr_" in k}
+    assert len(want) == 9
+    for k in want:  # forget the streams: the exporter starts from the sparse planes
+        tensors[k] = torch.empty((0,), dtype=torch.int32)
+    for k in [k for k in tensors if k.endswith(".compact3_use_block_gr")]:
+        tensors[k] = torch.tensor([False])
+    built, words = ce.build_grouped_blockgr_payloads(tensors, "compressed")
+    assert built == 3 and words == sum(int(v.numel()) for k, v in want.items() if k.endswith("q_gmap_gr_words"))
+    for k, v in want.items():
+        assert tensors[k].dtype == v.dtype and torch.equal(tensors[k], v), k
+    assert all(bool(tensors[k][0]) for k in tensors if k.endswith(".gate.compact3_use_block_gr"))
+
+
+def test_dense_restore_matches_oracle_and_k_bounds(lib):
+    from trismoe_b200 import checkpoint_export as ce, synth
+
+    shape = synth.LayerShape(96, 160, 2, 1, rank=80, group_size=16)
+    p = synth.synth_layer(shape, seed=9, keep_sparse_gmap=True)["gate"]
+    for e in range(2):
+        dense = ce.restore_dense_packed_gmap_from_sparse(p["q_gmap_sparse"][e], p["c_map"][e], 80, 160)
+        assert torch.equal(dense, p["_dense_gmap_words"][e])
+    assert ce.resolve_block_gr_search_bounds() == (0, 7) and ce.resolve_block_gr_search_bounds(fixed_k=3) == (3, 3)
+    with pytest.raises(ValueError):
+        ce.resolve_block_gr_search_bounds(fixed_k=3, k_min=1, k_max=2)
+    with pytest.raises(ValueError):
+        ce.resolve_block_gr_search_bounds(k_min=5, k_max=2)
+
+
+def test_export_file_round_trip_modes_and_layer_batches(lib, tmp_path):
+    """compressed / fixed-k / raw exports of a two-layer sidecar: metadata as the reference exporter
+    writes it, the sparse planes dropped unless asked for, streams that decode (oracle decoder)
+    back to the dense maps, and the layer-batched loader returning every layer once."""
+    from safetensors import safe_open
+
+    from trismoe_b200 import checkpoint_export as ce, sidecar, synth
+
+    shape = synth.LayerShape(64, 96, 3, 2, rank=64, group_size=32)
+    layers, dense = {}, {}
+    for L in range(3):
+        layer = synth.synth_layer(shape, seed=20 + L, keep_sparse_gmap=True, use_block_gr=False)
+        prefix = sidecar.layer_prefix(L)
+        layers[prefix] = {k: layer[k] for k in ("gate", "up", "down")}
+        dense[prefix] = {k: layer[k]["_dense_gmap_words"] for k in ("gate", "up", "down")}
+    src = os.path.join(tmp_path, "src", sidecar.GROUPED_PAYLOAD_SIDECAR_BASENAME)
+    os.makedirs(os.path.dirname(src))
+    sidecar.save_grouped_payloads_to_sidecar(src, layers)
+    for tag, kw in (("c", {}), ("k2", {"fixed_k": 2}), ("raw", {"mode": "raw", "keep_sparse": True})):
+        out = os.path.join(tmp_path, tag, sidecar.GROUPED_PAYLOAD_SIDECAR_BASENAME)
+        stats = ce.export_grouped_blockgr_checkpoint(src, out, **kw)
+        assert stats["built_grouped_payloads"] == 9
+        with safe_open(out, framework="pt") as fh:
+            meta = fh.metadata()
+            assert meta["olmoe_grouped_block_gr_export"] == "v1" and meta["olmoe_grouped_block_gr_mode"] == kw.get("mode", "compressed")
+            assert meta["olmoe_grouped_block_gr_keep_sparse"] == ("1" if kw.get("keep_sparse") else "0")
+            assert (meta.get("olmoe_grouped_block_gr_k") == "2") == (tag == "k2")
+        seen = []
+        for batch in ce.iter_layer_payload_batches(out, layers_per_batch=2):
+            assert 1 <= len(batch) <= 2
+            for prefix, by_key in batch.items():
+                seen.append(prefix)
+                for key, payload in by_key.items():
+                    assert payload["compact3_use_block_gr"] is True
+                    assert (payload["q_gmap_sparse"].numel() > 0) == bool(kw.get("keep_sparse"))
+                    meta_words = payload["q_gmap_gr_meta"].numpy()
+                    if tag == "k2":
+                        assert set(int(m) & 15 for m in meta_words.reshape(-1) if not int(m) & 16) <= {2}
+                    if tag == "raw":
+                        assert all(int(m) & 16 for m in meta_words.reshape(-1))
+                    for e in range(3):
+                        got = orc.gr_decode_tensor(payload["q_gmap_gr_words"][e].numpy(), payload["q_gmap_gr_offsets"][e].numpy(),
+                                                   payload["q_gmap_gr_meta"][e].numpy(), 2, int(payload["qweight1"].shape[2]))
+                        assert np.array_equal(got.view(np.int32), dense[prefix][key][e].numpy()), (tag, prefix, key, e)
+        assert seen == [sidecar.layer_prefix(L) for L in range(3)]
