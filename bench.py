@@ -482,6 +482,23 @@ def run_extra(args):
         rec["tflops"] = round(flops(synth.MIXTRAL, rec["tokens"]) / (rec["us_per_layer"] * 1e-6) / 1e12, 2)
     del mixtral
     torch.cuda.empty_cache()
+    # BASELINE config 2: the full 16-layer OLMoE-1B-7B-shaped decoder (fp16 attention, 16 heads of 128, vocab
+    # 50304), random prompt of 512 tokens, 256 generated tokens, batch 1 and 32; definitions of
+    # tools/benchmark_e2e_grid.py (decode tokens/s = batch * decode steps / decode time)
+    from trismoe_b200 import decode_harness as dh
+
+    full = stack(synth.OLMOE, LAYERS, 1234)
+    model = dh.TrisDecoder(full, dh.DecoderShape(), max_length=512 + 256, max_batch=32, device=device, seed=0)
+    out["e2e_decode_olmoe_16_layers"] = []
+    for B in (1, 32):
+        ids = torch.randint(0, 50304, (B, 512), generator=torch.Generator().manual_seed(B)).to(device)
+        dh.run_exact_generation(model, ids, 8)  # warm-up
+        rec = dh.run_exact_generation(model, ids, 256)
+        out["e2e_decode_olmoe_16_layers"].append({k: (round(v, 3) if isinstance(v, float) else v) for k, v in rec.items() if k != "tokens"})
+    for blk in full:
+        blk.raise_on_kernel_status()
+    del model, full
+    torch.cuda.empty_cache()
     for mode, fmt_gr in (("bitmap", False), ("payload", True)):
         blocks = stack(synth.OLMOE, 8, 700, keep_sparse_gmap=not fmt_gr, use_block_gr=fmt_gr)
         manager = staging.GroupedQGmapCPUStagingManager(blocks, mode=mode)

@@ -496,9 +496,11 @@ static int pick_ksplit(const TrisProjView* proj, const TrisRouteView* route, int
   return 1;
 }
 
-// Rows per segment (the launch's estimate) up to which the tile-record kernel is used; beyond it
-// the prefill-sized kernels take over.
-static int tiled_max_rows() { return grouped_tc_min_rows(); }
+// Rows per segment (the launch's estimate) up to which the tile-record kernel is used.  It multiplies
+// 32 rows per pass and re-unpacks the weights for every pass; from ~64 rows per segment on, the
+// plane-staging kernel (64 rows per pass) and, beyond grouped_tc_min_rows(), the tcgen05 kernel do
+// less work per row.
+static int tiled_max_rows() { return std::min(64, grouped_tc_min_rows()); }
 
 // Rows per activation tile: sized for the typical segment (mean + 4 sigma of a balanced
 // router), never above the caller's bound; longer segments take several passes.
@@ -620,7 +622,7 @@ extern "C" int tris_grouped_hidden_layout(const TrisProjView* proj_a, const Tris
   route.num_segments = num_segments;
   route.max_rows_per_segment = max_rows_per_segment;
   const bool records = proj_has_tile_records(*proj_a) && (proj_b == nullptr || proj_has_tile_records(*proj_b));
-  return (records && route_rows_hint(&route) <= grouped_tc_min_rows()) ? TRIS_OUT_F16_LANE_ORDER : TRIS_OUT_F16_PAIR_INTERLEAVED;
+  return (records && route_rows_hint(&route) <= tiled_max_rows()) ? TRIS_OUT_F16_LANE_ORDER : TRIS_OUT_F16_PAIR_INTERLEAVED;
 }
 
 extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
