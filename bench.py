@@ -285,7 +285,35 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_ms = max(start.elapsed_time(stop), (time.perf_counter() - t0) * 1e3) / args.steps
     clocks = sampler.stop()
+    olmoe_status = max(b.last_kernel_status() for b in blocks)  # sticky status words of every layer: 0 = no bounded wait ran out
 
+    # the Mixtral-shaped stack of the expert-parallel lines (config 3), here on one GPU: 4 of the 32 layers
+    del blocks
+    torch.cuda.empty_cache()
+    mixtral = {"shape": "8 experts, top-2, hidden 4096, intermediate 14336, rank-256 backbones", "layers_timed": 4,
+               "of_layers": 32, "experts_per_gpu": 8, "decode": []}
+    mblocks = []
+    for l in range(4):
+        layer = synth.synth_layer(synth.MIXTRAL, seed=600 + l)
+        blk = tm.TrisSparseMoeBlock(4096, 14336, 8, 2, True)
+        blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
+                                  layer["shared_down"], layer["router_weight"], device=device)
+        mblocks.append(blk)
+    for TB in (1, 64):
+        xm = synth.synth_activations(TB, 4096, seed=2000).to(device)
+
+        def mstep():
+            for blk in mblocks:
+                blk(xm.view(1, TB, 4096))
+
+        graph = capture(mstep)
+        mms = time_replays(graph, max(10, args.steps // 2), args.warmup, repeats=3)
+        mixtral["decode"].append({"tokens_per_gpu": TB, "tokens_per_s": round(TB / (mms * 1e-3), 1),
+                                  "us_per_layer": round(mms * 1e3 / 4, 2), "launch_mode": "cuda graph"})
+        del graph
+    mixtral["kernel_status"] = max(b.last_kernel_status() for b in mblocks)
+    del mblocks
+    torch.cuda.empty_cache()
     cpu = cpu_baseline(sample_tokens=T)
     out = {
         "metric": "decode_tokens_per_s", "value": round(head["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
@@ -298,7 +326,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},
         "gpu_launches": args.steps * REPEATS * LAYERS * LAUNCHES_PER_LAYER,
         "timing": f"median of {REPEATS} repeats of {args.steps} graph replays (CUDA events)",
-        "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+        "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "mixtral_ep": mixtral, "kernel_status": olmoe_status,
         "sweep": {str(t): {k: round(v, 3) for k, v in r.items()} for t, r in results.items()},
         "l2_resident": {"tokens": T, "us_per_layer": round(l2_resident_us, 3),
                         "note": "one layer replayed 16 times (payload stays in L2); the headline uses 16 distinct layers"},

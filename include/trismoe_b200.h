@@ -157,6 +157,16 @@ const char* tris_status_string(int status);
 /* Message of the last non-zero status returned on this thread (TORCH_CHECK text in CU). */
 const char* tris_last_error(void);
 
+/*
+ * Programmatic dependent launch for the stand-alone entry points (process-wide switch, off by
+ * default; returns the previous value).  When on, every kernel these entry points launch may start
+ * while its predecessor in the stream drains and waits (griddepcontrol.wait) before it touches what
+ * the predecessor wrote - the launch gaps of a chain of small kernels (router, route, exchange,
+ * grouped kernels, combine) overlap instead of adding up.  tris_moe_layer_forward always launches
+ * this way.  No reference counterpart.
+ */
+int tris_set_programmatic_launch(int32_t enable);
+
 /* ---- block Golomb-Rice ------------------------------------------------------------- */
 
 /*

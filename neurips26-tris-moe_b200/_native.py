@@ -67,6 +67,7 @@ SIGNATURES = {
     "tris_compact3_kernel_abi_version": (C.c_int, []),
     "tris_status_string": (C.c_char_p, [C.c_int]),
     "tris_last_error": (C.c_char_p, []),
+    "tris_set_programmatic_launch": (C.c_int, [_i32]),
     "tris_block_gr_encode_host": (C.c_int, [_vp, _i32, _i32, _i32, _vp, C.c_int64, _vp, _vp, _P(C.c_int64)]),
     "tris_block_gr_encode_host_k": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, C.c_int64, _vp, _vp, _P(C.c_int64)]),
     "tris_block_gr_index_bytes": (C.c_size_t, [_i32, _i32, _i32, _i32]),

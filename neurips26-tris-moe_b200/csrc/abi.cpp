@@ -1,5 +1,6 @@
 // Host-only part of the C ABI: version, status strings, thread-local error text and the
 // block Golomb-Rice encoder.
+#include <atomic>
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -35,6 +36,17 @@ int check_cuda(cudaError_t err, const char* what) {
 }
 
 }  // namespace tris
+
+namespace {
+std::atomic<int> g_programmatic_launch{0};
+}
+namespace tris {
+bool programmatic_launch_default() { return g_programmatic_launch.load(std::memory_order_relaxed) != 0; }
+}  // namespace tris
+
+extern "C" int tris_set_programmatic_launch(int32_t enable) {
+  return g_programmatic_launch.exchange(enable ? 1 : 0, std::memory_order_relaxed);
+}
 
 extern "C" int tris_abi_version(void) { return TRIS_B200_ABI_VERSION; }
 extern "C" int tris_compact3_kernel_abi_version(void) { return TRIS_COMPACT3_KERNEL_ABI_VERSION; }

@@ -91,6 +91,10 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Whether the stand-alone entry points launch with programmatic dependent launch
+// (tris_set_programmatic_launch).
+bool programmatic_launch_default();
+
 // Options of the launches the fused layer path makes.
 struct LaunchOpts {
   bool pdl = false;                  // programmatic dependent launch

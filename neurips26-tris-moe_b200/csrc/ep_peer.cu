@@ -49,6 +49,8 @@ __global__ void __launch_bounds__(128) ep_dispatch_peer_kernel(
     int row_stride, int32_t* __restrict__ combine_index, int32_t* __restrict__ overflow,
     int32_t* const* __restrict__ peer_flags) {
   __shared__ int32_t s_first[64];  // first grouped row owned by each rank (world <= 64)
+  pdl_wait();  // the route and the backbone outputs come from the kernels before this one
+  pdl_launch_dependents();
   const int base = num_experts / world, extra = num_experts % world;
   if (threadIdx.x < world) {  // rows are sorted by owner: binary search for each owner's first row
     const int d = threadIdx.x;
@@ -90,6 +92,8 @@ __global__ void __launch_bounds__(256) ep_return_peer_kernel(
     const __half* __restrict__ results, const __half* __restrict__ recv_rows, int row_stride, int rank_gu,
     int hidden, int world, int my_rank, int capacity, __half* const* __restrict__ peer_back,
     int32_t* const* __restrict__ peer_flags) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int vecs = hidden >> 3;
   for (int pos = blockIdx.x; pos < world * capacity; pos += gridDim.x) {
     const int s = pos / capacity, off = pos - s * capacity;
@@ -106,6 +110,7 @@ __global__ void __launch_bounds__(256) ep_return_peer_kernel(
 // *step.  Gives up after ~2 s and records TRIS_ERR_TIMEOUT.
 __global__ void ep_wait_kernel(const int32_t* flags, int32_t* step, int increment, int world, int32_t* status) {
   __shared__ int s_timeout;
+  pdl_wait();  // *step was advanced by an earlier wait kernel of this stream
   if (threadIdx.x == 0) s_timeout = 0;
   __syncthreads();
   const int32_t target = (*step + 1) * increment;
@@ -179,11 +184,13 @@ extern "C" int tris_ep_dispatch_peer(const void* hidden_gate_f16, const void* hi
                    capacity > 0,
                TRIS_ERR_INVALID_ARG, "tris_ep_dispatch_peer: bad sizes rows=%d world=%d rank=%d capacity=%d", num_rows,
                world, my_rank, capacity);
-  ep_dispatch_peer_kernel<<<kEpSignalCtas, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(hidden_gate_f16), static_cast<const __half*>(hidden_up_f16), rank_gu, selected_experts,
-      perm, grouped_token_indices, num_rows, num_experts, world, my_rank, capacity,
-      reinterpret_cast<__half* const*>(peer_recv_rows_dev), row_stride, combine_index, overflow_dev, peer_flags_dev);
-  return check_cuda(cudaGetLastError(), "ep_dispatch_peer_kernel launch");
+  return check_cuda(
+      launch_kernel(ep_dispatch_peer_kernel, dim3(kEpSignalCtas), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                    programmatic_launch_default(), 1, static_cast<const __half*>(hidden_gate_f16),
+                    static_cast<const __half*>(hidden_up_f16), rank_gu, selected_experts, perm, grouped_token_indices, num_rows,
+                    num_experts, world, my_rank, capacity, reinterpret_cast<__half* const*>(peer_recv_rows_dev), row_stride,
+                    combine_index, overflow_dev, peer_flags_dev),
+      "ep_dispatch_peer_kernel launch");
 }
 
 extern "C" int tris_ep_return_peer(const void* results_f16, const void* recv_rows_f16, int32_t row_stride,
@@ -196,16 +203,19 @@ extern "C" int tris_ep_return_peer(const void* results_f16, const void* recv_row
                "tris_ep_return_peer: bad sizes hidden=%d stride=%d rank=%d", hidden_size, row_stride, rank_gu);
   TRIS_REQUIRE(world >= 1 && world <= 64 && my_rank >= 0 && my_rank < world && capacity > 0, TRIS_ERR_INVALID_ARG,
                "tris_ep_return_peer: bad sizes world=%d rank=%d capacity=%d", world, my_rank, capacity);
-  ep_return_peer_kernel<<<kEpSignalCtas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(results_f16), static_cast<const __half*>(recv_rows_f16), row_stride, rank_gu,
-      hidden_size, world, my_rank, capacity, reinterpret_cast<__half* const*>(peer_back_dev), peer_flags_dev);
-  return check_cuda(cudaGetLastError(), "ep_return_peer_kernel launch");
+  return check_cuda(
+      launch_kernel(ep_return_peer_kernel, dim3(kEpSignalCtas), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    programmatic_launch_default(), 1, static_cast<const __half*>(results_f16),
+                    static_cast<const __half*>(recv_rows_f16), row_stride, rank_gu, hidden_size, world, my_rank, capacity,
+                    reinterpret_cast<__half* const*>(peer_back_dev), peer_flags_dev),
+      "ep_return_peer_kernel launch");
 }
 
 extern "C" int tris_ep_wait(const int32_t* flags_dev, int32_t* step_dev, int32_t world, int32_t* status_dev,
                             void* stream) {
   TRIS_REQUIRE(flags_dev && step_dev, TRIS_ERR_INVALID_ARG, "tris_ep_wait: null pointer");
   TRIS_REQUIRE(world >= 1 && world <= 64, TRIS_ERR_INVALID_ARG, "tris_ep_wait: world=%d", world);
-  ep_wait_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(flags_dev, step_dev, kEpSignalCtas, world, status_dev);
-  return check_cuda(cudaGetLastError(), "ep_wait_kernel launch");
+  return check_cuda(launch_kernel(ep_wait_kernel, dim3(1), dim3(64), 0, static_cast<cudaStream_t>(stream),
+                                  programmatic_launch_default(), 1, flags_dev, step_dev, kEpSignalCtas, world, status_dev),
+                    "ep_wait_kernel launch");
 }

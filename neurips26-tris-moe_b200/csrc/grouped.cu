@@ -627,7 +627,9 @@ extern "C" int tris_grouped_hidden_layout(const TrisProjView* proj_a, const Tris
 
 extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
                                     void* out_f16, void* stream) {
-  return grouped_forward_impl(proj, route, hidden_f16, out_f16, static_cast<cudaStream_t>(stream), LaunchOpts{});
+  LaunchOpts opts;
+  opts.pdl = programmatic_launch_default();
+  return grouped_forward_impl(proj, route, hidden_f16, out_f16, static_cast<cudaStream_t>(stream), opts);
 }
 
 int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjView* proj_b,
@@ -686,7 +688,9 @@ extern "C" int tris_grouped_pair_forward(const TrisProjView* proj_a, const TrisP
                                          const TrisRouteView* route, const void* hidden_a_f16,
                                          const void* hidden_b_f16, void* out_a_f16, void* out_b_f16,
                                          int32_t fuse_silu_mul, void* stream) {
+  LaunchOpts opts;
+  opts.pdl = programmatic_launch_default();
   return grouped_pair_forward_impl(proj_a, proj_b, route, hidden_a_f16, hidden_b_f16, out_a_f16, out_b_f16,
-                                   fuse_silu_mul, static_cast<cudaStream_t>(stream), LaunchOpts{});
+                                   fuse_silu_mul, static_cast<cudaStream_t>(stream), opts);
 }
 

@@ -379,9 +379,10 @@ extern "C" int tris_router_topk(const float* router_logits, int32_t num_tokens, 
                "tris_router_topk: supports up to %d experts and top-32", 32 * kMaxExpertsPerLane);
   if (num_tokens == 0) return TRIS_OK;
   const int threads = 128;
-  router_topk_kernel<<<ceil_div(num_tokens * 32, threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      router_logits, num_tokens, num_experts, top_k, norm_topk_prob, selected_experts, routing_weights);
-  return check_cuda(cudaGetLastError(), "router_topk_kernel launch");
+  return check_cuda(launch_kernel(router_topk_kernel, dim3(ceil_div(num_tokens * 32, threads)), dim3(threads), 0,
+                                  static_cast<cudaStream_t>(stream), programmatic_launch_default(), 1, router_logits,
+                                  num_tokens, num_experts, top_k, norm_topk_prob, selected_experts, routing_weights),
+                    "router_topk_kernel launch");
 }
 
 extern "C" int tris_build_grouped_route(const int32_t* selected_experts, int32_t num_tokens, int32_t top_k,
@@ -397,10 +398,11 @@ extern "C" int tris_build_grouped_route(const int32_t* selected_experts, int32_t
   TRIS_REQUIRE(num_experts <= 320, TRIS_ERR_UNSUPPORTED, "tris_build_grouped_route: more than 320 experts");
   int sel_cap = 0;
   const int smem = route_smem_bytes(num_experts, num_tokens * top_k, &sel_cap);
-  build_route_kernel<<<1, kRouteThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      selected_experts, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices, grouped_slots,
-      row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, sel_cap);
-  return check_cuda(cudaGetLastError(), "build_route_kernel launch");
+  return check_cuda(launch_kernel(build_route_kernel, dim3(1), dim3(kRouteThreads), smem, static_cast<cudaStream_t>(stream),
+                                  programmatic_launch_default(), 1, selected_experts, num_tokens, top_k, num_experts, m_tile,
+                                  perm, grouped_token_indices, grouped_slots, row_of_flat, expert_ids, segment_offsets,
+                                  problem_offsets, counts, sel_cap),
+                    "build_route_kernel launch");
 }
 
 int tris::combine_routed_impl(const void* down_out_f16, const int32_t* row_of_flat, const float* routing_weights,
@@ -423,5 +425,5 @@ extern "C" int tris_combine_routed(const void* down_out_f16, const int32_t* row_
                                    int32_t num_tokens, int32_t top_k, int32_t hidden_size, void* final_f16,
                                    void* stream) {
   return combine_routed_impl(down_out_f16, row_of_flat, routing_weights, num_tokens, top_k, hidden_size, final_f16,
-                             static_cast<cudaStream_t>(stream), false);
+                             static_cast<cudaStream_t>(stream), programmatic_launch_default());
 }

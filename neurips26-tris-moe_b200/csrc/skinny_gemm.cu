@@ -184,7 +184,7 @@ extern "C" int tris_shared_hidden_forward(const void* x_f16, const int32_t* row_
                TRIS_ERR_INVALID_ARG, "tris_shared_hidden_forward: the permuted layouts need rank % 32 == 0");
   SkinnyProblem pb{static_cast<const __half*>(shared_sv_f16), out, rank, out_mode};
   return launch_shared_hidden(&pb, 1, static_cast<const __half*>(x_f16), row_gather, num_rows, in_features,
-                              static_cast<cudaStream_t>(stream), false, num_rows_dev);
+                              static_cast<cudaStream_t>(stream), programmatic_launch_default(), num_rows_dev);
 }
 
 // Both input-side backbones and the router logits in one pass over x (what the layer entry
@@ -211,5 +211,5 @@ extern "C" int tris_input_projections(const void* x_f16, int32_t num_rows, int32
       {static_cast<const __half*>(router_weight_f16), router_logits_f32, num_experts, TRIS_OUT_F32},
   };
   return launch_shared_hidden(probs, router_weight_f16 ? 3 : 2, static_cast<const __half*>(x_f16), nullptr, num_rows,
-                              in_features, static_cast<cudaStream_t>(stream), false, nullptr);
+                              in_features, static_cast<cudaStream_t>(stream), programmatic_launch_default(), nullptr);
 }

@@ -208,6 +208,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         self.router_weight: Optional[torch.Tensor] = None
         self.capacity_tokens = 0  # tokens per rank the fixed-capacity exchange is sized for
         self.capacity_rows = 0    # rows per peer slot
+        _native.load().tris_set_programmatic_launch(1)  # the per-layer chain of small kernels overlaps its launch gaps
         self._overflow = None
         self._step_layouts = None
         self._kernel_status = None  # sticky status word of the grouped kernels (TRIS_ERR_TIMEOUT)
@@ -485,24 +486,23 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         return self._overflow is not None and bool(self._overflow.item())
 
 
-def run_bench(args, rank: int, world: int, device) -> None:
-    """Weak scaling: every rank decodes its own batch of 128 tokens through 16 layers whose
-    experts are sharded over the ranks.  Timed on the device (CUDA events), max over ranks."""
+def _build_ep_stack(shape, layers: int, seed: int, tokens: int, rows_per_peer, device, want_peer: bool):
+    """`layers` expert-parallel blocks of `shape` (same seeds on every rank: identical full payloads,
+    each rank keeps its slice) with the exchange sized for `tokens` tokens per rank; returns the
+    blocks and the name of the exchange that ended up in use on all ranks."""
     from . import synth
-    from .clocks import ClockSampler
 
-    layers, T = 16, 128
-    shape = synth.OLMOE
+    world = dist.get_world_size()
     blocks = []
     for l in range(layers):
-        layer = synth.synth_layer(shape, seed=1234 + l)  # same seed on every rank: identical full payloads
+        layer = synth.synth_layer(shape, seed=seed + l)
         blk = ExpertParallelMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
         blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
                                   layer["shared_down"], layer["router_weight"], device=device)
-        blocks.append(blk.set_capacity(T, balanced_rows_per_peer(T, shape.top_k, world)))
-    # exchange through peer memory unless TRIS_EP_EXCHANGE=nccl or the mapping cannot be set up
+        blocks.append(blk.set_capacity(tokens, rows_per_peer))
+        del layer
     exchange = "nccl all-to-all"
-    if os.environ.get("TRIS_EP_EXCHANGE", "peer") != "nccl":
+    if want_peer:
         try:
             for blk in blocks:
                 blk.use_peer_exchange()
@@ -517,9 +517,14 @@ def run_bench(args, rank: int, world: int, device) -> None:
         for blk in blocks:
             blk._peer = None
         exchange = "nccl all-to-all (peer mapping failed on a rank)"
-    x = synth.synth_activations(T, shape.hidden_size, seed=1000 + rank).to(device)
-    x_host = x.cpu().pin_memory()
-    y_host = torch.empty_like(x_host).pin_memory()
+    return blocks, exchange
+
+
+def _time_ep_stack(blocks, x: torch.Tensor, steps: int, warmup: int, device, repeats: int = 3):
+    """One step = the batch through every block.  Captures the step into a CUDA graph when it can,
+    times `steps` replays between barriers with CUDA events, max over ranks, median of `repeats`.
+    Returns (ms per step, launch mode, graph or None, static output or None)."""
+    T = int(x.shape[0])
 
     def step(inp):
         y = None
@@ -527,28 +532,7 @@ def run_bench(args, rank: int, world: int, device) -> None:
             y = blk(inp.view(1, T, -1))[0]
         return y
 
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            fn()
-        stop.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        ms = torch.tensor([start.elapsed_time(stop) / steps], device=device)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    sampler = ClockSampler(device.index or 0)
-    if rank == 0:
-        sampler.start()
-    # one CUDA graph per step (kernels and NCCL all-to-alls); eager launches if capture is refused
-    graph, mode = None, "eager"
+    graph, mode, y_static = None, "eager", None
     try:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -566,40 +550,172 @@ def run_bench(args, rank: int, world: int, device) -> None:
         graph = None
         mode = f"eager ({type(exc).__name__})"
         torch.cuda.synchronize()
-    ms = timed((graph.replay if graph is not None else (lambda: step(x))), args.steps, args.warmup)
+    fn = graph.replay if graph is not None else (lambda: step(x))
+    return _timed(fn, steps, warmup, device, repeats), mode, graph, y_static, step
 
-    def e2e():
-        if graph is not None:  # the captured step reads x and leaves its result in y_static
-            x.copy_(x_host, non_blocking=True)
-            graph.replay()
-            y_host.copy_(y_static.view(T, -1), non_blocking=True)
-        else:
-            xd = x_host.to(device, non_blocking=True)
-            y_host.copy_(step(xd).view(T, -1), non_blocking=True)
 
-    e2e_ms = timed(e2e, args.steps, args.warmup)
-    overflowed = torch.tensor([int(any(b.exchange_overflowed() for b in blocks))], device=device)
-    dist.all_reduce(overflowed, op=dist.ReduceOp.MAX)
-    timed_out = torch.tensor([int(any(b._peer is not None and b._peer.timed_out() for b in blocks))], device=device)
-    dist.all_reduce(timed_out, op=dist.ReduceOp.MAX)
+def _timed(fn, steps: int, warmup: int, device, repeats: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    samples = []
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = torch.tensor([start.elapsed_time(stop) / steps], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        samples.append(float(ms.item()))
+    samples.sort()
+    return samples[len(samples) // 2]
+
+
+def _ep_check(device, rank: int, world: int) -> dict:
+    """Correctness evidence that travels with the bench line (the two-GPU pytest cannot run on a
+    one-GPU box): one OLMoE-shaped layer through the expert-parallel block - over the NCCL
+    all-to-all and over the peer-memory exchange - and through the single-GPU block, on this
+    rank's own tokens.  max_abs / mean_rel are against the single-GPU result; the two exchanges
+    must agree bit for bit."""
+    from . import synth
+    from .moe_block import TrisSparseMoeBlock
+
+    shape, T = synth.OLMOE, 64
+    layer = synth.synth_layer(shape, seed=4321)
+    clone = lambda p: {k: (v.clone() if isinstance(v, torch.Tensor) and not k.startswith("_") else v) for k, v in p.items()}
+    full = TrisSparseMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
+    full.load_grouped_payloads(clone(layer["gate"]), clone(layer["up"]), clone(layer["down"]), layer["shared_gate"],
+                               layer["shared_up"], layer["shared_down"], layer["router_weight"], device=device)
+    blk = ExpertParallelMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
+    blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
+                              layer["shared_down"], layer["router_weight"], device=device)
+    blk.set_capacity(T)
+    x = synth.synth_activations(T, shape.hidden_size, seed=77 + rank).to(device)
+    want = full(x.view(1, T, -1))[0].float()
+    got_nccl = blk(x.view(1, T, -1))[0]
+    torch.cuda.synchronize()
+    bit_equal = None
+    try:
+        blk.use_peer_exchange()
+        got_peer = blk(x.view(1, T, -1))[0]
+        torch.cuda.synchronize()
+        bit_equal = bool(torch.equal(got_peer, got_nccl))
+    except Exception:  # noqa: BLE001 - no peer mapping on this box: the NCCL result stands alone
+        bit_equal = None
+    blk._peer = None
+    err = (got_nccl.float() - want).abs()
+    stats = torch.tensor([float(err.max()), float(err.mean()), float(want.abs().mean()),
+                          0.0 if bit_equal is None else (1.0 if bit_equal else -1.0),
+                          float(blk.kernel_status() + full.last_kernel_status())], device=device)
+    gathered = [torch.zeros_like(stats) for _ in range(world)]
+    dist.all_gather(gathered, stats)
+    allr = torch.stack(gathered).cpu()
+    max_abs = float(allr[:, 0].max())
+    mean_rel = float((allr[:, 1] / allr[:, 2].clamp_min(1e-30)).max())
+    bits = allr[:, 3]
+    out = {"max_abs": round(max_abs, 6), "mean_rel": round(mean_rel, 6),
+           "bit_equal_nccl_vs_peer": None if bool((bits == 0).any()) else bool((bits > 0).all()),
+           "kernel_status": int(allr[:, 4].max()), "tokens_per_rank": T, "layer": "OLMoE-shaped",
+           "against": "single-GPU TrisSparseMoeBlock on the same tokens, every rank"}
+    out["ok"] = bool(max_abs <= 2e-2 and mean_rel <= 1e-3 and out["kernel_status"] == 0 and out["bit_equal_nccl_vs_peer"] is not False)
+    return out
+
+
+def run_bench(args, rank: int, world: int, device) -> None:
+    """Weak scaling: every rank decodes its own batch of 128 tokens through 16 layers whose
+    experts are sharded over the ranks.  Timed on the device (CUDA events), max over ranks.
+    Headline: exchange sized for the worst case (tokens * top_k rows per peer: nothing can ever be
+    dropped); the same stack with slots for mean + 6 sigma of a balanced router is reported
+    beside it.  `mixtral_ep`: a Mixtral-shaped stack (8 experts, top-2, hidden 4096, intermediate
+    14336) at decode batch 1 and 64 per GPU.  `ep_check`: correctness of the expert-parallel block
+    against the single-GPU block, measured in this run."""
+    from . import synth
+    from .clocks import ClockSampler
+
+    layers, T = 16, 128
+    shape = synth.OLMOE
+    want_peer = os.environ.get("TRIS_EP_EXCHANGE", "peer") != "nccl"
+    check = _ep_check(device, rank, world)
+    sampler = ClockSampler(device.index or 0)
+    if rank == 0:
+        sampler.start()
+    x = synth.synth_activations(T, shape.hidden_size, seed=1000 + rank).to(device)
+    x_host = x.cpu().pin_memory()
+    y_host = torch.empty_like(x_host).pin_memory()
+    results = {}
+    for tag, rows_per_peer in (("balanced_6_sigma", balanced_rows_per_peer(T, shape.top_k, world)), ("never_dropping", None)):
+        blocks, exchange = _build_ep_stack(shape, layers, 1234, T, rows_per_peer, device, want_peer)
+        ms, mode, graph, y_static, step = _time_ep_stack(blocks, x, args.steps, args.warmup, device)
+        rec = {"ms_per_step": ms, "mode": mode, "exchange": exchange, "rows_per_peer": blocks[0].capacity_rows,
+               "peer": blocks[0]._peer is not None}
+        if tag == "never_dropping":
+            def e2e():
+                if graph is not None:  # the captured step reads x and leaves its result in y_static
+                    x.copy_(x_host, non_blocking=True)
+                    graph.replay()
+                    y_host.copy_(y_static.view(T, -1), non_blocking=True)
+                else:
+                    xd = x_host.to(device, non_blocking=True)
+                    y_host.copy_(step(xd).view(T, -1), non_blocking=True)
+
+            rec["e2e_ms"] = _timed(e2e, args.steps, args.warmup, device)
+        flags = torch.tensor([int(any(b.exchange_overflowed() for b in blocks)),
+                              int(any(b._peer is not None and b._peer.timed_out() for b in blocks)),
+                              max(b.kernel_status() for b in blocks)], device=device)
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+        rec["overflowed"], rec["timed_out"], rec["kernel_status"] = bool(flags[0].item()), bool(flags[1].item()), int(flags[2].item())
+        results[tag] = rec
+        del graph, y_static, blocks
+        torch.cuda.empty_cache()
+        dist.barrier()
+    # Mixtral-shaped stack: as many of the 32 layers as keep the run short (stated), decode batch 1 and 64 per GPU
+    mixtral_layers = 4
+    mixtral = {"shape": "8 experts, top-2, hidden 4096, intermediate 14336, rank-256 backbones", "layers_timed": mixtral_layers,
+               "of_layers": 32, "experts_per_gpu": round(synth.MIXTRAL.num_experts / world, 2), "decode": []}
+    mblocks, mexchange = _build_ep_stack(synth.MIXTRAL, mixtral_layers, 600, 64, None, device, want_peer)
+    mixtral["exchange"] = mexchange
+    for TB in (1, 64):
+        xm = synth.synth_activations(TB, synth.MIXTRAL.hidden_size, seed=2000 + rank).to(device)
+        ms, mode, graph, _, _ = _time_ep_stack(mblocks, xm, max(10, args.steps // 2), args.warmup, device)
+        mixtral["decode"].append({"tokens_per_gpu": TB, "tokens_per_s": round(TB * world / (ms * 1e-3), 1),
+                                  "us_per_layer": round(ms * 1e3 / mixtral_layers, 2), "launch_mode": mode})
+        del graph
+    mstat = torch.tensor([max(b.kernel_status() for b in mblocks), int(any(b.exchange_overflowed() for b in mblocks))], device=device)
+    dist.all_reduce(mstat, op=dist.ReduceOp.MAX)
+    mixtral["kernel_status"], mixtral["overflowed"] = int(mstat[0].item()), bool(mstat[1].item())
+    del mblocks
+    torch.cuda.empty_cache()
     if rank == 0:
         clocks = sampler.stop()
         total = T * world
+        head, alt = results["never_dropping"], results["balanced_6_sigma"]
+        ms, e2e_ms = head["ms_per_step"], head["e2e_ms"]
         print(json.dumps({
             "metric": "decode_tokens_per_s", "value": round(total / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "OLMoE-shaped 16-layer MoE stack, decode batch 128 per GPU, experts sharded over the "
                                    "GPUs (expert parallel), dispatch and combine over NVLink",
-                       "tokens_per_step": total, "layers": layers, "parallelism": f"ep{world}", "launch_mode": mode,
-                       "exchange": exchange, "exchange_rows_per_peer": blocks[0].capacity_rows,
-                       "exchange_overflowed": bool(overflowed.item()), "exchange_timed_out": bool(timed_out.item()),
-                       "cold_cache": "16 distinct layer payloads per rank"},
+                       "tokens_per_step": total, "layers": layers, "parallelism": f"ep{world}", "launch_mode": head["mode"],
+                       "exchange": head["exchange"], "exchange_rows_per_peer": head["rows_per_peer"],
+                       "exchange_capacity": "never dropping (tokens * top_k slots per peer)",
+                       "exchange_overflowed": head["overflowed"], "exchange_timed_out": head["timed_out"],
+                       "kernel_status": head["kernel_status"], "cold_cache": "16 distinct layer payloads per rank"},
             "e2e": {"value": round(total / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": T * 2048 * 2,
                     "d2h_bytes_per_step": T * 2048 * 2, "ms_per_step": round(e2e_ms, 4)},
+            "balanced_capacity": {"rows_per_peer": alt["rows_per_peer"], "tokens_per_s": round(total / (alt["ms_per_step"] * 1e-3), 1),
+                                  "ms_per_step": round(alt["ms_per_step"], 4), "overflowed": alt["overflowed"],
+                                  "note": "slots for mean + 6 sigma of a balanced router; a skewed router would drop rows (reported)"},
+            "mixtral_ep": mixtral, "ep_check": check,
             # per layer: router GEMM, top-k, route, two backbones, dispatch, wait, route of the received rows,
             # gate/up, down backbone, down, return, wait, combine (the all-to-all path has 2 fewer)
-            "gpu_launches": args.steps * layers * (14 if blocks[0]._peer is not None else 12),
+            "gpu_launches": args.steps * 3 * layers * (14 if head["peer"] else 12),
+            "timing": f"median of 3 repeats of {args.steps} steps, CUDA events, max over ranks",
             "roofline": None, "cpu_baseline": None, "clocks": clocks,
         }))
     dist.barrier()
