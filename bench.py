@@ -462,6 +462,66 @@ def run_ncu_case(args):
         torch.cuda.synchronize()
 
 
+def streaming_records(blocks, manager, shape, device):
+    """Times `forward_streaming` over the stack at batch 1 and 16: eager (with the pager's copy and stall
+    intervals from CUDA events) and as one CUDA graph."""
+    from trismoe_b200 import staging, synth
+
+    n_layers, H = len(blocks), shape.hidden_size
+    per_expert = [sum(manager.entries[(l, p)].block_bytes[k] for p in staging.PROJECTIONS
+                      for k in manager.entries[(l, p)].block_bytes) for l in range(n_layers)]
+    recs = []
+    for T in (1, 16):
+        x = synth.synth_activations(T, H, seed=T).to(device)
+
+        def step():
+            for l, blk in enumerate(blocks):
+                blk.forward_streaming(x.view(1, T, H), manager, l)
+
+        paged_bytes = 0
+        for l, blk in enumerate(blocks):  # bytes one pass pages: distinct routed experts x per-expert block sizes
+            _, logits = blk.forward_streaming(x.view(1, T, H), manager, l)
+            paged_bytes += torch.unique(torch.topk(logits, shape.top_k, dim=-1).indices).numel() * per_expert[l]
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        manager.overlap_report()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        start.record()
+        for _ in range(reps):
+            step()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / reps
+        rep = manager.overlap_report()
+        # the same step as one CUDA graph (kernels on two streams, ordered by events)
+        graph_ms, graph_err = None, None
+        try:
+            manager.collect_timings = False
+            graph = capture(step)
+            graph_ms = time_replays(graph, 10, 3)
+            del graph
+        except Exception as exc:  # noqa: BLE001
+            graph_ms, graph_err = None, str(exc)[:160]
+            torch.cuda.synchronize()
+        finally:
+            manager.collect_timings = True
+        best_ms = ms if graph_ms is None else min(ms, graph_ms)
+        recs.append({"tokens": T, "layers": n_layers,
+                     "us_per_layer": round(ms * 1e3 / n_layers, 2), "tokens_per_s": round(T / (ms * 1e-3), 1),
+                     "graph_us_per_layer": None if graph_ms is None else round(graph_ms * 1e3 / n_layers, 2),
+                     "graph_tokens_per_s": None if graph_ms is None else round(T / (graph_ms * 1e-3), 1),
+                     "graph_error": graph_err,
+                     "overlapped_fraction": None if rep["overlapped_fraction"] is None else round(rep["overlapped_fraction"], 3),
+                     "copy_ms_per_layer": round(rep["copy_ms"] / max(1, rep["layers"]), 4),
+                     "paged_mb_per_pass": round(paged_bytes / 1e6, 2),
+                     "pager_gbs": round(paged_bytes * reps / (rep["copy_ms"] * 1e-3) / 1e9, 2) if rep["copy_ms"] else None,
+                     "paged_gbs_over_step": round(paged_bytes / (best_ms * 1e-3) / 1e9, 2),
+                     "staging_buffer_mb": round(manager.buffer_nbytes / 1e6, 1)})
+    return recs
+
+
 def run_extra(args):
     """Secondary workloads (not the contract line): prints one JSON object with
     - prefill of 2048 tokens through OLMoE-shaped layers (tcgen05 grouped path),
@@ -527,55 +587,47 @@ def run_extra(args):
         blk.raise_on_kernel_status()
     del model, full
     torch.cuda.empty_cache()
-    for mode, fmt_gr in (("bitmap", False), ("payload", True)):
-        blocks = stack(synth.OLMOE, 8, 700, keep_sparse_gmap=not fmt_gr, use_block_gr=fmt_gr)
-        manager = staging.GroupedQGmapCPUStagingManager(blocks, mode=mode)
-        manager.initialize()
-        recs = []
-        for T in (1, 16):
-            x = synth.synth_activations(T, 2048, seed=T).to(device)
-            for _ in range(3):
-                for l, blk in enumerate(blocks):
-                    blk.forward_streaming(x.view(1, T, 2048), manager, l)
-            torch.cuda.synchronize()
-            manager.overlap_report()
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            reps = 10
-            for _ in range(reps):
-                for l, blk in enumerate(blocks):
-                    blk.forward_streaming(x.view(1, T, 2048), manager, l)
-            stop.record()
-            torch.cuda.synchronize()
-            ms = start.elapsed_time(stop) / reps
-            rep = manager.overlap_report()
-            # the same step as one CUDA graph (kernels on two streams, ordered by events)
-            graph_ms, graph_err = None, None
-            try:
-                manager.collect_timings = False
+    # host link peak: one large copy from pinned host memory by the copy engine (what the pager, which reads
+    # the same kind of buffer from inside a kernel, is compared with)
+    pinned = torch.empty((256 << 20,), dtype=torch.uint8, pin_memory=True)
+    pinned.fill_(1)
+    landing = torch.empty_like(pinned, device=device)
+    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = 0.0
+    for _ in range(4):
+        h0.record()
+        landing.copy_(pinned, non_blocking=True)
+        h1.record()
+        torch.cuda.synchronize()
+        best = max(best, pinned.numel() / (h0.elapsed_time(h1) * 1e-3) / 1e9)
+    out["host_to_device_copy_gbs"] = round(best, 2)
+    del pinned, landing
 
-                def step():
-                    for l, blk in enumerate(blocks):
-                        blk.forward_streaming(x.view(1, T, 2048), manager, l)
+    def stack_cycled(shape, layers, distinct, seed, **kw):
+        """`layers` blocks built from `distinct` synthetic layers (each block gets its own pinned host copy)."""
+        made = [synth.synth_layer(shape, seed=seed + l, **kw) for l in range(distinct)]
+        blocks = []
+        for l in range(layers):
+            layer = made[l % distinct]
+            fresh = lambda p: {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in layer[p].items()}
+            blk = tm.TrisSparseMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
+            blk.load_grouped_payloads(fresh("gate"), fresh("up"), fresh("down"), layer["shared_gate"], layer["shared_up"],
+                                      layer["shared_down"], layer["router_weight"], device=device)
+            blocks.append(blk)
+        return blocks
 
-                graph = capture(step)
-                graph_ms = time_replays(graph, 10, 3)
-                del graph
-            except Exception as exc:  # noqa: BLE001
-                graph_ms, graph_err = None, str(exc)[:160]
-                torch.cuda.synchronize()
-            finally:
-                manager.collect_timings = True
-            recs.append({"tokens": T, "us_per_layer": round(ms * 1e3 / len(blocks), 2), "tokens_per_s": round(T / (ms * 1e-3), 1),
-                         "graph_us_per_layer": None if graph_ms is None else round(graph_ms * 1e3 / len(blocks), 2),
-                         "graph_tokens_per_s": None if graph_ms is None else round(T / (graph_ms * 1e-3), 1),
-                         "graph_error": graph_err,
-                         "overlapped_fraction": None if rep["overlapped_fraction"] is None else round(rep["overlapped_fraction"], 3),
-                         "copy_ms_per_layer": round(rep["copy_ms"] / max(1, rep["layers"]), 4),
-                         "staging_buffer_mb": round(manager.buffer_nbytes / 1e6, 1)})
-        out["streaming_" + mode] = recs
-        del blocks, manager
-        torch.cuda.empty_cache()
+    # BASELINE config 4 (streaming): a Qwen3.5-35B-A3B-shaped stack of 40 layers (256 experts, top-8, hidden 2048,
+    # intermediate 512), batch 1 and 16; and the 8-layer OLMoE-shaped stack
+    for prefix, shape, n_layers, distinct in (("streaming_qwen35_40_layers_", synth.QWEN35, 40, 4), ("streaming_", synth.OLMOE, 8, 8)):
+        for mode, fmt_gr in (("bitmap", False), ("payload", True)):
+            blocks = stack_cycled(shape, n_layers, distinct, 700, keep_sparse_gmap=not fmt_gr, use_block_gr=fmt_gr)
+            manager = staging.GroupedQGmapCPUStagingManager(blocks, mode=mode)
+            manager.initialize()
+            out[prefix + mode] = streaming_records(blocks, manager, shape, device)
+            for blk in blocks:
+                blk.raise_on_kernel_status()
+            del blocks, manager
+            torch.cuda.empty_cache()
     print(json.dumps(out))
 
 

@@ -32,15 +32,16 @@ __global__ void __launch_bounds__(256) page_experts_kernel(const __grid_constant
   uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(job.dst) + seg * job.bytes_per_expert);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  // four independent 16-byte reads in flight per thread: host reads cross PCIe/C2C
-  for (; i + 3 * stride < vecs; i += 4 * stride) {
-    const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
-    dst[i] = a;
-    dst[i + stride] = b;
-    dst[i + 2 * stride] = c;
-    dst[i + 3 * stride] = d;
+  // eight independent 16-byte reads in flight per thread: host reads cross PCIe/C2C, whose latency
+  // (microseconds) has to be covered by bytes in flight
+  for (; i + 7 * stride < vecs; i += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldcs(src + i + j * stride);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[i + j * stride] = v[j];
   }
-  for (; i < vecs; i += stride) dst[i] = src[i];
+  for (; i < vecs; i += stride) dst[i] = __ldcs(src + i);
 }
 
 }  // namespace tris
@@ -78,7 +79,7 @@ extern "C" int tris_page_experts(const TrisPageJob* jobs, int32_t num_jobs, cons
   // Experts that get no slot (more live segments than num_segments) must not keep a stale entry:
   // the grouped kernels treat -1 as "not paged in", store nothing and report TRIS_ERR_WORKSPACE.
   TRIS_CUDA(cudaMemsetAsync(slot_table, 0xFF, sizeof(int32_t) * static_cast<size_t>(num_experts), static_cast<cudaStream_t>(stream)));
-  const int chunks = static_cast<int>(std::min<long long>(16, std::max<long long>(1, max_bytes / (256 * 16 * 4))));
+  const int chunks = static_cast<int>(std::min<long long>(16, std::max<long long>(1, max_bytes / (256 * 16 * 8))));
   page_experts_kernel<<<dim3(chunks, num_segments, num_jobs), 256, 0, static_cast<cudaStream_t>(stream)>>>(args);
   return check_cuda(cudaGetLastError(), "page_experts_kernel launch");
 }

@@ -225,7 +225,7 @@ class TrisSparseMoeBlock(nn.Module):
             if self._status_word is None or self._status_word.device != dev:
                 self._status_word = torch.zeros((1,), dtype=torch.int32, device=dev)
             rv.row_gather, rv.status_dev, rv.flags = tok.data_ptr(), self._status_word.data_ptr(), (1 if mode_gu else 0)
-            paged.wait()
+            paged.wait("gate_up")  # down keeps paging under the gate/up kernel and the down backbone
             mlp = torch.empty((R, I), dtype=f16, device=dev)
             _native.check(lib.tris_grouped_pair_forward(C.byref(paged.views["gate"]), C.byref(paged.views["up"]), C.byref(rv),
                                                         hg.data_ptr(), hu.data_ptr(), mlp.data_ptr(), None, 1, stream()),
@@ -234,6 +234,7 @@ class TrisSparseMoeBlock(nn.Module):
             _native.check(lib.tris_shared_hidden_forward(mlp.data_ptr(), None, R, None, I, self.shared_down.data_ptr(), r_d,
                                                          hd.data_ptr(), mode_d, stream()), "down backbone")
             rv.row_gather, rv.flags = None, (1 if mode_d else 0)
+            paged.wait("all")
             down = torch.empty((R, H), dtype=f16, device=dev)
             _native.check(lib.tris_grouped_forward(C.byref(paged.views["down"]), C.byref(rv), hd.data_ptr(), down.data_ptr(),
                                                    stream()), "grouped_forward")

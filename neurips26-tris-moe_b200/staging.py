@@ -94,7 +94,8 @@ class GroupedQGmapCPUStagingManager:
         self.entries = {}          # (block index, projection) -> _Entry
         self.buffers = {}          # (ring slot, projection, key) -> device staging tensor
         self.slot_tables = []      # per ring slot: int32 [E] expert -> staging slot
-        self._paged = []           # per ring slot: event "pager done"
+        self._paged = []           # per ring slot: event "pager done" (all three projections)
+        self._paged_gu = []        # per ring slot: event "gate and up paged" (down may still be in flight)
         self._consumed = []        # per ring slot: event "compute done with this slot"
         self._used = []
         self._copy_stream = None
@@ -147,6 +148,7 @@ class GroupedQGmapCPUStagingManager:
                 self.buffers[(ring, proj, key)] = torch.zeros((cap * per + 64,), dtype=torch.uint8, device=self.device)
             self.slot_tables.append(torch.zeros((E,), dtype=torch.int32, device=self.device))
             self._paged.append(torch.cuda.Event())
+            self._paged_gu.append(torch.cuda.Event())
             self._consumed.append(torch.cuda.Event())
             self._used.append(False)
             self._consumed_epoch.append(-1)
@@ -156,6 +158,12 @@ class GroupedQGmapCPUStagingManager:
         for entry in self.entries.values():
             for key in entry.host:
                 entry.payload[key] = torch.empty((0,), dtype=entry.host[key].dtype, device=self.device)
+            if self.mode == "payload":
+                # the resident tile-major copy of the same planes would defeat the point of paging them
+                for key in ("_tris_tile_records", "_tris_tile_desc", "_tris_col_records", "_tris_tile_meta"):
+                    entry.payload.pop(key, None)
+                view = proj_view(entry.payload)
+                view.tile_records = view.tile_desc = view.col_records = None
             entry.payload["_qgmap_staging"] = (self, entry)
         self._initialized = True
         return True
@@ -202,6 +210,8 @@ class GroupedQGmapCPUStagingManager:
                                                     table.data_ptr(), copy.cuda_stream), "page_experts")
                 self.pipeline_stats["chunks"] += 1
                 views[proj] = self._staged_view(entry, ring, proj, table)
+                if proj == "up":  # gate and up are in: the gate/up kernel may start while down is still paged
+                    self._paged_gu[ring].record(copy)
             if timed:
                 end.record(copy)
             self._paged[ring].record(copy)
@@ -235,10 +245,12 @@ class GroupedQGmapCPUStagingManager:
         """Overlapped fraction of the transfer time: 1 - (time compute stalled on a pager) /
         (pager time), from CUDA events; call after a synchronize."""
         copy_ms = stall_ms = 0.0
+        n = 0
         for c0, c1, w0, w1 in self._timings:
-            copy_ms += c0.elapsed_time(c1)
+            if c0 is not c1:  # a layer's second wait carries no copy interval of its own
+                copy_ms += c0.elapsed_time(c1)
+                n += 1
             stall_ms += w0.elapsed_time(w1)
-        n = len(self._timings)
         self._timings = []
         frac = 1.0 - stall_ms / copy_ms if copy_ms > 0 else None
         return {"layers": n, "copy_ms": copy_ms, "stall_ms": stall_ms, "overlapped_fraction": frac}
@@ -252,21 +264,30 @@ class _PagedLayer:
         self.manager, self.ring, self.views = manager, ring, views
         self._copy_start, self._copy_end = start, end
         self._waited = False
+        self._waited_gu = False
 
-    def wait(self) -> None:
-        """Makes the current (compute) stream wait for this layer's pager, timing the stall."""
-        if self._waited:
+    def wait(self, which: str = "all") -> None:
+        """Makes the current (compute) stream wait for this layer's pager, timing the stall.
+        ``which="gate_up"`` waits only until gate and up are in (the pager goes on with down, which
+        then pages under the gate/up kernel and the down backbone); ``"all"`` waits for everything."""
+        if self._waited or (which == "gate_up" and self._waited_gu):
             return
         compute = torch.cuda.current_stream(self.manager.device)
+        event = self.manager._paged_gu[self.ring] if which == "gate_up" else self.manager._paged[self.ring]
         if self._copy_start is None:
-            compute.wait_event(self.manager._paged[self.ring])
+            compute.wait_event(event)
         else:
             w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             w0.record(compute)
-            compute.wait_event(self.manager._paged[self.ring])
+            compute.wait_event(event)
             w1.record(compute)
-            self.manager._timings.append((self._copy_start, self._copy_end, w0, w1))
-        self._waited = True
+            # the copy interval is counted once (with the first wait), every wait adds its stall
+            zero = (w0, w0) if (self._waited_gu and which != "gate_up") else (self._copy_start, self._copy_end)
+            self.manager._timings.append((zero[0], zero[1], w0, w1))
+        if which == "gate_up":
+            self._waited_gu = True
+        else:
+            self._waited = True
 
     def release(self) -> None:
         """Marks the staging slots free once the kernels enqueued so far have consumed them."""
