@@ -93,7 +93,9 @@ class GroupedQGmapCPUStagingManager:
         self.device = None
         self.entries = {}          # (block index, projection) -> _Entry
         self.buffers = {}          # (ring slot, projection, key) -> device staging tensor
-        self.slot_tables = []      # per ring slot: int32 [E] expert -> staging slot
+        self.slot_tables = []      # per ring slot: {projection: int32 [E] expert -> staging slot}; one table per
+                                   # projection, because each pager call resets its table and down is paged
+                                   # while the gate/up kernel is still reading the tables of gate and up
         self._paged = []           # per ring slot: event "pager done" (all three projections)
         self._paged_gu = []        # per ring slot: event "gate and up paged" (down may still be in flight)
         self._consumed = []        # per ring slot: event "compute done with this slot"
@@ -146,7 +148,7 @@ class GroupedQGmapCPUStagingManager:
             for (proj, key), per in sizes.items():
                 # a few bytes of slack: the GR span copy may round its end up to 16 bytes
                 self.buffers[(ring, proj, key)] = torch.zeros((cap * per + 64,), dtype=torch.uint8, device=self.device)
-            self.slot_tables.append(torch.zeros((E,), dtype=torch.int32, device=self.device))
+            self.slot_tables.append({proj: torch.full((E,), -1, dtype=torch.int32, device=self.device) for proj in PROJECTIONS})
             self._paged.append(torch.cuda.Event())
             self._paged_gu.append(torch.cuda.Event())
             self._consumed.append(torch.cuda.Event())
@@ -188,7 +190,7 @@ class GroupedQGmapCPUStagingManager:
             copy.wait_event(self._consumed[ring])
             self.pipeline_stats["slot_reuses"] += 1
         nseg_bound = min(int(route["experts"]), int(route["rows"]), self.capacity)
-        table = self.slot_tables[ring]
+        tables = self.slot_tables[ring]
         timed = self.collect_timings
         start = end = None
         if timed:
@@ -207,9 +209,9 @@ class GroupedQGmapCPUStagingManager:
                     self.pipeline_stats["bytes"] += nseg_bound * entry.block_bytes[key]
                 _native.check(lib.tris_page_experts(jobs, len(entry.host), route["expert_ids"].data_ptr(),
                                                     route["counts"].data_ptr(), nseg_bound, int(route["experts"]),
-                                                    table.data_ptr(), copy.cuda_stream), "page_experts")
+                                                    tables[proj].data_ptr(), copy.cuda_stream), "page_experts")
                 self.pipeline_stats["chunks"] += 1
-                views[proj] = self._staged_view(entry, ring, proj, table)
+                views[proj] = self._staged_view(entry, ring, proj, tables[proj])
                 if proj == "up":  # gate and up are in: the gate/up kernel may start while down is still paged
                     self._paged_gu[ring].record(copy)
             if timed:
