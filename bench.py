@@ -587,6 +587,26 @@ def run_extra(args):
         blk.raise_on_kernel_status()
     del model, full
     torch.cuda.empty_cache()
+    # 4-bit backbones read in place (2048 x 2048, 128-column groups) against their fp16 expansion on the
+    # skinny / tcgen05 GEMMs: 80 distinct matrices per pass (160 MB of nibbles, 640 MB of fp16: both beyond L2)
+    from trismoe_b200 import Packed4Linear, compute_shared_hidden, dequantize_packed_4bit
+
+    rng = __import__("numpy").random.default_rng(0)
+    mats = [synth.packed4_matrix(rng, 2048, 2048, 128) for _ in range(80)]
+    packed = [Packed4Linear(m, device) for m in mats]
+    dense = [dequantize_packed_4bit(m, device) for m in mats]
+    out["packed4_backbone_2048x2048"] = []
+    for T in (1, 16, 128):
+        x = synth.synth_activations(T, 2048, seed=T).to(device)
+        g4 = capture(lambda: [p(x, 3) for p in packed])
+        g16 = capture(lambda: [compute_shared_hidden(x, w, layout=3) for w in dense])
+        t4, t16 = time_replays(g4, 10, 3) / len(mats), time_replays(g16, 10, 3) / len(mats)
+        out["packed4_backbone_2048x2048"].append({
+            "tokens": T, "nibbles_us": round(t4 * 1e3, 2), "fp16_us": round(t16 * 1e3, 2),
+            "nibbles_gbs": round(packed[0].nbytes / (t4 * 1e-3) / 1e9, 1), "fp16_gbs": round(dense[0].numel() * 2 / (t16 * 1e-3) / 1e9, 1)})
+        del g4, g16
+    del mats, packed, dense
+    torch.cuda.empty_cache()
     # host link peak: one large copy from pinned host memory by the copy engine (what the pager, which reads
     # the same kind of buffer from inside a kernel, is compared with)
     pinned = torch.empty((256 << 20,), dtype=torch.uint8, pin_memory=True)

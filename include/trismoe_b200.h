@@ -30,7 +30,7 @@ extern "C" {
 
 /* Mirrors TRIS_COMPACT3_KERNEL_ABI_VERSION (CPP:1138-1139); the payload layout is ABI 2. */
 #define TRIS_COMPACT3_KERNEL_ABI_VERSION 2
-#define TRIS_B200_ABI_VERSION 3
+#define TRIS_B200_ABI_VERSION 4
 
 enum {
   TRIS_OK = 0,
@@ -340,6 +340,53 @@ int tris_packed4_dequantize(const int32_t* qweight, const int32_t* qzeros, const
                             const int32_t* g_idx, int32_t rows, int32_t cols, int32_t num_groups,
                             void* weight_f16, void* stream);
 
+/*
+ * One or several GPTQ-style 4-bit matrices inside shared tensors, as the reference concatenates the
+ * null-space matrices of a layer's experts (build_grouped_ns_compensation_payload, QL:1734-1882):
+ * expert e's matrix has n outputs and k inputs and is found at
+ *   qweight[(kw_off[e] + k/8) * q_ld + n_off[e] + n]           (nibble k%8 of the word)
+ *   qzeros [(g_off[e] + group) * z_ld + z_off[e] + n/8]        (nibble n%8; zero point minus one)
+ *   scales [(g_off[e] + group) * s_ld + n_off[e] + n]          fp16
+ * with group = min(k / group_size, groups - 1) (group_size <= 0: one group).  Any of the offset /
+ * count arrays may be NULL (offset 0, the common n / k / num_groups).  C2 of the reference payload:
+ * n_off = ns_c2_rank_offsets, z_off = ns_c2_rank_word_offsets, n_count = ns_rank_per_expert,
+ * k = infeatures.  C1: kw_off = ns_c1_rank_word_offsets, g_off = ns_c1_group_offsets, k_count =
+ * ns_rank_per_expert, n = outfeatures.  A single PackedQuantMatrix4bit (QL:2637-2784) with uniform
+ * groups is the case num_experts = 1 with every array NULL.
+ */
+typedef struct TrisPacked4View {
+  const int32_t* qweight;
+  const int32_t* qzeros;
+  const void* scales;        /* fp16 */
+  const int32_t* n_off;      /* [num_experts] or NULL */
+  const int32_t* z_off;      /* [num_experts] or NULL */
+  const int32_t* kw_off;     /* [num_experts] or NULL */
+  const int32_t* g_off;      /* [num_experts] or NULL */
+  const int32_t* n_count;    /* [num_experts] or NULL: outputs of each expert (<= n)  */
+  const int32_t* k_count;    /* [num_experts] or NULL: inputs of each expert (<= k)   */
+  const int32_t* g_count;    /* [num_experts] or NULL: groups of each expert          */
+  int32_t q_ld, z_ld, s_ld;  /* elements per row of qweight / qzeros / scales         */
+  int32_t n, k, num_groups, group_size, num_experts;
+} TrisPacked4View;
+
+/*
+ * out[row, :] (+)= x[row, :] . dequant(W_e)^T for every routed segment (rows of segment s use the
+ * matrix of expert_ids[s]); route == NULL: one problem, expert 0, all num_rows rows.  Replaces
+ * grouped_ns_compensation_forward / run_grouped_ns_c1_forward (QL:2024-2128, 1963-2021;
+ * GroupedPacked4LinearOffset{Segment,Decode}{C2,C1}, CU:1208-2144) - call it once with the C2 view
+ * (out = hidden [R, max_ns_rank]) and once with the C1 view - and, with route == NULL, the packed
+ * backbone product of _run_packed_4bit_linear_cuda (QL:1148-1168; Packed4LinearKernelTiledLop3,
+ * CU:914-1104).  Weights are fp16((q - zero) * scale) bit for bit as PackedQuantMatrix4bit.dequantize
+ * builds them, sums are fp32, results rounded to fp16 once.  accumulate != 0: out = fp16(out + result)
+ * (what out.add_(compensation) does, QL:2620-2633).  route->row_gather, when set, names the source
+ * row of x for every grouped row.  out_mode: TRIS_OUT_F16, _PAIR_INTERLEAVED or _LANE_ORDER.  Group
+ * sizes must be multiples of 32 (or the matrix has one group).  Columns >= k_count[e] of x are never
+ * read, outputs >= n_count[e] never written.
+ */
+int tris_packed4_grouped_forward(const TrisPacked4View* w, const TrisRouteView* route, const void* x_f16,
+                                 int32_t x_ld, int32_t num_rows, void* out_f16, int32_t out_ld,
+                                 int32_t out_mode, int32_t accumulate, void* stream);
+
 
 /*
  * hidden = x . shared_sv^T (QuantLinear.compute_shared_hidden fp16 branch, QL:4454-4502):
@@ -459,6 +506,12 @@ typedef struct TrisMoeLayerView {
   TrisProjView gate;          /* O = I, r = r_gu                                          */
   TrisProjView up;
   TrisProjView down;          /* O = H, r = r_d                                           */
+  /* Optional: the same backbones as 4-bit packed matrices (num_experts = 1, no offset arrays),
+     read in place by tris_packed4_grouped_forward instead of the fp16 copies above, which may
+     then be NULL (shared_sv_quant, QL:4703-4706).  gate and up switch together. */
+  const TrisPacked4View* packed_gate;
+  const TrisPacked4View* packed_up;
+  const TrisPacked4View* packed_down;
 } TrisMoeLayerView;
 
 size_t tris_moe_layer_workspace_bytes(const TrisMoeLayerView* layer, int32_t num_tokens);

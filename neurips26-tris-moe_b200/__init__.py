@@ -38,9 +38,19 @@ from .compact3_linear import (  # noqa: F401
     run_compact3_gate_up_forward,
     run_compact3_qkv_forward,
 )
+from .ns_compensation import (  # noqa: F401
+    Packed4Linear,
+    build_grouped_ns_compensation_payload,
+    run_grouped_ns_c1_forward,
+    run_grouped_ns_compensation_forward,
+)
 from . import clocks, envflags, expert_parallel, synth  # noqa: F401
 
 __all__ = [
+    "Packed4Linear",
+    "build_grouped_ns_compensation_payload",
+    "run_grouped_ns_c1_forward",
+    "run_grouped_ns_compensation_forward",
     "Compact3Linear",
     "run_compact3_gate_up_forward",
     "run_compact3_qkv_forward",

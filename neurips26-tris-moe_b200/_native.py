@@ -39,7 +39,7 @@ class TrisPageJob(C.Structure):
     _fields_ = [("host_src", _vp), ("dst", _vp), ("bytes_per_expert", C.c_int64)]
 
 
-ABI_VERSION = 3  # TRIS_B200_ABI_VERSION of include/trismoe_b200.h
+ABI_VERSION = 4  # TRIS_B200_ABI_VERSION of include/trismoe_b200.h
 
 
 class TrisRouteView(C.Structure):
@@ -51,12 +51,23 @@ class TrisRouteView(C.Structure):
     ]
 
 
+class TrisPacked4View(C.Structure):
+    _fields_ = [
+        ("qweight", _vp), ("qzeros", _vp), ("scales", _vp),
+        ("n_off", _vp), ("z_off", _vp), ("kw_off", _vp), ("g_off", _vp),
+        ("n_count", _vp), ("k_count", _vp), ("g_count", _vp),
+        ("q_ld", _i32), ("z_ld", _i32), ("s_ld", _i32),
+        ("n", _i32), ("k", _i32), ("num_groups", _i32), ("group_size", _i32), ("num_experts", _i32),
+    ]
+
+
 class TrisMoeLayerView(C.Structure):
     _fields_ = [
         ("hidden_size", _i32), ("intermediate_size", _i32), ("num_experts", _i32), ("top_k", _i32),
         ("norm_topk_prob", _i32),
         ("router_weight", _vp), ("shared_gate", _vp), ("shared_up", _vp), ("shared_down", _vp),
         ("gate", TrisProjView), ("up", TrisProjView), ("down", TrisProjView),
+        ("packed_gate", _vp), ("packed_up", _vp), ("packed_down", _vp),
     ]
 
 
@@ -91,6 +102,7 @@ SIGNATURES = {
     "tris_router_topk": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "tris_input_projections": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i32, _vp, _vp]),
     "tris_packed4_dequantize": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "tris_packed4_grouped_forward": (C.c_int, [_P(TrisPacked4View), _P(TrisRouteView), _vp, _i32, _i32, _vp, _i32, _i32, _i32, _vp]),
     "tris_shared_hidden_forward": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _vp]),
     "tris_grouped_forward": (C.c_int, [_P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp]),
     "tris_grouped_pair_forward": (C.c_int, [_P(TrisProjView), _P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp, _vp, _i32, _vp]),

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libtrismoe_b200.so")
 LAST_LOG = ""
-SOURCES = ["grouped.cu", "grouped_tiled.cu", "tile_records.cu", "skinny_gemm.cu", "route.cu", "layer.cu", "paging.cu", "tc_gemm.cu", "grouped_umma.cu", "ep_peer.cu", "packed4.cu", "abi.cpp"]
+SOURCES = ["grouped.cu", "grouped_tiled.cu", "tile_records.cu", "skinny_gemm.cu", "route.cu", "layer.cu", "paging.cu", "tc_gemm.cu", "grouped_umma.cu", "ep_peer.cu", "packed4.cu", "packed4_gemm.cu", "abi.cpp"]
 HEADERS = ["common.cuh", "compact3_tile.cuh", "tile_records.cuh", "umma.cuh", os.path.join("..", "..", "include", "trismoe_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

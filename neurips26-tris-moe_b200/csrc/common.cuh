@@ -8,6 +8,7 @@
 #include "../../include/trismoe_b200.h"
 
 static_assert(sizeof(TrisProjView) == 224, "TrisProjView layout is part of the ABI");
+static_assert(sizeof(TrisPacked4View) == 112, "TrisPacked4View layout changed: update the ctypes mirror");
 static_assert(sizeof(TrisRouteView) == 80, "TrisRouteView layout is part of the ABI");
 
 namespace tris {

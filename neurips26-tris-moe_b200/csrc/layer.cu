@@ -67,7 +67,14 @@ static int validate_layer(const TrisMoeLayerView* L) {
                    L->top_k <= L->num_experts,
                TRIS_ERR_INVALID_ARG, "moe layer: bad dims H=%d I=%d E=%d k=%d", L->hidden_size, L->intermediate_size,
                L->num_experts, L->top_k);
-  TRIS_REQUIRE(L->shared_gate && L->shared_up && L->shared_down, TRIS_ERR_INVALID_ARG, "moe layer: backbone matrices missing");
+  const bool packed_gu = L->packed_gate && L->packed_up;
+  TRIS_REQUIRE((packed_gu || (L->shared_gate && L->shared_up)) && (L->packed_down || L->shared_down), TRIS_ERR_INVALID_ARG,
+               "moe layer: backbone matrices missing");
+  TRIS_REQUIRE(!packed_gu || (L->packed_gate->n == L->gate.rank && L->packed_up->n == L->up.rank &&
+                              L->packed_gate->k == L->hidden_size && L->packed_up->k == L->hidden_size),
+               TRIS_ERR_INVALID_ARG, "moe layer: packed gate/up backbones do not match rank / hidden size");
+  TRIS_REQUIRE(!L->packed_down || (L->packed_down->n == L->down.rank && L->packed_down->k == L->intermediate_size),
+               TRIS_ERR_INVALID_ARG, "moe layer: packed down backbone does not match rank / intermediate size");
   TRIS_REQUIRE(L->gate.out_features == L->intermediate_size && L->up.out_features == L->intermediate_size &&
                    L->down.out_features == L->hidden_size,
                TRIS_ERR_INVALID_ARG, "moe layer: projection out_features do not match H/I");
@@ -124,8 +131,11 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
   const int down_mode = hidden_mode(layer->down, layer->down);
   SkinnyProblem probs[3];
   int np = 0;
-  probs[np++] = {static_cast<const __half*>(layer->shared_gate), w.hidden_gate, layer->gate.rank, gu_mode};
-  probs[np++] = {static_cast<const __half*>(layer->shared_up), w.hidden_up, layer->up.rank, gu_mode};
+  const bool packed_gu = layer->packed_gate && layer->packed_up;  // 4-bit backbones are read in place
+  if (!packed_gu) {
+    probs[np++] = {static_cast<const __half*>(layer->shared_gate), w.hidden_gate, layer->gate.rank, gu_mode};
+    probs[np++] = {static_cast<const __half*>(layer->shared_up), w.hidden_up, layer->up.rank, gu_mode};
+  }
   const bool logits_given = router_logits != nullptr;
   const float* logits = router_logits;
   if (logits_given) {
@@ -146,8 +156,18 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
     st = route_launch();
     if (st != TRIS_OK) return st;
   }
-  st = launch_shared_hidden(probs, np, x, nullptr, T, layer->hidden_size, s, /*pdl=*/logits_given);
-  if (st != TRIS_OK) return st;
+  if (np > 0) {
+    st = launch_shared_hidden(probs, np, x, nullptr, T, layer->hidden_size, s, /*pdl=*/logits_given);
+    if (st != TRIS_OK) return st;
+  }
+  if (packed_gu) {
+    st = tris_packed4_grouped_forward(layer->packed_gate, nullptr, x, layer->hidden_size, T, w.hidden_gate, layer->gate.rank,
+                                      gu_mode, 0, s);
+    if (st != TRIS_OK) return st;
+    st = tris_packed4_grouped_forward(layer->packed_up, nullptr, x, layer->hidden_size, T, w.hidden_up, layer->up.rank, gu_mode,
+                                      0, s);
+    if (st != TRIS_OK) return st;
+  }
   if (!logits_given) {
     st = route_launch();
     if (st != TRIS_OK) return st;
@@ -168,8 +188,13 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
   if (st != TRIS_OK) return st;
 
   // down backbone on routed rows
-  SkinnyProblem down{static_cast<const __half*>(layer->shared_down), w.hidden_down, layer->down.rank, down_mode};
-  st = launch_shared_hidden(&down, 1, w.mlp, nullptr, R, layer->intermediate_size, s, /*pdl=*/true);
+  if (layer->packed_down) {
+    st = tris_packed4_grouped_forward(layer->packed_down, nullptr, w.mlp, layer->intermediate_size, R, w.hidden_down,
+                                      layer->down.rank, down_mode, 0, s);
+  } else {
+    SkinnyProblem down{static_cast<const __half*>(layer->shared_down), w.hidden_down, layer->down.rank, down_mode};
+    st = launch_shared_hidden(&down, 1, w.mlp, nullptr, R, layer->intermediate_size, s, /*pdl=*/true);
+  }
   if (st != TRIS_OK) return st;
 
   // grouped down: the route is older than the GEMM before it, so weights stage early

@@ -18,9 +18,11 @@ from torch import nn
 
 from . import _native, envflags
 from ._native import TrisMoeLayerView
+from .ns_compensation import Packed4Linear
 from .qlinear_grouped import (
     build_grouped_route,
     compute_shared_hidden,
+    dequantize_packed_4bit,
     prepare_grouped_payload,
     proj_view,
     run_grouped_structured_expert_forward,
@@ -48,33 +50,71 @@ class TrisSparseMoeBlock(nn.Module):
         self.register_buffer("shared_gate", torch.zeros((0, 0), dtype=torch.float16))
         self.register_buffer("shared_up", torch.zeros((0, 0), dtype=torch.float16))
         self.register_buffer("shared_down", torch.zeros((0, 0), dtype=torch.float16))
+        self.packed_backbones: dict = {}  # name -> Packed4Linear: backbones kept in their 4-bit nibbles
         self._grouped_payload_cache: dict = {}
         self._layer_view: Optional[TrisMoeLayerView] = None
+        self._expanded_view: Optional[TrisMoeLayerView] = None
         self._workspace: Optional[torch.Tensor] = None
         self._status_word: Optional[torch.Tensor] = None  # status of the kernels forward_streaming launches
 
     # -- loading ---------------------------------------------------------------------------
-    def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate: torch.Tensor,
-                              shared_up: torch.Tensor, shared_down: torch.Tensor,
-                              router_weight: Optional[torch.Tensor] = None, device=None) -> "TrisSparseMoeBlock":
+    # rows per call above which 4-bit backbones are expanded to fp16 scratch and run on the tcgen05 GEMM
+    PACKED_BACKBONE_MAX_ROWS = 256
+    _expand_scratch: dict = {}  # (device, name, shape) -> fp16 scratch shared by every block of a model
+
+    def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate, shared_up, shared_down,
+                              router_weight: Optional[torch.Tensor] = None, device=None,
+                              packed_backbone: Optional[str] = None) -> "TrisSparseMoeBlock":
         """Attaches the E-stacked payloads (``enable_grouped_deployment_only``,
-        modeling_olmoe.py:732-804) and the three fp16 backbones, moving everything to
-        ``device`` and deriving the decode index once."""
+        modeling_olmoe.py:732-804) and the three backbones, moving everything to ``device`` and
+        deriving the decode index once.  A backbone is an fp16 matrix ``[r, in]`` or, as real
+        checkpoints store it, a 4-bit packed payload dict (``shared_sv_quant``: ``qweight``, ``qzeros``,
+        ``scales``, ``g_idx``, ``rows``, ``cols``).  ``packed_backbone`` (default: the environment
+        variable ``TRIS_PACKED4_BACKBONE``, else ``"nibbles"``) says how packed backbones are kept:
+        ``"nibbles"`` - in place, read by the 4-bit GEMM (a quarter of the bytes; gate and up switch
+        together, matrices with non-uniform groups are expanded), ``"fp16"`` - expanded once at load."""
+        import os
+
         dev = torch.device(device) if device is not None else gate["qweight1"].device
         self._grouped_payload_cache = {
             "gate": prepare_grouped_payload(gate, dev),
             "up": prepare_grouped_payload(up, dev),
             "down": prepare_grouped_payload(down, dev),
         }
-        self.shared_gate = shared_gate.to(dev, torch.float16).contiguous()
-        self.shared_up = shared_up.to(dev, torch.float16).contiguous()
-        self.shared_down = shared_down.to(dev, torch.float16).contiguous()
+        mode = (packed_backbone or os.environ.get("TRIS_PACKED4_BACKBONE", "nibbles")).lower()
+        if mode not in ("nibbles", "fp16"):
+            raise ValueError("packed_backbone must be 'nibbles' or 'fp16'")
+        given = {"gate": shared_gate, "up": shared_up, "down": shared_down}
+        is_packed = {n: isinstance(m, dict) and "qweight" in m for n, m in given.items()}
+        keep = {n: mode == "nibbles" and is_packed[n] and Packed4Linear.supports(m) for n, m in given.items()}
+        keep["gate"] = keep["up"] = keep["gate"] and keep["up"]
+        self.packed_backbones = {}
+        for name, m in given.items():
+            if keep[name]:
+                self.packed_backbones[name] = Packed4Linear(m, dev)
+                dense = torch.zeros((0, 0), dtype=torch.float16, device=dev)
+            elif is_packed[name]:
+                dense = dequantize_packed_4bit(m, dev)
+            else:
+                dense = m.to(dev, torch.float16).contiguous()
+            setattr(self, "shared_" + name, dense)
         if router_weight is not None:
             self.gate.weight = nn.Parameter(router_weight.to(dev, torch.float16).contiguous(), requires_grad=False)
         else:
             self.gate.to(dev)
-        self._layer_view = None
+        self._layer_view = self._expanded_view = None
         return self
+
+    def backbone_rank(self, name: str) -> int:
+        p = self.packed_backbones.get(name)
+        return p.rows if p is not None else int(getattr(self, "shared_" + name).shape[0])
+
+    def backbone_hidden(self, name: str, x: torch.Tensor, layout: int = 0) -> torch.Tensor:
+        """``x . backbone^T`` (``compute_shared_hidden``) for the fp16 or the 4-bit form of a backbone."""
+        p = self.packed_backbones.get(name)
+        if p is not None:
+            return p(x, layout)
+        return compute_shared_hidden(x, getattr(self, "shared_" + name), layout=layout)
 
     def _get_grouped_payload(self, cache_key: str) -> dict:
         if cache_key not in self._grouped_payload_cache:
@@ -88,14 +128,44 @@ class TrisSparseMoeBlock(nn.Module):
             v.hidden_size, v.intermediate_size = self.hidden_size, self.intermediate_size
             v.num_experts, v.top_k, v.norm_topk_prob = self.num_experts, self.top_k, int(self.norm_topk_prob)
             v.router_weight = self.gate.weight.data_ptr()
-            v.shared_gate = self.shared_gate.data_ptr()
-            v.shared_up = self.shared_up.data_ptr()
-            v.shared_down = self.shared_down.data_ptr()
+            for name in ("gate", "up", "down"):
+                p = self.packed_backbones.get(name)
+                setattr(v, "shared_" + name, None if p is not None else getattr(self, "shared_" + name).data_ptr())
+                setattr(v, "packed_" + name, None if p is None else C.addressof(p._view))
             v.gate, v.up, v.down = views
             for k in ("gate", "up", "down"):
                 self._get_grouped_payload(k)["_tris_layer_dirty"] = False
-            self._layer_view = v
+            self._layer_view, self._expanded_view = v, None
         return self._layer_view
+
+    def _expanded_layer_view(self, dev) -> TrisMoeLayerView:
+        """The layer view with every 4-bit backbone expanded into fp16 scratch (enqueued on the current
+        stream): what large batches use, where the dense tcgen05 GEMM beats re-expanding nibbles for
+        every 128 rows.  The scratch is shared by all blocks of a model."""
+        base = self.layer_view()
+        if self._expanded_view is None:
+            v = TrisMoeLayerView()
+            C.pointer(v)[0] = base
+            self._expanded_view = v
+        v = self._expanded_view
+        lib = _native.load()
+        for name, p in self.packed_backbones.items():
+            key = (str(dev), name, p.rows, p.cols)
+            scratch = TrisSparseMoeBlock._expand_scratch.get(key)
+            if scratch is None:
+                scratch = torch.empty((p.rows, p.cols), dtype=torch.float16, device=dev)
+                TrisSparseMoeBlock._expand_scratch[key] = scratch
+            g_idx = getattr(p, "_g_idx", None)
+            if g_idx is None:
+                g_idx = (torch.arange(p.cols, device=dev, dtype=torch.int32) // max(1, p.group_size)).clamp_(max=p.groups - 1)
+                p._g_idx = g_idx.contiguous()
+            with torch.cuda.device(dev):
+                _native.check(lib.tris_packed4_dequantize(p.qweight.data_ptr(), p.qzeros.data_ptr(), p.scales.data_ptr(),
+                                                          p._g_idx.data_ptr(), p.rows, p.cols, p.groups, scratch.data_ptr(),
+                                                          torch.cuda.current_stream(dev).cuda_stream), "packed4_dequantize")
+            setattr(v, "shared_" + name, scratch.data_ptr())
+            setattr(v, "packed_" + name, None)
+        return v
 
     def workspace(self, num_tokens: int, device) -> torch.Tensor:
         lib = _native.load()
@@ -163,9 +233,12 @@ class TrisSparseMoeBlock(nn.Module):
             logits_in, logits_out = None, logits.data_ptr()
         if T:
             ws = self.workspace(T, dev)
+            view = self.layer_view()
+            if self.packed_backbones and T * self.top_k > self.PACKED_BACKBONE_MAX_ROWS:
+                view = self._expanded_layer_view(dev)
             with torch.cuda.device(dev):
                 _native.check(
-                    lib.tris_moe_layer_forward(C.byref(self.layer_view()), x.data_ptr(), logits_in, T, y.data_ptr(),
+                    lib.tris_moe_layer_forward(C.byref(view), x.data_ptr(), logits_in, T, y.data_ptr(),
                                                logits_out, ws.data_ptr(), ws.numel(),
                                                torch.cuda.current_stream(dev).cuda_stream),
                     "moe_layer_forward",
@@ -212,13 +285,10 @@ class TrisSparseMoeBlock(nn.Module):
             route = {"expert_ids": ids, "segment_offsets": seg, "counts": counts, "experts": E, "rows": R}
             paged = manager.page_layer(block_index, route)  # side stream, starts now
 
-            r_gu, r_d = int(self.shared_gate.shape[0]), int(self.shared_down.shape[0])
+            r_gu, r_d = self.backbone_rank("gate"), self.backbone_rank("down")
             mode_gu, mode_d = (2 if r_gu % 32 == 0 else 0), (2 if r_d % 32 == 0 else 0)
-            hg = torch.empty((T, r_gu), dtype=f16, device=dev)
-            hu = torch.empty((T, r_gu), dtype=f16, device=dev)
-            for sv, out in ((self.shared_gate, hg), (self.shared_up, hu)):
-                _native.check(lib.tris_shared_hidden_forward(x.data_ptr(), None, T, None, H, sv.data_ptr(), r_gu,
-                                                             out.data_ptr(), mode_gu, stream()), "backbone")
+            hg = self.backbone_hidden("gate", x, mode_gu)
+            hu = self.backbone_hidden("up", x, mode_gu)
             rv = _native.TrisRouteView()
             rv.expert_ids, rv.segment_offsets, rv.num_segments_dev = ids.data_ptr(), seg.data_ptr(), counts.data_ptr()
             rv.num_segments, rv.num_rows, rv.max_rows_per_segment = min(E, R), R, T
@@ -230,9 +300,7 @@ class TrisSparseMoeBlock(nn.Module):
             _native.check(lib.tris_grouped_pair_forward(C.byref(paged.views["gate"]), C.byref(paged.views["up"]), C.byref(rv),
                                                         hg.data_ptr(), hu.data_ptr(), mlp.data_ptr(), None, 1, stream()),
                           "grouped_pair_forward")
-            hd = torch.empty((R, r_d), dtype=f16, device=dev)
-            _native.check(lib.tris_shared_hidden_forward(mlp.data_ptr(), None, R, None, I, self.shared_down.data_ptr(), r_d,
-                                                         hd.data_ptr(), mode_d, stream()), "down backbone")
+            hd = self.backbone_hidden("down", mlp, mode_d)
             rv.row_gather, rv.flags = None, (1 if mode_d else 0)
             paged.wait("all")
             down = torch.empty((R, H), dtype=f16, device=dev)
@@ -261,12 +329,12 @@ class TrisSparseMoeBlock(nn.Module):
         tok, slots = route["grouped_token_indices"], route["grouped_slots"]
         x_grouped = x.index_select(0, tok)
         grouped_routing = routing[tok, slots].unsqueeze(-1)
-        gate_hidden = compute_shared_hidden(x, self.shared_gate).index_select(0, tok)
-        up_hidden = compute_shared_hidden(x, self.shared_up).index_select(0, tok)
+        gate_hidden = self.backbone_hidden("gate", x).index_select(0, tok)
+        up_hidden = self.backbone_hidden("up", x).index_select(0, tok)
         gate_out, up_out = run_grouped_structured_expert_pair_forward(
             self._get_grouped_payload("gate"), self._get_grouped_payload("up"), gate_hidden, up_hidden, x_grouped, route)
         mlp = torch.nn.functional.silu(gate_out) * up_out
-        down_hidden = compute_shared_hidden(mlp, self.shared_down)
+        down_hidden = self.backbone_hidden("down", mlp)
         down_out = run_grouped_structured_expert_forward(self._get_grouped_payload("down"), down_hidden, mlp, route)
         final = x.new_zeros(x.shape)
         final.index_add_(0, tok, (down_out * grouped_routing).to(x.dtype))

@@ -459,11 +459,14 @@ def _ns_payload_is_noop(ns_payload) -> bool:
     if ns_payload is None:
         return True
     if isinstance(ns_payload, dict):
-        rank = ns_payload.get("rank", ns_payload.get("ns_rank", 0))
-        try:
-            return int(rank) == 0
-        except (TypeError, ValueError):
-            return False
+        for key in ("max_ns_rank", "rank", "ns_rank"):
+            if key in ns_payload:
+                v = ns_payload[key]
+                try:
+                    return int(v.item() if isinstance(v, torch.Tensor) else v) == 0
+                except (TypeError, ValueError):
+                    return False
+        return True
     return False
 
 
@@ -500,8 +503,10 @@ def run_grouped_structured_expert_forward(
         payload_or_modules, hidden_grouped.device, hidden_grouped.dtype)
     if payload is None:
         return envflags.return_or_raise_none("run_grouped_structured_expert_forward", "no grouped payload")
-    if not _ns_payload_is_noop(ns_payload):
-        raise RuntimeError("trismoe_b200: null-space compensation of rank > 0 is not supported by this build")
+    with_ns = not _ns_payload_is_noop(ns_payload)
+    if with_ns and (x_grouped is None or isinstance(route.get("_out_row_scatter"), torch.Tensor)):
+        return envflags.return_or_raise_none("run_grouped_structured_expert_forward",
+                                             "null-space compensation needs x_grouped and outputs in grouped row order")
     lib = _native.load()
     view = proj_view(payload)
     E, O, rank, _ = payload["_tris_dims"]
@@ -519,6 +524,10 @@ def run_grouped_structured_expert_forward(
             lib.tris_grouped_forward(C.byref(view), C.byref(rv), hidden.data_ptr(), out.data_ptr(), _stream_ptr(hidden.device)),
             "grouped_forward",
         )
+    if with_ns:  # out += (x . C2^T) . C1^T of each row's expert (qlinear_cuda.py:2318-2333)
+        from .ns_compensation import run_grouped_ns_compensation_forward
+
+        run_grouped_ns_compensation_forward(ns_payload, x_grouped, route, out=out, accumulate=True)
     return out
 
 
@@ -554,8 +563,12 @@ def run_grouped_structured_expert_pair_forward(
     pb = payload_or_modules_b if isinstance(payload_or_modules_b, dict) else build_grouped_precomputed_payload(payload_or_modules_b, dev, dt)
     if pa is None or pb is None:
         return envflags.return_or_raise_none("run_grouped_structured_expert_pair_forward", "no grouped payload"), None
-    if not (_ns_payload_is_noop(ns_payload_a) and _ns_payload_is_noop(ns_payload_b)):
-        raise RuntimeError("trismoe_b200: null-space compensation of rank > 0 is not supported by this build")
+    ns_a, ns_b = not _ns_payload_is_noop(ns_payload_a), not _ns_payload_is_noop(ns_payload_b)
+    if (ns_a or ns_b) and (x_grouped is None or isinstance(route.get("_out_row_scatter"), torch.Tensor)):
+        return envflags.return_or_raise_none("run_grouped_structured_expert_pair_forward",
+                                             "null-space compensation needs x_grouped and outputs in grouped row order"), None
+    # the compensation is added to gate and up before the activation: with it the pair runs unfused
+    fuse_requested, fuse_silu_mul = fuse_silu_mul, bool(fuse_silu_mul) and not (ns_a or ns_b)
     lib = _native.load()
     va, vb = proj_view(pa), proj_view(pb)
     _, O, rank, _ = pa["_tris_dims"]
@@ -576,6 +589,15 @@ def run_grouped_structured_expert_pair_forward(
                                           int(bool(fuse_silu_mul)), _stream_ptr(dev)),
             "grouped_pair_forward",
         )
+    if ns_a or ns_b:  # qlinear_cuda.py:2611-2633
+        from .ns_compensation import run_grouped_ns_compensation_forward
+
+        if ns_a:
+            run_grouped_ns_compensation_forward(ns_payload_a, x_grouped, route, out=out_a, accumulate=True)
+        if ns_b:
+            run_grouped_ns_compensation_forward(ns_payload_b, x_grouped, route, out=out_b, accumulate=True)
+        if fuse_requested:
+            return (torch.nn.functional.silu(out_a.float()) * out_b.float()).to(torch.float16), None
     return out_a, out_b
 
 

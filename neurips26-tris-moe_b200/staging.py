@@ -40,6 +40,7 @@ from .qlinear_grouped import proj_view
 BITMAP_KEYS = ("q_gmap_sparse",)
 PAYLOAD_KEYS = ("qweight1", "qweight2_sparse", "q_gmap_sparse", "q_gmap_gr_words", "_tris_gr_index", "col_pack3", "row_pack3")
 PROJECTIONS = ("gate", "up", "down")
+MAX_PAGE_JOBS = 16  # TRIS_MAX_PAGE_JOBS of the C header
 
 
 class _Entry:
@@ -93,9 +94,9 @@ class GroupedQGmapCPUStagingManager:
         self.device = None
         self.entries = {}          # (block index, projection) -> _Entry
         self.buffers = {}          # (ring slot, projection, key) -> device staging tensor
-        self.slot_tables = []      # per ring slot: {projection: int32 [E] expert -> staging slot}; one table per
-                                   # projection, because each pager call resets its table and down is paged
-                                   # while the gate/up kernel is still reading the tables of gate and up
+        self.slot_tables = []      # per ring slot: {"gate" (shared with up), "down"}: int32 [E] expert -> staging
+                                   # slot; down has its own because each pager call resets its table and down is
+                                   # paged while the gate/up kernel is still reading the table of gate and up
         self._paged = []           # per ring slot: event "pager done" (all three projections)
         self._paged_gu = []        # per ring slot: event "gate and up paged" (down may still be in flight)
         self._consumed = []        # per ring slot: event "compute done with this slot"
@@ -148,7 +149,7 @@ class GroupedQGmapCPUStagingManager:
             for (proj, key), per in sizes.items():
                 # a few bytes of slack: the GR span copy may round its end up to 16 bytes
                 self.buffers[(ring, proj, key)] = torch.zeros((cap * per + 64,), dtype=torch.uint8, device=self.device)
-            self.slot_tables.append({proj: torch.full((E,), -1, dtype=torch.int32, device=self.device) for proj in PROJECTIONS})
+            self.slot_tables.append({proj: torch.full((E,), -1, dtype=torch.int32, device=self.device) for proj in ("gate", "down")})
             self._paged.append(torch.cuda.Event())
             self._paged_gu.append(torch.cuda.Event())
             self._consumed.append(torch.cuda.Event())
@@ -199,20 +200,27 @@ class GroupedQGmapCPUStagingManager:
         with torch.cuda.stream(copy):
             if timed:
                 start.record(copy)
-            for proj in PROJECTIONS:
-                entry = self.entries[(block_index, proj)]
-                jobs = (TrisPageJob * len(entry.host))()
-                for j, (key, host) in enumerate(entry.host.items()):
-                    jobs[j].host_src = host.data_ptr()
-                    jobs[j].dst = self.buffers[(ring, proj, key)].data_ptr()
-                    jobs[j].bytes_per_expert = entry.block_bytes[key]
-                    self.pipeline_stats["bytes"] += nseg_bound * entry.block_bytes[key]
-                _native.check(lib.tris_page_experts(jobs, len(entry.host), route["expert_ids"].data_ptr(),
-                                                    route["counts"].data_ptr(), nseg_bound, int(route["experts"]),
-                                                    tables[proj].data_ptr(), copy.cuda_stream), "page_experts")
-                self.pipeline_stats["chunks"] += 1
-                views[proj] = self._staged_view(entry, ring, proj, tables[proj])
-                if proj == "up":  # gate and up are in: the gate/up kernel may start while down is still paged
+            # gate and up go in one launch (they are needed together and share a slot table), down in a second one
+            # that runs while the gate/up kernel computes
+            for group in (("gate", "up"), ("down",)):
+                pairs = [(proj, key) for proj in group for key in self.entries[(block_index, proj)].host]
+                table = tables[group[0]]
+                for lo in range(0, len(pairs), MAX_PAGE_JOBS):
+                    part = pairs[lo: lo + MAX_PAGE_JOBS]
+                    jobs = (TrisPageJob * len(part))()
+                    for j, (proj, key) in enumerate(part):
+                        entry = self.entries[(block_index, proj)]
+                        jobs[j].host_src = entry.host[key].data_ptr()
+                        jobs[j].dst = self.buffers[(ring, proj, key)].data_ptr()
+                        jobs[j].bytes_per_expert = entry.block_bytes[key]
+                        self.pipeline_stats["bytes"] += nseg_bound * entry.block_bytes[key]
+                    _native.check(lib.tris_page_experts(jobs, len(part), route["expert_ids"].data_ptr(),
+                                                        route["counts"].data_ptr(), nseg_bound, int(route["experts"]),
+                                                        table.data_ptr(), copy.cuda_stream), "page_experts")
+                    self.pipeline_stats["chunks"] += 1
+                for proj in group:
+                    views[proj] = self._staged_view(self.entries[(block_index, proj)], ring, proj, table)
+                if group[0] == "gate":  # the gate/up kernel may start while down is still paged
                     self._paged_gu[ring].record(copy)
             if timed:
                 end.record(copy)

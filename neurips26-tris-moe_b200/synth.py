@@ -176,3 +176,17 @@ def projection_algorithmic_bytes(payload: dict, experts) -> int:
         else:
             total += 4 * math.ceil((r - s_e) / 32) * O + 4 * (pr + 1)
     return total
+
+
+def packed4_matrix(rng: np.random.Generator, rows: int, cols: int, group_size: int = 128, scale_std: float = 0.02) -> dict:
+    """Random 4-bit packed matrix ``[rows, cols]`` in the layout of ``PackedQuantMatrix4bit``
+    (qlinear_cuda.py:2637-2784): qweight ``[ceil(cols/8), rows]`` int32, qzeros
+    ``[groups, ceil(rows/8)]`` int32 (zero points minus one), scales ``[groups, rows]`` fp16, g_idx
+    ``[cols]`` with uniform groups."""
+    groups = max(1, -(-cols // group_size))
+    qweight = rng.integers(-2**31, 2**31, size=(-(-cols // 8), rows), dtype=np.int64).astype(np.int32)
+    qzeros = rng.integers(-2**31, 2**31, size=(groups, -(-rows // 8)), dtype=np.int64).astype(np.int32)
+    scales = np.abs(rng.normal(0, scale_std, size=(groups, rows))).astype(np.float16)
+    g_idx = np.minimum(np.arange(cols) // group_size, groups - 1).astype(np.int32)
+    return {"qweight": torch.from_numpy(qweight), "qzeros": torch.from_numpy(qzeros), "scales": torch.from_numpy(scales),
+            "g_idx": torch.from_numpy(g_idx), "rows": rows, "cols": cols}

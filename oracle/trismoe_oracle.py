@@ -269,3 +269,52 @@ def dequantize_packed4(qweight: np.ndarray, qzeros: np.ndarray, scales: np.ndarr
     diff = (intweight - zeros[g]).astype(np.float16)                                           # exact: |q - z| <= 16
     weight = (diff.astype(np.float32) * scales.astype(np.float16)[g].astype(np.float32)).astype(np.float16)
     return np.ascontiguousarray(weight.T)
+
+
+def ns_expert_matrices(payload: dict, e: int) -> tuple:
+    """(C1 [out, rank], C2 [rank, in]) fp16 of expert e from a grouped compensation payload with
+    the reference's keys and layout (build_grouped_ns_compensation_payload,
+    qlinear_cuda.py:1734-1882): C2 matrices are concatenated along the output axis of
+    ns_c2_qweight / _scales (offset ns_c2_rank_offsets[e]) and of ns_c2_qzeros (word offset
+    ns_c2_rank_word_offsets[e]); C1 matrices along the input axis of ns_c1_qweight (word-row offset
+    ns_c1_rank_word_offsets[e]) and of ns_c1_qzeros / _scales (group-row offset
+    ns_c1_group_offsets[e]).  Groups are uniform: group = min(col // group_size, groups - 1), as the
+    reference kernels index them (dot8_packed4_uniform_shared_stride, TriSMoE_cuda_kernel.cu:1119-1174).
+    Returns (None, None) for an expert of rank 0."""
+    rank = int(payload["ns_rank_per_expert"][e])
+    if rank <= 0:
+        return None, None
+    infeatures, outfeatures = int(payload["infeatures"]), int(payload["outfeatures"])
+    group_size = int(payload["group_size"])
+    off, woff = int(payload["ns_c2_rank_offsets"][e]), int(payload["ns_c2_rank_word_offsets"][e])
+    zwords = (rank + 7) // 8
+    groups2 = int(payload["ns_c2_scales"].shape[0])
+    g2 = np.minimum(np.arange(infeatures) // max(1, group_size), groups2 - 1)
+    c2 = dequantize_packed4(payload["ns_c2_qweight"][:, off:off + rank], payload["ns_c2_qzeros"][:, woff:woff + zwords],
+                            payload["ns_c2_scales"][:, off:off + rank], g2, rank, infeatures)
+    kw, go = int(payload["ns_c1_rank_word_offsets"][e]), int(payload["ns_c1_group_offsets"][e])
+    goffs = [int(v) for v in payload["ns_c1_group_offsets"]] + [int(payload["ns_c1_qzeros"].shape[0])]
+    groups1 = max(1, goffs[e + 1] - go)
+    kwords = (rank + 7) // 8
+    g1 = np.minimum(np.arange(rank) // max(1, group_size), groups1 - 1)
+    c1 = dequantize_packed4(payload["ns_c1_qweight"][kw:kw + kwords], payload["ns_c1_qzeros"][go:go + groups1],
+                            payload["ns_c1_scales"][go:go + groups1], g1, outfeatures, rank)
+    return c1, c2
+
+
+def ns_compensation_fp32(payload: dict, x_grouped: np.ndarray, expert_ids, segment_offsets) -> np.ndarray:
+    """[R, outfeatures] fp32 compensation of grouped rows: for the rows of each segment,
+    F.linear(F.linear(x, C2), C1) with the fp16 matrices of the segment's expert
+    (QuantLinear.forward, qlinear_cuda.py:4737-4747; _apply_grouped_ns_compensation,
+    qlinear_cuda.py:1917-1948), sums in fp32, the intermediate rounded to fp16 as both the
+    reference's fallback and its kernels do (TriSMoE_cuda_kernel.cu:1305); rows of experts
+    without a pair get zeros."""
+    out = np.zeros((x_grouped.shape[0], int(payload["outfeatures"])), np.float32)
+    for s, e in enumerate(expert_ids):
+        a, b = int(segment_offsets[s]), int(segment_offsets[s + 1])
+        c1, c2 = ns_expert_matrices(payload, int(e))
+        if c1 is None or b <= a:
+            continue
+        hidden = (x_grouped[a:b].astype(np.float32) @ c2.astype(np.float32).T).astype(np.float16)
+        out[a:b] = hidden.astype(np.float32) @ c1.astype(np.float32).T
+    return out

@@ -9,7 +9,9 @@ Reference code exercised (paths inside the TriS-MoE tree):
   qlinear_cuda.py: QuantLinear.pack_expert, _restore_dense_bool_matrix_from_sparse,
                    _pack_block_gr_gmap_tensor, _dequantize_compact3_matrix,
                    ExpertSharedMatrix.set_shared_sv, build_grouped_route (torch branch),
-                   PackedQuantMatrix4bit.set_quantized / dequantize                 (4-bit backbone)
+                   PackedQuantMatrix4bit.set_quantized / dequantize                 (4-bit backbone),
+                   build_grouped_ns_compensation_payload, _apply_grouped_ns_compensation,
+                   QuantLinear._get_ns_matrices                      (null-space compensation, ns_mode == 2)
   modeling_olmoe.py: OlmoeSparseMoeBlock.forward -> _forward_expert_loop  (fp16 CPU layer output)
   grouped_payload_sidecar.py: save_grouped_payload_sidecar, load_grouped_payload_from_sidecar
                    (a sidecar file written by the reference and what its own loader returns from it)
@@ -257,6 +259,55 @@ def case_backbone4(QL):
     save("backbone4.npz", out)
 
 
+def case_ns_compensation(QL):
+    """Null-space compensation: QuantLinear modules with ns_mode == 2 and 4-bit C1/C2 pairs ->
+    build_grouped_ns_compensation_payload (the grouped payload tensors) and the reference's
+    per-segment fallback _apply_grouped_ns_compensation (F.linear(F.linear(x, c2), c1) in fp16 on
+    CPU) on a grouped batch."""
+    rng = np.random.default_rng(77)
+    infeatures, outfeatures, group = 256, 96, 128
+    ranks = [16, 0, 24, 16, 40]
+
+    def packed(rows, cols, group_size):
+        groups = max(1, math.ceil(cols / group_size))
+        qweight = rng.integers(-2**31, 2**31, size=(math.ceil(cols / 8), rows), dtype=np.int64).astype(np.int32)
+        qzeros = rng.integers(-2**31, 2**31, size=(groups, math.ceil(rows / 8)), dtype=np.int64).astype(np.int32)
+        scales = np.abs(rng.normal(0, 0.02, size=(groups, rows))).astype(np.float16)
+        g_idx = np.minimum(np.arange(cols) // group_size, groups - 1).astype(np.int32)
+        return (torch.from_numpy(qweight), torch.from_numpy(qzeros), torch.from_numpy(scales), torch.from_numpy(g_idx), rows, cols)
+
+    modules = []
+    for rank in ranks:
+        m = QL.QuantLinear(1, group, infeatures, outfeatures, False)
+        if rank:
+            m.ns_mode.fill_(2)
+            m.ns_c2_quant.set_quantized(*packed(rank, infeatures, group))
+            m.ns_c1_quant.set_quantized(*packed(outfeatures, rank, group))
+        m._refresh_runtime_scalar_cache()
+        modules.append(m)
+    payload = QL.build_grouped_ns_compensation_payload(modules, torch.device("cpu"), torch.float16)
+    assert payload is not None and int(payload["max_ns_rank"]) == max(ranks)
+    out = {}
+    for k, v in payload.items():
+        out["payload_" + k] = v.numpy() if isinstance(v, torch.Tensor) else np.array(int(v), np.int64)
+    expert_ids = np.array([0, 1, 2, 4], np.int32)       # expert 3 gets no rows, expert 1 has no pair
+    lengths = np.array([3, 2, 9, 5], np.int64)
+    seg = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    x = (rng.standard_normal((int(seg[-1]), infeatures)) * 0.5).astype(np.float16)
+    tiles = np.concatenate([[0], np.cumsum((lengths + 3) // 4)]).astype(np.int32)   # 4-row problem tiles per segment
+    route = {"expert_ids": torch.from_numpy(expert_ids), "segment_offsets": torch.from_numpy(seg),
+             "problem_offsets": torch.from_numpy(tiles), "total_problem_tiles": torch.tensor([int(tiles[-1])])}
+    assert QL._coerce_grouped_route(route, torch.device("cpu")) is not None
+    comp = torch.zeros((x.shape[0], outfeatures), dtype=torch.float16)
+    QL._apply_grouped_ns_compensation(modules, torch.from_numpy(x), route, [comp])
+    for e, rank in enumerate(ranks):
+        if rank:
+            c1, c2 = modules[e]._get_ns_matrices(torch.device("cpu"), torch.float16)
+            out[f"c1_{e}"], out[f"c2_{e}"] = c1.numpy(), c2.numpy()
+    out.update(expert_ids=expert_ids, segment_offsets=seg, x=x, compensation_f16=comp.numpy(), ranks=np.array(ranks, np.int64))
+    save("ns_compensation.npz", out)
+
+
 def main():
     torch.manual_seed(0)
     QL, MO, PU = load_reference()
@@ -267,6 +318,7 @@ def main():
     case_gr_sweep(QL)
     case_layer(QL, MO, PU)
     case_backbone4(QL)
+    case_ns_compensation(QL)
 
 
 if __name__ == "__main__":

@@ -21,7 +21,7 @@ def test_every_declared_symbol_is_exported(lib):
     for name in names:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     assert set(names) == set(tm._native.SIGNATURES), "ctypes table and header disagree"
-    assert lib.tris_abi_version() == 3
+    assert lib.tris_abi_version() == tm._native.ABI_VERSION == 4
     assert lib.tris_compact3_kernel_abi_version() == 2
 
 
@@ -49,6 +49,7 @@ def test_struct_sizes_match_c_layout(lib):
     assert C.sizeof(tm._native.TrisProjView) == 224  # static_assert in csrc/common.cuh
     assert tm._native.TrisProjView.tile_records.offset == 184
     assert C.sizeof(tm._native.TrisRouteView) == 80
+    assert C.sizeof(tm._native.TrisPacked4View) == 112
     assert tm._native.TrisRouteView.row_gather.offset == 40
     assert tm._native.TrisRouteView.out_row_scatter.offset == 64
 

@@ -208,3 +208,70 @@ def test_cpu_reference_port_block_matches_reference_block(lib):
     y32 = orc.moe_layer_fp32(z["x"], logits, weights, shared, k, True)
     max_abs, mean_rel = orc.error_metrics(y, y32)
     assert max_abs <= 2e-2 and mean_rel <= 5e-3, (max_abs, mean_rel)
+
+
+# ---------------------------------------------------------------------------------------
+# null-space compensation (ns_mode == 2)
+# ---------------------------------------------------------------------------------------
+def _ns_payload(z):
+    return {k[len("payload_"):]: z[k] for k in z.files if k.startswith("payload_")}
+
+
+def test_ns_matrices_match_reference_dequantize():
+    """Per-expert C1 / C2 sliced out of the reference's grouped compensation payload and dequantised
+    by the oracle equal QuantLinear._get_ns_matrices (PackedQuantMatrix4bit.dequantize) bit for bit."""
+    z = load_golden("ns_compensation.npz")
+    payload = _ns_payload(z)
+    for e, rank in enumerate(z["ranks"]):
+        c1, c2 = orc.ns_expert_matrices(payload, e)
+        if rank == 0:
+            assert c1 is None and c2 is None
+            continue
+        assert np.array_equal(c1.view(np.uint16), z[f"c1_{e}"].view(np.uint16)), e
+        assert np.array_equal(c2.view(np.uint16), z[f"c2_{e}"].view(np.uint16)), e
+
+
+def test_ns_compensation_oracle_matches_reference_fallback():
+    """The fp32 oracle against the reference's per-segment fallback (fp16 F.linear twice on CPU):
+    within the layer tolerance; rows of the expert without a pair stay zero."""
+    z = load_golden("ns_compensation.npz")
+    got = orc.ns_compensation_fp32(_ns_payload(z), z["x"], z["expert_ids"], z["segment_offsets"])
+    want = z["compensation_f16"].astype(np.float32)
+    assert np.abs(want).mean() > 1e-3
+    max_abs, mean_rel = orc.error_metrics(got, want)
+    assert max_abs <= 2e-2 and mean_rel <= 1e-3, (max_abs, mean_rel)
+    seg = z["segment_offsets"]
+    assert not got[seg[1]:seg[2]].any() and not want[seg[1]:seg[2]].any()
+
+
+def test_ns_payload_builder_matches_reference_layout():
+    """build_grouped_ns_compensation_payload of the package reproduces the reference's payload
+    tensors (offset tables, concatenated C2 / C1) from the per-expert matrices."""
+    import torch
+
+    import trismoe_b200 as tm
+
+    z = load_golden("ns_compensation.npz")
+    ref = _ns_payload(z)
+    infeatures, outfeatures, group = int(ref["infeatures"]), int(ref["outfeatures"]), int(ref["group_size"])
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    experts = []
+    for e, rank in enumerate(int(r) for r in z["ranks"]):
+        if rank == 0:
+            experts.append(None)
+            continue
+        off, woff = int(ref["ns_c2_rank_offsets"][e]), int(ref["ns_c2_rank_word_offsets"][e])
+        kw, go = int(ref["ns_c1_rank_word_offsets"][e]), int(ref["ns_c1_group_offsets"][e])
+        zw, kwords = (rank + 7) // 8, (rank + 7) // 8
+        c2 = {"qweight": t(ref["ns_c2_qweight"][:, off:off + rank]), "qzeros": t(ref["ns_c2_qzeros"][:, woff:woff + zw]),
+              "scales": t(ref["ns_c2_scales"][:, off:off + rank]), "g_idx": t((np.arange(infeatures) // group).astype(np.int32)),
+              "rows": rank, "cols": infeatures}
+        c1 = {"qweight": t(ref["ns_c1_qweight"][kw:kw + kwords]), "qzeros": t(ref["ns_c1_qzeros"][go:go + 1]),
+              "scales": t(ref["ns_c1_scales"][go:go + 1]), "g_idx": t(np.zeros(rank, np.int32)), "rows": outfeatures, "cols": rank}
+        experts.append({"c1": c1, "c2": c2})
+    got = tm.build_grouped_ns_compensation_payload(experts, "cpu", torch.float16)
+    assert got is not None
+    for key, want in ref.items():
+        have = got[key]
+        have = have.numpy() if isinstance(have, torch.Tensor) else np.array(int(have))
+        assert np.array_equal(have, want), key
