@@ -23,10 +23,23 @@ namespace tris {
 
 constexpr int kP4Threads = 256;
 constexpr int kP4Warps = 8;
-constexpr int kP4ChunkCols = 32 * kP4Warps;       // contraction columns staged per step
-constexpr int kP4RowHalfs = kP4ChunkCols + 8;     // +16 bytes: rows land on different banks
-constexpr int kP4TileN = 16;                      // outputs per CTA
-constexpr int kP4RedStride = 20;                  // floats per (warp, activation row) in the reduction buffer
+constexpr int kP4TileN = 16;              // outputs per CTA
+constexpr int kP4SuperCols = 4096;        // contraction columns whose nibbles a CTA holds in shared memory at once
+constexpr int kP4SuperWords = kP4SuperCols / 8;
+constexpr int kP4RedStride = 20;          // floats per (warp, activation row) in the reduction buffer
+constexpr int kP4MaxGroups = kP4SuperCols / 32 + 1;  // groups a super chunk can touch (group size >= 32)
+// fp16 scales of 16 outputs + two zero words per group, rounded so that what follows stays 16-byte aligned
+constexpr int kP4GroupBytes = (kP4MaxGroups * (kP4TileN * 2 + 8) + 15) & ~15;
+static_assert((kP4SuperWords * kP4TileN * 4) % 16 == 0 && kP4GroupBytes % 16 == 0, "activation stages must start on 16 bytes");
+
+// activation columns per staged chunk: about 32 KB per stage (64 KB at 128 rows), two stages
+__host__ __device__ constexpr int p4_chunk_cols(int nt) { return nt == 1 ? 2048 : nt == 2 ? 1024 : nt == 4 ? 512 : 256; }
+__host__ __device__ constexpr int p4_row_halfs(int nt) { return p4_chunk_cols(nt) + 8; }  // +16 bytes: rows on different banks
+__host__ __device__ constexpr size_t p4_stage_bytes(int nt) { return static_cast<size_t>(8 * nt) * p4_row_halfs(nt) * 2; }
+__host__ __device__ constexpr size_t p4_red_bytes(int nt) { return static_cast<size_t>(kP4Warps) * 8 * nt * kP4RedStride * 4; }
+__host__ __device__ constexpr size_t p4_smem_bytes(int nt) {
+  return kP4SuperWords * kP4TileN * 4 + kP4GroupBytes + (2 * p4_stage_bytes(nt) > p4_red_bytes(nt) ? 2 * p4_stage_bytes(nt) : p4_red_bytes(nt));
+}
 
 struct P4Args {
   TrisPacked4View w;
@@ -43,13 +56,12 @@ struct P4Args {
   int out_mode;
   int accumulate;
   int x_aligned;  // rows of x start on 16-byte boundaries
+  int w_aligned;  // rows of qweight start on 16-byte boundaries
 };
 
 __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
 // byte t of `word` holds the nibbles of input columns 2t (low) and 2t+1 (high): returns
 // half2(fp16((q_lo - zero) * scale), fp16((q_hi - zero) * scale)); zc = 1024 + zero as half2
 __device__ __forceinline__ uint32_t p4_dequant_pair(uint32_t word, int t, __half2 zc, __half2 sc) {
@@ -60,10 +72,15 @@ __device__ __forceinline__ uint32_t p4_dequant_pair(uint32_t word, int t, __half
 
 template <int NT>
 __global__ void __launch_bounds__(kP4Threads) packed4_gemm_kernel(const __grid_constant__ P4Args a) {
-  extern __shared__ __align__(16) unsigned char p4_smem[];
-  __half* xs = reinterpret_cast<__half*>(p4_smem);  // [8 * NT][kP4RowHalfs]
-  float* red = reinterpret_cast<float*>(p4_smem);   // [kP4Warps][8 * NT][kP4RedStride], after the main loop
   constexpr int kRows = 8 * NT;
+  constexpr int kChunk = p4_chunk_cols(NT);
+  constexpr int kRowHalfs = p4_row_halfs(NT);
+  extern __shared__ __align__(16) unsigned char p4_smem[];
+  uint32_t* ws = reinterpret_cast<uint32_t*>(p4_smem);                                   // [kP4SuperWords][16] nibble words
+  __half* gsc = reinterpret_cast<__half*>(p4_smem + kP4SuperWords * kP4TileN * 4);      // [kP4MaxGroups][16] scales
+  uint32_t* gzw = reinterpret_cast<uint32_t*>(gsc + kP4MaxGroups * kP4TileN);            // [kP4MaxGroups][2] zero words
+  __half* xs = reinterpret_cast<__half*>(p4_smem + kP4SuperWords * kP4TileN * 4 + kP4GroupBytes);  // [2][kRows][kRowHalfs]
+  float* red = reinterpret_cast<float*>(xs);                                             // after the main loop
 
   pdl_wait();  // activations (and a device-built route) come from the kernels before this one
   int e = 0, row0 = 0, rows = a.num_rows;
@@ -88,66 +105,102 @@ __global__ void __launch_bounds__(kP4Threads) packed4_gemm_kernel(const __grid_c
   const int32_t* qw = a.w.qweight + static_cast<size_t>(a.w.kw_off ? a.w.kw_off[e] : 0) * a.w.q_ld + n_off;
   const int32_t* qz = a.w.qzeros + static_cast<size_t>(g_off) * a.w.z_ld + (a.w.z_off ? a.w.z_off[e] : 0);
   const __half* sc = static_cast<const __half*>(a.w.scales) + static_cast<size_t>(g_off) * a.w.s_ld + n_off;
-  // outputs of this thread's A fragment rows (clamped: the results of rows >= N are never stored)
-  const int na = min(n0 + g, N - 1), nb = min(n0 + g + 8, N - 1);
   const int kwords = (K + 7) >> 3;
+  const bool quad16 = a.w_aligned && ((n_off + n0) & 3) == 0;  // 16-byte copies of four outputs' words
+
+  // stage activation rows [r0, r0 + kRows) x columns [k, k + kChunk) into stage `st`: 16-byte granules, zero past K / rows
+  auto stage_x = [&](int st, int r0, int k_begin) {
+    __half* base = xs + static_cast<size_t>(st) * kRows * kRowHalfs;
+    for (int i = tid; i < kRows * (kChunk / 8); i += kP4Threads) {
+      const int r = i / (kChunk / 8), c = i % (kChunk / 8);
+      const int k = k_begin + 8 * c;
+      const int valid = (r0 + r < rows) ? max(0, min(8, K - k)) : 0;
+      __half* dst = base + r * kRowHalfs + 8 * c;
+      if (k >= ((K + 31) & ~31)) continue;  // past the last 32-column block that holds a column: never read
+      const int src_row = valid ? (a.row_gather ? a.row_gather[row0 + r0 + r] : row0 + r0 + r) : 0;
+      const __half* src = a.x + static_cast<size_t>(src_row) * a.x_ld + k;
+      if (a.x_aligned) {
+        cp_async16_zfill(dst, valid ? src : a.x, 2 * valid);
+      } else {
+        for (int j = 0; j < 8; ++j) dst[j] = j < valid ? src[j] : __ushort_as_half(0);
+      }
+    }
+  };
 
   for (int r0 = 0; r0 < rows; r0 += kRows) {
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-    for (int k0 = 0; k0 < K; k0 += kP4ChunkCols) {
-      // this warp's 32 columns: four words per output, loaded first so that they fly during the staging
-      const int kc = k0 + 32 * warp;
-      uint32_t wa[4], wb[4];
-      const int kw0 = kc >> 3;
+    for (int kk0 = 0; kk0 < K; kk0 += kP4SuperCols) {
+      // every nibble this CTA needs for these columns, requested at once: [word row][16 outputs]
+      const int nkw = min(kP4SuperWords, kwords - (kk0 >> 3));
+      for (int i = tid; i < nkw * 4; i += kP4Threads) {
+        const int kw = i >> 2, q = i & 3;
+        const int32_t* row = qw + static_cast<size_t>((kk0 >> 3) + kw) * a.w.q_ld;
+        uint32_t* dst = ws + kw * kP4TileN + 4 * q;
+        if (quad16 && n0 + 4 * q + 3 < N) {
+          cp_async16_zfill(dst, row + n0 + 4 * q, 16);
+        } else {  // ragged edge or unaligned rows: word by word, outputs past N repeat the last one
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int kw = min(kw0 + i, kwords - 1);  // past the end: any word, its activations are zero
-        wa[i] = static_cast<uint32_t>(__ldg(qw + static_cast<size_t>(kw) * a.w.q_ld + na));
-        wb[i] = static_cast<uint32_t>(__ldg(qw + static_cast<size_t>(kw) * a.w.q_ld + nb));
+          for (int j = 0; j < 4; ++j) cp_async_4(dst + j, row + min(n0 + 4 * q + j, N - 1));
+        }
       }
-      const int grp = min(a.w.group_size > 0 ? kc / a.w.group_size : 0, G - 1);
-      const uint32_t za = (static_cast<uint32_t>(__ldg(qz + static_cast<size_t>(grp) * a.w.z_ld + (na >> 3))) >> (4 * (na & 7))) & 0xFu;
-      const uint32_t zb = (static_cast<uint32_t>(__ldg(qz + static_cast<size_t>(grp) * a.w.z_ld + (nb >> 3))) >> (4 * (nb & 7))) & 0xFu;
-      const __half2 zca = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u + za + 1u)));
-      const __half2 zcb = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u + zb + 1u)));
-      const __half2 sca = __half2half2(__ldg(sc + static_cast<size_t>(grp) * a.w.s_ld + na));
-      const __half2 scb = __half2half2(__ldg(sc + static_cast<size_t>(grp) * a.w.s_ld + nb));
-
-      // stage activation rows [r0, r0 + kRows) x columns [k0, k0 + 256): 16-byte granules, zero past K / rows
-      for (int i = tid; i < kRows * (kP4ChunkCols / 8); i += kP4Threads) {
-        const int r = i / (kP4ChunkCols / 8), c = i % (kP4ChunkCols / 8);
-        const int k = k0 + 8 * c;
-        const int valid = (r0 + r < rows) ? max(0, min(8, K - k)) : 0;
-        __half* dst = xs + r * kP4RowHalfs + 8 * c;
-        const int src_row = valid ? (a.row_gather ? a.row_gather[row0 + r0 + r] : row0 + r0 + r) : 0;
-        const __half* src = a.x + static_cast<size_t>(src_row) * a.x_ld + k;
-        if (a.x_aligned) {
-          cp_async16_zfill(dst, valid ? src : a.x, 2 * valid);
+      const int span = min(kP4SuperCols, K - kk0);
+      // scales and zero points of the groups these columns fall into (outputs past N repeat the last one)
+      const int gs = a.w.group_size > 0 ? a.w.group_size : (K + kP4SuperCols);
+      const int grp0 = min(kk0 / gs, G - 1);
+      const int ngrp = min((kk0 + span - 1) / gs, G - 1) - grp0 + 1;
+      for (int i = tid; i < ngrp * (kP4TileN + 2); i += kP4Threads) {
+        const int gi = i / (kP4TileN + 2), j = i % (kP4TileN + 2);
+        if (j < kP4TileN) {
+          gsc[gi * kP4TileN + j] = __ldg(sc + static_cast<size_t>(grp0 + gi) * a.w.s_ld + min(n0 + j, N - 1));
         } else {
-          for (int j = 0; j < 8; ++j) dst[j] = j < valid ? src[j] : __ushort_as_half(0);
+          gzw[gi * 2 + (j - kP4TileN)] =
+              static_cast<uint32_t>(__ldg(qz + static_cast<size_t>(grp0 + gi) * a.w.z_ld + (min(n0 + 8 * (j - kP4TileN), N - 1) >> 3)));
         }
       }
-      cp_async_wait_all();
-      __syncthreads();
-
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const uint32_t a0 = p4_dequant_pair(wa[2 * s], t, zca, sca);
-        const uint32_t a1 = p4_dequant_pair(wb[2 * s], t, zcb, scb);
-        const uint32_t a2 = p4_dequant_pair(wa[2 * s + 1], t, zca, sca);
-        const uint32_t a3 = p4_dequant_pair(wb[2 * s + 1], t, zcb, scb);
-        const __half* xk = xs + g * kP4RowHalfs + 32 * warp + 16 * s + 2 * t;
-#pragma unroll
-        for (int i = 0; i < NT; ++i) {
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xk + i * 8 * kP4RowHalfs);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xk + i * 8 * kP4RowHalfs + 8);
-          mma_m16n8k16(acc[i], a0, a1, a2, a3, b0, b1);
+      const int nchunks = (span + kChunk - 1) / kChunk;
+      stage_x(0, r0, kk0);
+      cp_async_commit();
+      for (int c = 0; c < nchunks; ++c) {
+        if (c + 1 < nchunks) {
+          stage_x((c + 1) & 1, r0, kk0 + (c + 1) * kChunk);
+          cp_async_commit();
+          cp_async_wait<1>();
+        } else {
+          cp_async_wait<0>();
         }
+        __syncthreads();
+        const __half* xb = xs + static_cast<size_t>(c & 1) * kRows * kRowHalfs;
+        for (int blk = warp; blk < kChunk / 32; blk += kP4Warps) {
+          const int kl = c * kChunk + 32 * blk;  // column inside this super chunk
+          const int kc = kk0 + kl;
+          if (kc >= K) break;
+          const int gi = min(kc / gs, G - 1) - grp0;
+          const uint32_t za = (gzw[gi * 2] >> (4 * g)) & 0xFu, zb = (gzw[gi * 2 + 1] >> (4 * g)) & 0xFu;
+          const __half2 zca = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u + za + 1u)));
+          const __half2 zcb = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u + zb + 1u)));
+          const __half2 sca = __half2half2(gsc[gi * kP4TileN + g]);
+          const __half2 scb = __half2half2(gsc[gi * kP4TileN + g + 8]);
+          const uint32_t* wk = ws + (kl >> 3) * kP4TileN;
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            const uint32_t a0 = p4_dequant_pair(wk[(2 * s) * kP4TileN + g], t, zca, sca);
+            const uint32_t a1 = p4_dequant_pair(wk[(2 * s) * kP4TileN + g + 8], t, zcb, scb);
+            const uint32_t a2 = p4_dequant_pair(wk[(2 * s + 1) * kP4TileN + g], t, zca, sca);
+            const uint32_t a3 = p4_dequant_pair(wk[(2 * s + 1) * kP4TileN + g + 8], t, zcb, scb);
+            const __half* xk = xb + g * kRowHalfs + 32 * blk + 16 * s + 2 * t;
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+              const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xk + i * 8 * kRowHalfs);
+              const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xk + i * 8 * kRowHalfs + 8);
+              mma_m16n8k16(acc[i], a0, a1, a2, a3, b0, b1);
+            }
+          }
+        }
+        __syncthreads();  // this stage (and, after the last chunk, the nibble tile) may be overwritten now
       }
-      __syncthreads();  // the next chunk (or the reduction buffer) overwrites the staged rows
     }
 
     // add the eight warps' partial sums: red[warp][activation row][output]
@@ -178,10 +231,7 @@ __global__ void __launch_bounds__(kP4Threads) packed4_gemm_kernel(const __grid_c
 
 template <int NT>
 static int launch_p4(const P4Args& args, dim3 grid, cudaStream_t stream) {
-  constexpr int kRows = 8 * NT;
-  const size_t stage = static_cast<size_t>(kRows) * kP4RowHalfs * sizeof(__half);
-  const size_t red = static_cast<size_t>(kP4Warps) * kRows * kP4RedStride * sizeof(float);
-  const size_t smem = std::max(stage, red);
+  constexpr size_t smem = p4_smem_bytes(NT);
   if (smem > 48 * 1024) {
     TRIS_CUDA(cudaFuncSetAttribute(packed4_gemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   }
@@ -231,6 +281,7 @@ extern "C" int tris_packed4_grouped_forward(const TrisPacked4View* w, const Tris
   args.out_mode = out_mode;
   args.accumulate = accumulate ? 1 : 0;
   args.x_aligned = ((reinterpret_cast<uintptr_t>(x_f16) & 15u) == 0 && x_ld % 8 == 0) ? 1 : 0;
+  args.w_aligned = ((reinterpret_cast<uintptr_t>(w->qweight) & 15u) == 0 && w->q_ld % 4 == 0) ? 1 : 0;
   const dim3 grid(ceil_div(w->n, kP4TileN), route ? route->num_segments : 1);
   TRIS_REQUIRE(grid.y <= 65535u, TRIS_ERR_UNSUPPORTED, "tris_packed4_grouped_forward: more than 65535 segments");
   cudaStream_t s = static_cast<cudaStream_t>(stream);

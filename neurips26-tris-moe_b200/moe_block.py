@@ -53,13 +53,15 @@ class TrisSparseMoeBlock(nn.Module):
         self.packed_backbones: dict = {}  # name -> Packed4Linear: backbones kept in their 4-bit nibbles
         self._grouped_payload_cache: dict = {}
         self._layer_view: Optional[TrisMoeLayerView] = None
-        self._expanded_view: Optional[TrisMoeLayerView] = None
+        self._expanded_view: Optional[dict] = None  # expanded backbone names -> layer view
         self._workspace: Optional[torch.Tensor] = None
         self._status_word: Optional[torch.Tensor] = None  # status of the kernels forward_streaming launches
 
     # -- loading ---------------------------------------------------------------------------
-    # rows per call above which 4-bit backbones are expanded to fp16 scratch and run on the tcgen05 GEMM
-    PACKED_BACKBONE_MAX_ROWS = 256
+    # activation rows above which a 4-bit backbone is expanded to fp16 scratch and run on the dense GEMM
+    # (measured on B200, 2048 x 2048: the 4-bit GEMM takes 7 / 8 / 16 / 23 us at 1 / 16 / 64 / 128 rows, the
+    # expansion 4 us plus 7 / 8 / 14 / 15 us of fp16 GEMM)
+    PACKED_BACKBONE_MAX_ROWS = 64
     _expand_scratch: dict = {}  # (device, name, shape) -> fp16 scratch shared by every block of a model
 
     def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate, shared_up, shared_down,
@@ -138,27 +140,30 @@ class TrisSparseMoeBlock(nn.Module):
             self._layer_view, self._expanded_view = v, None
         return self._layer_view
 
-    def _expanded_layer_view(self, dev) -> TrisMoeLayerView:
-        """The layer view with every 4-bit backbone expanded into fp16 scratch (enqueued on the current
-        stream): what large batches use, where the dense tcgen05 GEMM beats re-expanding nibbles for
-        every 128 rows.  The scratch is shared by all blocks of a model."""
+    def _expanded_layer_view(self, dev, names) -> TrisMoeLayerView:
+        """The layer view with the 4-bit backbones in ``names`` expanded into fp16 scratch (enqueued on
+        the current stream): what large batches use, where the dense GEMM beats re-expanding nibbles for
+        every pass over the rows.  The scratch is shared by all blocks of a model."""
         base = self.layer_view()
         if self._expanded_view is None:
+            self._expanded_view = {}
+        key = tuple(sorted(names))
+        v = self._expanded_view.get(key)
+        if v is None:
             v = TrisMoeLayerView()
             C.pointer(v)[0] = base
-            self._expanded_view = v
-        v = self._expanded_view
+            self._expanded_view[key] = v
         lib = _native.load()
-        for name, p in self.packed_backbones.items():
-            key = (str(dev), name, p.rows, p.cols)
-            scratch = TrisSparseMoeBlock._expand_scratch.get(key)
+        for name in key:
+            p = self.packed_backbones[name]
+            skey = (str(dev), name, p.rows, p.cols)
+            scratch = TrisSparseMoeBlock._expand_scratch.get(skey)
             if scratch is None:
                 scratch = torch.empty((p.rows, p.cols), dtype=torch.float16, device=dev)
-                TrisSparseMoeBlock._expand_scratch[key] = scratch
-            g_idx = getattr(p, "_g_idx", None)
-            if g_idx is None:
+                TrisSparseMoeBlock._expand_scratch[skey] = scratch
+            if getattr(p, "_g_idx", None) is None:
                 g_idx = (torch.arange(p.cols, device=dev, dtype=torch.int32) // max(1, p.group_size)).clamp_(max=p.groups - 1)
-                p._g_idx = g_idx.contiguous()
+                p._g_idx = g_idx.to(torch.int32).contiguous()
             with torch.cuda.device(dev):
                 _native.check(lib.tris_packed4_dequantize(p.qweight.data_ptr(), p.qzeros.data_ptr(), p.scales.data_ptr(),
                                                           p._g_idx.data_ptr(), p.rows, p.cols, p.groups, scratch.data_ptr(),
@@ -234,8 +239,13 @@ class TrisSparseMoeBlock(nn.Module):
         if T:
             ws = self.workspace(T, dev)
             view = self.layer_view()
-            if self.packed_backbones and T * self.top_k > self.PACKED_BACKBONE_MAX_ROWS:
-                view = self._expanded_layer_view(dev)
+            if self.packed_backbones:  # gate and up see T rows, down T * top_k
+                big = [n for n in self.packed_backbones
+                       if (T * self.top_k if n == "down" else T) > self.PACKED_BACKBONE_MAX_ROWS]
+                if "gate" in big or "up" in big:
+                    big = sorted(set(big) | ({"gate", "up"} & set(self.packed_backbones)))
+                if big:
+                    view = self._expanded_layer_view(dev, big)
             with torch.cuda.device(dev):
                 _native.check(
                     lib.tris_moe_layer_forward(C.byref(view), x.data_ptr(), logits_in, T, y.data_ptr(),

@@ -198,7 +198,7 @@ def test_grouped_operators_add_compensation(lib):
     assert torch.equal(fused, (torch.nn.functional.silu(a1.float()) * b1.float()).half())
 
 
-@pytest.mark.parametrize("tokens", [1, 24, 300])
+@pytest.mark.parametrize("tokens", [1, 24, 40, 300])
 def test_moe_block_with_packed_backbones(lib, tokens):
     """A block whose three backbones arrive as 4-bit payloads: kept in their nibbles (decode batches
     run the 4-bit GEMM inside tris_moe_layer_forward, large batches expand into shared scratch) vs the
@@ -209,8 +209,8 @@ def test_moe_block_with_packed_backbones(lib, tokens):
     shape = synth.LayerShape(256, 192, 8, 2, rank=96, group_size=32)
     layer = synth.synth_layer(shape, seed=21)
     rng = np.random.default_rng(tokens)
-    packed = {"gate": synth.packed4_matrix(rng, 96, 256, 128, scale_std=0.05), "up": synth.packed4_matrix(rng, 96, 256, 128, scale_std=0.05),
-              "down": synth.packed4_matrix(rng, 96, 192, 64, scale_std=0.05)}
+    packed = {"gate": synth.packed4_matrix(rng, 96, 256, 128, scale_std=0.02), "up": synth.packed4_matrix(rng, 96, 256, 128, scale_std=0.02),
+              "down": synth.packed4_matrix(rng, 96, 192, 64, scale_std=0.02)}
     blocks = {}
     for mode in ("nibbles", "fp16"):
         blk = tm.TrisSparseMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, shape.norm_topk_prob)
