@@ -32,7 +32,7 @@ from .qlinear_grouped import (  # noqa: F401
     run_grouped_structured_expert_forward,
     run_grouped_structured_expert_pair_forward,
 )
-from .moe_block import TrisSparseMoeBlock  # noqa: F401
+from .moe_block import TrisQwen2SparseMoeBlock, TrisSparseMoeBlock  # noqa: F401
 from .compact3_linear import (  # noqa: F401
     Compact3Linear,
     run_compact3_gate_up_forward,
@@ -59,6 +59,7 @@ __all__ = [
     "HIDDEN_ROW_MAJOR",
     "TRIS_COMPACT3_KERNEL_ABI_VERSION",
     "ExpertSharedMatrix",
+    "TrisQwen2SparseMoeBlock",
     "TrisSparseMoeBlock",
     "block_gr_encode",
     "build_compact3_packed_payload",

@@ -51,6 +51,8 @@ class TrisSparseMoeBlock(nn.Module):
         self.register_buffer("shared_up", torch.zeros((0, 0), dtype=torch.float16))
         self.register_buffer("shared_down", torch.zeros((0, 0), dtype=torch.float16))
         self.packed_backbones: dict = {}  # name -> Packed4Linear: backbones kept in their 4-bit nibbles
+        self.input_scales: dict = {}      # name -> fp16 [in]: vector null-space input scale (ns_mode == 1)
+        self.ns_payloads: dict = {}       # name -> grouped null-space compensation payload (ns_mode == 2)
         self._grouped_payload_cache: dict = {}
         self._layer_view: Optional[TrisMoeLayerView] = None
         self._expanded_view: Optional[dict] = None  # expanded backbone names -> layer view
@@ -66,7 +68,7 @@ class TrisSparseMoeBlock(nn.Module):
 
     def load_grouped_payloads(self, gate: dict, up: dict, down: dict, shared_gate, shared_up, shared_down,
                               router_weight: Optional[torch.Tensor] = None, device=None,
-                              packed_backbone: Optional[str] = None) -> "TrisSparseMoeBlock":
+                              packed_backbone: Optional[str] = None, input_scales: Optional[dict] = None) -> "TrisSparseMoeBlock":
         """Attaches the E-stacked payloads (``enable_grouped_deployment_only``,
         modeling_olmoe.py:732-804) and the three backbones, moving everything to ``device`` and
         deriving the decode index once.  A backbone is an fp16 matrix ``[r, in]`` or, as real
@@ -74,7 +76,12 @@ class TrisSparseMoeBlock(nn.Module):
         ``scales``, ``g_idx``, ``rows``, ``cols``).  ``packed_backbone`` (default: the environment
         variable ``TRIS_PACKED4_BACKBONE``, else ``"nibbles"``) says how packed backbones are kept:
         ``"nibbles"`` - in place, read by the 4-bit GEMM (a quarter of the bytes; gate and up switch
-        together, matrices with non-uniform groups are expanded), ``"fp16"`` - expanded once at load."""
+        together, matrices with non-uniform groups are expanded), ``"fp16"`` - expanded once at load.
+        ``input_scales`` (``{"gate" | "up" | "down": fp16 [in]}``): the vector null-space input scale of
+        ``ns_mode == 1`` checkpoints (``expert_input_scale`` of expert 0, qlinear_cuda.py:3918-3923): the
+        backbone of that projection sees ``x * scale`` rounded to fp16 (qlinear_cuda.py:4477-4480); the
+        matching output scale travels in the payload (``output_scale``).  With input scales the block
+        runs operator by operator (gate and up no longer share their input rows)."""
         import os
 
         dev = torch.device(device) if device is not None else gate["qweight1"].device
@@ -104,7 +111,22 @@ class TrisSparseMoeBlock(nn.Module):
             self.gate.weight = nn.Parameter(router_weight.to(dev, torch.float16).contiguous(), requires_grad=False)
         else:
             self.gate.to(dev)
+        self.input_scales = {n: v.reshape(-1).to(dev, torch.float16).contiguous() for n, v in (input_scales or {}).items()}
+        if set(self.input_scales) - set(given):
+            raise ValueError("input_scales keys must be among 'gate', 'up', 'down'")
         self._layer_view = self._expanded_view = None
+        return self
+
+    def load_ns_compensation_payloads(self, gate_ns: Optional[dict] = None, up_ns: Optional[dict] = None,
+                                      down_ns: Optional[dict] = None) -> "TrisSparseMoeBlock":
+        """Attaches the grouped null-space compensation payloads of ``ns_mode == 2`` checkpoints (the
+        ``gate_ns`` / ``up_ns`` / ``down_ns`` entries of the reference's payload cache,
+        modeling_olmoe.py:950-975; built by ``build_grouped_ns_compensation_payload``).  With any of
+        them the block runs operator by operator and each grouped operator adds its compensation."""
+        from .ns_compensation import ns_payload_max_rank
+
+        self.ns_payloads = {n: p for n, p in (("gate", gate_ns), ("up", up_ns), ("down", down_ns))
+                            if p is not None and ns_payload_max_rank(p) > 0}
         return self
 
     def backbone_rank(self, name: str) -> int:
@@ -113,6 +135,9 @@ class TrisSparseMoeBlock(nn.Module):
 
     def backbone_hidden(self, name: str, x: torch.Tensor, layout: int = 0) -> torch.Tensor:
         """``x . backbone^T`` (``compute_shared_hidden``) for the fp16 or the 4-bit form of a backbone."""
+        scale = self.input_scales.get(name)
+        if scale is not None:
+            x = x * scale
         p = self.packed_backbones.get(name)
         if p is not None:
             return p(x, layout)
@@ -220,7 +245,8 @@ class TrisSparseMoeBlock(nn.Module):
         ``OlmoeSparseMoeBlock.forward`` (modeling_olmoe.py:1046-1105).  ``router_logits``
         (fp32 ``[T, E]``) may be passed in to skip the router linear."""
         _native.require_cuda(hidden_states, "TrisSparseMoeBlock.forward")
-        if not envflags.grouped_experts_enabled():  # TRIS_GROUPED_EXPERTS=0: operator by operator
+        if not envflags.grouped_experts_enabled() or self.input_scales or self.ns_payloads:
+            # TRIS_GROUPED_EXPERTS=0, per-projection input scales or null-space pairs: operator by operator
             return self.forward_grouped_ops(hidden_states, router_logits)
         if hidden_states.dtype != torch.float16:
             raise RuntimeError(f"trismoe_b200: grouped expert kernels require float16 hidden states, got {hidden_states.dtype}")
@@ -342,10 +368,52 @@ class TrisSparseMoeBlock(nn.Module):
         gate_hidden = self.backbone_hidden("gate", x).index_select(0, tok)
         up_hidden = self.backbone_hidden("up", x).index_select(0, tok)
         gate_out, up_out = run_grouped_structured_expert_pair_forward(
-            self._get_grouped_payload("gate"), self._get_grouped_payload("up"), gate_hidden, up_hidden, x_grouped, route)
+            self._get_grouped_payload("gate"), self._get_grouped_payload("up"), gate_hidden, up_hidden, x_grouped, route,
+            ns_payload_a=self.ns_payloads.get("gate"), ns_payload_b=self.ns_payloads.get("up"))
         mlp = torch.nn.functional.silu(gate_out) * up_out
         down_hidden = self.backbone_hidden("down", mlp)
-        down_out = run_grouped_structured_expert_forward(self._get_grouped_payload("down"), down_hidden, mlp, route)
+        down_out = run_grouped_structured_expert_forward(self._get_grouped_payload("down"), down_hidden, mlp, route,
+                                                         ns_payload=self.ns_payloads.get("down"))
         final = x.new_zeros(x.shape)
         final.index_add_(0, tok, (down_out * grouped_routing).to(x.dtype))
         return final.reshape(shape), router_logits
+
+
+class TrisQwen2SparseMoeBlock(TrisSparseMoeBlock):
+    """``Qwen2MoeSparseMoeBlock`` of the reference (modeling_qwen2_moe.py:249-822): the routed experts
+    of :class:`TrisSparseMoeBlock` plus one always-on shared expert - a dense gate/up/down MLP of
+    ordinary compact3 linears whose output is scaled by ``sigmoid(shared_expert_gate(x))`` and added
+    (modeling_qwen2_moe.py:815-818).  The shared expert's gate and up run as one dual launch with
+    SiLU*mul fused (``run_compact3_shared_expert_gate_up_forward``, modeling_qwen2_moe.py:117-123)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, num_experts_per_tok: int,
+                 norm_topk_prob: bool = False):
+        super().__init__(hidden_size, intermediate_size, num_experts, num_experts_per_tok, norm_topk_prob)
+        self.shared_expert_gate = nn.Linear(self.hidden_size, 1, bias=False, dtype=torch.float16)
+        self.shared_expert = None  # (gate, up, down) Compact3Linear
+
+    def load_shared_expert(self, gate_proj, up_proj, down_proj, shared_expert_gate_weight: torch.Tensor, device=None):
+        """``gate_proj`` / ``up_proj`` / ``down_proj``: :class:`~.compact3_linear.Compact3Linear` modules or the
+        per-module compact3 payload dicts they are built from; ``shared_expert_gate_weight``: ``[1, hidden]``."""
+        from .compact3_linear import Compact3Linear
+
+        dev = torch.device(device) if device is not None else self.gate.weight.device
+        mods = [m if isinstance(m, Compact3Linear) else Compact3Linear(m, device=dev) for m in (gate_proj, up_proj, down_proj)]
+        self.shared_expert = tuple(mods)
+        self.shared_expert_gate.weight = nn.Parameter(shared_expert_gate_weight.reshape(1, self.hidden_size).to(dev, torch.float16).contiguous(),
+                                                      requires_grad=False)
+        return self
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
+        from .compact3_linear import run_compact3_gate_up_forward
+
+        if self.shared_expert is None:
+            raise RuntimeError("trismoe_b200: the shared expert was not loaded (load_shared_expert)")
+        routed, logits = super().forward(hidden_states, router_logits)
+        gate_proj, up_proj, down_proj = self.shared_expert
+        mlp = run_compact3_gate_up_forward(gate_proj, up_proj, hidden_states, fuse_silu_mul=True)
+        shared = down_proj(mlp)
+        if shared is None:
+            raise RuntimeError("trismoe_b200: shared expert kernels returned no result")
+        scale = torch.sigmoid(torch.nn.functional.linear(hidden_states, self.shared_expert_gate.weight))
+        return routed + scale * shared, logits

@@ -89,3 +89,35 @@ def test_fused_qkv_and_dual_gate_up(lib):
     a, b = tm.run_compact3_gate_up_forward(gate, up, x.cuda(), fuse_silu_mul=False)
     _check(a, g32)
     _check(b, u32)
+
+
+def test_qwen2_block_with_shared_expert(lib):
+    """Qwen2-MoE style block: routed experts + an always-on shared expert (compact3 gate/up/down) scaled
+    by sigmoid(shared_expert_gate(x)), against the fp32 oracle."""
+    import trismoe_b200 as tm
+    from trismoe_b200 import synth
+
+    shape = synth.LayerShape(256, 192, 8, 2, rank=96, group_size=32)
+    layer = synth.synth_layer(shape, seed=41)
+    rng = np.random.default_rng(41)
+    g_pay, g_w = _single(rng, 320, 256)
+    u_pay, u_w = _single(rng, 320, 256)
+    d_pay, d_w = _single(rng, 256, 320, group=64)
+    gate_w = (rng.standard_normal((1, 256)) / 16).astype(np.float16)
+    blk = tm.TrisQwen2SparseMoeBlock(shape.hidden_size, shape.intermediate_size, shape.num_experts, shape.top_k, True)
+    blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"],
+                              layer["shared_down"], layer["router_weight"], device="cuda")
+    blk.load_shared_expert(g_pay, u_pay, d_pay, torch.from_numpy(gate_w))
+    T = 11
+    x = (synth.synth_activations(T, 256, seed=3).float() * 0.25).half()   # keeps the MLP outputs of order one
+    logits = synth.synth_router_logits(T, shape.num_experts, seed=4)
+    y, _ = blk(x.cuda().view(1, T, -1), router_logits=logits.cuda())
+    weights = {n: [orc.dequantize_expert(to_numpy_payload(layer[n]), e) for e in range(shape.num_experts)] for n in ("gate", "up", "down")}
+    shared = {n: layer["shared_" + n].numpy() for n in ("gate", "up", "down")}
+    ref = orc.moe_layer_fp32(x.numpy(), logits.numpy(), weights, shared, shape.top_k, True)
+    xf = x.numpy().astype(np.float32)
+    gate_o, up_o = xf @ g_w.astype(np.float32).T, xf @ u_w.astype(np.float32).T
+    mlp = gate_o / (1.0 + np.exp(-gate_o)) * up_o
+    shared_out = mlp @ d_w.astype(np.float32).T
+    ref = ref + 1.0 / (1.0 + np.exp(-(xf @ gate_w.astype(np.float32).T))) * shared_out
+    _check(y.view(T, -1), ref)

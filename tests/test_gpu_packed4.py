@@ -232,3 +232,57 @@ def test_moe_block_with_packed_backbones(lib, tokens):
     y_ops, _ = blocks["nibbles"].forward_grouped_ops(x.view(1, tokens, -1), router_logits=logits)
     _check(y_ops.view(tokens, -1), ref, floor=1e-4)
     blocks["nibbles"].raise_on_kernel_status()
+
+
+def test_moe_block_with_vector_and_matrix_null_space(lib):
+    """A block as a real ns checkpoint hands it over: per-projection input scales (ns_mode == 1, with the
+    row scale in the payload's output_scale) and null-space pairs (ns_mode == 2) - against the fp32
+    oracle with the scales folded into the weights and the compensation added per projection."""
+    import trismoe_b200 as tm
+    from trismoe_b200 import synth
+
+    rng = np.random.default_rng(9)
+    shape = synth.LayerShape(256, 192, 8, 2, rank=96, group_size=32)
+    layer = synth.synth_layer(shape, seed=51)
+    E, H, I = shape.num_experts, shape.hidden_size, shape.intermediate_size
+    in_scale = {"gate": (1 + 0.2 * rng.standard_normal(H)).astype(np.float16), "up": (1 + 0.2 * rng.standard_normal(H)).astype(np.float16),
+                "down": (1 + 0.2 * rng.standard_normal(I)).astype(np.float16)}
+    out_scale = {"gate": (1 + 0.2 * rng.standard_normal((E, I))).astype(np.float16), "up": (1 + 0.2 * rng.standard_normal((E, I))).astype(np.float16),
+                 "down": (1 + 0.2 * rng.standard_normal((E, H))).astype(np.float16)}
+    for n in ("gate", "up", "down"):
+        layer[n]["output_scale"] = torch.from_numpy(out_scale[n])
+        layer[n]["has_output_scale"] = True
+    ranks = [16, 0, 24, 16, 8, 40, 0, 16]
+    ns = {"gate": _ns_layer(rng, E, H, I, ranks), "up": _ns_layer(rng, E, H, I, ranks[::-1]), "down": _ns_layer(rng, E, I, H, ranks)}
+    blk = tm.TrisSparseMoeBlock(H, I, E, shape.top_k, shape.norm_topk_prob)
+    blk.load_grouped_payloads(layer["gate"], layer["up"], layer["down"], layer["shared_gate"], layer["shared_up"], layer["shared_down"],
+                              layer["router_weight"], device="cuda", input_scales={n: torch.from_numpy(v) for n, v in in_scale.items()})
+    blk.load_ns_compensation_payloads(ns["gate"], ns["up"], ns["down"])
+    T = 13
+    x = (synth.synth_activations(T, H, seed=2).float() * 0.25).half()   # keeps the outputs of order one
+    logits = synth.synth_router_logits(T, E, seed=6)
+    y, _ = blk(x.cuda().view(1, T, -1), router_logits=logits.cuda())
+
+    # fp32 restatement of QuantLinear.forward (mode 5) per routed expert, qlinear_cuda.py:4692-4749
+    w = {n: [orc.dequantize_expert(to_numpy_payload({k: v for k, v in layer[n].items() if k not in ("output_scale", "has_output_scale")}), e)
+             .astype(np.float32) for e in range(E)] for n in ("gate", "up", "down")}
+    sv = {n: layer["shared_" + n].numpy().astype(np.float32) for n in ("gate", "up", "down")}
+    np_ns = {n: {k: (v.cpu().numpy() if isinstance(v, torch.Tensor) else v) for k, v in ns[n].items() if not k.startswith("_tris")} for n in ns}
+
+    def linear(n, e, xin):
+        out = ((xin * in_scale[n].astype(np.float32)) @ sv[n].T) @ w[n][e].T * out_scale[n][e].astype(np.float32)
+        c1, c2 = orc.ns_expert_matrices(np_ns[n], e)
+        if c1 is not None:
+            out = out + (xin @ c2.astype(np.float32).T) @ c1.astype(np.float32).T
+        return out
+
+    xf = x.numpy().astype(np.float32)
+    sel, wts = orc.router_topk(logits.numpy(), shape.top_k, shape.norm_topk_prob)
+    ref = np.zeros((T, H), np.float32)
+    for t in range(T):
+        for s in range(shape.top_k):
+            e = int(sel[t, s])
+            gate_o, up_o = linear("gate", e, xf[t:t + 1]), linear("up", e, xf[t:t + 1])
+            mlp = gate_o / (1.0 + np.exp(-gate_o)) * up_o
+            ref[t] += wts[t, s] * linear("down", e, mlp)[0]
+    _check(y.view(T, -1), ref, floor=1e-4)
