@@ -501,6 +501,11 @@ static int pick_ksplit(const TrisProjView* proj, const TrisRouteView* route, int
 // plane-staging kernel (64 rows per pass) and, beyond grouped_tc_min_rows(), the tcgen05 kernel do
 // less work per row.
 static int tiled_max_rows() { return std::min(64, grouped_tc_min_rows()); }
+// Above that, up to the tcgen05 threshold, the tile-record kernel that keeps a chunk's unpacked weights in
+// registers across row passes takes single-chunk projections (rank <= 256).
+static bool tiled_takes(const TrisProjView& v, int rows) {
+  return rows <= tiled_max_rows() || (v.rank <= 256 && rows <= grouped_tc_min_rows());
+}
 
 // Rows per activation tile: sized for the typical segment (mean + 4 sigma of a balanced
 // router), never above the caller's bound; longer segments take several passes.
@@ -596,7 +601,7 @@ int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* ro
   const bool col_scaled = route->hidden_col_scale != nullptr;
   TRIS_REQUIRE(!col_scaled || (proj_has_tile_records(*proj) && !a.hidden_interleaved && !lane_order), TRIS_ERR_UNSUPPORTED,
                "tris_grouped_forward: hidden_col_scale needs tile records and row-major activations");
-  if (proj_has_tile_records(*proj) && !a.hidden_interleaved && (lane_order || col_scaled || rows_hint(route) <= tiled_max_rows()))
+  if (proj_has_tile_records(*proj) && !a.hidden_interleaved && (lane_order || col_scaled || tiled_takes(*proj, rows_hint(route))))
     return launch_grouped_tiled(proj, nullptr, route, hidden_f16, nullptr, out_f16, nullptr, 0, rows_hint(route), stream, opts);
   TRIS_REQUIRE(!a.hidden_interleaved || proj->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
                "tris_grouped_forward: pair-interleaved activations need rank % 32 == 0");
@@ -622,7 +627,7 @@ extern "C" int tris_grouped_hidden_layout(const TrisProjView* proj_a, const Tris
   route.num_segments = num_segments;
   route.max_rows_per_segment = max_rows_per_segment;
   const bool records = proj_has_tile_records(*proj_a) && (proj_b == nullptr || proj_has_tile_records(*proj_b));
-  return (records && route_rows_hint(&route) <= tiled_max_rows()) ? TRIS_OUT_F16_LANE_ORDER : TRIS_OUT_F16_PAIR_INTERLEAVED;
+  return (records && tiled_takes(*proj_a, route_rows_hint(&route))) ? TRIS_OUT_F16_LANE_ORDER : TRIS_OUT_F16_PAIR_INTERLEAVED;
 }
 
 extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
@@ -659,7 +664,7 @@ int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjVi
   const bool col_scaled = route->hidden_col_scale != nullptr;
   TRIS_REQUIRE(!col_scaled || (records && !a.hidden_interleaved && !lane_order), TRIS_ERR_UNSUPPORTED,
                "tris_grouped_pair_forward: hidden_col_scale needs tile records and row-major activations");
-  if (records && !a.hidden_interleaved && (lane_order || col_scaled || rows_hint(route) <= tiled_max_rows()))
+  if (records && !a.hidden_interleaved && (lane_order || col_scaled || tiled_takes(*proj_a, rows_hint(route))))
     return launch_grouped_tiled(proj_a, proj_b, route, hidden_a_f16, hidden_b_f16, out_a_f16, out_b_f16, fuse_silu_mul ? 2 : 1,
                                 rows_hint(route), stream, opts);
   TRIS_REQUIRE(!a.hidden_interleaved || proj_a->rank % 32 == 0, TRIS_ERR_INVALID_ARG,

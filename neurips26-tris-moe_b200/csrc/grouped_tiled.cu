@@ -198,6 +198,27 @@ __device__ __forceinline__ void gather_salient(uint8_t* hsal, const uint8_t* hro
 // ---- main loop of one 256-column chunk ----------------------------------------------------------
 // NTC (compile time) = live 8-row tiles of this pass.  The packed rows are walked slot by slot
 // (runs of rows that share their row scales), so the inner loop has no branch but its own.
+// Second pass of a chunk: the salient columns, compacted into 32-slot "salient words" whose
+// activations gather_salient put into hsal.
+template <int NT, int NTC>
+__device__ __forceinline__ void sal_chunk_n(const StagedTile& st, const uint8_t* hsal_set, int out_local, int lane,
+                                            float (&acc)[NT][4]) {
+  const int g = lane >> 2, t = lane & 3;
+  const ColHeader* ch = reinterpret_cast<const ColHeader*>(st.col);
+  const int sal_words = ch->sal_words;
+  const uint8_t* s_base = hsal_set + g * 64 + t * 16;
+  for (int q = 0; q < sal_words; ++q) {
+    uint32_t a[2][4];
+    unpack_fragments_sal(st, q, out_local, lane, a);
+#pragma unroll
+    for (int nt = 0; nt < NTC; ++nt) {
+      const uint4 hv = *reinterpret_cast<const uint4*>(s_base + (q * NT + nt) * 8 * 64);
+      mma_m16n8k16(acc[nt], a[0][0], a[1][0], a[0][1], a[1][1], hv.x, hv.y);
+      mma_m16n8k16(acc[nt], a[0][2], a[1][2], a[0][3], a[1][3], hv.z, hv.w);
+    }
+  }
+}
+
 template <int NT, int NTC>
 __device__ __forceinline__ void main_chunk_n(const StagedTile& st, const uint8_t* hrows_set, const uint8_t* hsal_set,
                                              int out_local, int lane, float (&acc)[NT][4]) {
@@ -221,18 +242,7 @@ __device__ __forceinline__ void main_chunk_n(const StagedTile& st, const uint8_t
       }
     }
   }
-  const int sal_words = ch->sal_words;
-  const uint8_t* s_base = hsal_set + g * 64 + t * 16;
-  for (int q = 0; q < sal_words; ++q) {
-    uint32_t a[2][4];
-    unpack_fragments_sal(st, q, out_local, lane, a);
-#pragma unroll
-    for (int nt = 0; nt < NTC; ++nt) {
-      const uint4 hv = *reinterpret_cast<const uint4*>(s_base + (q * NT + nt) * 8 * 64);
-      mma_m16n8k16(acc[nt], a[0][0], a[1][0], a[0][1], a[1][1], hv.x, hv.y);
-      mma_m16n8k16(acc[nt], a[0][2], a[1][2], a[0][3], a[1][3], hv.z, hv.w);
-    }
-  }
+  sal_chunk_n<NT, NTC>(st, hsal_set, out_local, lane, acc);
 }
 
 template <int NT>
@@ -242,6 +252,63 @@ __device__ __forceinline__ void main_chunk(const StagedTile& st, const uint8_t* 
   else if (NT == 2 || nt_count == 2) main_chunk_n<NT, (NT >= 2 ? 2 : NT)>(st, hrows_set, hsal_set, out_local, lane, acc);
   else if (NT == 3 || nt_count == 3) main_chunk_n<NT, (NT >= 3 ? 3 : NT)>(st, hrows_set, hsal_set, out_local, lane, acc);
   else main_chunk_n<NT, NT>(st, hrows_set, hsal_set, out_local, lane, acc);
+}
+
+// ---- weights of a chunk kept in registers across row passes (segments of many rows) ------------------
+// A warp owns 16 outputs x 256 columns = 64 half2 per lane: unpacked once per unit, after which a
+// row pass costs only the activation loads and the MMAs.  Returns the packed rows of the chunk.
+__device__ __forceinline__ int unpack_chunk_ns(const StagedTile& st, int out_local, int lane, uint32_t (&a)[kChunkRows][2][4]) {
+  const ColHeader* ch = reinterpret_cast<const ColHeader*>(st.col);
+  const int num_slots = ch->num_slots;
+  const int p_total = num_slots > 0 ? min(static_cast<int>(ch->slot_end[num_slots - 1]), kChunkRows) : 0;
+  int slot = 0;
+  RowScalesNs rs = load_row_scales_ns(st, 0, out_local, lane);
+#pragma unroll
+  for (int p = 0; p < kChunkRows; ++p) {
+    if (p < p_total) {
+      while (slot + 1 < num_slots && p >= ch->slot_end[slot]) {
+        ++slot;
+        rs = load_row_scales_ns(st, slot, out_local, lane);
+      }
+      unpack_fragments_ns(st, p, out_local, lane, rs, a[p]);
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[p][h][i] = 0u;
+    }
+  }
+  return p_total;
+}
+
+template <int NT, int NTC>
+__device__ __forceinline__ void main_chunk_cached_n(const StagedTile& st, const uint32_t (&a)[kChunkRows][2][4], int p_total,
+                                                    const uint8_t* hrows_set, const uint8_t* hsal_set, int out_local, int lane,
+                                                    float (&acc)[NT][4]) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint8_t* h_base = hrows_set + g * kHiddenRowBytes + t * 16;
+#pragma unroll
+  for (int p = 0; p < kChunkRows; ++p) {
+    if (p < p_total) {
+#pragma unroll
+      for (int nt = 0; nt < NTC; ++nt) {
+        const uint4 hv = *reinterpret_cast<const uint4*>(h_base + nt * 8 * kHiddenRowBytes + p * 64);
+        mma_m16n8k16(acc[nt], a[p][0][0], a[p][1][0], a[p][0][1], a[p][1][1], hv.x, hv.y);
+        mma_m16n8k16(acc[nt], a[p][0][2], a[p][1][2], a[p][0][3], a[p][1][3], hv.z, hv.w);
+      }
+    }
+  }
+  sal_chunk_n<NT, NTC>(st, hsal_set, out_local, lane, acc);
+}
+
+template <int NT>
+__device__ __forceinline__ void main_chunk_cached(const StagedTile& st, const uint32_t (&a)[kChunkRows][2][4], int p_total,
+                                                  const uint8_t* hrows_set, const uint8_t* hsal_set, int out_local, int lane,
+                                                  int nt_count, float (&acc)[NT][4]) {
+  if (NT == 1 || nt_count == 1) main_chunk_cached_n<NT, 1>(st, a, p_total, hrows_set, hsal_set, out_local, lane, acc);
+  else if (NT == 2 || nt_count == 2) main_chunk_cached_n<NT, (NT >= 2 ? 2 : NT)>(st, a, p_total, hrows_set, hsal_set, out_local, lane, acc);
+  else if (NT == 3 || nt_count == 3) main_chunk_cached_n<NT, (NT >= 3 ? 3 : NT)>(st, a, p_total, hrows_set, hsal_set, out_local, lane, acc);
+  else main_chunk_cached_n<NT, NT>(st, a, p_total, hrows_set, hsal_set, out_local, lane, acc);
 }
 
 // ---- epilogue of one row pass --------------------------------------------------------------------
@@ -348,8 +415,10 @@ __device__ __forceinline__ bool unit_live(const TiledArgs& args, const UnitRoute
 
 // ---- one CTA per unit, any number of chunks ---------------------------------------------------------
 // grid (tiles (dual) or ceil(tiles / 2) (single), segment bound)
-template <int NT, int MODE>
-__global__ void __launch_bounds__(kThreads, 3) grouped_tiled_kernel(const __grid_constant__ TiledArgs args) {
+// CACHE: single-chunk projections keep their unpacked weights in registers across the row passes of a
+// segment (64 more registers: two CTAs per SM instead of three) - the variant for prefill-sized segments.
+template <int NT, int MODE, bool CACHE>
+__global__ void __launch_bounds__(kThreads, CACHE ? 2 : 3) grouped_tiled_kernel(const __grid_constant__ TiledArgs args) {
   constexpr bool DUAL = MODE != MODE_SINGLE;
   constexpr int NH = DUAL ? 2 : 1;
   extern __shared__ uint4 smem_raw[];
@@ -402,6 +471,8 @@ __global__ void __launch_bounds__(kThreads, 3) grouped_tiled_kernel(const __grid
   int staged_chunk = -1;
   uint32_t par_w = 0u, par_h = 0u;
   bool dead = false;
+  uint32_t a_cache[CACHE ? kChunkRows : 1][2][4];
+  int cached_rows = -1;  // packed rows held in a_cache once the chunk has been unpacked
   for (int r0 = unit.row_begin; r0 < unit.row_end; r0 += NT * 8) {
     const int rows = min(NT * 8, unit.row_end - r0);
     const int nt_count = (rows + 7) >> 3;
@@ -455,7 +526,18 @@ __global__ void __launch_bounds__(kThreads, 3) grouped_tiled_kernel(const __grid
       }
       gather_salient<NT, NH>(hsal, hrows, rows, args.sal_slots, col_of);
       __syncthreads();
-      if (tile_valid) main_chunk<NT>(st, hrows_set, hsal_set, og * 16, lane, nt_count, acc);
+      if (tile_valid) {
+        if constexpr (CACHE) {
+          if (chunks == 1) {
+            if (cached_rows < 0) cached_rows = unpack_chunk_ns(st, og * 16, lane, a_cache);
+            main_chunk_cached<NT>(st, a_cache, cached_rows, hrows_set, hsal_set, og * 16, lane, nt_count, acc);
+          } else {
+            main_chunk<NT>(st, hrows_set, hsal_set, og * 16, lane, nt_count, acc);
+          }
+        } else {
+          main_chunk<NT>(st, hrows_set, hsal_set, og * 16, lane, nt_count, acc);
+        }
+      }
     }
     if (dead) continue;
     finish_rows<NT, MODE>(args, hrows, r, og, tile_valid, expert, tile0, r0, rows, nt_count, acc);
@@ -697,6 +779,9 @@ __global__ void __launch_bounds__(kThreads) tiled_dump_kernel(TrisProjView v, in
 }
 
 // ---- host side --------------------------------------------------------------------------------------
+// typical rows per segment up to which the persistent decode kernels are used
+constexpr int kTiledDecodeMaxRows = 64;
+
 static inline int rec_slot_bytes_for(int max_record_bytes) { return ((max_record_bytes + 15) & ~15) + 16; }
 
 static int sm_count() {
@@ -743,7 +828,7 @@ static int launch_tiled(const TiledArgs& args, cudaStream_t stream, bool pdl) {
   }
   const size_t smem = smem_layout(args.rec_slot_bytes, args.col_slot_bytes, args.sal_slots, NH, NT, 1).total;
   TRIS_REQUIRE(smem <= 227 * 1024, TRIS_ERR_UNSUPPORTED, "grouped_tiled_kernel: %zu bytes of shared memory", smem);
-  auto kernel = grouped_tiled_kernel<NT, MODE>;
+  auto kernel = grouped_tiled_kernel<NT, MODE, false>;
   static size_t configured[64] = {};
   int st = configure_smem(kernel, smem, configured);
   if (st != TRIS_OK) return st;
@@ -751,8 +836,27 @@ static int launch_tiled(const TiledArgs& args, cudaStream_t stream, bool pdl) {
                     "grouped_tiled_kernel launch");
 }
 
+// Prefill-sized segments of a single-chunk projection: one CTA per unit, 32 rows per pass, weights
+// unpacked once per unit and kept in registers.
+template <int MODE>
+static int launch_tiled_cached(const TiledArgs& args, cudaStream_t stream, bool pdl) {
+  constexpr int NH = (MODE == MODE_SINGLE) ? 1 : 2;
+  constexpr int NT = 4;
+  const int tiles = tiles_per_expert(args.proj[0].out_features);
+  const int units_x = MODE == MODE_SINGLE ? (tiles + 1) / 2 : tiles;
+  const size_t smem = smem_layout(args.rec_slot_bytes, args.col_slot_bytes, args.sal_slots, NH, NT, 1).total;
+  TRIS_REQUIRE(smem <= 227 * 1024, TRIS_ERR_UNSUPPORTED, "grouped_tiled_kernel: %zu bytes of shared memory", smem);
+  auto kernel = grouped_tiled_kernel<NT, MODE, true>;
+  static size_t configured[64] = {};
+  int st = configure_smem(kernel, smem, configured);
+  if (st != TRIS_OK) return st;
+  return check_cuda(launch_kernel(kernel, dim3(units_x, args.num_segments), dim3(kThreads), smem, stream, pdl, 1, args),
+                    "grouped_tiled_kernel (cached weights) launch");
+}
+
 template <int MODE>
 static int dispatch_tiled(const TiledArgs& args, int max_rows, cudaStream_t stream, bool pdl) {
+  if (max_rows > kTiledDecodeMaxRows && num_chunks(args.proj[0].rank) == 1) return launch_tiled_cached<MODE>(args, stream, pdl);
   if (max_rows <= 8) return launch_tiled<1, MODE>(args, stream, pdl);
   if (max_rows <= 16) return launch_tiled<2, MODE>(args, stream, pdl);
   if (max_rows <= 24) return launch_tiled<3, MODE>(args, stream, pdl);
@@ -774,7 +878,7 @@ int launch_grouped_tiled(const TrisProjView* proj_a, const TrisProjView* proj_b,
   // Rows per pass: a longer segment costs a second pass that only re-unpacks (the decoded planes
   // stay), so size the activation tile for mean + 2 sigma of a balanced router rather than for the
   // worst case; smaller tiles mean more resident CTAs.
-  if (route->num_segments > 0) {
+  if (route->num_segments > 0 && max_rows <= kTiledDecodeMaxRows) {
     const double mean = static_cast<double>(route->num_rows) / route->num_segments;
     max_rows = std::max(1, std::min(max_rows, static_cast<int>(ceil(mean + 2.0 * sqrt(mean)))));
   }
