@@ -428,13 +428,25 @@ def run_reference(args):
 def run_ncu_case(args):
     """Small fixed launch sequence for profiler captures (no timing, no graphs):
     `layer`   - one warm-up pass and one pass of the whole block over `--layers` layers;
-    `grouped` - two passes of the grouped gate/up and grouped down kernels alone."""
+    `grouped` - two passes of the grouped gate/up and grouped down kernels alone;
+    `packed4` - two passes of the 4-bit GEMM over 80 distinct 2048 x 2048 matrices, `--tokens` rows."""
     import trismoe_b200 as tm
     from trismoe_b200 import synth
 
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
     T = args.tokens
+    if args.ncu_case == "packed4":  # 80 distinct 2048 x 2048 4-bit matrices (176 MB > L2), two passes
+        import numpy as np
+
+        rng = np.random.default_rng(0)
+        mats = [tm.Packed4Linear(synth.packed4_matrix(rng, 2048, 2048, 128), device) for _ in range(80)]
+        x = synth.synth_activations(T, 2048, seed=T).to(device)
+        for _ in range(2):
+            for m in mats:
+                m(x, 3)
+            torch.cuda.synchronize()
+        return
     blocks, _ = build_stack(device, layers=args.layers)
     x = synth.synth_activations(T, 2048, seed=T).to(device)
     if args.ncu_case == "layer":
@@ -657,7 +669,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ncu-case", default=None, choices=["layer", "grouped"],
+    ap.add_argument("--ncu-case", default=None, choices=["layer", "grouped", "packed4"],
                     help="run a short untimed launch sequence for a profiler capture and exit")
     ap.add_argument("--extra", action="store_true", help="run the secondary workloads (prefill, Mixtral shape, streaming)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers for --ncu-case")

@@ -121,7 +121,7 @@ int combine_routed_impl(const void* down_out_f16, const int32_t* row_of_flat, co
 int launch_router_route(const float* logits, int num_tokens, int num_experts, int top_k, int norm, int m_tile,
                         int32_t* selected, float* weights, int32_t* perm, int32_t* tok, int32_t* slot,
                         int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets, int32_t* problem_offsets,
-                        int32_t* counts, cudaStream_t stream);
+                        int32_t* counts, cudaStream_t stream, int32_t* scratch = nullptr, size_t scratch_bytes = 0);
 
 // ---- device helpers -------------------------------------------------------------------
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {

@@ -150,7 +150,10 @@ extern "C" int tris_moe_layer_forward(const TrisMoeLayerView* layer, const void*
   auto route_launch = [&]() {
     return launch_router_route(logits, T, layer->num_experts, layer->top_k, layer->norm_topk_prob, 4, w.selected,
                                w.weights, w.perm, w.tok, w.slot, w.row_of_flat, w.expert_ids, w.segment_offsets,
-                               w.problem_offsets, w.counts, s);
+                               w.problem_offsets, w.counts, s,
+                               // nothing uses the grouped-down output buffer before the route exists: scratch of the
+                               // multi-CTA route
+                               reinterpret_cast<int32_t*>(w.down_out), 2 * static_cast<size_t>(R) * layer->hidden_size);
   };
   if (logits_given) {
     st = route_launch();

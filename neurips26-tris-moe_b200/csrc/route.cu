@@ -72,42 +72,12 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int num_tok
                  selected + static_cast<size_t>(warp) * top_k, weights + static_cast<size_t>(warp) * top_k, lane);
 }
 
-// Single CTA.  Stable counting sort of the flat (token, slot) list by expert: every warp owns
-// a contiguous chunk of the list, counts its experts, a scan over (expert, warp) turns the
-// counts into write offsets, and a second pass places the elements in order.
-// `sh` holds (34 * E) ints: count[E], start[E], per-warp counts/offsets [32][E].
-__device__ __forceinline__ void build_route_body(
-    int32_t* sh, const int32_t* selected, int num_tokens, int top_k, int num_experts, int m_tile,
-    int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
-    int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
-    int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
-  constexpr int NW = kRouteThreads / 32;
-  int32_t* count = sh;                      // [E]
-  int32_t* start = sh + num_experts;        // [E] first grouped row of each expert
-  int32_t* woff = sh + 2 * num_experts;     // [NW][E]
-  const int R = num_tokens * top_k;
-  const int tid = threadIdx.x;
-  const int warp = tid >> 5, lane = tid & 31;
-  const int chunk = ((R + NW - 1) / NW + 31) & ~31;  // elements per warp, whole 32-element batches
-  const int f0 = warp * chunk, f1 = min(R, f0 + chunk);
-  for (int i = tid; i < NW * num_experts; i += kRouteThreads) woff[i] = 0;
-  __syncthreads();
-  for (int base = f0; base < f1; base += 32) {
-    const int f = base + lane;
-    int e = (f < f1) ? selected[f] : -1;
-    if (e >= num_experts) e = -1;
-    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
-    if (e >= 0 && lane == __ffs(peers) - 1) woff[warp * num_experts + e] += __popc(peers);
-    __syncwarp();
-  }
-  __syncthreads();
-  for (int e = tid; e < num_experts; e += kRouteThreads) {
-    int total = 0;
-    for (int w = 0; w < NW; ++w) total += woff[w * num_experts + e];
-    count[e] = total;
-  }
-  __syncthreads();
-  if (warp == 0) {
+// One warp: per-expert row counts -> first grouped row of every expert (`start`) and the segment
+// arrays of the active experts (padded to num_experts so that no size is read back).
+__device__ __forceinline__ void route_scan_segments(const int32_t* count, int32_t* start, int num_experts, int m_tile,
+                                                    int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
+                                                    int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out,
+                                                    int lane) {
     // each lane owns a contiguous run of experts; warp scan of (segments, rows, tiles)
     const int epl = (num_experts + 31) / 32;
     const int e0 = lane * epl, e1 = min(num_experts, e0 + epl);
@@ -149,6 +119,44 @@ __device__ __forceinline__ void build_route_body(
       counts_out[1] = ntiles;
     }
   }
+
+// Single CTA.  Stable counting sort of the flat (token, slot) list by expert: every warp owns
+// a contiguous chunk of the list, counts its experts, a scan over (expert, warp) turns the
+// counts into write offsets, and a second pass places the elements in order.
+// `sh` holds (34 * E) ints: count[E], start[E], per-warp counts/offsets [32][E].
+__device__ __forceinline__ void build_route_body(
+    int32_t* sh, const int32_t* selected, int num_tokens, int top_k, int num_experts, int m_tile,
+    int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
+    int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
+    int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
+  constexpr int NW = kRouteThreads / 32;
+  int32_t* count = sh;                      // [E]
+  int32_t* start = sh + num_experts;        // [E] first grouped row of each expert
+  int32_t* woff = sh + 2 * num_experts;     // [NW][E]
+  const int R = num_tokens * top_k;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int chunk = ((R + NW - 1) / NW + 31) & ~31;  // elements per warp, whole 32-element batches
+  const int f0 = warp * chunk, f1 = min(R, f0 + chunk);
+  for (int i = tid; i < NW * num_experts; i += kRouteThreads) woff[i] = 0;
+  __syncthreads();
+  for (int base = f0; base < f1; base += 32) {
+    const int f = base + lane;
+    int e = (f < f1) ? selected[f] : -1;
+    if (e >= num_experts) e = -1;
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+    if (e >= 0 && lane == __ffs(peers) - 1) woff[warp * num_experts + e] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = tid; e < num_experts; e += kRouteThreads) {
+    int total = 0;
+    for (int w = 0; w < NW; ++w) total += woff[w * num_experts + e];
+    count[e] = total;
+  }
+  __syncthreads();
+  if (warp == 0)
+    route_scan_segments(count, start, num_experts, m_tile, expert_ids, segment_offsets, problem_offsets, counts_out, lane);
   __syncthreads();
   for (int e = tid; e < num_experts; e += kRouteThreads) {  // counts -> write offsets per warp
     int run = start[e];
@@ -190,6 +198,134 @@ __global__ void __launch_bounds__(kRouteThreads) build_route_kernel(
   pdl_launch_dependents();
   build_route_body(sh, selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat, expert_ids,
                    segment_offsets, problem_offsets, counts_out);
+}
+
+// ---- the same route built by several CTAs (prefill-sized batches) -------------------------------------
+// count: every CTA histograms its 2048-element chunk of the flat list; scan: one CTA turns the
+// (chunk, expert) counts into write offsets and writes the segment arrays; place: every CTA places
+// its chunk, warp by warp in list order, so rows of a segment stay in ascending (token, slot) order.
+constexpr int kRouteParChunk = 2048;
+constexpr int kRouteParThreads = 256;
+
+__global__ void __launch_bounds__(kRouteParThreads) route_count_kernel(const int32_t* __restrict__ selected, int num_rows,
+                                                                       int num_experts, int32_t* __restrict__ counts_blk) {
+  extern __shared__ int32_t sh[];  // [E]
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < num_experts; e += kRouteParThreads) sh[e] = 0;
+  __syncthreads();
+  const int f0 = blockIdx.x * kRouteParChunk, f1 = min(num_rows, f0 + kRouteParChunk);
+  for (int f = f0 + threadIdx.x; f < f1; f += kRouteParThreads) {
+    const int e = selected[f];
+    if (e >= 0 && e < num_experts) atomicAdd(&sh[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += kRouteParThreads) counts_blk[blockIdx.x * num_experts + e] = sh[e];
+}
+
+__global__ void __launch_bounds__(kRouteThreads) route_scan_kernel(int32_t* __restrict__ counts_blk, int num_blocks, int num_experts,
+                                                                   int m_tile, int32_t* __restrict__ expert_ids,
+                                                                   int32_t* __restrict__ segment_offsets,
+                                                                   int32_t* __restrict__ problem_offsets,
+                                                                   int32_t* __restrict__ counts_out) {
+  extern __shared__ int32_t sh[];  // count[E], start[E]
+  int32_t* count = sh;
+  int32_t* start = sh + num_experts;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < num_experts; e += kRouteThreads) {
+    int total = 0;
+    for (int b = 0; b < num_blocks; ++b) total += counts_blk[b * num_experts + e];
+    count[e] = total;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32)
+    route_scan_segments(count, start, num_experts, m_tile, expert_ids, segment_offsets, problem_offsets, counts_out, threadIdx.x);
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += kRouteThreads) {  // counts -> first row of every (chunk, expert)
+    int run = start[e];
+    for (int b = 0; b < num_blocks; ++b) {
+      const int c = counts_blk[b * num_experts + e];
+      counts_blk[b * num_experts + e] = run;
+      run += c;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kRouteParThreads) route_place_kernel(const int32_t* __restrict__ selected, int num_rows, int top_k,
+                                                                       int num_experts, const int32_t* __restrict__ start_blk,
+                                                                       int32_t* __restrict__ perm, int32_t* __restrict__ tok,
+                                                                       int32_t* __restrict__ slot, int32_t* __restrict__ row_of_flat) {
+  constexpr int NW = kRouteParThreads / 32;
+  extern __shared__ int32_t sh[];  // woff[NW][E]
+  int32_t* woff = sh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int i = tid; i < NW * num_experts; i += kRouteParThreads) woff[i] = 0;
+  __syncthreads();
+  const int f0 = blockIdx.x * kRouteParChunk + warp * (kRouteParChunk / NW);
+  const int f1 = min(num_rows, f0 + kRouteParChunk / NW);
+  for (int base = f0; base < f1; base += 32) {
+    const int f = base + lane;
+    int e = (f < f1) ? selected[f] : -1;
+    if (e >= num_experts) e = -1;
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+    if (e >= 0 && lane == __ffs(peers) - 1) woff[warp * num_experts + e] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = tid; e < num_experts; e += kRouteParThreads) {
+    int run = start_blk[blockIdx.x * num_experts + e];
+    for (int w = 0; w < NW; ++w) {
+      const int c = woff[w * num_experts + e];
+      woff[w * num_experts + e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  for (int base = f0; base < f1; base += 32) {
+    const int f = base + lane;
+    int e = (f < f1) ? selected[f] : -1;
+    if (e >= num_experts) e = -1;
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+    if (e >= 0) {
+      const int pos = woff[warp * num_experts + e] + __popc(peers & ((1u << lane) - 1u));
+      perm[pos] = f;
+      const int tk = f / top_k;
+      tok[pos] = tk;
+      slot[pos] = f - tk * top_k;
+      row_of_flat[f] = pos;
+    } else if (f < f1) {
+      row_of_flat[f] = -1;
+    }
+    __syncwarp();
+    if (e >= 0 && lane == __ffs(peers) - 1) woff[warp * num_experts + e] += __popc(peers);
+    __syncwarp();
+  }
+}
+
+// Route of a prefill-sized batch with `scratch` (>= ceil(R / 2048) * E ints, caller-owned, free until
+// the launch ends); launched after the kernel that wrote `selected`.
+static int launch_route_parallel(const int32_t* selected, int num_tokens, int top_k, int num_experts, int m_tile, int32_t* perm,
+                                 int32_t* tok, int32_t* slot, int32_t* row_of_flat, int32_t* expert_ids,
+                                 int32_t* segment_offsets, int32_t* problem_offsets, int32_t* counts, int32_t* scratch,
+                                 cudaStream_t stream) {
+  const int R = num_tokens * top_k;
+  const int nb = ceil_div(R, kRouteParChunk);
+  int st = check_cuda(launch_kernel(route_count_kernel, dim3(nb), dim3(kRouteParThreads), sizeof(int32_t) * num_experts, stream,
+                                    /*pdl=*/true, 1, selected, R, num_experts, scratch),
+                      "route_count_kernel launch");
+  if (st != TRIS_OK) return st;
+  st = check_cuda(launch_kernel(route_scan_kernel, dim3(1), dim3(kRouteThreads), 2 * sizeof(int32_t) * num_experts, stream,
+                                /*pdl=*/true, 1, scratch, nb, num_experts, m_tile, expert_ids, segment_offsets, problem_offsets,
+                                counts),
+                  "route_scan_kernel launch");
+  if (st != TRIS_OK) return st;
+  return check_cuda(launch_kernel(route_place_kernel, dim3(nb), dim3(kRouteParThreads),
+                                  sizeof(int32_t) * (kRouteParThreads / 32) * num_experts, stream, /*pdl=*/true, 1, selected, R,
+                                  top_k, num_experts, static_cast<const int32_t*>(scratch), perm, tok, slot, row_of_flat),
+                    "route_place_kernel launch");
 }
 
 // Router head and route in one single-CTA launch (decode-sized batches).
@@ -268,7 +404,7 @@ static int route_smem_bytes(int num_experts, int rows, int* sel_cap) {
 int launch_router_route(const float* logits, int num_tokens, int num_experts, int top_k, int norm, int m_tile,
                         int32_t* selected, float* weights, int32_t* perm, int32_t* tok, int32_t* slot,
                         int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets, int32_t* problem_offsets,
-                        int32_t* counts, cudaStream_t stream) {
+                        int32_t* counts, cudaStream_t stream, int32_t* scratch, size_t scratch_bytes) {
   TRIS_REQUIRE(num_experts <= 32 * kMaxExpertsPerLane && top_k <= 32 && top_k <= num_experts, TRIS_ERR_UNSUPPORTED,
                "router: supports up to %d experts and top-32", 32 * kMaxExpertsPerLane);
   int sel_cap = 0;
@@ -284,6 +420,11 @@ int launch_router_route(const float* logits, int num_tokens, int num_experts, in
                                                                                  norm, selected, weights);
   int st = check_cuda(cudaGetLastError(), "router_topk_kernel launch");
   if (st != TRIS_OK) return st;
+  const int rows = num_tokens * top_k;
+  if (scratch && rows >= 2 * kRouteParChunk &&
+      scratch_bytes >= sizeof(int32_t) * static_cast<size_t>(ceil_div(rows, kRouteParChunk)) * num_experts)
+    return launch_route_parallel(selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat, expert_ids,
+                                 segment_offsets, problem_offsets, counts, scratch, stream);
   return check_cuda(launch_kernel(build_route_kernel, dim3(1), dim3(kRouteThreads), smem, stream, /*pdl=*/true, 1,
                                   static_cast<const int32_t*>(selected), num_tokens, top_k, num_experts, m_tile, perm,
                                   tok, slot, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, sel_cap),
