@@ -310,11 +310,11 @@ __global__ void __launch_bounds__(kRouteParThreads) route_place_kernel(const int
 static int launch_route_parallel(const int32_t* selected, int num_tokens, int top_k, int num_experts, int m_tile, int32_t* perm,
                                  int32_t* tok, int32_t* slot, int32_t* row_of_flat, int32_t* expert_ids,
                                  int32_t* segment_offsets, int32_t* problem_offsets, int32_t* counts, int32_t* scratch,
-                                 cudaStream_t stream) {
+                                 cudaStream_t stream, bool first_pdl = true) {
   const int R = num_tokens * top_k;
   const int nb = ceil_div(R, kRouteParChunk);
   int st = check_cuda(launch_kernel(route_count_kernel, dim3(nb), dim3(kRouteParThreads), sizeof(int32_t) * num_experts, stream,
-                                    /*pdl=*/true, 1, selected, R, num_experts, scratch),
+                                    first_pdl, 1, selected, R, num_experts, scratch),
                       "route_count_kernel launch");
   if (st != TRIS_OK) return st;
   st = check_cuda(launch_kernel(route_scan_kernel, dim3(1), dim3(kRouteThreads), 2 * sizeof(int32_t) * num_experts, stream,
@@ -536,9 +536,31 @@ extern "C" int tris_build_grouped_route(const int32_t* selected_experts, int32_t
                TRIS_ERR_INVALID_ARG, "tris_build_grouped_route: null pointer");
   TRIS_REQUIRE(num_tokens >= 0 && top_k > 0 && num_experts > 0 && m_tile > 0, TRIS_ERR_INVALID_ARG,
                "tris_build_grouped_route: bad sizes T=%d k=%d E=%d m_tile=%d", num_tokens, top_k, num_experts, m_tile);
+  return tris_build_grouped_route_scratch(selected_experts, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices,
+                                          grouped_slots, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts,
+                                          nullptr, 0, stream);
+}
+
+extern "C" int tris_build_grouped_route_scratch(const int32_t* selected_experts, int32_t num_tokens, int32_t top_k,
+                                                int32_t num_experts, int32_t m_tile, int32_t* perm,
+                                                int32_t* grouped_token_indices, int32_t* grouped_slots,
+                                                int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets,
+                                                int32_t* problem_offsets, int32_t* counts, int32_t* scratch,
+                                                size_t scratch_bytes, void* stream) {
+  TRIS_REQUIRE(selected_experts && perm && grouped_token_indices && grouped_slots && row_of_flat && expert_ids &&
+                   segment_offsets && problem_offsets && counts,
+               TRIS_ERR_INVALID_ARG, "tris_build_grouped_route: null pointer");
+  TRIS_REQUIRE(num_tokens >= 0 && top_k > 0 && num_experts > 0 && m_tile > 0, TRIS_ERR_INVALID_ARG,
+               "tris_build_grouped_route: bad sizes T=%d k=%d E=%d m_tile=%d", num_tokens, top_k, num_experts, m_tile);
   TRIS_REQUIRE(num_experts <= 320, TRIS_ERR_UNSUPPORTED, "tris_build_grouped_route: more than 320 experts");
+  const int rows = num_tokens * top_k;
+  if (scratch && rows >= 2 * kRouteParChunk &&
+      scratch_bytes >= sizeof(int32_t) * static_cast<size_t>(ceil_div(rows, kRouteParChunk)) * num_experts)
+    return launch_route_parallel(selected_experts, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices,
+                                 grouped_slots, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, scratch,
+                                 static_cast<cudaStream_t>(stream), programmatic_launch_default());
   int sel_cap = 0;
-  const int smem = route_smem_bytes(num_experts, num_tokens * top_k, &sel_cap);
+  const int smem = route_smem_bytes(num_experts, rows, &sel_cap);
   return check_cuda(launch_kernel(build_route_kernel, dim3(1), dim3(kRouteThreads), smem, static_cast<cudaStream_t>(stream),
                                   programmatic_launch_default(), 1, selected_experts, num_tokens, top_k, num_experts, m_tile,
                                   perm, grouped_token_indices, grouped_slots, row_of_flat, expert_ids, segment_offsets,

@@ -255,16 +255,18 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         lib = _native.load()
         T, k = (int(s) for s in selected_i32.shape)
         R, E, dev = T * k, num_experts, selected_i32.device
-        buf = torch.empty((4 * R + 3 * E + 6,), dtype=torch.int32, device=dev)
+        scratch_n = ((R + 2047) // 2048) * E  # lets the sort of a large slot list run on several CTAs
+        buf = torch.empty((4 * R + 3 * E + 6 + scratch_n,), dtype=torch.int32, device=dev)
         perm, tok, slot, rof = (buf[i * R:(i + 1) * R] for i in range(4))
         ids = buf[4 * R: 4 * R + E]
         seg = buf[4 * R + E: 4 * R + 2 * E + 1]
         prob = buf[4 * R + 2 * E + 1: 4 * R + 3 * E + 2]
         counts = buf[4 * R + 3 * E + 2: 4 * R + 3 * E + 6]
-        _native.check(lib.tris_build_grouped_route(selected_i32.data_ptr(), T, k, E, 4, perm.data_ptr(), tok.data_ptr(),
-                                                   slot.data_ptr(), rof.data_ptr(), ids.data_ptr(), seg.data_ptr(),
-                                                   prob.data_ptr(), counts.data_ptr(),
-                                                   torch.cuda.current_stream(dev).cuda_stream), "build_grouped_route")
+        scratch = buf[4 * R + 3 * E + 6:]
+        _native.check(lib.tris_build_grouped_route_scratch(selected_i32.data_ptr(), T, k, E, 4, perm.data_ptr(), tok.data_ptr(),
+                                                           slot.data_ptr(), rof.data_ptr(), ids.data_ptr(), seg.data_ptr(),
+                                                           prob.data_ptr(), counts.data_ptr(), scratch.data_ptr(), 4 * scratch_n,
+                                                           torch.cuda.current_stream(dev).cuda_stream), "build_grouped_route")
         return {"perm": perm, "tok": tok, "slot": slot, "row_of_flat": rof, "expert_ids": ids, "segment_offsets": seg,
                 "counts": counts, "_buf": buf, "rows": R, "experts": E, "max_rows": T}
 

@@ -358,7 +358,8 @@ def build_grouped_route(selected_experts: torch.Tensor, num_experts: int, m_tile
     lib = _native.load()
     sel = selected_experts.to(torch.int32).contiguous()
     E = int(num_experts)
-    buf = torch.empty((4 * R + 3 * E + 2 + 2,), dtype=torch.int32, device=device)
+    scratch_n = ((R + 2047) // 2048) * E  # scratch that lets the sort of >= 4096 rows run on several CTAs
+    buf = torch.empty((4 * R + 3 * E + 2 + 2 + scratch_n,), dtype=torch.int32, device=device)
     perm, tok, slot, rof = (buf[i * R:(i + 1) * R] for i in range(4))
     base = 4 * R
     expert_ids = buf[base: base + E]
@@ -367,9 +368,10 @@ def build_grouped_route(selected_experts: torch.Tensor, num_experts: int, m_tile
     counts = buf[base + 3 * E + 2: base + 3 * E + 4]
     with torch.cuda.device(device):
         _native.check(
-            lib.tris_build_grouped_route(sel.data_ptr(), T, k, E, int(m_tile), perm.data_ptr(), tok.data_ptr(),
-                                         slot.data_ptr(), rof.data_ptr(), expert_ids.data_ptr(), seg.data_ptr(),
-                                         prob.data_ptr(), counts.data_ptr(), _stream_ptr(device)),
+            lib.tris_build_grouped_route_scratch(sel.data_ptr(), T, k, E, int(m_tile), perm.data_ptr(), tok.data_ptr(),
+                                                 slot.data_ptr(), rof.data_ptr(), expert_ids.data_ptr(), seg.data_ptr(),
+                                                 prob.data_ptr(), counts.data_ptr(), buf[base + 3 * E + 4:].data_ptr(),
+                                                 4 * scratch_n, _stream_ptr(device)),
             "build_grouped_route",
         )
     nseg, tiles = (int(v) for v in counts.cpu().tolist())
