@@ -260,7 +260,7 @@ int tris_build_grouped_route(const int32_t* selected_experts, int32_t num_tokens
 /*
  * The same route for large batches: with `scratch` (caller-owned device memory, at least
  * ceil(num_tokens * top_k / 2048) * num_experts int32, free for the duration of the launches) and
- * >= 4096 routed rows the sort runs on several CTAs (count, scan, place) instead of one; results
+ * >= 8192 routed rows the sort runs on several CTAs (count, scan, place) instead of one; results
  * are identical.  scratch == NULL behaves like tris_build_grouped_route.
  */
 int tris_build_grouped_route_scratch(const int32_t* selected_experts, int32_t num_tokens, int32_t top_k,

@@ -421,7 +421,7 @@ int launch_router_route(const float* logits, int num_tokens, int num_experts, in
   int st = check_cuda(cudaGetLastError(), "router_topk_kernel launch");
   if (st != TRIS_OK) return st;
   const int rows = num_tokens * top_k;
-  if (scratch && rows >= 2 * kRouteParChunk &&
+  if (scratch && rows >= 4 * kRouteParChunk &&
       scratch_bytes >= sizeof(int32_t) * static_cast<size_t>(ceil_div(rows, kRouteParChunk)) * num_experts)
     return launch_route_parallel(selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat, expert_ids,
                                  segment_offsets, problem_offsets, counts, scratch, stream);
@@ -554,7 +554,7 @@ extern "C" int tris_build_grouped_route_scratch(const int32_t* selected_experts,
                "tris_build_grouped_route: bad sizes T=%d k=%d E=%d m_tile=%d", num_tokens, top_k, num_experts, m_tile);
   TRIS_REQUIRE(num_experts <= 320, TRIS_ERR_UNSUPPORTED, "tris_build_grouped_route: more than 320 experts");
   const int rows = num_tokens * top_k;
-  if (scratch && rows >= 2 * kRouteParChunk &&
+  if (scratch && rows >= 4 * kRouteParChunk &&
       scratch_bytes >= sizeof(int32_t) * static_cast<size_t>(ceil_div(rows, kRouteParChunk)) * num_experts)
     return launch_route_parallel(selected_experts, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices,
                                  grouped_slots, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, scratch,

@@ -358,7 +358,7 @@ def build_grouped_route(selected_experts: torch.Tensor, num_experts: int, m_tile
     lib = _native.load()
     sel = selected_experts.to(torch.int32).contiguous()
     E = int(num_experts)
-    scratch_n = ((R + 2047) // 2048) * E  # scratch that lets the sort of >= 4096 rows run on several CTAs
+    scratch_n = ((R + 2047) // 2048) * E  # scratch that lets the sort of >= 8192 rows run on several CTAs
     buf = torch.empty((4 * R + 3 * E + 2 + 2 + scratch_n,), dtype=torch.int32, device=device)
     perm, tok, slot, rof = (buf[i * R:(i + 1) * R] for i in range(4))
     base = 4 * R

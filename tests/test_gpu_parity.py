@@ -202,7 +202,7 @@ def test_shared_hidden_vs_fp32(tm, n, k, m):
 
 
 @pytest.mark.parametrize("T,k,E", [(1, 8, 64), (8, 8, 64), (128, 8, 64), (64, 2, 8), (16, 8, 256), (700, 2, 8),
-                                   (700, 8, 64), (2048, 8, 64), (2500, 2, 8), (1111, 8, 256)])  # >= 4096 rows: multi-CTA sort
+                                   (700, 8, 64), (2048, 8, 64), (5000, 2, 8), (1111, 8, 256)])  # >= 8192 rows: multi-CTA sort
 def test_route_matches_oracle(tm, T, k, E):
     rng = np.random.default_rng(T * 31 + E)
     sel = np.stack([rng.choice(E, size=k, replace=False) for _ in range(T)]).astype(np.int64)
