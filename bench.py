@@ -248,7 +248,7 @@ def run_ours(args):
         del graph
     dom = max(kern, key=lambda n: kern[n]["us_per_launch"])
     roofline = {
-        "bound": "hbm", "kernel": f"grouped_tiled_persistent_kernel ({'gate/up dual + SiLU*mul' if dom == 'pair' else 'down'})",
+        "bound": "hbm", "kernel": f"grouped_tiled_kernel ({'gate/up dual + SiLU*mul' if dom == 'pair' else 'down'})",
         "achieved": round(kern[dom]["gbs"], 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
         "frac": round(kern[dom]["gbs"] / peak, 4), "frac_of_nominal_8TBs": round(kern[dom]["gbs"] / NOMINAL_HBM_GBS, 4),
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the

@@ -415,10 +415,14 @@ __device__ __forceinline__ bool unit_live(const TiledArgs& args, const UnitRoute
 
 // ---- one CTA per unit, any number of chunks ---------------------------------------------------------
 // grid (tiles (dual) or ceil(tiles / 2) (single), segment bound)
+// One CTA per unit, four CTAs per SM (64 registers, a single record stage): measured on B200 at the OLMoE
+// shape this beats the persistent kernel below (three CTAs per SM, 80 registers, records of the next unit
+// prefetched) by 16 % per launch at batch 128 - the kernel is bound by instruction issue, and a fourth
+// resident CTA hides more latency than the prefetch does; five CTAs (48 registers, spills) are slower.
 // CACHE: single-chunk projections keep their unpacked weights in registers across the row passes of a
-// segment (64 more registers: two CTAs per SM instead of three) - the variant for prefill-sized segments.
+// segment (64 more registers: two CTAs per SM) - the variant for prefill-sized segments.
 template <int NT, int MODE, bool CACHE>
-__global__ void __launch_bounds__(kThreads, CACHE ? 2 : 3) grouped_tiled_kernel(const __grid_constant__ TiledArgs args) {
+__global__ void __launch_bounds__(kThreads, CACHE ? 2 : 4) grouped_tiled_kernel(const __grid_constant__ TiledArgs args) {
   constexpr bool DUAL = MODE != MODE_SINGLE;
   constexpr int NH = DUAL ? 2 : 1;
   extern __shared__ uint4 smem_raw[];
@@ -812,21 +816,23 @@ static int launch_tiled(const TiledArgs& args, cudaStream_t stream, bool pdl) {
   constexpr int NH = (MODE == MODE_SINGLE) ? 1 : 2;
   const int tiles = tiles_per_expert(args.proj[0].out_features);
   const int units_x = MODE == MODE_SINGLE ? (tiles + 1) / 2 : tiles;
-  if (num_chunks(args.proj[0].rank) == 1) {
-    const size_t smem = smem_layout(args.rec_slot_bytes, args.col_slot_bytes, args.sal_slots, NH, NT, 2).total;
-    if (smem <= 227 * 1024) {
+  const size_t smem = smem_layout(args.rec_slot_bytes, args.col_slot_bytes, args.sal_slots, NH, NT, 1).total;
+  const bool four_per_sm = 4 * (smem + 1024) <= 227 * 1024;
+  if (num_chunks(args.proj[0].rank) == 1 && !four_per_sm) {
+    // the one-CTA-per-unit kernel would not reach four CTAs per SM: persistent CTAs that prefetch the next record
+    const size_t smem2 = smem_layout(args.rec_slot_bytes, args.col_slot_bytes, args.sal_slots, NH, NT, 2).total;
+    if (smem2 <= 227 * 1024) {
       auto kernel = grouped_tiled_persistent_kernel<NT, MODE>;
       static size_t configured[64] = {};  // per instantiation, per device: largest size set so far
-      int st = configure_smem(kernel, smem, configured);
+      int st = configure_smem(kernel, smem2, configured);
       if (st != TRIS_OK) return st;
-      const int per_sm = std::max<int>(1, std::min<size_t>(3, (227 * 1024) / (smem + 1024)));
+      const int per_sm = std::max<int>(1, std::min<size_t>(3, (227 * 1024) / (smem2 + 1024)));
       const long long units = static_cast<long long>(units_x) * args.num_segments;
       const int grid = static_cast<int>(std::min<long long>(units, static_cast<long long>(sm_count()) * per_sm));
-      return check_cuda(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, stream, pdl, 1, args),
+      return check_cuda(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem2, stream, pdl, 1, args),
                         "grouped_tiled_persistent_kernel launch");
     }
   }
-  const size_t smem = smem_layout(args.rec_slot_bytes, args.col_slot_bytes, args.sal_slots, NH, NT, 1).total;
   TRIS_REQUIRE(smem <= 227 * 1024, TRIS_ERR_UNSUPPORTED, "grouped_tiled_kernel: %zu bytes of shared memory", smem);
   auto kernel = grouped_tiled_kernel<NT, MODE, false>;
   static size_t configured[64] = {};
