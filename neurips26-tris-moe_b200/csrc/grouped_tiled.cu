@@ -441,6 +441,7 @@ __global__ void __launch_bounds__(kThreads, CACHE ? 2 : 4) grouped_tiled_kernel(
     mbar_init(&mbar[1], kWarps);
     fence_mbar_init();
   }
+  reinterpret_cast<uint4*>(gmap_base)[tid] = make_uint4(0u, 0u, 0u, 0u);  // both g_map planes, for the first chunk
   __syncthreads();
   // Activations come from the predecessor kernel; the route arrays too, unless the caller says
   // they are older, in which case the weight staging below overlaps the predecessor.
@@ -489,7 +490,9 @@ __global__ void __launch_bounds__(kThreads, CACHE ? 2 : 4) grouped_tiled_kernel(
 
     for (int kc = 0; kc < chunks; ++kc) {
       const int p0 = kc * kChunkRows;
-      __syncthreads();  // earlier consumers of the staging buffers are done
+      // the first chunk of a unit starts right behind the set-up barrier (planes already zeroed there)
+      const bool first_iter = staged_chunk < 0;
+      if (!first_iter) __syncthreads();  // earlier consumers of the staging buffers are done
       if (dead) break;
       const bool need_w = staged_chunk != kc;
       if (need_w) {
@@ -502,12 +505,12 @@ __global__ void __launch_bounds__(kThreads, CACHE ? 2 : 4) grouped_tiled_kernel(
           issue_record(v, expert, kc, d, rec_base + rr * args.rec_slot_bytes,
                        (DUAL || rr == 0) ? col_base + rr * args.col_slot_bytes : nullptr, valid, &mbar[0]);
         }
-        reinterpret_cast<uint4*>(gmap_base)[tid] = make_uint4(0u, 0u, 0u, 0u);  // 256 threads x 16 B = both planes
+        if (!first_iter) reinterpret_cast<uint4*>(gmap_base)[tid] = make_uint4(0u, 0u, 0u, 0u);  // 256 threads x 16 B = both planes
       }
       if (waited) issue_hidden<NT, NH>(hrows, args.hidden, rank, p0, rows, lane_order, args.hidden_stride, &mbar[1], row_src, args.col_scale);
       bool ok = true;
       if (need_w) {
-        __syncthreads();  // planes zeroed
+        if (!first_iter) __syncthreads();  // planes zeroed
         ok = mbar_wait_bounded(&mbar[0], par_w);
         par_w ^= 1u;
         if (ok && tile_valid) gr_decode_block(st.rec, og, const_cast<uint32_t*>(st.gmap), lane);
