@@ -258,16 +258,19 @@ int tris_build_grouped_route(const int32_t* selected_experts, int32_t num_tokens
                              int32_t* problem_offsets, int32_t* counts, void* stream);
 
 /*
- * The same route for large batches: with `scratch` (caller-owned device memory, at least
+ * The same route with two extensions.  (1) Entry f of the flat id list is read as
+ * selected_experts[f * selected_stride] - id_offset (1 and 0 for a plain [T, k] array): the receiver
+ * of an expert-parallel exchange finds the id of slot f behind that slot's activation row and
+ * numbered globally, and routes in place.  (2) With `scratch` (caller-owned device memory, at least
  * ceil(num_tokens * top_k / 2048) * num_experts int32, free for the duration of the launches) and
  * >= 8192 routed rows the sort runs on several CTAs (count, scan, place) instead of one; results
- * are identical.  scratch == NULL behaves like tris_build_grouped_route.
+ * are identical.  scratch == NULL keeps the single CTA.
  */
-int tris_build_grouped_route_scratch(const int32_t* selected_experts, int32_t num_tokens, int32_t top_k,
-                                     int32_t num_experts, int32_t m_tile, int32_t* perm,
-                                     int32_t* grouped_token_indices, int32_t* grouped_slots, int32_t* row_of_flat,
-                                     int32_t* expert_ids, int32_t* segment_offsets, int32_t* problem_offsets,
-                                     int32_t* counts, int32_t* scratch, size_t scratch_bytes, void* stream);
+int tris_build_grouped_route_ex(const int32_t* selected_experts, int32_t selected_stride, int32_t id_offset,
+                                int32_t num_tokens, int32_t top_k, int32_t num_experts, int32_t m_tile, int32_t* perm,
+                                int32_t* grouped_token_indices, int32_t* grouped_slots, int32_t* row_of_flat,
+                                int32_t* expert_ids, int32_t* segment_offsets, int32_t* problem_offsets,
+                                int32_t* counts, int32_t* scratch, size_t scratch_bytes, void* stream);
 
 /*
  * Router head of OlmoeSparseMoeBlock.forward (MO:1052-1058): softmax over fp32 logits

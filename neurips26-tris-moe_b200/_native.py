@@ -91,7 +91,7 @@ SIGNATURES = {
     "tris_tile_records_plan": (C.c_int, [_P(TrisProjView), _vp, _vp, _vp]),
     "tris_tile_records_build": (C.c_int, [_P(TrisProjView), _vp, _vp, _vp, _i32, _vp]),
     "tris_build_grouped_route": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "tris_build_grouped_route_scratch": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "tris_build_grouped_route_ex": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "tris_ep_pack_rows": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
     "tris_ep_signal_increment": (C.c_int, []),
     "tris_ep_enable_peer_access": (C.c_int, [_i32]),

@@ -82,6 +82,13 @@ __global__ void __launch_bounds__(128) ep_dispatch_peer_kernel(
     const int vecs = rank_gu >> 3;
     for (int i = threadIdx.x; i < 2 * vecs; i += blockDim.x) dst[i] = (i < vecs) ? g[i] : u[i - vecs];
   }
+  // rows beyond an owner's capacity are dropped: their combine index says so (every flat entry is
+  // written by exactly one thread of this launch, so the caller need not initialise the array)
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < num_rows; row += gridDim.x * blockDim.x) {
+    int d = 0;
+    while (d + 1 < world && row >= s_first[d + 1]) ++d;
+    if (row - s_first[d] >= capacity) combine_index[perm[row]] = -1;
+  }
   ep_signal_peers(peer_flags, world, my_rank);
 }
 

@@ -72,6 +72,15 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int num_tok
                  selected + static_cast<size_t>(warp) * top_k, weights + static_cast<size_t>(warp) * top_k, lane);
 }
 
+// The flat (token, slot) list of expert ids: entry f is base[f * stride] - offset (stride 1, offset 0 for
+// a plain [T, k] array; an exchange buffer keeps the id of slot f behind that slot's activation row and
+// numbers experts globally).
+struct SelectedIds {
+  const int32_t* base;
+  int stride, offset;
+  __device__ __forceinline__ int operator[](int f) const { return base[static_cast<size_t>(f) * stride] - offset; }
+};
+
 // One warp: per-expert row counts -> first grouped row of every expert (`start`) and the segment
 // arrays of the active experts (padded to num_experts so that no size is read back).
 __device__ __forceinline__ void route_scan_segments(const int32_t* count, int32_t* start, int num_experts, int m_tile,
@@ -125,7 +134,7 @@ __device__ __forceinline__ void route_scan_segments(const int32_t* count, int32_
 // counts into write offsets, and a second pass places the elements in order.
 // `sh` holds (34 * E) ints: count[E], start[E], per-warp counts/offsets [32][E].
 __device__ __forceinline__ void build_route_body(
-    int32_t* sh, const int32_t* selected, int num_tokens, int top_k, int num_experts, int m_tile,
+    int32_t* sh, const SelectedIds selected, int num_tokens, int top_k, int num_experts, int m_tile,
     int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
     int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
     int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out) {
@@ -189,7 +198,7 @@ __device__ __forceinline__ void build_route_body(
 }
 
 __global__ void __launch_bounds__(kRouteThreads) build_route_kernel(
-    const int32_t* __restrict__ selected, int num_tokens, int top_k, int num_experts, int m_tile,
+    const SelectedIds selected, int num_tokens, int top_k, int num_experts, int m_tile,
     int32_t* __restrict__ perm, int32_t* __restrict__ tok, int32_t* __restrict__ slot,
     int32_t* __restrict__ row_of_flat, int32_t* __restrict__ expert_ids, int32_t* __restrict__ segment_offsets,
     int32_t* __restrict__ problem_offsets, int32_t* __restrict__ counts_out, int sel_cap) {
@@ -207,7 +216,7 @@ __global__ void __launch_bounds__(kRouteThreads) build_route_kernel(
 constexpr int kRouteParChunk = 2048;
 constexpr int kRouteParThreads = 256;
 
-__global__ void __launch_bounds__(kRouteParThreads) route_count_kernel(const int32_t* __restrict__ selected, int num_rows,
+__global__ void __launch_bounds__(kRouteParThreads) route_count_kernel(const SelectedIds selected, int num_rows,
                                                                        int num_experts, int32_t* __restrict__ counts_blk) {
   extern __shared__ int32_t sh[];  // [E]
   pdl_wait();
@@ -252,7 +261,7 @@ __global__ void __launch_bounds__(kRouteThreads) route_scan_kernel(int32_t* __re
   }
 }
 
-__global__ void __launch_bounds__(kRouteParThreads) route_place_kernel(const int32_t* __restrict__ selected, int num_rows, int top_k,
+__global__ void __launch_bounds__(kRouteParThreads) route_place_kernel(const SelectedIds selected, int num_rows, int top_k,
                                                                        int num_experts, const int32_t* __restrict__ start_blk,
                                                                        int32_t* __restrict__ perm, int32_t* __restrict__ tok,
                                                                        int32_t* __restrict__ slot, int32_t* __restrict__ row_of_flat) {
@@ -307,7 +316,7 @@ __global__ void __launch_bounds__(kRouteParThreads) route_place_kernel(const int
 
 // Route of a prefill-sized batch with `scratch` (>= ceil(R / 2048) * E ints, caller-owned, free until
 // the launch ends); launched after the kernel that wrote `selected`.
-static int launch_route_parallel(const int32_t* selected, int num_tokens, int top_k, int num_experts, int m_tile, int32_t* perm,
+static int launch_route_parallel(const SelectedIds selected, int num_tokens, int top_k, int num_experts, int m_tile, int32_t* perm,
                                  int32_t* tok, int32_t* slot, int32_t* row_of_flat, int32_t* expert_ids,
                                  int32_t* segment_offsets, int32_t* problem_offsets, int32_t* counts, int32_t* scratch,
                                  cudaStream_t stream, bool first_pdl = true) {
@@ -343,7 +352,7 @@ __global__ void __launch_bounds__(kRouteThreads) router_route_kernel(
                    selected + static_cast<size_t>(tk) * top_k, weights + static_cast<size_t>(tk) * top_k, lane);
   __syncthreads();  // selected[] written above is read back by every thread below
   pdl_launch_dependents();
-  build_route_body(sh, selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat,
+  build_route_body(sh, SelectedIds{selected, 1, 0}, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat,
                    expert_ids, segment_offsets, problem_offsets, counts_out);
 }
 
@@ -423,10 +432,10 @@ int launch_router_route(const float* logits, int num_tokens, int num_experts, in
   const int rows = num_tokens * top_k;
   if (scratch && rows >= 4 * kRouteParChunk &&
       scratch_bytes >= sizeof(int32_t) * static_cast<size_t>(ceil_div(rows, kRouteParChunk)) * num_experts)
-    return launch_route_parallel(selected, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat, expert_ids,
-                                 segment_offsets, problem_offsets, counts, scratch, stream);
+    return launch_route_parallel(SelectedIds{selected, 1, 0}, num_tokens, top_k, num_experts, m_tile, perm, tok, slot, row_of_flat,
+                                 expert_ids, segment_offsets, problem_offsets, counts, scratch, stream);
   return check_cuda(launch_kernel(build_route_kernel, dim3(1), dim3(kRouteThreads), smem, stream, /*pdl=*/true, 1,
-                                  static_cast<const int32_t*>(selected), num_tokens, top_k, num_experts, m_tile, perm,
+                                  SelectedIds{selected, 1, 0}, num_tokens, top_k, num_experts, m_tile, perm,
                                   tok, slot, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, sel_cap),
                     "build_route_kernel launch");
 }
@@ -479,6 +488,13 @@ __global__ void __launch_bounds__(128) ep_pack_rows_kernel(
     uint4* dst = reinterpret_cast<uint4*>(send_rows + static_cast<size_t>(pos) * send_row_stride);
     const int vecs = rank_gu >> 3;
     for (int i = threadIdx.x; i < 2 * vecs; i += blockDim.x) dst[i] = (i < vecs) ? g[i] : u[i - vecs];
+  }
+  // rows beyond an owner's capacity are dropped: their combine index says so (every flat entry is
+  // written by exactly one thread of this launch, so the caller need not initialise the array)
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < num_rows; row += gridDim.x * blockDim.x) {
+    int d = 0;
+    while (d + 1 < world && row >= s_first[d + 1]) ++d;
+    if (row - s_first[d] >= capacity) combine_index[perm[row]] = -1;
   }
 }
 
@@ -536,33 +552,35 @@ extern "C" int tris_build_grouped_route(const int32_t* selected_experts, int32_t
                TRIS_ERR_INVALID_ARG, "tris_build_grouped_route: null pointer");
   TRIS_REQUIRE(num_tokens >= 0 && top_k > 0 && num_experts > 0 && m_tile > 0, TRIS_ERR_INVALID_ARG,
                "tris_build_grouped_route: bad sizes T=%d k=%d E=%d m_tile=%d", num_tokens, top_k, num_experts, m_tile);
-  return tris_build_grouped_route_scratch(selected_experts, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices,
-                                          grouped_slots, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts,
-                                          nullptr, 0, stream);
+  return tris_build_grouped_route_ex(selected_experts, 1, 0, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices,
+                                     grouped_slots, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, nullptr, 0,
+                                     stream);
 }
 
-extern "C" int tris_build_grouped_route_scratch(const int32_t* selected_experts, int32_t num_tokens, int32_t top_k,
-                                                int32_t num_experts, int32_t m_tile, int32_t* perm,
-                                                int32_t* grouped_token_indices, int32_t* grouped_slots,
-                                                int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets,
-                                                int32_t* problem_offsets, int32_t* counts, int32_t* scratch,
-                                                size_t scratch_bytes, void* stream) {
+extern "C" int tris_build_grouped_route_ex(const int32_t* selected_experts, int32_t selected_stride, int32_t id_offset,
+                                           int32_t num_tokens, int32_t top_k, int32_t num_experts, int32_t m_tile,
+                                           int32_t* perm, int32_t* grouped_token_indices, int32_t* grouped_slots,
+                                           int32_t* row_of_flat, int32_t* expert_ids, int32_t* segment_offsets,
+                                           int32_t* problem_offsets, int32_t* counts, int32_t* scratch,
+                                           size_t scratch_bytes, void* stream) {
   TRIS_REQUIRE(selected_experts && perm && grouped_token_indices && grouped_slots && row_of_flat && expert_ids &&
                    segment_offsets && problem_offsets && counts,
                TRIS_ERR_INVALID_ARG, "tris_build_grouped_route: null pointer");
   TRIS_REQUIRE(num_tokens >= 0 && top_k > 0 && num_experts > 0 && m_tile > 0, TRIS_ERR_INVALID_ARG,
                "tris_build_grouped_route: bad sizes T=%d k=%d E=%d m_tile=%d", num_tokens, top_k, num_experts, m_tile);
   TRIS_REQUIRE(num_experts <= 320, TRIS_ERR_UNSUPPORTED, "tris_build_grouped_route: more than 320 experts");
+  TRIS_REQUIRE(selected_stride >= 1, TRIS_ERR_INVALID_ARG, "tris_build_grouped_route: selected_stride %d", selected_stride);
+  const SelectedIds ids{selected_experts, selected_stride, id_offset};
   const int rows = num_tokens * top_k;
   if (scratch && rows >= 4 * kRouteParChunk &&
       scratch_bytes >= sizeof(int32_t) * static_cast<size_t>(ceil_div(rows, kRouteParChunk)) * num_experts)
-    return launch_route_parallel(selected_experts, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices,
+    return launch_route_parallel(ids, num_tokens, top_k, num_experts, m_tile, perm, grouped_token_indices,
                                  grouped_slots, row_of_flat, expert_ids, segment_offsets, problem_offsets, counts, scratch,
                                  static_cast<cudaStream_t>(stream), programmatic_launch_default());
   int sel_cap = 0;
   const int smem = route_smem_bytes(num_experts, rows, &sel_cap);
   return check_cuda(launch_kernel(build_route_kernel, dim3(1), dim3(kRouteThreads), smem, static_cast<cudaStream_t>(stream),
-                                  programmatic_launch_default(), 1, selected_experts, num_tokens, top_k, num_experts, m_tile,
+                                  programmatic_launch_default(), 1, ids, num_tokens, top_k, num_experts, m_tile,
                                   perm, grouped_token_indices, grouped_slots, row_of_flat, expert_ids, segment_offsets,
                                   problem_offsets, counts, sel_cap),
                     "build_route_kernel launch");

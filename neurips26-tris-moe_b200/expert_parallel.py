@@ -252,9 +252,15 @@ class ExpertParallelMoeBlock(torch.nn.Module):
 
     # -- C-ABI helpers ---------------------------------------------------------------------
     def _route(self, selected_i32: torch.Tensor, num_experts: int):
-        lib = _native.load()
+        """Device-built route of ``selected_i32 [T, k]``."""
         T, k = (int(s) for s in selected_i32.shape)
-        R, E, dev = T * k, num_experts, selected_i32.device
+        return self._route_raw(selected_i32.data_ptr(), 1, 0, T, k, num_experts, selected_i32.device, selected_i32)
+
+    def _route_raw(self, ids_ptr: int, ids_stride: int, id_offset: int, T: int, k: int, num_experts: int, dev, keep=None):
+        """Route of the ``T * k`` expert ids found at ``ids_ptr[f * ids_stride] - id_offset`` (int32); ``keep``
+        is the tensor that owns that memory."""
+        lib = _native.load()
+        R, E = T * k, num_experts
         scratch_n = ((R + 2047) // 2048) * E  # lets the sort of a large slot list run on several CTAs
         buf = torch.empty((4 * R + 3 * E + 6 + scratch_n,), dtype=torch.int32, device=dev)
         perm, tok, slot, rof = (buf[i * R:(i + 1) * R] for i in range(4))
@@ -263,12 +269,12 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         prob = buf[4 * R + 2 * E + 1: 4 * R + 3 * E + 2]
         counts = buf[4 * R + 3 * E + 2: 4 * R + 3 * E + 6]
         scratch = buf[4 * R + 3 * E + 6:]
-        _native.check(lib.tris_build_grouped_route_scratch(selected_i32.data_ptr(), T, k, E, 4, perm.data_ptr(), tok.data_ptr(),
-                                                           slot.data_ptr(), rof.data_ptr(), ids.data_ptr(), seg.data_ptr(),
-                                                           prob.data_ptr(), counts.data_ptr(), scratch.data_ptr(), 4 * scratch_n,
-                                                           torch.cuda.current_stream(dev).cuda_stream), "build_grouped_route")
+        _native.check(lib.tris_build_grouped_route_ex(int(ids_ptr), int(ids_stride), int(id_offset), T, k, E, 4, perm.data_ptr(),
+                                                      tok.data_ptr(), slot.data_ptr(), rof.data_ptr(), ids.data_ptr(), seg.data_ptr(),
+                                                      prob.data_ptr(), counts.data_ptr(), scratch.data_ptr(), 4 * scratch_n,
+                                                      torch.cuda.current_stream(dev).cuda_stream), "build_grouped_route")
         return {"perm": perm, "tok": tok, "slot": slot, "row_of_flat": rof, "expert_ids": ids, "segment_offsets": seg,
-                "counts": counts, "_buf": buf, "rows": R, "experts": E, "max_rows": T}
+                "counts": counts, "_buf": buf, "rows": R, "experts": E, "max_rows": T, "_keep": keep}
 
     def _route_view(self, route: dict, row_gather, layout: int, hidden_stride: int = 0) -> TrisRouteView:
         rv = TrisRouteView()
@@ -308,13 +314,14 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         d = grouped_hidden_layout(self.payloads["down"], None, rows, min(local, rows), per_rank * self.world)
         return gu, d
 
-    def _local_experts(self, recv_hidden: torch.Tensor, recv_local_ids: torch.Tensor, rows_hint: int = 0,
+    def _local_experts(self, recv_hidden: torch.Tensor, recv_local_ids: Optional[torch.Tensor], rows_hint: int = 0,
                        layouts=None) -> torch.Tensor:
         """gate/up -> SiLU*mul -> down for the rows this rank received; returns [rows, H] in the
         received order.  ``recv_hidden`` is [rows, >= 2*r]: gate and up backbone outputs side by
         side at the start of every row (anything behind them is skipped through the row stride).
         Rows with a negative id are padding: they are in no segment and their output rows are
-        never written."""
+        never written.  ``recv_local_ids=None``: the (global) expert id of every row is the int32 right
+        behind its two activation rows, where the exchange kernels put it; it is read in place."""
         lib = _native.load()
         dev = recv_hidden.device
         Rr = int(recv_hidden.shape[0])
@@ -329,7 +336,10 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         stride = int(recv_hidden.shape[1])
         hg_ptr = recv_hidden.data_ptr()
         hu_ptr = hg_ptr + 2 * r_gu
-        route = self._route(recv_local_ids.reshape(Rr, 1).contiguous(), self.hi - self.lo)
+        if recv_local_ids is None:  # ids behind the rows, numbered globally: routed in place
+            route = self._route_raw(hg_ptr + 4 * r_gu, stride // 2, self.lo, Rr, 1, self.hi - self.lo, dev, keep=recv_hidden)
+        else:
+            route = self._route(recv_local_ids.reshape(Rr, 1).contiguous(), self.hi - self.lo)
         route["max_rows"] = rows_hint if rows_hint > 0 else Rr
         va, vb, vd = (proj_view(self.payloads[n]) for n in ("gate", "up", "down"))
         mlp = torch.empty((Rr, self.intermediate_size), dtype=torch.float16, device=dev)
@@ -419,7 +429,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         stride = 2 * r_gu + 8  # halves per slot: gate row, up row, 16 bytes that start with the expert id
         stream = torch.cuda.current_stream(dev).cuda_stream
         send_rows = torch.empty((slots, stride), dtype=torch.float16, device=dev)
-        index = torch.full((max(R, 1),), -1, dtype=torch.int32, device=dev)
+        index = torch.empty((max(R, 1),), dtype=torch.int32, device=dev)  # every entry is written by the pack kernel
         if self._overflow is None or self._overflow.device != dev:
             self._overflow = torch.zeros((1,), dtype=torch.int32, device=dev)
         _native.check(lib.tris_ep_pack_rows(hg.data_ptr(), hu.data_ptr(), r_gu, sel.data_ptr(), route["perm"].data_ptr(),
@@ -428,10 +438,9 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                                             self._overflow.data_ptr(), stream), "ep_pack_rows")
         recv_rows = torch.empty_like(send_rows)
         dist.all_to_all_single(recv_rows, send_rows, group=self.group)
-        recv_ids = recv_rows.view(torch.int32)[:, r_gu]  # the int32 right behind the 2*r_gu halves
-        local_ids = recv_ids - self.lo  # padding slots (-1) stay negative and are skipped by the route
+        # the id of every slot is the int32 right behind its 2*r_gu halves (padding slots: -1)
         expected = max(1, (N * R) // max(1, self.hi - self.lo))  # rows per local expert if routing is balanced
-        result = self._local_experts(recv_rows, local_ids, rows_hint=int(expected + 4 * expected ** 0.5),
+        result = self._local_experts(recv_rows, None, rows_hint=int(expected + 4 * expected ** 0.5),
                                      layouts=self._step_layouts)
         back = torch.empty_like(result)
         dist.all_to_all_single(back, result, group=self.group)
@@ -451,7 +460,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         if capacity * N != pb.recv.shape[0] or stride != pb.recv.shape[1]:
             raise RuntimeError("trismoe_b200: exchange sizes changed after use_peer_exchange(); call it again on every rank")
         stream = torch.cuda.current_stream(dev).cuda_stream
-        index = torch.full((max(R, 1),), -1, dtype=torch.int32, device=dev)
+        index = torch.empty((max(R, 1),), dtype=torch.int32, device=dev)  # every entry is written by the dispatch kernel
         if self._overflow is None or self._overflow.device != dev:
             self._overflow = torch.zeros((1,), dtype=torch.int32, device=dev)
         _native.check(lib.tris_ep_dispatch_peer(hg.data_ptr(), hu.data_ptr(), r_gu, sel.data_ptr(), route["perm"].data_ptr(),
@@ -460,10 +469,8 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                                                 self._overflow.data_ptr(), pb.dflag_ptrs.data_ptr(), stream), "ep_dispatch_peer")
         _native.check(lib.tris_ep_wait(pb.flags[0].data_ptr(), pb.steps[0:].data_ptr(), N, pb.status.data_ptr(), stream),
                       "ep_wait (rows)")
-        recv_ids = pb.recv.view(torch.int32)[:, r_gu]
-        local_ids = recv_ids - self.lo
         expected = max(1, (N * R) // max(1, self.hi - self.lo))
-        result = self._local_experts(pb.recv, local_ids, rows_hint=int(expected + 4 * expected ** 0.5),
+        result = self._local_experts(pb.recv, None, rows_hint=int(expected + 4 * expected ** 0.5),
                                      layouts=self._step_layouts)
         _native.check(lib.tris_ep_return_peer(result.data_ptr(), pb.recv.data_ptr(), stride, r_gu, self.hidden_size, N,
                                               self.rank, capacity, pb.back_ptrs.data_ptr(), pb.rflag_ptrs.data_ptr(),

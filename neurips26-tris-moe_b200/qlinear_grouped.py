@@ -368,10 +368,10 @@ def build_grouped_route(selected_experts: torch.Tensor, num_experts: int, m_tile
     counts = buf[base + 3 * E + 2: base + 3 * E + 4]
     with torch.cuda.device(device):
         _native.check(
-            lib.tris_build_grouped_route_scratch(sel.data_ptr(), T, k, E, int(m_tile), perm.data_ptr(), tok.data_ptr(),
-                                                 slot.data_ptr(), rof.data_ptr(), expert_ids.data_ptr(), seg.data_ptr(),
-                                                 prob.data_ptr(), counts.data_ptr(), buf[base + 3 * E + 4:].data_ptr(),
-                                                 4 * scratch_n, _stream_ptr(device)),
+            lib.tris_build_grouped_route_ex(sel.data_ptr(), 1, 0, T, k, E, int(m_tile), perm.data_ptr(), tok.data_ptr(),
+                                            slot.data_ptr(), rof.data_ptr(), expert_ids.data_ptr(), seg.data_ptr(),
+                                            prob.data_ptr(), counts.data_ptr(), buf[base + 3 * E + 4:].data_ptr(),
+                                            4 * scratch_n, _stream_ptr(device)),
             "build_grouped_route",
         )
     nseg, tiles = (int(v) for v in counts.cpu().tolist())
