@@ -847,3 +847,42 @@ def test_kernel_status_word_is_sticky_and_surfaces(tm, small_layer):
     lib = tm._native.load()
     tm._native.check(lib.tris_moe_layer_last_status(None, 1, torch.cuda.current_stream().cuda_stream, C.byref(word)), "status")
     assert word.value == 0
+
+
+@pytest.mark.parametrize("slots,E,stride,offset", [(300, 8, 1, 0), (2048, 32, 260, 32), (9000, 8, 260, 56), (8192, 1, 7, 3)])
+def test_route_reads_strided_offset_ids_in_place(tm, slots, E, stride, offset):
+    """tris_build_grouped_route_ex on ids left behind exchange rows: entry f is ids[f * stride] - offset,
+    negative and out-of-range entries are padding; large lists take the multi-CTA sort.  Against the
+    oracle's route of the same ids (top_k = 1)."""
+    rng = np.random.default_rng(slots + E)
+    ids = rng.integers(-1, E, size=slots).astype(np.int32)          # -1: padding
+    ids[rng.random(slots) < 0.05] = E + 3                              # out of range: padding as well
+    raw = np.full((slots, stride), -7, np.int32)
+    raw[:, 0] = np.where(ids >= 0, ids + offset, ids if offset == 0 else -1)
+    dev = torch.from_numpy(raw).cuda()
+    R = slots
+    scratch_n = ((R + 2047) // 2048) * E
+    buf = torch.empty((4 * R + 3 * E + 6 + scratch_n,), dtype=torch.int32, device="cuda")
+    perm, tok, slot, rof = (buf[i * R:(i + 1) * R] for i in range(4))
+    eids, seg = buf[4 * R: 4 * R + E], buf[4 * R + E: 4 * R + 2 * E + 1]
+    prob, counts = buf[4 * R + 2 * E + 1: 4 * R + 3 * E + 2], buf[4 * R + 3 * E + 2: 4 * R + 3 * E + 6]
+    lib = tm._native.load()
+    tm._native.check(lib.tris_build_grouped_route_ex(dev.data_ptr(), stride, offset, R, 1, E, 4, perm.data_ptr(), tok.data_ptr(),
+                                                     slot.data_ptr(), rof.data_ptr(), eids.data_ptr(), seg.data_ptr(), prob.data_ptr(),
+                                                     counts.data_ptr(), buf[4 * R + 3 * E + 6:].data_ptr(), 4 * scratch_n,
+                                                     torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    valid = (ids >= 0) & (ids < E)
+    order = np.argsort(np.where(valid, ids, E), kind="stable")[: int(valid.sum())]   # stable by expert, padding dropped
+    nseg = int(counts[0].item())
+    present = sorted(set(ids[valid].tolist()))
+    assert nseg == len(present)
+    assert eids[:nseg].cpu().tolist() == present
+    lengths = [int((ids[valid] == e).sum()) for e in present]
+    assert seg[: nseg + 1].cpu().tolist() == np.concatenate([[0], np.cumsum(lengths)]).tolist()
+    n_valid = int(valid.sum())
+    assert np.array_equal(perm[:n_valid].cpu().numpy(), order)
+    assert np.array_equal(tok[:n_valid].cpu().numpy(), order)
+    inv = rof.cpu().numpy()
+    assert np.all(inv[~valid] == -1)
+    assert np.array_equal(order[inv[valid]], np.nonzero(valid)[0])
