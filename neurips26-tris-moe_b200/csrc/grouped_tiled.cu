@@ -207,9 +207,10 @@ __device__ __forceinline__ void sal_chunk_n(const StagedTile& st, const uint8_t*
   const ColHeader* ch = reinterpret_cast<const ColHeader*>(st.col);
   const int sal_words = ch->sal_words;
   const uint8_t* s_base = hsal_set + g * 64 + t * 16;
+  const LaneShifts ls = lane_shifts(t);
   for (int q = 0; q < sal_words; ++q) {
     uint32_t a[2][4];
-    unpack_fragments_sal(st, q, out_local, lane, a);
+    unpack_fragments_sal(st, q, out_local, lane, ls, a);
 #pragma unroll
     for (int nt = 0; nt < NTC; ++nt) {
       const uint4 hv = *reinterpret_cast<const uint4*>(s_base + (q * NT + nt) * 8 * 64);
@@ -226,6 +227,7 @@ __device__ __forceinline__ void main_chunk_n(const StagedTile& st, const uint8_t
   const uint8_t* h_base = hrows_set + g * kHiddenRowBytes + t * 16;
   const ColHeader* ch = reinterpret_cast<const ColHeader*>(st.col);
   const int num_slots = ch->num_slots;
+  const LaneShifts ls = lane_shifts(t);
   int p = 0;
   for (int slot = 0; slot < num_slots; ++slot) {
     const int p_end = ch->slot_end[slot];
@@ -233,7 +235,7 @@ __device__ __forceinline__ void main_chunk_n(const StagedTile& st, const uint8_t
 #pragma unroll 2
     for (; p < p_end; ++p) {
       uint32_t a[2][4];
-      unpack_fragments_ns(st, p, out_local, lane, rs, a);
+      unpack_fragments_ns(st, p, out_local, lane, rs, ls, a);
 #pragma unroll
       for (int nt = 0; nt < NTC; ++nt) {
         const uint4 hv = *reinterpret_cast<const uint4*>(h_base + nt * 8 * kHiddenRowBytes + p * 64);
@@ -263,6 +265,7 @@ __device__ __forceinline__ int unpack_chunk_ns(const StagedTile& st, int out_loc
   const int p_total = num_slots > 0 ? min(static_cast<int>(ch->slot_end[num_slots - 1]), kChunkRows) : 0;
   int slot = 0;
   RowScalesNs rs = load_row_scales_ns(st, 0, out_local, lane);
+  const LaneShifts ls = lane_shifts(lane & 3);
 #pragma unroll
   for (int p = 0; p < kChunkRows; ++p) {
     if (p < p_total) {
@@ -270,7 +273,7 @@ __device__ __forceinline__ int unpack_chunk_ns(const StagedTile& st, int out_loc
         ++slot;
         rs = load_row_scales_ns(st, slot, out_local, lane);
       }
-      unpack_fragments_ns(st, p, out_local, lane, rs, a[p]);
+      unpack_fragments_ns(st, p, out_local, lane, rs, ls, a[p]);
     } else {
 #pragma unroll
       for (int h = 0; h < 2; ++h)
@@ -739,6 +742,7 @@ __global__ void __launch_bounds__(kThreads) tiled_dump_kernel(TrisProjView v, in
   if (!weights_out) return;
   StagedTile st{rec, col, gmap};
   const int g = lane >> 2, t = lane & 3;
+  const LaneShifts ls = lane_shifts(t);
   auto store_pair = [&](int o, int col_lo, uint32_t bits) {
     if (o >= v.out_features) return;
     __half* row = weights_out + (static_cast<size_t>(e) * v.out_features + o) * v.rank;
@@ -753,7 +757,7 @@ __global__ void __launch_bounds__(kThreads) tiled_dump_kernel(TrisProjView v, in
       const RowScalesNs rs = load_row_scales_ns(st, slot, warp * 16, lane);
       for (; p < ch->slot_end[slot]; ++p) {
         uint32_t a[2][4];
-        unpack_fragments_ns(st, p, warp * 16, lane, rs, a);
+        unpack_fragments_ns(st, p, warp * 16, lane, rs, ls, a);
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -766,7 +770,7 @@ __global__ void __launch_bounds__(kThreads) tiled_dump_kernel(TrisProjView v, in
     const int sal_words = reinterpret_cast<const ColHeader*>(col)->sal_words;
     for (int q = 0; q < sal_words; ++q) {
       uint32_t a[2][4];
-      unpack_fragments_sal(st, q, warp * 16, lane, a);
+      unpack_fragments_sal(st, q, warp * 16, lane, ls, a);
       const uint16_t* salcol = reinterpret_cast<const uint16_t*>(col + kColHdrBytes + kColTabBytes + q * kSalEntryBytes + 192);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {

@@ -295,14 +295,17 @@ __device__ __forceinline__ void gr_decode_block(const uint8_t* rec, int b, uint3
 //     the low half and bit 31 over the high half (selector 0xBB99), or bits 7 / 23 (0xAA88).
 struct LaneShifts {
   uint32_t mul_a, mul_b;  // 1 << (7 - t), 1 << (3 - t)
+  uint32_t mul_8;         // 256: moves bits 7 / 23 up to 15 / 31
 };
 __device__ __forceinline__ LaneShifts lane_shifts(int t) {
   LaneShifts ls;
   ls.mul_a = 1u << (7 - t);
   ls.mul_b = 1u << (3 - t);
   // keep the compiler from turning the multiplications back into (ALU pipe) shifts
+  ls.mul_8 = 256u;
   asm("" : "+r"(ls.mul_a));
   asm("" : "+r"(ls.mul_b));
+  asm("" : "+r"(ls.mul_8));
   return ls;
 }
 __device__ __forceinline__ uint32_t mask_hi(uint32_t w) { return prmt(w, 0u, 0xBB99u); }
@@ -327,8 +330,7 @@ __device__ __forceinline__ void unpack_row_ns(uint32_t s1, uint32_t gm, __half2 
   const uint32_t gA = gm * ls.mul_a, gB = gm * ls.mul_b;
   const uint32_t cd[4] = {c01.x, c01.z, c23.x, c23.z};
   const uint32_t cn[4] = {c01.y, c01.w, c23.y, c23.w};
-  uint32_t up8 = 256u;
-  asm("" : "+r"(up8));
+  const uint32_t up8 = ls.mul_8;
   const uint32_t sg[4] = {sA, sA * up8, sB, sB * up8};
   const uint32_t mg[4] = {mask_hi(gA), mask_lo(gA), mask_hi(gB), mask_lo(gB)};
 #pragma unroll
@@ -348,8 +350,7 @@ __device__ __forceinline__ void unpack_row_sal(uint32_t w1, uint32_t w2, __half2
   const uint32_t s2A = w2 * ls.mul_a, s2B = w2 * ls.mul_b;
   const uint32_t c1[4] = {c01.x, c01.z, c23.x, c23.z};
   const uint32_t c2[4] = {c01.y, c01.w, c23.y, c23.w};
-  uint32_t up8 = 256u;
-  asm("" : "+r"(up8));
+  const uint32_t up8 = ls.mul_8;
   const uint32_t g1[4] = {s1A, s1A * up8, s1B, s1B * up8};
   const uint32_t g2[4] = {s2A, s2A * up8, s2B, s2B * up8};
 #pragma unroll
@@ -393,9 +394,8 @@ __device__ __forceinline__ RowScalesNs load_row_scales_ns(const StagedTile& st, 
 
 // A fragments of packed row p for the lane's outputs o and o + 8 (o = out_local + g).
 __device__ __forceinline__ void unpack_fragments_ns(const StagedTile& st, int p, int out_local, int lane,
-                                                    const RowScalesNs& rs, uint32_t (&a)[2][4]) {
+                                                    const RowScalesNs& rs, const LaneShifts& ls, uint32_t (&a)[2][4]) {
   const int g = lane >> 2, t = lane & 3;
-  const LaneShifts ls = lane_shifts(t);
   const uint4* ct = reinterpret_cast<const uint4*>(st.col + kColHdrBytes) + (p * 4 + t) * 2;
   const uint4 c01 = ct[0], c23 = ct[1];
   const uint32_t* s1 = reinterpret_cast<const uint32_t*>(st.rec + kHdrBytes) + p * kTileOut + out_local + g;
@@ -405,7 +405,7 @@ __device__ __forceinline__ void unpack_fragments_ns(const StagedTile& st, int p,
 }
 
 __device__ __forceinline__ void unpack_fragments_sal(const StagedTile& st, int q, int out_local, int lane,
-                                                     uint32_t (&a)[2][4]) {
+                                                     const LaneShifts& ls, uint32_t (&a)[2][4]) {
   const int g = lane >> 2, t = lane & 3;
   const RecHeader* hdr = reinterpret_cast<const RecHeader*>(st.rec);
   const ColHeader* ch = reinterpret_cast<const ColHeader*>(st.col);
@@ -418,7 +418,6 @@ __device__ __forceinline__ void unpack_fragments_sal(const StagedTile& st, int q
   const uint4 c01 = sc[0], c23 = sc[1];
   const uint32_t* w1 = reinterpret_cast<const uint32_t*>(st.rec + hdr->off_ss1) + q * kTileOut + out_local + g;
   const uint32_t* w2 = reinterpret_cast<const uint32_t*>(st.rec + hdr->off_ss2) + q * kTileOut + out_local + g;
-  const LaneShifts ls = lane_shifts(t);
   unpack_row_sal(w1[0], w2[0], r1[0], r2[0], c01, c23, ls, a[0]);
   unpack_row_sal(w1[8], w2[8], r1[1], r2[1], c01, c23, ls, a[1]);
 }
