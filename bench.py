@@ -437,8 +437,6 @@ def run_ncu_case(args):
     device = torch.device("cuda", 0)
     T = args.tokens
     if args.ncu_case == "packed4":  # 80 distinct 2048 x 2048 4-bit matrices (176 MB > L2), two passes
-        import numpy as np
-
         rng = np.random.default_rng(0)
         mats = [tm.Packed4Linear(synth.packed4_matrix(rng, 2048, 2048, 128), device) for _ in range(80)]
         x = synth.synth_activations(T, 2048, seed=T).to(device)
@@ -603,7 +601,7 @@ def run_extra(args):
     # skinny / tcgen05 GEMMs: 80 distinct matrices per pass (160 MB of nibbles, 640 MB of fp16: both beyond L2)
     from trismoe_b200 import Packed4Linear, compute_shared_hidden, dequantize_packed_4bit
 
-    rng = __import__("numpy").random.default_rng(0)
+    rng = np.random.default_rng(0)
     mats = [synth.packed4_matrix(rng, 2048, 2048, 128) for _ in range(80)]
     packed = [Packed4Linear(m, device) for m in mats]
     dense = [dequantize_packed_4bit(m, device) for m in mats]
