@@ -741,6 +741,11 @@ struct GroupedArgs {
   int32_t hidden_stride;        // halves between consecutive activation rows (>= rank)
   int32_t weights_before_wait;  // route arrays were final before the predecessor kernel started
   int32_t ksplit;               // CTAs per cluster sharing one tile: each takes 8/ksplit packed rows of a chunk
+  // tile-record form of the tcgen05 kernel (grouped_umma.cu): activation rows in lane order, slot sizes of the
+  // staged records
+  int32_t hidden_lane_order;
+  int32_t rec_slot_bytes;
+  int32_t col_slot_bytes;
 };
 
 enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };

@@ -586,6 +586,20 @@ extern "C" int tris_compact3_dequantize(const TrisProjView* proj, void* weights_
   return check_cuda(cudaGetLastError(), "compact3_dump_kernel launch");
 }
 
+// Tile-record form of the tcgen05 kernel: lane-order activation rows, single-chunk projections, segments
+// above the tensor-core threshold.
+static bool umma_records_applicable(const TrisProjView& v, const GroupedArgs& a, bool lane_order, int rows) {
+  const int stride = a.hidden_stride > 0 ? a.hidden_stride : v.rank;
+  return lane_order && rows > grouped_tc_min_rows() && v.rank % 32 == 0 && v.rank <= 256 && stride % 8 == 0 && stride >= v.rank;
+}
+static void fill_record_slots(GroupedArgs& a) {
+  const int rec = std::max(a.proj[0].max_record_bytes, a.proj[1].max_record_bytes);
+  a.rec_slot_bytes = ((rec + 15) & ~15) + 16;
+  a.col_slot_bytes = std::max(a.proj[0].col_record_bytes, a.proj[1].col_record_bytes);
+  a.hidden_lane_order = 1;
+  a.ksplit = 1;
+}
+
 int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
                                void* out_f16, cudaStream_t stream, LaunchOpts opts) {
   int st = validate_proj(proj, "tris_grouped_forward", true);
@@ -601,6 +615,15 @@ int tris::grouped_forward_impl(const TrisProjView* proj, const TrisRouteView* ro
   const bool col_scaled = route->hidden_col_scale != nullptr;
   TRIS_REQUIRE(!col_scaled || (proj_has_tile_records(*proj) && !a.hidden_interleaved && !lane_order), TRIS_ERR_UNSUPPORTED,
                "tris_grouped_forward: hidden_col_scale needs tile records and row-major activations");
+  if (proj_has_tile_records(*proj) && !a.hidden_interleaved && umma_records_applicable(*proj, a, lane_order, rows_hint(route))) {
+    if (a.hidden_stride <= 0) a.hidden_stride = proj->rank;
+    a.proj[0] = a.proj[1] = *proj;
+    a.hidden[0] = a.hidden[1] = static_cast<const __half*>(hidden_f16);
+    a.out[0] = a.out[1] = static_cast<__half*>(out_f16);
+    a.weights_before_wait = opts.pdl && opts.weights_before_wait;
+    fill_record_slots(a);
+    return launch_grouped_umma(a, 1, EPI_STORE, stream, opts.pdl);
+  }
   if (proj_has_tile_records(*proj) && !a.hidden_interleaved && (lane_order || col_scaled || tiled_takes(*proj, rows_hint(route))))
     return launch_grouped_tiled(proj, nullptr, route, hidden_f16, nullptr, out_f16, nullptr, 0, rows_hint(route), stream, opts);
   TRIS_REQUIRE(!a.hidden_interleaved || proj->rank % 32 == 0, TRIS_ERR_INVALID_ARG,
@@ -627,7 +650,10 @@ extern "C" int tris_grouped_hidden_layout(const TrisProjView* proj_a, const Tris
   route.num_segments = num_segments;
   route.max_rows_per_segment = max_rows_per_segment;
   const bool records = proj_has_tile_records(*proj_a) && (proj_b == nullptr || proj_has_tile_records(*proj_b));
-  return (records && tiled_takes(*proj_a, route_rows_hint(&route))) ? TRIS_OUT_F16_LANE_ORDER : TRIS_OUT_F16_PAIR_INTERLEAVED;
+  // single-chunk projections with records read lane order at every size (decode kernels, the register-cached
+  // kernel, the tile-record form of the tcgen05 kernel); larger ranks only where the decode kernels take them
+  return (records && (proj_a->rank <= 256 || tiled_takes(*proj_a, route_rows_hint(&route)))) ? TRIS_OUT_F16_LANE_ORDER
+                                                                                             : TRIS_OUT_F16_PAIR_INTERLEAVED;
 }
 
 extern "C" int tris_grouped_forward(const TrisProjView* proj, const TrisRouteView* route, const void* hidden_f16,
@@ -664,6 +690,18 @@ int tris::grouped_pair_forward_impl(const TrisProjView* proj_a, const TrisProjVi
   const bool col_scaled = route->hidden_col_scale != nullptr;
   TRIS_REQUIRE(!col_scaled || (records && !a.hidden_interleaved && !lane_order), TRIS_ERR_UNSUPPORTED,
                "tris_grouped_pair_forward: hidden_col_scale needs tile records and row-major activations");
+  if (records && !a.hidden_interleaved && umma_records_applicable(*proj_a, a, lane_order, rows_hint(route))) {
+    if (a.hidden_stride <= 0) a.hidden_stride = proj_a->rank;
+    a.proj[0] = *proj_a;
+    a.proj[1] = *proj_b;
+    a.hidden[0] = static_cast<const __half*>(hidden_a_f16);
+    a.hidden[1] = static_cast<const __half*>(hidden_b_f16);
+    a.out[0] = static_cast<__half*>(out_a_f16);
+    a.out[1] = static_cast<__half*>(out_b_f16);
+    a.weights_before_wait = opts.pdl && opts.weights_before_wait;
+    fill_record_slots(a);
+    return launch_grouped_umma(a, 2, fuse_silu_mul ? EPI_SILU_MUL : EPI_STORE, stream, opts.pdl);
+  }
   if (records && !a.hidden_interleaved && (lane_order || col_scaled || tiled_takes(*proj_a, rows_hint(route))))
     return launch_grouped_tiled(proj_a, proj_b, route, hidden_a_f16, hidden_b_f16, out_a_f16, out_b_f16, fuse_silu_mul ? 2 : 1,
                                 rows_hint(route), stream, opts);

@@ -86,31 +86,6 @@ __device__ __forceinline__ uint32_t lane_copy_bytes(void* dst, const void* src, 
   return 0;
 }
 
-__device__ __forceinline__ uint2 load_desc(const TrisProjView& v, int expert, int tile, int chunk) {
-  const int idx = (expert * tiles_per_expert(v.out_features) + tile) * num_chunks(v.rank) + chunk;
-  return reinterpret_cast<const uint2*>(v.tile_desc)[idx];
-}
-
-// Starts the copies of one tile record (descriptor d) and, optionally, of the column record of
-// (expert, chunk); arrives on `bar` with the byte count.  One thread.
-__device__ __forceinline__ void issue_record(const TrisProjView& v, int expert, int chunk, uint2 d, uint8_t* rec_dst,
-                                             uint8_t* col_dst, bool valid, uint64_t* bar) {
-  fence_proxy_async();
-  uint32_t bytes = 0;
-  if (valid) {
-    bulk_g2s(rec_dst, static_cast<const uint8_t*>(v.tile_records) + static_cast<size_t>(d.x) * 16, d.y, bar);
-    bytes = d.y;
-    if (col_dst) {
-      bulk_g2s(col_dst,
-               static_cast<const uint8_t*>(v.col_records) + (static_cast<size_t>(expert) * num_chunks(v.rank) + chunk) * v.col_record_bytes,
-               static_cast<uint32_t>(v.col_record_bytes), bar);
-      bytes += static_cast<uint32_t>(v.col_record_bytes);
-    }
-  }
-  if (bytes) mbar_arrive_expect_tx(bar, bytes);
-  else mbar_arrive(bar);
-}
-
 // Activation rows of a pass into hrows[set][row]; row_src(n) = source row or -1.  Lane-order
 // rows are copied as they are (lanes 0-7 of every warp issue one bulk copy per round); row-major
 // rows are re-ordered by all threads.  Lane 0 of every warp arrives on `bar`.

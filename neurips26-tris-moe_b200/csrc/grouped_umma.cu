@@ -18,6 +18,7 @@
 #include <atomic>
 
 #include "compact3_tile.cuh"
+#include "tile_records.cuh"
 #include "umma.cuh"
 
 namespace tris {
@@ -36,8 +37,98 @@ __device__ __forceinline__ void mbar_inval(uint64_t* bar) {
   asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Phase 1 from tile records (REC): the 128-output tile is two 64-output records of the chunk plus the
+// (expert, chunk) column record, fetched with three bulk copies; 8 warps decode the 8 Golomb-Rice blocks,
+// then warp w unpacks record w / 4, outputs 16 * (w % 4) .. + 15: the non-salient fragments of a packed row
+// are the lane's eight consecutive K positions of the lane-order activation layout, i.e. one 16-byte
+// core-matrix row of the A operand; the salient columns are then written over their (zero) places.
+// Staging area inside the region that later holds the B operand: [mbarrier 64][record 0][record 1][column
+// record][two g_map planes].
+template <int NPROJ>
+__device__ __forceinline__ bool umma_unpack_from_records(const GroupedArgs& args, uint8_t* region, uint8_t* a_op, int expert,
+                                                         int warp, int lane, uint32_t& parity) {
+  using namespace tr;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(region);
+  uint8_t* rec_base = region + 64;
+  uint8_t* col = rec_base + 2 * args.rec_slot_bytes;
+  uint32_t* gmap_base = reinterpret_cast<uint32_t*>(col + args.col_slot_bytes);
+  const int tiles = tiles_per_expert(args.proj[0].out_features);
+  const int tile0 = 2 * static_cast<int>(blockIdx.x);
+  const int r = warp >> 2, og = warp & 3, g = lane >> 2, t = lane & 3;
+  bool ok = true;
+#pragma unroll 1
+  for (int proj = 0; proj < NPROJ; ++proj) {
+    const TrisProjView& v = args.proj[proj];
+    __syncthreads();  // the staging area is free (previous projection unpacked)
+    if (lane == 0 && warp < 2) {
+      const bool valid = tile0 + warp < tiles;
+      const uint2 d = valid ? load_desc(v, expert, tile0 + warp, 0) : make_uint2(0u, 0u);
+      issue_record(v, expert, 0, d, rec_base + warp * args.rec_slot_bytes, warp == 0 ? col : nullptr, valid, bar);
+    }
+    reinterpret_cast<uint4*>(gmap_base)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);  // both planes
+    __syncthreads();
+    ok = mbar_wait_bounded(bar, parity) && ok;
+    parity ^= 1u;
+    const bool tile_valid = tile0 + r < tiles;
+    StagedTile st{rec_base + r * args.rec_slot_bytes, col, gmap_base + r * 512};
+    if (ok && tile_valid) gr_decode_block(st.rec, og, const_cast<uint32_t*>(st.gmap), lane);
+    if (__syncthreads_or(!ok)) {  // also publishes the decoded planes
+      mbar_wait_bounded(bar, parity ^ 1u);  // copies that may still be in flight must not land in a dead CTA
+      return false;
+    }
+    uint8_t* a_dst = a_op + proj * (kTcM * 256 * 2);
+    const int out0 = r * kTileOut + og * 16 + g;  // this lane's outputs inside the 128-output tile: out0, out0 + 8
+    const LaneShifts ls = lane_shifts(t);
+    const ColHeader* ch = reinterpret_cast<const ColHeader*>(col);
+    if (tile_valid) {
+      int p = 0;
+      for (int slot = 0; slot < ch->num_slots; ++slot) {
+        const RowScalesNs rs = load_row_scales_ns(st, slot, og * 16, lane);
+        const int p_end = min(static_cast<int>(ch->slot_end[slot]), kChunkRows);
+        for (; p < p_end; ++p) {
+          uint32_t a[2][4];
+          unpack_fragments_ns(st, p, og * 16, lane, rs, ls, a);
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            *reinterpret_cast<uint4*>(a_dst + ((4 * p + t) * kTcM + out0 + 8 * h) * 16) = make_uint4(a[h][0], a[h][1], a[h][2], a[h][3]);
+        }
+      }
+      __syncwarp();  // the salient halves below land in core-matrix rows other lanes of this warp wrote above
+      const int sal_words = ch->sal_words;
+      for (int q = 0; q < sal_words; ++q) {
+        uint32_t a[2][4];
+        unpack_fragments_sal(st, q, og * 16, lane, ls, a);
+        const uint16_t* salcol = reinterpret_cast<const uint16_t*>(col + kColHdrBytes + kColTabBytes + q * kSalEntryBytes + 192);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int slot = lane_pair_col(t, i);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const unsigned c = salcol[slot + 16 * half];  // column inside the chunk, 0xFFFF: unused slot
+            if (c == 0xFFFFu) continue;
+            const int pos = lane_order_pos(static_cast<int>(c & 31u));
+            const int kchunk = 4 * static_cast<int>(c >> 5) + (pos >> 3);
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              *reinterpret_cast<uint16_t*>(a_dst + (kchunk * kTcM + out0 + 8 * h) * 16 + (pos & 7) * 2) =
+                  static_cast<uint16_t>(half ? (a[h][i] >> 16) : (a[h][i] & 0xFFFFu));
+          }
+        }
+      }
+    } else {
+      // outputs past the projection: a zero tile (their results are never stored, but keep the MMA finite)
+      const int pr = (v.rank + 31) >> 5;
+      for (int p = 0; p < pr && p < kChunkRows; ++p)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          *reinterpret_cast<uint4*>(a_dst + ((4 * p + t) * kTcM + out0 + 8 * h) * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  return ok;
+}
+
 // grid (ceil(O/128), num_segments bound); 256 threads
-template <int NPROJ, int EPI>
+template <int NPROJ, int EPI, bool REC>
 __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_constant__ GroupedArgs args) {
   constexpr int NB = UmmaGeom<NPROJ>::NB;
   extern __shared__ uint4 smem_raw[];
@@ -51,7 +142,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
   int32_t* flag = reinterpret_cast<int32_t*>(mma_bar + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  init_stage_barriers(stage.mbar);
+  uint64_t* rec_bar = reinterpret_cast<uint64_t*>(shared_region);  // REC: record copies (two issuing lanes arrive)
+  if (REC) {
+    if (threadIdx.x == 0) mbar_init(rec_bar, 2);
+  } else {
+    init_stage_barriers(stage.mbar);
+  }
   if (threadIdx.x == 0) {
     mbar_init(mma_bar, 1);
     fence_mbar_init();
@@ -89,7 +185,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
   const int pr = proj_packed_rows(args.proj[0]);
   bool ok = true;
 
-  if (live) {
+  if (live && REC) {
+    uint32_t rec_parity = 0u;
+    ok = umma_unpack_from_records<NPROJ>(args, shared_region, a_op, expert, warp, lane, rec_parity);
+  } else if (live) {
     const int e = args.proj[0].expert_slot ? args.proj[0].expert_slot[expert] : expert;
     const int g = lane >> 2, t = lane & 3;
     // ---- phase 1: decode and unpack each projection's tile into its A operand --------------
@@ -123,9 +222,13 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
   // whose memory becomes the B operand).
   ok = !__syncthreads_or(!ok);
   if (threadIdx.x == 0) {
-    mbar_inval(&stage.mbar[0]);
-    mbar_inval(&stage.mbar[1]);
-    mbar_inval(&stage.mbar[2]);
+    if (REC) {
+      mbar_inval(rec_bar);
+    } else {
+      mbar_inval(&stage.mbar[0]);
+      mbar_inval(&stage.mbar[1]);
+      mbar_inval(&stage.mbar[2]);
+    }
   }
   __syncthreads();
 
@@ -225,9 +328,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_umma_kernel(const __grid_
   if (unpaged && threadIdx.x == 0 && args.status) atomicExch(args.status, TRIS_ERR_WORKSPACE);
 }
 
-template <int NPROJ, int EPI>
+template <int NPROJ, int EPI, bool REC>
 static int launch_umma_grouped(const GroupedArgs& args, cudaStream_t stream, bool pdl) {
-  auto kernel = grouped_umma_kernel<NPROJ, EPI>;
+  auto kernel = grouped_umma_kernel<NPROJ, EPI, REC>;
   const size_t smem = UmmaGeom<NPROJ>::kSmemBytes;
   static bool configured[64] = {};
   int dev = 0;
@@ -254,14 +357,21 @@ int grouped_tc_min_rows() { return g_tc_min_rows.load(std::memory_order_relaxed)
 // most one 256-column chunk.
 bool grouped_umma_applicable(const GroupedArgs& args, int rows_hint) {
   const TrisProjView& v = args.proj[0];
-  return rows_hint > g_tc_min_rows.load(std::memory_order_relaxed) && args.hidden_interleaved && (v.rank % 32) == 0 && v.rank <= 256 && args.ksplit <= 1 &&
-         (args.hidden_stride % 8) == 0;
+  return rows_hint > g_tc_min_rows.load(std::memory_order_relaxed) && (args.hidden_interleaved || args.hidden_lane_order) &&
+         (v.rank % 32) == 0 && v.rank <= 256 && args.ksplit <= 1 && (args.hidden_stride % 8) == 0;
 }
 
 int launch_grouped_umma(const GroupedArgs& args, int nproj, int epi, cudaStream_t stream, bool pdl) {
-  if (nproj == 1) return launch_umma_grouped<1, EPI_STORE>(args, stream, pdl);
-  if (epi == EPI_SILU_MUL) return launch_umma_grouped<2, EPI_SILU_MUL>(args, stream, pdl);
-  return launch_umma_grouped<2, EPI_STORE>(args, stream, pdl);
+  if (args.hidden_lane_order) {  // tile records
+    TRIS_REQUIRE(64 + 2 * static_cast<size_t>(args.rec_slot_bytes) + args.col_slot_bytes + 4096 <= static_cast<size_t>(UmmaGeom<1>::kUnionBytes),
+                 TRIS_ERR_UNSUPPORTED, "grouped_umma_kernel: tile records of %d bytes do not fit the staging area", args.rec_slot_bytes);
+    if (nproj == 1) return launch_umma_grouped<1, EPI_STORE, true>(args, stream, pdl);
+    if (epi == EPI_SILU_MUL) return launch_umma_grouped<2, EPI_SILU_MUL, true>(args, stream, pdl);
+    return launch_umma_grouped<2, EPI_STORE, true>(args, stream, pdl);
+  }
+  if (nproj == 1) return launch_umma_grouped<1, EPI_STORE, false>(args, stream, pdl);
+  if (epi == EPI_SILU_MUL) return launch_umma_grouped<2, EPI_SILU_MUL, false>(args, stream, pdl);
+  return launch_umma_grouped<2, EPI_STORE, false>(args, stream, pdl);
 }
 
 }  // namespace tris

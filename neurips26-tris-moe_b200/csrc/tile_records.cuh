@@ -372,6 +372,32 @@ __device__ __forceinline__ void row_scales_sal(uint2 rp_lo, uint2 rp_hi, __half2
   r2 = u32_as_h2(prmt(rp_lo.x, rp_hi.x, 0x7632u));
 }
 
+// ---- fetching records ----------------------------------------------------------------------------
+__device__ __forceinline__ uint2 load_desc(const TrisProjView& v, int expert, int tile, int chunk) {
+  const int idx = (expert * tiles_per_expert(v.out_features) + tile) * num_chunks(v.rank) + chunk;
+  return reinterpret_cast<const uint2*>(v.tile_desc)[idx];
+}
+
+// Starts the copies of one tile record (descriptor d) and, optionally, of the column record of
+// (expert, chunk); arrives on `bar` with the byte count.  One thread.
+__device__ __forceinline__ void issue_record(const TrisProjView& v, int expert, int chunk, uint2 d, uint8_t* rec_dst,
+                                             uint8_t* col_dst, bool valid, uint64_t* bar) {
+  fence_proxy_async();
+  uint32_t bytes = 0;
+  if (valid) {
+    bulk_g2s(rec_dst, static_cast<const uint8_t*>(v.tile_records) + static_cast<size_t>(d.x) * 16, d.y, bar);
+    bytes = d.y;
+    if (col_dst) {
+      bulk_g2s(col_dst,
+               static_cast<const uint8_t*>(v.col_records) + (static_cast<size_t>(expert) * num_chunks(v.rank) + chunk) * v.col_record_bytes,
+               static_cast<uint32_t>(v.col_record_bytes), bar);
+      bytes += static_cast<uint32_t>(v.col_record_bytes);
+    }
+  }
+  if (bytes) mbar_arrive_expect_tx(bar, bytes);
+  else mbar_arrive(bar);
+}
+
 // ---- a staged tile: pointers into shared memory ----------------------------------------------
 struct StagedTile {
   const uint8_t* rec;    // tile record
