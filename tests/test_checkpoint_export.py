@@ -96,3 +96,27 @@ def test_export_file_round_trip_modes_and_layer_batches(lib, tmp_path):
                                                    payload["q_gmap_gr_meta"][e].numpy(), 2, int(payload["qweight1"].shape[2]))
                         assert np.array_equal(got.view(np.int32), dense[prefix][key][e].numpy()), (tag, prefix, key, e)
         assert seen == [sidecar.layer_prefix(L) for L in range(3)]
+
+
+def test_packed4_group_rules_on_cpu():
+    """Which 4-bit matrices the in-place GEMM takes (uniform groups of a multiple of 32 columns, or one group)
+    and the group size the reference infers from g_idx (_infer_packed_group_size_from_g_idx, qlinear_cuda.py:460-483)."""
+    import numpy as np
+    import torch
+
+    import trismoe_b200 as tm
+    from trismoe_b200 import synth
+    from trismoe_b200.ns_compensation import infer_packed_group_size
+
+    rng = np.random.default_rng(0)
+    uniform = synth.packed4_matrix(rng, 64, 256, 128)
+    assert infer_packed_group_size(uniform) == 128 and tm.Packed4Linear.supports(uniform)
+    one_group = synth.packed4_matrix(rng, 40, 200, 200)
+    assert infer_packed_group_size(one_group) == 200 and tm.Packed4Linear.supports(one_group)
+    narrow = synth.packed4_matrix(rng, 40, 96, 16)          # uniform, but 16-column groups
+    assert infer_packed_group_size(narrow) == 16 and not tm.Packed4Linear.supports(narrow)
+    permuted = dict(uniform)
+    permuted["g_idx"] = torch.from_numpy(rng.permutation(uniform["g_idx"].numpy()))
+    assert infer_packed_group_size(permuted) == 256 and not tm.Packed4Linear.supports(permuted)
+    with __import__("pytest").raises(RuntimeError):
+        tm.Packed4Linear(uniform, "cpu")                    # no CPU path
