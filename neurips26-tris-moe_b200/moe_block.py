@@ -356,6 +356,8 @@ class TrisSparseMoeBlock(nn.Module):
         x = hidden_states.reshape(-1, shape[-1])
         if router_logits is None:
             router_logits = torch.nn.functional.linear(x, self.gate.weight)
+        if x.shape[0] == 0:
+            return x.new_zeros(shape), router_logits
         routing = torch.softmax(router_logits, dim=1, dtype=torch.float)
         routing, selected = torch.topk(routing, self.top_k, dim=-1)
         if self.norm_topk_prob:
@@ -374,8 +376,11 @@ class TrisSparseMoeBlock(nn.Module):
         down_hidden = self.backbone_hidden("down", mlp)
         down_out = run_grouped_structured_expert_forward(self._get_grouped_payload("down"), down_hidden, mlp, route,
                                                          ns_payload=self.ns_payloads.get("down"))
-        final = x.new_zeros(x.shape)
-        final.index_add_(0, tok, (down_out * grouped_routing).to(x.dtype))
+        # weighted sum of every token's k expert rows, taken in slot order (the reference scatters them with
+        # index_add_, whose atomic order varies from run to run; this is the same sum, reproducible)
+        weighted = (down_out * grouped_routing).to(x.dtype)
+        rows_of_token = route["_row_of_flat"].to(torch.long)
+        final = weighted.index_select(0, rows_of_token).view(x.shape[0], self.top_k, x.shape[1]).float().sum(dim=1).to(x.dtype)
         return final.reshape(shape), router_logits
 
 

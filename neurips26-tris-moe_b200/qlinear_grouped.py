@@ -338,6 +338,7 @@ def _empty_grouped_route(device):
         "perm": z_long, "grouped_token_indices": z_long, "grouped_slots": z_long,
         "grouped_expert_ids": z_i32, "expert_ids": z_i32, "segment_offsets": zero, "problem_offsets": zero.clone(),
         "total_problem_tiles": torch.zeros((1,), dtype=torch.int64), "total_problem_tiles_host": 0,
+        "_row_of_flat": z_i32.clone(), "_max_rows_per_segment": 0,
     }
 
 

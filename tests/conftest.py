@@ -30,3 +30,16 @@ def lib():
     import trismoe_b200
 
     return trismoe_b200._native.load()
+
+
+_RUNTIME_SWITCHES = ("TRIS_GROUPED_EXPERTS", "OLMOE_GROUPED_EXPERTS", "TRIS_DEPLOYMENT_ONLY", "OLMOE_DEPLOYMENT_ONLY",
+                     "TRIS_COMPACT3_BLOCK_GR", "TRIS_GROUPED_QGMAP_CPU_STAGING", "OLMOE_GROUPED_QGMAP_CPU_STAGING",
+                     "MIXTRAL_GROUPED_QGMAP_CPU_STAGING", "TRIS_PACKED4_BACKBONE")
+
+
+@pytest.fixture(autouse=True)
+def default_runtime_switches(monkeypatch):
+    """The tests describe the default behaviour: environment switches a shell may carry are taken out
+    (tests of the switches set them themselves)."""
+    for name in _RUNTIME_SWITCHES:
+        monkeypatch.delenv(name, raising=False)
