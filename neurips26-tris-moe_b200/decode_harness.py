@@ -35,17 +35,20 @@ class DecoderShape:
 
 
 def _rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    v = x.float()
-    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
+    return F.rms_norm(x, (x.shape[-1],), weight, eps)  # one kernel; statistics in fp32
 
 
-def _rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
-    """x [B, heads, S, D], positions [B, S] (int64) -> rotary embedding in fp32, returned as fp16."""
+def _rope_tables(max_length: int, head_dim: int, theta: float, device):
+    """cos / sin of every (position, frequency), fp32 [max_length, head_dim / 2]."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    ang = torch.arange(max_length, device=device, dtype=torch.float32)[:, None] * inv
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [B, heads, S, D]; cos / sin [B, 1, S, D/2] (fp32, already gathered at the tokens' positions)."""
     d = x.shape[-1]
-    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
-    ang = positions.to(torch.float32)[:, None, :, None] * inv  # [B, 1, S, D/2]
-    cos, sin = ang.cos(), ang.sin()
-    x1, x2 = x.float()[..., : d // 2], x.float()[..., d // 2:]
+    x1, x2 = x[..., : d // 2].float(), x[..., d // 2:].float()
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
 
 
@@ -64,6 +67,8 @@ class TrisDecoder(torch.nn.Module):
         self.embed = rnd(shape.vocab_size, H, std=1.0)
         self.lm_head = rnd(shape.vocab_size, H, std=1.0 / math.sqrt(H))
         self.final_norm = torch.ones(H, dtype=torch.float16, device=dev)
+        self.rope_cos, self.rope_sin = _rope_tables(self.max_length, hd, shape.rope_theta, dev)
+        self.key_index = torch.arange(self.max_length, device=dev)[None, None, None, :]
         self.layers = []
         for _ in self.blocks:
             self.layers.append({
@@ -73,31 +78,34 @@ class TrisDecoder(torch.nn.Module):
                 "v": torch.zeros((max_batch, nkv, max_length, hd), dtype=torch.float16, device=dev),
             })
 
-    def _attention(self, layer: dict, x: torch.Tensor, positions: torch.Tensor, batch: int) -> torch.Tensor:
+    def _attention(self, layer: dict, x: torch.Tensor, positions: torch.Tensor, batch: int, rope, mask) -> torch.Tensor:
         """x [B, S, H]; positions [B, S] absolute positions of these tokens.  Writes K/V at the
-        positions and attends over cache entries <= the token's own position."""
+        positions and attends over cache entries <= the token's own position.  ``rope`` (cos, sin at the
+        positions) and ``mask`` are the same for every layer of a step and are built once per step."""
         s = self.shape
         B, S, _ = x.shape
-        qkv = F.linear(x, layer["wqkv"]).view(B, S, s.num_heads + 2 * s.num_kv_heads, s.head_dim).transpose(1, 2)
-        q, k, v = qkv[:, : s.num_heads], qkv[:, s.num_heads: s.num_heads + s.num_kv_heads], qkv[:, s.num_heads + s.num_kv_heads:]
-        q, k = _rope(q, positions, s.rope_theta), _rope(k, positions, s.rope_theta)
-        idx = positions[:, None, :, None].expand(B, s.num_kv_heads, S, s.head_dim)
+        nq, nkv = s.num_heads, s.num_kv_heads
+        qkv = F.linear(x, layer["wqkv"]).view(B, S, nq + 2 * nkv, s.head_dim).transpose(1, 2)
+        qk = _rope(qkv[:, : nq + nkv], *rope)  # queries and keys rotate together
+        q, k, v = qk[:, :nq], qk[:, nq:], qkv[:, nq + nkv:]
+        idx = positions[:, None, :, None].expand(B, nkv, S, s.head_dim)
         layer["k"][:batch].scatter_(2, idx, k)
-        layer["v"][:batch].scatter_(2, idx, v.contiguous())
+        layer["v"][:batch].scatter_(2, idx, v)
         keys, vals = layer["k"][:batch], layer["v"][:batch]
-        if s.num_kv_heads != s.num_heads:
-            rep = s.num_heads // s.num_kv_heads
+        if nkv != nq:
+            rep = nq // nkv
             keys, vals = keys.repeat_interleave(rep, dim=1), vals.repeat_interleave(rep, dim=1)
-        mask = torch.arange(self.max_length, device=x.device)[None, None, None, :] <= positions[:, None, :, None]
         out = F.scaled_dot_product_attention(q, keys, vals, attn_mask=mask)
-        return F.linear(out.transpose(1, 2).reshape(B, S, s.num_heads * s.head_dim), layer["wo"])
+        return F.linear(out.transpose(1, 2).reshape(B, S, nq * s.head_dim), layer["wo"])
 
     def forward(self, token_ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """token_ids, positions [B, S] -> logits of the last position [B, vocab] (fp32)."""
         B, S = token_ids.shape
         h = F.embedding(token_ids, self.embed)
+        rope = (self.rope_cos[positions][:, None], self.rope_sin[positions][:, None])  # [B, 1, S, D/2]
+        mask = self.key_index <= positions[:, None, :, None]
         for layer, blk in zip(self.layers, self.blocks):
-            h = h + self._attention(layer, _rms_norm(h, layer["ln1"], self.shape.rms_eps), positions, B)
+            h = h + self._attention(layer, _rms_norm(h, layer["ln1"], self.shape.rms_eps), positions, B, rope, mask)
             y, _ = blk(_rms_norm(h, layer["ln2"], self.shape.rms_eps))
             h = h + y
         last = _rms_norm(h[:, -1], self.final_norm, self.shape.rms_eps)
