@@ -2,7 +2,8 @@
 layer-batched loader (TriS-MoE tree: ``tools/export_grouped_blockgr_checkpoint.py:140-233``,
 ``build_grouped_blockgr_payloads`` in ``tools/rewrite_runtime_min_checkpoint.py:363-444``,
 ``restore_dense_packed_gmap_from_sparse`` :147-159, ``drop_blockgr_sparse_payloads``; the
-layer-batched loader of ``auto_gptq/modeling/_base.py:708-781``).
+layer-batched loader of ``auto_gptq/modeling/_base.py:708-781``; the single-file streaming export of
+``tools/export_grouped_streaming_sparse_checkpoint.py``).
 
 ``export_grouped_blockgr_checkpoint`` turns a sidecar (or embedded checkpoint) whose grouped
 payloads carry the sparse g_map planes into one that carries the block-GR streams, tensor names,
@@ -230,6 +231,105 @@ def export_grouped_blockgr_checkpoint(source_path: str, output_path: str, mode: 
     return {"built_grouped_payloads": built, "built_grouped_words": words, "grouped_blockgr_payload_count": with_streams,
             "removed_grouped_sparse_keys": removed, "derived_payloads": derived, "blockgr_k_search_min": lo,
             "blockgr_k_search_max": hi, "keep_sparse": bool(keep_sparse)}
+
+
+STREAMING_READY_METADATA_KEY = "olmoe_grouped_qgmap_cpu_staging_ready"
+STREAMING_SINGLE_FILE_METADATA_KEY = "olmoe_grouped_qgmap_cpu_staging_single_file"
+# per-expert module state a deployment-only checkpoint keeps (grouped_payload_sidecar.py:38-46)
+DEPLOYMENT_ONLY_EXPERT_LEAVES = frozenset({"mode", "ns_mode", "ns_vector_row", "ns_vector_col", "expert_input_scale"})
+_EXPERT_MODULES = {"gate_proj": "gate_proj", "up_proj": "up_proj", "down_proj": "down_proj",  # OLMoE / Qwen naming
+                   "w1": "gate_proj", "w3": "up_proj", "w2": "down_proj"}  # Mixtral naming
+
+
+def split_moe_expert_tensor_name(name: str) -> Optional[Tuple[str, str]]:
+    """``model.layers.<i>.mlp.experts.<e>.<proj>.<leaf>`` (or Mixtral's ``block_sparse_moe.experts.<e>.w1|w2|w3``)
+    -> (logical projection, leaf); None for every other tensor (grouped_payload_sidecar.py:467-497)."""
+    parts = name.split(".")
+    if len(parts) < 8 or parts[0] != "model" or parts[1] != "layers" or not parts[2].isdigit():
+        return None
+    if parts[4] != "experts" or not parts[5].isdigit():
+        return None
+    if parts[3] == "mlp":
+        allowed = ("gate_proj", "up_proj", "down_proj")
+    elif parts[3] == "block_sparse_moe":
+        allowed = ("w1", "w2", "w3")
+    else:
+        return None
+    if parts[6] not in allowed:
+        return None
+    return _EXPERT_MODULES[parts[6]], ".".join(parts[7:])
+
+
+def build_deployment_only_checkpoint_tensors(tensors: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """Drops what a grouped runtime never reads: per-expert module tensors other than the few state
+    leaves, keeping grouped payload tensors and everything outside the expert modules
+    (``build_deployment_only_checkpoint_tensors``, grouped_payload_sidecar.py:508-517)."""
+    kept = {}
+    for name, t in tensors.items():
+        if split_payload_tensor_name(name) is None:
+            expert = split_moe_expert_tensor_name(name)
+            if expert is not None and expert[1] not in DEPLOYMENT_ONLY_EXPERT_LEAVES:
+                continue
+        kept[name] = t
+    return kept
+
+
+def repair_grouped_payload_tensors(tensors: Dict[str, torch.Tensor]) -> int:
+    """An all-zero ``output_scale`` of a compact3 payload (written by an exporter that had none) becomes ones with
+    ``has_output_scale`` cleared; returns how many payloads were repaired (grouped_payload_sidecar.py:306-337)."""
+    repaired = 0
+    for (prefix, key), payload in collect_grouped_payloads(tensors).items():
+        if key not in GROUPED_PRECOMPUTED_KEYS or not _flag(payload, "is_compact3"):
+            continue
+        scale = payload.get("output_scale")
+        if not isinstance(scale, torch.Tensor) or scale.numel() == 0 or bool(torch.any(scale != 0)):
+            continue
+        tensors[payload_tensor_name(prefix, key, "output_scale")] = torch.ones_like(scale).contiguous()
+        flag_name = payload_tensor_name(prefix, key, "has_output_scale")
+        if flag_name in tensors:
+            tensors[flag_name] = torch.zeros_like(tensors[flag_name], dtype=torch.bool).contiguous()
+        repaired += 1
+    return repaired
+
+
+def has_sparse_qgmap_payloads(tensors: Dict[str, torch.Tensor]) -> bool:
+    """True when a grouped projection or an attention linear carries the sparse g_map planes the
+    bitmap streaming manager pages (export_grouped_streaming_sparse_checkpoint.py:55-66)."""
+    for name in tensors:
+        split = split_payload_tensor_name(name)
+        if split is not None:
+            if split[1] in GROUPED_PRECOMPUTED_KEYS and split[2] == "q_gmap_sparse":
+                return True
+        elif ".self_attn." in name and name.endswith(".q_gmap_sparse"):
+            return True
+    return False
+
+
+def export_grouped_streaming_sparse_checkpoint(source_path: str, output_path: str) -> dict:
+    """A single-file checkpoint ready for host-staged bitmap streaming out of a sparse grouped checkpoint
+    (tools/export_grouped_streaming_sparse_checkpoint.py:37-86): deployment-only tensor filter, output-scale repair,
+    a source without sparse g_map planes refused, embedded + deployment-only metadata and the two staging-ready keys."""
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    with safe_open(source_path, framework="pt", device="cpu") as fh:
+        metadata = {str(k): str(v) for k, v in (fh.metadata() or {}).items()}
+        tensors = {k: fh.get_tensor(k).contiguous() for k in fh.keys()}
+    total = len(tensors)
+    tensors = build_deployment_only_checkpoint_tensors(tensors)
+    repaired = repair_grouped_payload_tensors(tensors)
+    if not has_sparse_qgmap_payloads(tensors):
+        raise ValueError("source checkpoint does not contain sparse qgmap payloads; "
+                         "the streaming export expects a sparse source checkpoint")
+    metadata["format"] = "pt"
+    metadata[GROUPED_PAYLOAD_EMBEDDED_METADATA_KEY] = "v1"
+    metadata[GROUPED_PAYLOAD_DEPLOYMENT_ONLY_METADATA_KEY] = "v1"
+    metadata[STREAMING_READY_METADATA_KEY] = "v1"
+    metadata[STREAMING_SINGLE_FILE_METADATA_KEY] = "1"
+    os.makedirs(os.path.dirname(os.path.abspath(output_path)), exist_ok=True)
+    save_file(tensors, output_path, metadata=metadata)
+    return {"streaming_sparse": True, "single_file": True, "repaired_grouped_output_scales": repaired,
+            "kept_tensors": len(tensors), "dropped_tensors": total - len(tensors)}
 
 
 def layer_prefixes_in(path: str) -> List[str]:

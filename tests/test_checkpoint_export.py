@@ -120,3 +120,68 @@ def test_packed4_group_rules_on_cpu():
     assert infer_packed_group_size(permuted) == 256 and not tm.Packed4Linear.supports(permuted)
     with __import__("pytest").raises(RuntimeError):
         tm.Packed4Linear(uniform, "cpu")                    # no CPU path
+
+
+def test_streaming_sparse_single_file_export(lib, tmp_path):
+    """The single-file streaming export: expert module tensors other than the kept state leaves are dropped (OLMoE and
+    Mixtral naming), payload and non-expert tensors stay, an all-zero compact3 output scale is repaired, the metadata
+    carries the embedded / deployment-only / staging-ready keys, payloads load back unchanged, and a source without
+    sparse g_map planes is refused."""
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    from trismoe_b200 import checkpoint_export as ce, sidecar, synth
+
+    assert ce.split_moe_expert_tensor_name("model.layers.3.mlp.experts.12.up_proj.qweight1") == ("up_proj", "qweight1")
+    assert ce.split_moe_expert_tensor_name("model.layers.0.block_sparse_moe.experts.1.w2.ns_vector_row") == ("down_proj", "ns_vector_row")
+    assert ce.split_moe_expert_tensor_name("model.layers.0.mlp.experts.1.router.weight") is None
+    assert ce.split_moe_expert_tensor_name("model.layers.0.mlp.gate.weight") is None
+    assert ce.split_moe_expert_tensor_name("model.layers.0.mlp.experts.1.gate_proj") is None
+
+    shape = synth.LayerShape(64, 96, 2, 1, rank=64, group_size=32)
+    layer = synth.synth_layer(shape, seed=31, keep_sparse_gmap=True, use_block_gr=False)
+    prefix = sidecar.layer_prefix(0)
+    src = os.path.join(tmp_path, "src.safetensors")
+    sidecar.save_grouped_payloads_to_sidecar(src, {prefix: {k: layer[k] for k in ("gate", "up", "down")}}, embedded=True)
+    tensors, meta = _load_all(src)
+    scale_name = sidecar.payload_tensor_name(prefix, "down", "output_scale")
+    tensors[scale_name] = torch.zeros_like(tensors[scale_name])
+    tensors[sidecar.payload_tensor_name(prefix, "down", "has_output_scale")] = torch.tensor([True])
+    extra = {"model.embed_tokens.weight": torch.ones(4, 4, dtype=torch.float16),
+             "model.layers.0.mlp.gate.weight": torch.ones(2, 4, dtype=torch.float16),
+             "model.layers.0.self_attn.q_proj.qweight1": torch.ones(3, dtype=torch.int32),
+             "model.layers.0.mlp.experts.0.gate_proj.qweight1": torch.ones(5, dtype=torch.int32),
+             "model.layers.0.mlp.experts.0.gate_proj.ns_mode": torch.tensor([2], dtype=torch.int32),
+             "model.layers.0.mlp.experts.1.down_proj.expert_input_scale": torch.ones(4, dtype=torch.float16),
+             "model.layers.0.block_sparse_moe.experts.1.w3.scale_u": torch.ones(4, dtype=torch.float16),
+             "model.layers.0.block_sparse_moe.experts.1.w3.mode": torch.tensor([1], dtype=torch.int32)}
+    tensors.update(extra)
+    save_file({k: v.contiguous() for k, v in tensors.items()}, src, metadata={**meta, "note": "kept"})
+
+    out = os.path.join(tmp_path, "out", "model.safetensors")
+    stats = ce.export_grouped_streaming_sparse_checkpoint(src, out)
+    assert stats["repaired_grouped_output_scales"] == 1 and stats["dropped_tensors"] == 2 and stats["single_file"]
+    got, got_meta = _load_all(out)
+    assert "model.layers.0.mlp.experts.0.gate_proj.qweight1" not in got
+    assert "model.layers.0.block_sparse_moe.experts.1.w3.scale_u" not in got
+    for name in extra:
+        if not name.endswith(("gate_proj.qweight1", "w3.scale_u")):
+            assert torch.equal(got[name], extra[name]), name
+    assert got_meta["format"] == "pt" and got_meta["note"] == "kept"
+    assert got_meta[sidecar.GROUPED_PAYLOAD_EMBEDDED_METADATA_KEY] == "v1"
+    assert got_meta[sidecar.GROUPED_PAYLOAD_DEPLOYMENT_ONLY_METADATA_KEY] == "v1"
+    assert got_meta["olmoe_grouped_qgmap_cpu_staging_ready"] == "v1"
+    assert got_meta["olmoe_grouped_qgmap_cpu_staging_single_file"] == "1"
+    assert bool(torch.all(got[scale_name] == 1)) and not bool(got[sidecar.payload_tensor_name(prefix, "down", "has_output_scale")][0])
+    for key in ("gate", "up", "down"):
+        payload = sidecar.load_grouped_payload_from_sidecar(out, prefix, key)
+        assert torch.equal(payload["q_gmap_sparse"], layer[key]["q_gmap_sparse"].cpu())
+        assert torch.equal(payload["qweight1"], layer[key]["qweight1"].cpu())
+        staged = sidecar.load_grouped_qgmap_from_sidecar(out, prefix, key, pin_memory=False)
+        assert staged is not None and torch.equal(staged["q_gmap_sparse_prefix"], layer[key]["q_gmap_sparse_prefix"].cpu())
+
+    dense_only = {k: v for k, v in got.items() if not k.endswith(("q_gmap_sparse", "q_gmap_sparse_prefix"))}
+    bad = os.path.join(tmp_path, "dense.safetensors")
+    save_file(dense_only, bad, metadata=got_meta)
+    with pytest.raises(ValueError, match="sparse qgmap"):
+        ce.export_grouped_streaming_sparse_checkpoint(bad, os.path.join(tmp_path, "out2", "model.safetensors"))
