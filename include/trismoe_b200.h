@@ -478,6 +478,15 @@ int tris_combine_routed(const void* down_out_f16, const int32_t* row_of_flat,
  */
 int tris_set_grouped_tc_min_rows(int32_t rows);
 
+/*
+ * Upper limit on how many CTAs share the row passes of one (segment, output tile) unit in the
+ * register-cached grouped kernel (segments of more than 64 rows); returns the previous value.  The
+ * launcher splits only while there are fewer units than two CTAs per SM - few local experts with long
+ * segments, as on an expert-parallel rank.  Default 4; 1 switches the split off.  Results do not depend
+ * on it.  Process-wide; no reference counterpart.
+ */
+int tris_set_grouped_row_split_max(int32_t ctas);
+
 /* ---- streaming ----------------------------------------------------------------------- */
 
 /* One tensor to page: expert e's block of `bytes_per_expert` bytes (a multiple of 16) is

@@ -109,6 +109,7 @@ SIGNATURES = {
     "tris_grouped_pair_forward": (C.c_int, [_P(TrisProjView), _P(TrisProjView), _P(TrisRouteView), _vp, _vp, _vp, _vp, _i32, _vp]),
     "tris_grouped_hidden_layout": (C.c_int, [_P(TrisProjView), _P(TrisProjView), _i32, _i32, _i32]),
     "tris_set_grouped_tc_min_rows": (C.c_int, [_i32]),
+    "tris_set_grouped_row_split_max": (C.c_int, [_i32]),
     "tris_combine_routed": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "tris_page_experts": (C.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _vp]),
     "tris_moe_layer_workspace_bytes": (C.c_size_t, [_P(TrisMoeLayerView), _i32]),

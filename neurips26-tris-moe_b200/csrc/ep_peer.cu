@@ -42,13 +42,16 @@ __device__ __forceinline__ void ep_signal_peers(int32_t* const* peer_flags, int 
 // layout is row off of the rows owned by rank d; it is written to rank d's receive buffer at
 // slot (my_rank, off): two backbone outputs of rank_gu halves each and, behind them, the expert
 // id as an int32 (unused slots: -1).  combine_index[flat] = d * capacity + off.
+// Two phases, so that a capacity far above the rows in use (the never-dropping world * tokens * top_k)
+// costs one 4-byte store per slot and nothing else: (1) one thread per slot writes the id word and the
+// combine index; (2) thread groups copy the rows in use, one group per row.
 __global__ void __launch_bounds__(128) ep_dispatch_peer_kernel(
     const __half* __restrict__ hidden_gate, const __half* __restrict__ hidden_up, int rank_gu,
     const int32_t* __restrict__ selected, const int32_t* __restrict__ perm, const int32_t* __restrict__ tok,
     int num_rows, int num_experts, int world, int my_rank, int capacity, __half* const* __restrict__ peer_recv,
     int row_stride, int32_t* __restrict__ combine_index, int32_t* __restrict__ overflow,
     int32_t* const* __restrict__ peer_flags) {
-  __shared__ int32_t s_first[64];  // first grouped row owned by each rank (world <= 64)
+  __shared__ int32_t s_first[65];  // first grouped row owned by each rank (world <= 64), then num_rows
   pdl_wait();  // the route and the backbone outputs come from the kernels before this one
   pdl_launch_dependents();
   const int base = num_experts / world, extra = num_experts % world;
@@ -62,53 +65,80 @@ __global__ void __launch_bounds__(128) ep_dispatch_peer_kernel(
     }
     s_first[d] = lo;
   }
+  if (threadIdx.x == 0) s_first[world] = num_rows;
   __syncthreads();
-  for (int pos = blockIdx.x; pos < world * capacity; pos += gridDim.x) {
+  const int total = world * capacity;
+  for (int pos = blockIdx.x * blockDim.x + threadIdx.x; pos < total; pos += gridDim.x * blockDim.x) {
     const int d = pos / capacity, off = pos - d * capacity;
-    const int row = s_first[d] + off;
-    const int row_end = (d + 1 < world) ? s_first[d + 1] : num_rows;
+    const int row = s_first[d] + off, row_end = s_first[d + 1];
     const bool used = row < row_end;
+    const int flat = used ? perm[row] : 0;
     __half* slot = peer_recv[d] + (static_cast<size_t>(my_rank) * capacity + off) * row_stride;
-    if (threadIdx.x == 0) {
-      *reinterpret_cast<int32_t*>(slot + 2 * rank_gu) = used ? selected[perm[row]] : -1;
-      if (used) combine_index[perm[row]] = pos;
-      if (off == capacity - 1 && row + 1 < row_end) *overflow = 1;  // more rows for this rank than slots
-    }
-    if (!used) continue;
-    const int t = tok[row];
-    const uint4* g = reinterpret_cast<const uint4*>(hidden_gate + static_cast<size_t>(t) * rank_gu);
-    const uint4* u = reinterpret_cast<const uint4*>(hidden_up + static_cast<size_t>(t) * rank_gu);
-    uint4* dst = reinterpret_cast<uint4*>(slot);
-    const int vecs = rank_gu >> 3;
-    for (int i = threadIdx.x; i < 2 * vecs; i += blockDim.x) dst[i] = (i < vecs) ? g[i] : u[i - vecs];
+    *reinterpret_cast<int32_t*>(slot + 2 * rank_gu) = used ? selected[flat] : -1;
+    if (used) combine_index[flat] = pos;
+    if (off == capacity - 1 && row + 1 < row_end) *overflow = 1;  // more rows for this rank than slots
   }
-  // rows beyond an owner's capacity are dropped: their combine index says so (every flat entry is
-  // written by exactly one thread of this launch, so the caller need not initialise the array)
-  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < num_rows; row += gridDim.x * blockDim.x) {
-    int d = 0;
-    while (d + 1 < world && row >= s_first[d + 1]) ++d;
-    if (row - s_first[d] >= capacity) combine_index[perm[row]] = -1;
+  // rows: 2 * rank_gu / 8 16-byte vectors each, `lanes` threads per row.  Rows beyond an owner's capacity are
+  // dropped and their combine index says so (every flat entry is written by exactly one thread of this
+  // launch, so the caller need not initialise the array).
+  const int vecs = rank_gu >> 3, per_row = 2 * vecs;
+  const int lanes = min(per_row, static_cast<int>(blockDim.x));
+  const int groups = blockDim.x / lanes;
+  const int grp = threadIdx.x / lanes, l = threadIdx.x - grp * lanes;
+  if (grp < groups) {
+    for (int row = blockIdx.x * groups + grp; row < num_rows; row += gridDim.x * groups) {
+      int d = 0;
+      while (d + 1 < world && row >= s_first[d + 1]) ++d;
+      const int off = row - s_first[d];
+      if (off >= capacity) {
+        if (l == 0) combine_index[perm[row]] = -1;
+        continue;
+      }
+      const int t = tok[row];
+      const uint4* g = reinterpret_cast<const uint4*>(hidden_gate + static_cast<size_t>(t) * rank_gu);
+      const uint4* u = reinterpret_cast<const uint4*>(hidden_up + static_cast<size_t>(t) * rank_gu);
+      uint4* dst = reinterpret_cast<uint4*>(peer_recv[d] + (static_cast<size_t>(my_rank) * capacity + off) * row_stride);
+      for (int i = l; i < per_row; i += lanes) dst[i] = (i < vecs) ? g[i] : u[i - vecs];
+    }
   }
   ep_signal_peers(peer_flags, world, my_rank);
 }
 
 // Return.  results [world * capacity, hidden] holds, in received-slot order, the output rows of
 // the rows this rank processed; block s goes back to rank s, into block my_rank of its result
-// buffer.  Rows whose received id is negative (padding) are skipped.
+// buffer.  Rows whose received id is negative (padding) are skipped: every thread looks at one slot
+// of a batch, the slots in use are listed in shared memory and the warps copy those, one row each.
 __global__ void __launch_bounds__(256) ep_return_peer_kernel(
     const __half* __restrict__ results, const __half* __restrict__ recv_rows, int row_stride, int rank_gu,
     int hidden, int world, int my_rank, int capacity, __half* const* __restrict__ peer_back,
     int32_t* const* __restrict__ peer_flags) {
+  __shared__ int32_t s_live[256];
+  __shared__ int s_count;
   pdl_wait();
   pdl_launch_dependents();
   const int vecs = hidden >> 3;
-  for (int pos = blockIdx.x; pos < world * capacity; pos += gridDim.x) {
-    const int s = pos / capacity, off = pos - s * capacity;
-    const int32_t id = *reinterpret_cast<const int32_t*>(recv_rows + static_cast<size_t>(pos) * row_stride + 2 * rank_gu);
-    if (id < 0) continue;
-    const uint4* src = reinterpret_cast<const uint4*>(results + static_cast<size_t>(pos) * hidden);
-    uint4* dst = reinterpret_cast<uint4*>(peer_back[s] + (static_cast<size_t>(my_rank) * capacity + off) * hidden);
-    for (int i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = src[i];
+  const int total = world * capacity;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  // slot of (batch, thread, CTA): consecutive threads of a CTA are gridDim.x slots apart, so the slots in
+  // use (the first few of every peer's block) spread over all CTAs
+  for (int first = 0; first < total; first += gridDim.x * blockDim.x) {
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    const int pos = first + threadIdx.x * gridDim.x + blockIdx.x;
+    if (pos < total) {
+      const int32_t id = *reinterpret_cast<const int32_t*>(recv_rows + static_cast<size_t>(pos) * row_stride + 2 * rank_gu);
+      if (id >= 0) s_live[atomicAdd(&s_count, 1)] = pos;
+    }
+    __syncthreads();
+    const int n = s_count;
+    for (int j = warp; j < n; j += warps) {
+      const int p = s_live[j];
+      const int s = p / capacity, off = p - s * capacity;
+      const uint4* src = reinterpret_cast<const uint4*>(results + static_cast<size_t>(p) * hidden);
+      uint4* dst = reinterpret_cast<uint4*>(peer_back[s] + (static_cast<size_t>(my_rank) * capacity + off) * hidden);
+      for (int i = lane; i < vecs; i += 32) dst[i] = src[i];
+    }
+    __syncthreads();  // the list is rebuilt by the next batch
   }
   ep_signal_peers(peer_flags, world, my_rank);
 }

@@ -26,6 +26,7 @@
 #include <math.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "tile_records.cuh"
 
@@ -432,7 +433,12 @@ __global__ void __launch_bounds__(kThreads, CACHE ? 2 : 4) grouped_tiled_kernel(
   const int seg = blockIdx.y;
   const UnitRoute unit = load_unit_route(args, seg);
   const int nseg = args.num_segments_dev ? min(*args.num_segments_dev, args.num_segments) : args.num_segments;
-  if (seg >= nseg || !unit_live(args, unit)) return;
+  // Row split: CTA z of a unit takes the row passes z, z + gridDim.z, ... of its segment (the launcher
+  // splits when there are fewer units than CTA slots); a CTA without a pass leaves at once.
+  // (Only the register-cached kernel is launched with gridDim.z > 1.)
+  const int row_first = unit.row_begin + (CACHE ? static_cast<int>(blockIdx.z) * (NT * 8) : 0);
+  const int row_step = (CACHE ? static_cast<int>(gridDim.z) : 1) * (NT * 8);
+  if (seg >= nseg || !unit_live(args, unit) || row_first >= unit.row_end) return;
   const int expert = unit.expert;
 
   const int r = warp >> 2, og = warp & 3;  // record and 16-output group of this warp
@@ -456,7 +462,7 @@ __global__ void __launch_bounds__(kThreads, CACHE ? 2 : 4) grouped_tiled_kernel(
   bool dead = false;
   uint32_t a_cache[CACHE ? kChunkRows : 1][2][4];
   int cached_rows = -1;  // packed rows held in a_cache once the chunk has been unpacked
-  for (int r0 = unit.row_begin; r0 < unit.row_end; r0 += NT * 8) {
+  for (int r0 = row_first; r0 < unit.row_end; r0 += row_step) {
     const int rows = min(NT * 8, unit.row_end - r0);
     const int nt_count = (rows + 7) >> 3;
     float acc[NT][4];
@@ -826,8 +832,19 @@ static int launch_tiled(const TiledArgs& args, cudaStream_t stream, bool pdl) {
 
 // Prefill-sized segments of a single-chunk projection: one CTA per unit, 32 rows per pass, weights
 // unpacked once per unit and kept in registers.
+// Row split of the cached kernel: with fewer units than CTA slots (two per SM) - few local experts with long
+// segments, as on an expert-parallel rank - up to `g_row_split_max` CTAs share a unit's row passes, each
+// decoding and unpacking the unit's weights for itself.
+static std::atomic<int> g_row_split_max{4};
+static int cached_row_split(int units, int max_rows) {
+  const int limit = g_row_split_max.load(std::memory_order_relaxed);
+  if (limit <= 1 || units <= 0) return 1;
+  const int passes = (max_rows + 31) / 32;
+  return std::max(1, std::min({limit, 2 * sm_count() / units, passes}));
+}
+
 template <int MODE>
-static int launch_tiled_cached(const TiledArgs& args, cudaStream_t stream, bool pdl) {
+static int launch_tiled_cached(const TiledArgs& args, int max_rows, cudaStream_t stream, bool pdl) {
   constexpr int NH = (MODE == MODE_SINGLE) ? 1 : 2;
   constexpr int NT = 4;
   const int tiles = tiles_per_expert(args.proj[0].out_features);
@@ -838,13 +855,14 @@ static int launch_tiled_cached(const TiledArgs& args, cudaStream_t stream, bool 
   static size_t configured[64] = {};
   int st = configure_smem(kernel, smem, configured);
   if (st != TRIS_OK) return st;
-  return check_cuda(launch_kernel(kernel, dim3(units_x, args.num_segments), dim3(kThreads), smem, stream, pdl, 1, args),
+  const int split = cached_row_split(units_x * args.num_segments, max_rows);
+  return check_cuda(launch_kernel(kernel, dim3(units_x, args.num_segments, split), dim3(kThreads), smem, stream, pdl, 1, args),
                     "grouped_tiled_kernel (cached weights) launch");
 }
 
 template <int MODE>
 static int dispatch_tiled(const TiledArgs& args, int max_rows, cudaStream_t stream, bool pdl) {
-  if (max_rows > kTiledDecodeMaxRows && num_chunks(args.proj[0].rank) == 1) return launch_tiled_cached<MODE>(args, stream, pdl);
+  if (max_rows > kTiledDecodeMaxRows && num_chunks(args.proj[0].rank) == 1) return launch_tiled_cached<MODE>(args, max_rows, stream, pdl);
   if (max_rows <= 8) return launch_tiled<1, MODE>(args, stream, pdl);
   if (max_rows <= 16) return launch_tiled<2, MODE>(args, stream, pdl);
   // 24 rows per pass also for segments of up to 64 rows: with 32 rows per pass the tile no longer fits four
@@ -915,3 +933,7 @@ int launch_tiled_dump(const TrisProjView* proj, int32_t* dense_out, void* weight
 }
 
 }  // namespace tris
+
+extern "C" int tris_set_grouped_row_split_max(int32_t ctas) {
+  return tris::tr::g_row_split_max.exchange(ctas < 1 ? 1 : (ctas > 16 ? 16 : ctas), std::memory_order_relaxed);
+}

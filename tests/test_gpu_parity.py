@@ -729,6 +729,48 @@ def test_layer_olmoe_shape_prefill_512(tm, olmoe_layer, kernel):
         assert torch.allclose(y_one.view(-1).float(), y.view(T, -1)[t].float(), atol=3e-3, rtol=3e-3)
 
 
+def test_row_split_of_long_segments_leaves_results_unchanged(tm):
+    """Few experts with long, uneven segments (an expert-parallel rank's shape): the register-cached kernel
+    shares a unit's 32-row passes among up to four CTAs.  With the split switched off the outputs are the same
+    bits; segments of 1, 33, 70, 130 and 300 rows cover CTAs without a pass, a ragged last pass and CTAs with
+    several passes; the result agrees with the fp32 oracle."""
+    from trismoe_b200 import synth
+
+    shape = synth.LayerShape(128, 192, 6, 1, rank=128, group_size=32)
+    layer = synth.synth_layer(shape, seed=77)
+    payloads = {n: tm.prepare_grouped_payload(layer[n], "cuda") for n in ("gate", "up", "down")}
+    lengths = [1, 33, 0, 70, 130, 300]
+    ids = np.concatenate([np.full(n, e, dtype=np.int64) for e, n in enumerate(lengths)])
+    rng = np.random.default_rng(5)
+    ids = ids[rng.permutation(ids.size)]
+    R = int(ids.size)
+    route = tm.build_grouped_route(torch.from_numpy(ids.reshape(R, 1)).cuda(), shape.num_experts)
+    hg = (torch.randn((R, 128), generator=torch.Generator().manual_seed(1)) * 0.5).half().cuda()
+    hu = (torch.randn((R, 128), generator=torch.Generator().manual_seed(2)) * 0.5).half().cuda()
+    hd = (torch.randn((R, 128), generator=torch.Generator().manual_seed(3)) * 0.5).half().cuda()
+    lib = tm._native.load()
+    outs = {}
+    previous = lib.tris_set_grouped_row_split_max(1)
+    try:
+        for limit in (1, 4, 16):
+            lib.tris_set_grouped_row_split_max(limit)
+            mlp = tm.run_grouped_structured_expert_pair_forward(payloads["gate"], payloads["up"], hg, hu, None, route, fuse_silu_mul=True)
+            down = tm.run_grouped_structured_expert_forward(payloads["down"], hd, None, route)
+            torch.cuda.synchronize()
+            outs[limit] = (mlp.clone(), down.clone())
+    finally:
+        lib.tris_set_grouped_row_split_max(previous)
+    for limit in (4, 16):
+        assert torch.equal(outs[limit][0], outs[1][0]) and torch.equal(outs[limit][1], outs[1][1]), limit
+    # oracle: rows of the grouped order against the dequantized expert matrices
+    order = route["grouped_token_indices"].cpu().numpy()
+    w_down = [orc.dequantize_expert(to_numpy_payload(layer["down"]), e) for e in range(shape.num_experts)]
+    hd_f32 = hd.cpu().numpy().astype(np.float32)  # row i of a grouped operand is grouped row i; its expert is that of flat entry order[i]
+    ref = np.stack([hd_f32[i] @ w_down[int(ids[order[i]])].astype(np.float32).T for i in range(R)])
+    max_abs, mean_rel = orc.error_metrics(outs[4][1].float().cpu().numpy(), ref)
+    assert np.abs(ref).mean() > 1e-4 and max_abs <= MAX_ABS and mean_rel <= MEAN_REL, (max_abs, mean_rel)
+
+
 # ---------------------------------------------------------------------------------------
 # (10) expert-parallel exchange: a wait for a peer that never signals ends by itself
 # ---------------------------------------------------------------------------------------
