@@ -754,7 +754,7 @@ def test_row_split_of_long_segments_leaves_results_unchanged(tm):
     try:
         for limit in (1, 4, 16):
             lib.tris_set_grouped_row_split_max(limit)
-            mlp = tm.run_grouped_structured_expert_pair_forward(payloads["gate"], payloads["up"], hg, hu, None, route, fuse_silu_mul=True)
+            mlp, _ = tm.run_grouped_structured_expert_pair_forward(payloads["gate"], payloads["up"], hg, hu, None, route, fuse_silu_mul=True)
             down = tm.run_grouped_structured_expert_forward(payloads["down"], hd, None, route)
             torch.cuda.synchronize()
             outs[limit] = (mlp.clone(), down.clone())
