@@ -439,7 +439,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         recv_rows = torch.empty_like(send_rows)
         dist.all_to_all_single(recv_rows, send_rows, group=self.group)
         # the id of every slot is the int32 right behind its 2*r_gu halves (padding slots: -1)
-        expected = max(1, (N * R) // max(1, self.hi - self.lo))  # rows per local expert if routing is balanced
+        expected = max(1, R // max(1, self.hi - self.lo))  # rows per local expert if routing is balanced: a rank receives about as many rows as it sends
         result = self._local_experts(recv_rows, None, rows_hint=int(expected + 4 * expected ** 0.5),
                                      layouts=self._step_layouts)
         back = torch.empty_like(result)
@@ -469,7 +469,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
                                                 self._overflow.data_ptr(), pb.dflag_ptrs.data_ptr(), stream), "ep_dispatch_peer")
         _native.check(lib.tris_ep_wait(pb.flags[0].data_ptr(), pb.steps[0:].data_ptr(), N, pb.status.data_ptr(), stream),
                       "ep_wait (rows)")
-        expected = max(1, (N * R) // max(1, self.hi - self.lo))
+        expected = max(1, R // max(1, self.hi - self.lo))  # as in the NCCL path
         result = self._local_experts(pb.recv, None, rows_hint=int(expected + 4 * expected ** 0.5),
                                      layouts=self._step_layouts)
         _native.check(lib.tris_ep_return_peer(result.data_ptr(), pb.recv.data_ptr(), stride, r_gu, self.hidden_size, N,
